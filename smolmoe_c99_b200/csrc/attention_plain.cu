@@ -1,0 +1,139 @@
+// Attention of one query against its visible keys, one warp per (token, head), for any
+// head size that is a multiple of 8 up to 256 and any number of heads and groups.
+//
+// It is the attention of the true 32-bit path (prefill and decode alike) and the fallback
+// of the bfloat16 path. Keys are visited in ascending order in groups of 32 counted from
+// the first visible key, with a running maximum and sum (the reference's two-pass softmax,
+// src/kernels.c:1138-1176, gives the same value up to rounding). What a query's result
+// depends on: the query, its visible keys and values, the scale and the window -- not the
+// batch, not the step it came in, not where the keys lie in the cache.
+#include <math_constants.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace sm {
+
+constexpr int kWarpsPerBlock = 4;
+constexpr int kMaxHeadDim = 256;
+
+template <typename T> struct Load8;
+template <> struct Load8<float> {
+    __device__ __forceinline__ static void load(const float* p, float (&v)[8]) {
+        float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+};
+template <> struct Load8<__nv_bfloat16> {
+    __device__ __forceinline__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+        uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+};
+
+template <typename T, bool PAGED>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(AttentionArgs a) {
+    __shared__ __align__(16) float q_shared[kWarpsPerBlock][kMaxHeadDim];
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    long long item = (long long)blockIdx.x * kWarpsPerBlock + warp;
+    if (item >= (long long)a.T * a.heads) return;  // whole warp leaves together
+    int t = (int)(item / a.heads), h = (int)(item % a.heads);
+    int hd = a.head_dim;
+    int kvh = h / (a.heads / a.kv_heads);  // src/model.c:461
+    int pos = a.positions[t];
+    int start = (a.window > 0 && pos >= a.window) ? pos - a.window + 1 : 0;  // src/model.c:462
+
+    const T* q = (const T*)a.q + ((size_t)t * a.heads + h) * hd;
+    float* qs = q_shared[warp];
+    for (int d = lane; d < hd; d += 32) qs[d] = to_float(q[d]);
+    __syncwarp();
+
+    const T* kbase = (const T*)(PAGED ? a.k_pool : a.k_packed);
+    const T* vbase = (const T*)(PAGED ? a.v_pool : a.v_packed);
+    PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
+    int slot = PAGED ? a.token_slot[t] : 0;
+    int seq_start = PAGED ? 0 : a.token_seq_start[t];
+
+    float m = -CUDART_INF_F, l = 0.f;
+    float acc[kMaxHeadDim / 32];
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
+
+    for (int base = start; base <= pos; base += 32) {
+        int p = base + lane;
+        bool valid = p <= pos;
+        unsigned long long row = 0;
+        float s = -CUDART_INF_F;
+        if (valid) {
+            row = PAGED ? (unsigned long long)paged.row_offset(slot, p, kvh)
+                        : ((unsigned long long)(seq_start + p) * a.kv_heads + kvh) * hd;
+            const T* kr = kbase + row;
+            float dot = 0.f;
+            for (int d = 0; d < hd; d += 8) {
+                float kv[8];
+                Load8<T>::load(kr + d, kv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+            }
+            s = dot * a.scale;
+        }
+        float m_new = fmaxf(m, warp_max(s));
+        float corr = expf(m - m_new);  // first group: exp(-inf) = 0
+        float e = valid ? expf(s - m_new) : 0.f;
+        l = l * corr + warp_sum(e);
+#pragma unroll
+        for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= corr;
+        int n_valid = min(32, pos - base + 1);
+        for (int j = 0; j < n_valid; ++j) {
+            float pj = __shfl_sync(0xffffffffu, e, j);
+            unsigned long long rj = __shfl_sync(0xffffffffu, row, j);
+            const T* vr = vbase + rj;
+#pragma unroll
+            for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+                int d = lane + 32 * i;
+                if (d < hd) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
+            }
+        }
+        m = m_new;
+    }
+    float inv = 1.0f / l;
+    T* o = (T*)a.out + ((size_t)t * a.heads + h) * hd;
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+        int d = lane + 32 * i;
+        if (d < hd) o[d] = from_float<T>(acc[i] * inv);
+    }
+}
+
+void attention_plain(const AttentionArgs& a, cudaStream_t stream) {
+    if (a.T <= 0) return;
+    if (a.head_dim % 8 || a.head_dim > kMaxHeadDim || a.head_dim <= 0)
+        throw std::invalid_argument("attention_plain: head_dim " + std::to_string(a.head_dim) +
+                                    " must be a multiple of 8 between 8 and 256");
+    if (a.heads % a.kv_heads)
+        throw std::invalid_argument("attention_plain: kv_heads must divide heads");
+    bool paged = a.k_packed == nullptr;
+    if (paged && (a.k_pool == nullptr || a.page_table == nullptr))
+        throw std::invalid_argument("attention_plain: neither packed keys nor a cache were given");
+    long long items = (long long)a.T * a.heads;
+    unsigned blocks = (unsigned)((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    int threads = kWarpsPerBlock * 32;
+    if (a.dt == F32) {
+        if (paged) attention_plain_kernel<float, true><<<blocks, threads, 0, stream>>>(a);
+        else attention_plain_kernel<float, false><<<blocks, threads, 0, stream>>>(a);
+    } else {
+        if (paged) attention_plain_kernel<__nv_bfloat16, true><<<blocks, threads, 0, stream>>>(a);
+        else attention_plain_kernel<__nv_bfloat16, false><<<blocks, threads, 0, stream>>>(a);
+    }
+}
+
+}  // namespace sm

@@ -1,0 +1,100 @@
+// The C interface of the kernel library: plain functions over device pointers, so that it
+// can be loaded with dlopen/ctypes and has no dependency beyond the CUDA runtime. Each
+// function returns 0 or a non-zero status and leaves a message for sm_last_error(), in the
+// manner of the reference's status channel (src/util.h:28-70): after an error the next call
+// still works.
+#include <cuda_runtime.h>
+
+#include <exception>
+#include <string>
+
+#include "kernels.h"
+
+namespace {
+thread_local std::string g_last_error;
+
+template <typename F>
+int guarded(F&& body) {
+    try {
+        body();
+        cudaError_t e = cudaPeekAtLastError();
+        if (e != cudaSuccess) {
+            g_last_error = std::string("CUDA: ") + cudaGetErrorString(e);
+            cudaGetLastError();
+            return 2;
+        }
+        return 0;
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+        return 1;
+    } catch (...) {
+        g_last_error = "unknown error";
+        return 1;
+    }
+}
+}  // namespace
+
+#define SM_API extern "C" __attribute__((visibility("default")))
+
+SM_API const char* sm_last_error() { return g_last_error.c_str(); }
+
+SM_API int sm_embedding(const void* table, int table_dt, const int32_t* tokens, float* out, int T, int D, int V,
+                        int32_t* status, void* stream) {
+    return guarded([&] { sm::embedding(table, (sm::DType)table_dt, tokens, out, T, D, V, status, (cudaStream_t)stream); });
+}
+
+SM_API int sm_rmsnorm(const float* x, const void* w, int w_dt, float eps, void* out, int out_dt,
+                      const int32_t* rows, int n_rows, int D, void* stream) {
+    return guarded([&] {
+        sm::rmsnorm(x, w, (sm::DType)w_dt, eps, out, (sm::DType)out_dt, rows, n_rows, D, (cudaStream_t)stream);
+    });
+}
+
+SM_API int sm_swiglu(const float* gate_up, void* out, int out_dt, int T, int H, void* stream) {
+    return guarded([&] { sm::swiglu(gate_up, out, (sm::DType)out_dt, T, H, (cudaStream_t)stream); });
+}
+
+SM_API int sm_rope_store(const float* qkv, int T, int heads, int kv_heads, int head_dim, int rotary_dim,
+                         const int32_t* positions, const float* cos_table, const float* sin_table, void* q_out,
+                         void* k_packed, void* v_packed, int dt, void* k_pool, void* v_pool,
+                         const int32_t* page_table, int table_stride, int ring, const int32_t* token_slot,
+                         const int32_t* token_end, void* stream) {
+    return guarded([&] {
+        sm::RopeStoreArgs a{qkv, T, heads, kv_heads, head_dim, rotary_dim, positions, cos_table, sin_table,
+                            q_out, k_packed, v_packed, (sm::DType)dt, k_pool, v_pool, page_table, table_stride,
+                            ring, token_slot, token_end};
+        sm::rope_store(a, (cudaStream_t)stream);
+    });
+}
+
+SM_API int sm_gemm_simt(const void* x, int x_dt, const void* w, int w_dt, const void* bias, int bias_dt, void* out,
+                        int out_dt, int T, int N, int K, int accumulate, void* stream) {
+    return guarded([&] {
+        sm::gemm_simt(x, (sm::DType)x_dt, w, (sm::DType)w_dt, bias, (sm::DType)bias_dt, out, (sm::DType)out_dt, T, N,
+                      K, accumulate != 0, (cudaStream_t)stream);
+    });
+}
+
+SM_API int sm_attention_plain(const void* q, void* out, int dt, int T, int heads, int kv_heads, int head_dim,
+                              float scale, int window, const int32_t* positions, const void* k_packed,
+                              const void* v_packed, const int32_t* token_seq_start, const void* k_pool,
+                              const void* v_pool, const int32_t* page_table, int table_stride, int ring,
+                              const int32_t* token_slot, void* stream) {
+    return guarded([&] {
+        sm::AttentionArgs a{q, out, (sm::DType)dt, T, heads, kv_heads, head_dim, scale, window, positions,
+                            k_packed, v_packed, token_seq_start, k_pool, v_pool, page_table, table_stride, ring,
+                            token_slot};
+        sm::attention_plain(a, (cudaStream_t)stream);
+    });
+}
+
+SM_API int sm_argmax(const float* logits, const uint8_t* banned, int32_t* out, int B, int V, void* stream) {
+    return guarded([&] { sm::argmax(logits, banned, out, B, V, (cudaStream_t)stream); });
+}
+
+SM_API int sm_sample(const float* logits, const uint8_t* banned, int32_t* out, uint32_t* rng_state, int B, int V,
+                     float temperature, int top_k, float top_p, void* stream) {
+    return guarded([&] {
+        sm::sample(logits, banned, out, rng_state, B, V, temperature, top_k, top_p, (cudaStream_t)stream);
+    });
+}

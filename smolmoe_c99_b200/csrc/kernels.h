@@ -1,0 +1,93 @@
+// Host-side launchers of every kernel in this library. Pointers are device pointers; each
+// call enqueues on `stream` and returns. Arithmetic is float everywhere; `DType` names the
+// storage of a tensor. A launcher that cannot take a size throws std::invalid_argument
+// with the size in the message rather than compute a wrong result.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sm {
+
+enum DType : int { F32 = 0, BF16 = 1 };
+
+// ---- elementwise.cu -------------------------------------------------------------------
+// out[t, :] = table[tokens[t], :] as float. A token outside [0, V) sets *status |= 1 and
+// its row is zeroed.
+void embedding(const void* table, DType table_dt, const int32_t* tokens, float* out, int T, int D,
+               int V, int32_t* status, cudaStream_t stream);
+
+// y = x * (1 / sqrtf(mean(x^2) + eps)) * w for each row (src/model.c:334-342 of the reference).
+// `rows` (nullable) picks the input rows: out[r] = norm(x[rows[r]]).
+void rmsnorm(const float* x, const void* w, DType w_dt, float eps, void* out, DType out_dt,
+             const int32_t* rows, int n_rows, int D, cudaStream_t stream);
+
+// out[t, j] = up[t, j] * (gate[t, j] / (1 + exp(-gate[t, j]))), gate = gate_up[t, j],
+// up = gate_up[t, H + j] (src/vecmath.c:78-81).
+void swiglu(const float* gate_up, void* out, DType out_dt, int T, int H, cudaStream_t stream);
+
+struct RopeStoreArgs {
+    const float* qkv;           // [T, (heads + 2 kv_heads) * head_dim], bias already added
+    int T, heads, kv_heads, head_dim, rotary_dim;
+    const int32_t* positions;   // [T] absolute positions
+    const float* cos_table;     // [max_positions, rotary_dim / 2]
+    const float* sin_table;
+    void* q_out;                // [T, heads, head_dim]
+    void* k_packed;             // [T, kv_heads, head_dim] or null
+    void* v_packed;
+    DType dt;                   // storage of q_out, k_packed, v_packed and the pools
+    void* k_pool;               // one layer's page pool or null
+    void* v_pool;
+    const int32_t* page_table;  // [slots, table_stride]
+    int table_stride;
+    int ring;                   // 0, or the number of positions a windowed group keeps
+    const int32_t* token_slot;  // [T]
+    const int32_t* token_end;   // [T] the sequence's length after this step
+};
+// Rotates q and k (pairs (i, i + rotary_dim/2), src/model.c:439-450 with the converter's
+// permutation undone), writes q, and writes k and v to the packed buffers and the cache.
+void rope_store(const RopeStoreArgs& a, cudaStream_t stream);
+
+// ---- gemm_simt.cu ---------------------------------------------------------------------
+// out[t, n] (+)= sum_k x[t, k] * w[n, k] + bias[n]; float FMA in ascending k for every
+// element, whatever T is. x: F32 or BF16; w, bias: F32 or BF16; out: F32 or BF16.
+void gemm_simt(const void* x, DType x_dt, const void* w, DType w_dt, const void* bias, DType bias_dt,
+               void* out, DType out_dt, int T, int N, int K, bool accumulate, cudaStream_t stream);
+
+// ---- attention_plain.cu ---------------------------------------------------------------
+struct AttentionArgs {
+    const void* q;              // [T, heads, head_dim]
+    void* out;                  // [T, heads, head_dim]
+    DType dt;
+    int T, heads, kv_heads, head_dim;
+    float scale;
+    int window;                 // 0: every key up to the query's position
+    const int32_t* positions;   // [T]
+    // keys and values either packed for this step's own tokens ...
+    const void* k_packed;       // [T, kv_heads, head_dim] or null
+    const void* v_packed;
+    const int32_t* token_seq_start;  // [T] packed index of position 0 of the token's sequence
+    // ... or in the cache
+    const void* k_pool;
+    const void* v_pool;
+    const int32_t* page_table;
+    int table_stride;
+    int ring;
+    const int32_t* token_slot;  // [T]
+};
+// One warp per (token, head); keys in ascending order in groups of 32 from the first
+// visible key, so the result depends only on the query, the visible keys and the window.
+void attention_plain(const AttentionArgs& a, cudaStream_t stream);
+
+// ---- sampling.cu ----------------------------------------------------------------------
+// out[b] = argmax over the allowed ids of logits[b, :], the lowest id on ties
+// (src/sampler.c:57-63). `banned` (nullable) is one byte per id.
+void argmax(const float* logits, const uint8_t* banned, int32_t* out, int B, int V, cudaStream_t stream);
+
+// Temperature sampling with optional top-k (0 or >= V: off) and top-p (1: off), one
+// xorshift32 state per row, advanced once per call (src/sampler.c:103-127). out[b] = -1
+// when every id is banned.
+void sample(const float* logits, const uint8_t* banned, int32_t* out, uint32_t* rng_state, int B, int V,
+            float temperature, int top_k, float top_p, cudaStream_t stream);
+
+}  // namespace sm

@@ -1,0 +1,68 @@
+"""One step's work as the kernels see it: the tokens of all sequences packed one after
+another, with each token's position, slot and sequence.
+
+The requests of a step either all start at their first token (``prefill``: whole prompts of
+unequal lengths) or all go on by one token (``decode``)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+
+
+@dataclass
+class StepBatch:
+    mode: str                       # "prefill" or "decode"
+    n_seqs: int
+    n_tokens: int
+    slots: List[int]                # per sequence
+    seq_lens: List[int]             # tokens of each sequence in this step
+    max_seq_len: int                # longest sequence after this step
+    tokens: torch.Tensor            # int32 [T]
+    positions: torch.Tensor         # int32 [T] absolute positions
+    token_slot: torch.Tensor        # int32 [T]
+    token_end: torch.Tensor         # int32 [T] the token's sequence length after this step
+    token_seq_start: torch.Tensor   # int32 [T] packed index of the sequence's first token
+    cu_seqlens: torch.Tensor        # int32 [B + 1]
+    slot_ids: torch.Tensor          # int32 [B]
+    seq_ends: torch.Tensor          # int32 [B] lengths after this step
+
+
+def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence[Sequence[int]],
+              device: torch.device) -> StepBatch:
+    """``starts[i]`` is the length of sequence ``i`` before this step."""
+    if not slots:
+        raise ValueError("a step needs at least one sequence")
+    lens = [len(t) for t in token_lists]
+    if any(n == 0 for n in lens):
+        raise ValueError("every sequence of a step brings at least one token")
+    if all(s == 0 for s in starts):
+        mode = "prefill"
+    elif all(n == 1 for n in lens):
+        mode = "decode"
+    else:
+        raise ValueError("the sequences of a step either all start at their first token or all go on by one token")
+    tokens: List[int] = []
+    positions: List[int] = []
+    token_slot: List[int] = []
+    token_end: List[int] = []
+    token_seq_start: List[int] = []
+    cu = [0]
+    for slot, start, toks in zip(slots, starts, token_lists):
+        first = len(tokens)
+        n = len(toks)
+        tokens.extend(int(t) for t in toks)
+        positions.extend(range(start, start + n))
+        token_slot.extend([slot] * n)
+        token_end.extend([start + n] * n)
+        token_seq_start.extend([first] * n)
+        cu.append(first + n)
+    host = torch.tensor([tokens, positions, token_slot, token_end, token_seq_start], dtype=torch.int32)
+    dev = host.to(device)
+    per_seq = torch.tensor([list(slots), [s + n for s, n in zip(starts, lens)]], dtype=torch.int32).to(device)
+    return StepBatch(
+        mode=mode, n_seqs=len(slots), n_tokens=len(tokens), slots=list(slots), seq_lens=lens,
+        max_seq_len=max(s + n for s, n in zip(starts, lens)),
+        tokens=dev[0], positions=dev[1], token_slot=dev[2], token_end=dev[3], token_seq_start=dev[4],
+        cu_seqlens=torch.tensor(cu, dtype=torch.int32).to(device), slot_ids=per_seq[0], seq_ends=per_seq[1])

@@ -1,0 +1,217 @@
+"""Python faces of the CUDA kernels: each takes torch CUDA tensors, checks them, and calls
+the C function on the current stream. Nothing here computes; there is no fallback."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+PAGE_SIZE = 64  # positions per cache page; must equal sm::kPageSize
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments (the message names the size) or CUDA reported an error."""
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported dtype {t.dtype}: kernels take float32 and bfloat16")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, what: str, dtype=None, ndim=None) -> torch.Tensor:
+    if not t.is_cuda:
+        raise KernelError(f"{what} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{what} must have {ndim} dimensions, got {t.dim()}")
+    return t
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class Ops:
+    """The kernel library, loaded (and built if needed) at construction."""
+
+    def __init__(self) -> None:
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this library runs on an NVIDIA B200 only (no CPU fallback)")
+        self.lib = build.load()
+
+    def _check(self, status: int) -> None:
+        if status:
+            raise KernelError(self.lib.sm_last_error().decode("utf-8", "replace"))
+
+    # ---- elementwise -------------------------------------------------------------------
+    def embedding(self, table: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _need(table, "embedding table", ndim=2)
+        _need(tokens, "tokens", torch.int32, 1)
+        out = torch.empty((tokens.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+        self._check(self.lib.sm_embedding(_ptr(table), _dt(table), _ptr(tokens), _ptr(out), tokens.numel(),
+                                          table.shape[1], table.shape[0], _ptr(status), _stream()))
+        return out
+
+    def rmsnorm(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _need(x, "norm input", torch.float32, 2)
+        _need(weight, "norm weight", ndim=1)
+        if weight.numel() != x.shape[1]:
+            raise KernelError(f"norm weight has {weight.numel()} elements, rows have {x.shape[1]}")
+        n = x.shape[0] if rows is None else _need(rows, "rows", torch.int32, 1).numel()
+        out = torch.empty((n, x.shape[1]), dtype=out_dtype, device=x.device)
+        self._check(self.lib.sm_rmsnorm(_ptr(x), _ptr(weight), _dt(weight), ctypes.c_float(eps), _ptr(out), _dt(out),
+                                        _ptr(rows), n, x.shape[1], _stream()))
+        return out
+
+    def swiglu(self, gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        _need(gate_up, "gate_up", torch.float32, 2)
+        hidden = gate_up.shape[1] // 2
+        out = torch.empty((gate_up.shape[0], hidden), dtype=out_dtype, device=gate_up.device)
+        self._check(self.lib.sm_swiglu(_ptr(gate_up), _ptr(out), _dt(out), gate_up.shape[0], hidden, _stream()))
+        return out
+
+    def rope_store(self, qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim, rotary_dim, out_dtype,
+                   want_packed, k_pool=None, v_pool=None, page_table=None, ring=0, token_slot=None, token_end=None):
+        """Returns (q, k_packed, v_packed); the packed keys and values are None unless asked for."""
+        _need(qkv, "qkv", torch.float32, 2)
+        T = qkv.shape[0]
+        if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+            raise KernelError(f"qkv rows have {qkv.shape[1]} elements, expected {(heads + 2 * kv_heads) * head_dim}")
+        _need(positions, "positions", torch.int32, 1)
+        _need(cos_table, "cos table", torch.float32, 2)
+        _need(sin_table, "sin table", torch.float32, 2)
+        if cos_table.shape[1] != rotary_dim // 2:
+            raise KernelError("cos/sin tables do not match rotary_dim")
+        q = torch.empty((T, heads, head_dim), dtype=out_dtype, device=qkv.device)
+        kp = vp = None
+        if want_packed:
+            kp = torch.empty((T, kv_heads, head_dim), dtype=out_dtype, device=qkv.device)
+            vp = torch.empty_like(kp)
+        table_stride = 0
+        if k_pool is not None:
+            _need(k_pool, "key pool", out_dtype)
+            _need(v_pool, "value pool", out_dtype)
+            _need(page_table, "page table", torch.int32, 2)
+            _need(token_slot, "token_slot", torch.int32, 1)
+            _need(token_end, "token_end", torch.int32, 1)
+            table_stride = page_table.shape[1]
+        self._check(self.lib.sm_rope_store(
+            _ptr(qkv), T, heads, kv_heads, head_dim, rotary_dim, _ptr(positions), _ptr(cos_table), _ptr(sin_table),
+            _ptr(q), _ptr(kp), _ptr(vp), _dt(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), table_stride, ring,
+            _ptr(token_slot), _ptr(token_end), _stream()))
+        return q, kp, vp
+
+    # ---- matrix products ---------------------------------------------------------------
+    def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                  accumulate: bool = False) -> torch.Tensor:
+        _need(x, "x", ndim=2)
+        _need(w, "w", ndim=2)
+        _need(out, "out", ndim=2)
+        T, K = x.shape
+        N = w.shape[0]
+        if w.shape[1] != K or tuple(out.shape) != (T, N):
+            raise KernelError(f"gemm shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if bias is not None and _need(bias, "bias", ndim=1).numel() != N:
+            raise KernelError(f"bias has {bias.numel()} elements, expected {N}")
+        self._check(self.lib.sm_gemm_simt(_ptr(x), _dt(x), _ptr(w), _dt(w), _ptr(bias),
+                                          _dt(bias) if bias is not None else F32, _ptr(out), _dt(out), T, N, K,
+                                          int(accumulate), _stream()))
+        return out
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+               out_dtype: Optional[torch.dtype] = None, accumulate: bool = False) -> torch.Tensor:
+        """out (+)= x @ w.T + bias. float32 operands run on the CUDA cores in float; bfloat16
+        operands run on the tensor cores where the shape allows, else on the CUDA cores."""
+        if out is None:
+            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+        return self.gemm_simt(x, w, bias, out, accumulate)
+
+    def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor, hidden: int, out_dtype: torch.dtype) -> torch.Tensor:
+        """act(x @ w_gate.T) * (x @ w_up.T) with w_gate_up = [w_gate; w_up]."""
+        gate_up = self.linear(x, w_gate_up, None, out_dtype=torch.float32)
+        return self.swiglu(gate_up, out_dtype)
+
+    # ---- attention ---------------------------------------------------------------------
+    def attention_plain(self, q, positions, scale, window, *, k_packed=None, v_packed=None, token_seq_start=None,
+                        k_pool=None, v_pool=None, page_table=None, ring=0, token_slot=None, kv_heads=None):
+        _need(q, "q", ndim=3)
+        T, heads, head_dim = q.shape
+        _need(positions, "positions", torch.int32, 1)
+        out = torch.empty_like(q)
+        table_stride = 0
+        if k_packed is not None:
+            _need(k_packed, "packed keys", q.dtype, 3)
+            _need(v_packed, "packed values", q.dtype, 3)
+            _need(token_seq_start, "token_seq_start", torch.int32, 1)
+            kv_heads = k_packed.shape[1]
+        else:
+            _need(k_pool, "key pool", q.dtype)
+            _need(v_pool, "value pool", q.dtype)
+            _need(page_table, "page table", torch.int32, 2)
+            _need(token_slot, "token_slot", torch.int32, 1)
+            table_stride = page_table.shape[1]
+        self._check(self.lib.sm_attention_plain(
+            _ptr(q), _ptr(out), _dt(q), T, heads, kv_heads, head_dim, ctypes.c_float(scale), int(window or 0),
+            _ptr(positions), _ptr(k_packed), _ptr(v_packed), _ptr(token_seq_start), _ptr(k_pool), _ptr(v_pool),
+            _ptr(page_table), table_stride, ring, _ptr(token_slot), _stream()))
+        return out
+
+    def attention_prefill(self, q, k_packed, v_packed, step, scale, window):
+        """Causal attention of whole prompts over their own keys (sequences start at 0)."""
+        return self.attention_plain(q, step.positions, scale, window, k_packed=k_packed, v_packed=v_packed,
+                                    token_seq_start=step.token_seq_start)
+
+    def attention_cached(self, q, step, scale, window, cache, kv_heads):
+        """Attention of this step's tokens over the keys and values in the cache."""
+        return self.attention_plain(q, step.positions, scale, window, k_pool=cache.k_pool, v_pool=cache.v_pool,
+                                    page_table=cache.page_table, ring=cache.ring, token_slot=step.token_slot,
+                                    kv_heads=kv_heads)
+
+    # ---- sampling ----------------------------------------------------------------------
+    def argmax(self, logits: torch.Tensor, banned: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+        _need(logits, "logits", torch.float32, 2)
+        if banned is not None:
+            _need(banned, "banned", torch.uint8, 1)
+        if out is None:
+            out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+        self._check(self.lib.sm_argmax(_ptr(logits), _ptr(banned), _ptr(out), logits.shape[0], logits.shape[1], _stream()))
+        return out
+
+    def sample(self, logits, rng_state, temperature, top_k, top_p, banned=None, out=None):
+        _need(logits, "logits", torch.float32, 2)
+        _need(rng_state, "rng_state", torch.int32, 1)  # xorshift32 words, one per row
+        if rng_state.numel() != logits.shape[0]:
+            raise KernelError("one rng state per row is needed")
+        if banned is not None:
+            _need(banned, "banned", torch.uint8, 1)
+        if out is None:
+            out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+        self._check(self.lib.sm_sample(_ptr(logits), _ptr(banned), _ptr(out), _ptr(rng_state), logits.shape[0],
+                                       logits.shape[1], ctypes.c_float(temperature), int(top_k), ctypes.c_float(top_p),
+                                       _stream()))
+        return out
+
+
+_ops: Optional[Ops] = None
+
+
+def get_ops() -> Ops:
+    global _ops
+    if _ops is None:
+        _ops = Ops()
+    return _ops

@@ -1,0 +1,87 @@
+"""The attention mixer: q/k/v projections with bias, rotation of q and k, cache write,
+causal attention over all keys or a window of them with grouped heads, output projection
+added to the residual (reference: src/model.c:493-542; head-to-group map and window start:
+src/model.c:459-472; scores, softmax and value sum: src/kernels.c:1138-1176).
+
+Sizes and constants (hidden size, heads, groups, head size, window, scale, bias, position
+encoding) are parameters of the part. With ``kv_from_cache`` the part has no k/v
+projections of its own and attends over the cache of the run it is pointed at.
+"""
+from __future__ import annotations
+
+from typing import List, Mapping, Optional
+
+import torch
+
+from ..config.spec import PartSpec
+from .base import MIXERS, POSITIONS, KVNeed, ParamSpec, Part, Runtime, full_name
+
+
+@MIXERS.register("attention")
+class Attention(Part):
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        super().__init__(spec, runtime)
+        self.hidden = int(spec["hidden_size"])
+        self.heads = int(spec["heads"])
+        self.kv_heads = int(spec["kv_heads"])
+        self.head_dim = int(spec["head_dim"])
+        self.window = spec.get("window")
+        self.scale = float(spec["scale"])
+        self.bias = bool(spec.get("qkv_bias", False))
+        self.kv_from_cache = bool(spec.get("kv_from_cache", False))
+        if self.heads % self.kv_heads:
+            raise ValueError(f"kv_heads {self.kv_heads} must divide heads {self.heads}")
+        if self.head_dim % 16 or self.head_dim > 256:
+            raise ValueError(f"head_dim {self.head_dim}: the attention kernels take multiples of 16 up to 256")
+        pos_spec: PartSpec = spec["position"]
+        self.position = POSITIONS.get(pos_spec.kind)(pos_spec, runtime)
+        self.w_qkv = self.b_qkv = self.w_o = None
+
+    # ---- weights -----------------------------------------------------------------------
+    @classmethod
+    def param_specs(cls, spec: PartSpec, prefix: str) -> List[ParamSpec]:
+        d, hd = int(spec["hidden_size"]), int(spec["head_dim"])
+        qd, kd = int(spec["heads"]) * hd, int(spec["kv_heads"]) * hd
+        names = spec.names
+        keys = [("q", qd)] if spec.get("kv_from_cache") else [("q", qd), ("k", kd), ("v", kd)]
+        out = [ParamSpec(k, full_name(prefix, names[k]), (rows, d)) for k, rows in keys]
+        out.append(ParamSpec("o", full_name(prefix, names["o"]), (d, qd)))
+        if spec.get("qkv_bias"):
+            out += [ParamSpec(k + "_bias", full_name(prefix, names[k + "_bias"]), (rows,)) for k, rows in keys]
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        keys = ["q"] if self.kv_from_cache else ["q", "k", "v"]
+        # one product for q, k and v, as the reference computes them (src/model.c:506-509)
+        self.w_qkv = torch.cat([tensors[k] for k in keys], dim=0).contiguous()
+        self.b_qkv = torch.cat([tensors[k + "_bias"] for k in keys], dim=0).contiguous() if self.bias else None
+        self.w_o = tensors["o"]
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec):
+        if spec.get("kv_from_cache"):
+            return None
+        return KVNeed(int(spec["kv_heads"]), int(spec["head_dim"]), spec.get("window"))
+
+    # ---- one step ----------------------------------------------------------------------
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
+        ops, rt = self.runtime.ops, self.runtime
+        T = x.shape[0]
+        cos, sin = self.position.tables(rt.max_positions)
+        kv_heads_here = 0 if self.kv_from_cache else self.kv_heads
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
+        prefill = step.mode == "prefill"
+        if cache.kind != "kv":
+            raise RuntimeError("attention needs a key/value cache")
+        q, k_packed, v_packed = ops.rope_store(
+            qkv, step.positions, cos, sin, self.heads, kv_heads_here, self.head_dim, self.position.rotary_dim,
+            rt.dtype, want_packed=prefill and not self.kv_from_cache,
+            k_pool=None if self.kv_from_cache else cache.k_pool, v_pool=None if self.kv_from_cache else cache.v_pool,
+            page_table=cache.page_table, ring=cache.ring, token_slot=step.token_slot, token_end=step.token_end)
+        if prefill and not self.kv_from_cache:
+            att = ops.attention_prefill(q, k_packed, v_packed, step, self.scale, self.window)
+        else:
+            if prefill and cache.ring and step.max_seq_len > cache.ring:
+                raise RuntimeError("a prompt longer than the window cannot be read back from a windowed cache")
+            att = ops.attention_cached(q, step, self.scale, self.window, cache, self.kv_heads)
+        ops.linear(att.view(T, self.heads * self.head_dim), self.w_o, None, out=residual, accumulate=True)

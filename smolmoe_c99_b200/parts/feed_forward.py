@@ -1,0 +1,38 @@
+"""The gated feed-forward: down(up(x) * act(gate(x))), added to the residual; gate and up
+are one product (reference: src/model.c:547-561; SiLU: src/vecmath.c:78-81)."""
+from __future__ import annotations
+
+from typing import List, Mapping
+
+import torch
+
+from ..config.spec import PartSpec
+from .base import FEED_FORWARDS, ParamSpec, Part, Runtime, full_name
+
+
+@FEED_FORWARDS.register("gated_mlp")
+class GatedMLP(Part):
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        super().__init__(spec, runtime)
+        self.hidden = int(spec["hidden_size"])
+        self.intermediate = int(spec["intermediate_size"])
+        if spec.get("activation", "silu") != "silu":
+            raise ValueError(f"gated_mlp: activation {spec.get('activation')!r} is not built (silu is)")
+        self.w_gate_up = self.w_down = None
+
+    @classmethod
+    def param_specs(cls, spec: PartSpec, prefix: str) -> List[ParamSpec]:
+        d, h = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        n = spec.names
+        return [ParamSpec("gate", full_name(prefix, n["gate"]), (h, d)),
+                ParamSpec("up", full_name(prefix, n["up"]), (h, d)),
+                ParamSpec("down", full_name(prefix, n["down"]), (d, h))]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
+        self.w_down = tensors["down"]
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, step) -> None:
+        ops = self.runtime.ops
+        h = ops.gated_linear(x, self.w_gate_up, self.intermediate, self.runtime.dtype)
+        ops.linear(h, self.w_down, None, out=residual, accumulate=True)
