@@ -7,7 +7,7 @@ from typing import Optional
 
 import torch
 
-from . import build
+from .build import load as load_library
 
 F32, BF16 = 0, 1
 PAGE_SIZE = 64  # positions per cache page; must equal sm::kPageSize
@@ -51,7 +51,7 @@ class Ops:
     def __init__(self) -> None:
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: this library runs on an NVIDIA B200 only (no CPU fallback)")
-        self.lib = build.load()
+        self.lib = load_library()
 
     def _check(self, status: int) -> None:
         if status:
