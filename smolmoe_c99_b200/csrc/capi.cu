@@ -98,3 +98,17 @@ SM_API int sm_sample(const float* logits, const uint8_t* banned, int32_t* out, u
         sm::sample(logits, banned, out, rng_state, B, V, temperature, top_k, top_p, (cudaStream_t)stream);
     });
 }
+
+SM_API int sm_gemm_tc_supports(int T, int N, int K) { return sm::gemm_tc_supports(T, N, K) ? 1 : 0; }
+
+SM_API long long sm_gemm_tc_workspace_bytes(int T, int N, int K, int dual) {
+    return (long long)sm::gemm_tc_workspace_bytes(T, N, K, dual != 0);
+}
+
+SM_API int sm_gemm_tc(const void* x, const void* w, const void* bias, int bias_dt, void* out, int out_dt, int T,
+                      int N, int K, int mode, int up_offset, float* workspace, int* error, void* stream) {
+    return guarded([&] {
+        sm::gemm_tc(x, w, bias, (sm::DType)bias_dt, out, (sm::DType)out_dt, T, N, K, mode, up_offset, workspace, error,
+                    (cudaStream_t)stream);
+    });
+}

@@ -54,6 +54,17 @@ void rope_store(const RopeStoreArgs& a, cudaStream_t stream);
 void gemm_simt(const void* x, DType x_dt, const void* w, DType w_dt, const void* bias, DType bias_dt,
                void* out, DType out_dt, int T, int N, int K, bool accumulate, cudaStream_t stream);
 
+// ---- gemm_tc.cu -----------------------------------------------------------------------
+// The same product for bfloat16 x and w on the tcgen05 tensor cores (TMA-fed, accumulator
+// in tensor memory). mode 0: out = x w^T + bias (out F32 or BF16); 1: float out += x w^T;
+// 2: out = act(x w_gate^T) * (x w_up^T) where w holds the gate rows [0, N) and the up rows
+// [up_offset, up_offset + N). Shapes whose K is split over several CTAs need a workspace
+// of gemm_tc_workspace_bytes(). *error becomes non-zero if a bounded wait ran out.
+bool gemm_tc_supports(int T, int N, int K);
+size_t gemm_tc_workspace_bytes(int T, int N, int K, bool dual);
+void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N,
+             int K, int mode, int up_offset, float* workspace, int* error, cudaStream_t stream);
+
 // ---- attention_plain.cu ---------------------------------------------------------------
 struct AttentionArgs {
     const void* q;              // [T, heads, head_dim]

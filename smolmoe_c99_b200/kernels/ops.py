@@ -52,6 +52,9 @@ class Ops:
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: this library runs on an NVIDIA B200 only (no CPU fallback)")
         self.lib = load_library()
+        self.lib.sm_gemm_tc_workspace_bytes.restype = ctypes.c_longlong
+        self.use_tensor_cores = True  # False routes bfloat16 products to the CUDA-core kernel
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
 
     def _check(self, status: int) -> None:
         if status:
@@ -139,12 +142,53 @@ class Ops:
         operands run on the tensor cores where the shape allows, else on the CUDA cores."""
         if out is None:
             out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+        if self._tensor_core_ok(x, w) and (not accumulate or out.dtype == torch.float32):
+            return self.gemm_tc(x, w, bias, out, mode=1 if accumulate else 0)
         return self.gemm_simt(x, w, bias, out, accumulate)
 
     def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor, hidden: int, out_dtype: torch.dtype) -> torch.Tensor:
         """act(x @ w_gate.T) * (x @ w_up.T) with w_gate_up = [w_gate; w_up]."""
+        if self._tensor_core_ok(x, w_gate_up):
+            out = torch.empty((x.shape[0], hidden), dtype=out_dtype, device=x.device)
+            return self.gemm_tc(x, w_gate_up, None, out, mode=2, up_offset=hidden)
         gate_up = self.linear(x, w_gate_up, None, out_dtype=torch.float32)
         return self.swiglu(gate_up, out_dtype)
+
+    def _tensor_core_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        return (self.use_tensor_cores and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and bool(self.lib.sm_gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1])))
+
+    def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int = 0,
+                up_offset: int = 0) -> torch.Tensor:
+        """The tcgen05 product. mode 0: out = x w^T + bias; 1: float out += x w^T;
+        2: out = act(x w[:N]^T) * (x w[up_offset:up_offset+N]^T)."""
+        _need(x, "x", torch.bfloat16, 2)
+        _need(w, "w", torch.bfloat16, 2)
+        _need(out, "out", ndim=2)
+        T, K = x.shape
+        N = out.shape[1]
+        rows_needed = up_offset + N if mode == 2 else N
+        if w.shape[1] != K or out.shape[0] != T or w.shape[0] != rows_needed:
+            raise KernelError(f"gemm shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if mode == 1 and out.dtype != torch.float32:
+            raise KernelError("accumulation needs a float32 output")
+        if bias is not None and _need(bias, "bias", ndim=1).numel() != N:
+            raise KernelError(f"bias has {bias.numel()} elements, expected {N}")
+        if T == 0:
+            return out
+        need = int(self.lib.sm_gemm_tc_workspace_bytes(T, N, K, int(mode == 2)))
+        workspace = torch.empty((need // 4,), dtype=torch.float32, device=x.device) if need else None
+        self._check(self.lib.sm_gemm_tc(_ptr(x), _ptr(w), _ptr(bias), _dt(bias) if bias is not None else F32, _ptr(out),
+                                        _dt(out), T, N, K, mode, up_offset, _ptr(workspace), _ptr(self.error_flag),
+                                        _stream()))
+        return out
+
+    def check_error_flag(self) -> None:
+        """Raises if a kernel gave up on a bounded wait since the last check (synchronises)."""
+        code = int(self.error_flag.item())
+        if code:
+            self.error_flag.zero_()
+            raise KernelError(f"a kernel's bounded wait ran out (code {code}); its output is not valid")
 
     # ---- attention ---------------------------------------------------------------------
     def attention_plain(self, q, positions, scale, window, *, k_packed=None, v_packed=None, token_seq_start=None,

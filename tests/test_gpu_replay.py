@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 # max |engine - plain| over all logits. float32: both sides compute in float with different
 # summation orders; logits are O(1). bfloat16: the plain side rounds where the engine stores.
-TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+TOL = {"float32": 5e-6, "bfloat16": 1e-2}
 
 
 def _requests(name, lengths, seed):
