@@ -1,0 +1,244 @@
+// Decode attention over the paged cache for bfloat16: one new token per sequence attends
+// to its sequence's keys, split along the positions so that one long sequence fills many
+// SMs (the reference scans [start, pos] per head on one thread: src/kernels.c:1156-1176).
+//
+// Kernel 1, one CTA per (kv head, sequence, chunk of kChunk positions): the group's query
+// heads share every key and value row that is read. Scores for the chunk, their running
+// maximum and sum, and the unnormalised weighted values go to a workspace:
+//   part_o [B, heads, splits, head_dim] float, part_ml [B, heads, splits, 2] float.
+// Kernel 2, one warp per (sequence, head): merges the chunks that hold visible keys in
+// ascending order and writes the normalised result.
+// Chunks without visible keys (beyond the sequence, or before the window) do no work and
+// are not read by the merge.
+#include <math_constants.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace sm {
+
+namespace {
+
+constexpr int kChunk = 128;       // positions per CTA
+constexpr int kThreads = 128;
+constexpr int kHeadPass = 8;      // query heads handled per pass over the keys
+constexpr int kMaxHeadDim = 256;
+
+struct DecodeArgs {
+    const __nv_bfloat16* q;       // [B, heads, head_dim]
+    __nv_bfloat16* out;           // [B, heads, head_dim]
+    const __nv_bfloat16* k_pool;
+    const __nv_bfloat16* v_pool;
+    const int32_t* page_table;
+    int table_stride, ring;
+    const int32_t* slots;         // [B]
+    const int32_t* positions;     // [B] position of the new token (its key is already in the cache)
+    int B, heads, kv_heads, head_dim, window, splits;
+    float scale;
+    float* part_o;
+    float* part_ml;
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+    const int hd = a.head_dim, group = a.heads / a.kv_heads;
+    const int pos = a.positions[b];
+    const int start = (a.window > 0 && pos >= a.window) ? pos - a.window + 1 : 0;
+    const int c0 = split * kChunk;
+    if (c0 > pos || c0 + kChunk <= start) return;   // no visible key in this chunk
+    const int lo = max(c0, start), hi = min(c0 + kChunk - 1, pos);   // visible keys [lo, hi]
+
+    float* qs = reinterpret_cast<float*>(smem_raw);                    // [group][hd]
+    float* sc = qs + group * hd;                                       // [group][kChunk] scores, then weights
+    unsigned long long* rows = reinterpret_cast<unsigned long long*>(sc + group * kChunk);  // [kChunk]
+    float* red = reinterpret_cast<float*>(rows + kChunk);              // [key groups][kHeadPass][hd]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const __nv_bfloat16* qb = a.q + ((size_t)b * a.heads + (size_t)kvh * group) * hd;
+    for (int i = tid; i < group * hd; i += kThreads) qs[i] = __bfloat162float(qb[i]);
+    const int slot = a.slots[b];
+    PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
+    const int p = c0 + tid;
+    const bool valid = p >= lo && p <= hi;
+    unsigned long long row = 0;
+    if (valid) row = (unsigned long long)paged.row_offset(slot, p, kvh);
+    rows[tid] = row;
+    __syncthreads();
+
+    // scores: one key per thread, kHeadPass heads at a time
+    for (int g0 = 0; g0 < group; g0 += kHeadPass) {
+        float s[kHeadPass];
+#pragma unroll
+        for (int g = 0; g < kHeadPass; ++g) s[g] = 0.f;
+        if (valid) {
+            const __nv_bfloat16* kr = a.k_pool + row;
+            for (int d = 0; d < hd; d += 8) {
+                float kv[8];
+                load8(kr + d, kv);
+#pragma unroll
+                for (int g = 0; g < kHeadPass; ++g) {
+                    if (g0 + g < group) {
+                        const float4 qa = *reinterpret_cast<const float4*>(qs + (g0 + g) * hd + d);
+                        const float4 qc = *reinterpret_cast<const float4*>(qs + (g0 + g) * hd + d + 4);
+                        s[g] = fmaf(qa.x, kv[0], s[g]); s[g] = fmaf(qa.y, kv[1], s[g]);
+                        s[g] = fmaf(qa.z, kv[2], s[g]); s[g] = fmaf(qa.w, kv[3], s[g]);
+                        s[g] = fmaf(qc.x, kv[4], s[g]); s[g] = fmaf(qc.y, kv[5], s[g]);
+                        s[g] = fmaf(qc.z, kv[6], s[g]); s[g] = fmaf(qc.w, kv[7], s[g]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < kHeadPass; ++g)
+            if (g0 + g < group) sc[(g0 + g) * kChunk + tid] = valid ? s[g] * a.scale : -CUDART_INF_F;
+    }
+    __syncthreads();
+
+    // per head: maximum, weights exp(s - m) and their sum; warps take heads in turn
+    for (int g = warp; g < group; g += kThreads / 32) {
+        float m = -CUDART_INF_F;
+        for (int i = lane; i < kChunk; i += 32) m = fmaxf(m, sc[g * kChunk + i]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int i = lane; i < kChunk; i += 32) {
+            float e = expf(sc[g * kChunk + i] - m);   // masked keys: exp(-inf) = 0
+            sc[g * kChunk + i] = e;
+            l += e;
+        }
+        l = warp_sum(l);
+        if (lane == 0) {
+            float* ml = a.part_ml + (((size_t)b * a.heads + kvh * group + g) * a.splits + split) * 2;
+            ml[0] = m;
+            ml[1] = l;
+        }
+    }
+    __syncthreads();
+
+    // weighted values: a thread owns two neighbouring dims; thread groups take keys in turn
+    const int half = hd / 2;
+    const int key_groups = kThreads / half > 0 ? kThreads / half : 1;   // hd <= 256 -> half <= 128
+    const int kg = tid / half, dd = tid - kg * half;
+    const int first = lo - c0, last = hi - c0;
+    for (int g0 = 0; g0 < group; g0 += kHeadPass) {
+        float acc[kHeadPass][2];
+#pragma unroll
+        for (int g = 0; g < kHeadPass; ++g) acc[g][0] = acc[g][1] = 0.f;
+        if (kg < key_groups) {
+            for (int j = first + kg; j <= last; j += key_groups) {
+                const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(a.v_pool + rows[j] + 2 * dd);
+                const float2 v = __bfloat1622float2(v2);
+#pragma unroll
+                for (int g = 0; g < kHeadPass; ++g) {
+                    if (g0 + g < group) {
+                        float w = sc[(g0 + g) * kChunk + j];
+                        acc[g][0] = fmaf(w, v.x, acc[g][0]);
+                        acc[g][1] = fmaf(w, v.y, acc[g][1]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < kHeadPass; ++g) {
+                red[((size_t)kg * kHeadPass + g) * hd + 2 * dd] = acc[g][0];
+                red[((size_t)kg * kHeadPass + g) * hd + 2 * dd + 1] = acc[g][1];
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < kHeadPass * hd; i += kThreads) {
+            int g = i / hd, d = i - g * hd;
+            if (g0 + g < group) {
+                float sum = 0.f;
+                for (int k = 0; k < key_groups; ++k) sum += red[((size_t)k * kHeadPass + g) * hd + d];
+                a.part_o[(((size_t)b * a.heads + kvh * group + g0 + g) * a.splits + split) * hd + d] = sum;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void decode_merge_kernel(DecodeArgs a) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= a.B * a.heads) return;
+    const int b = warp / a.heads, hd = a.head_dim;
+    const int pos = a.positions[b];
+    const int start = (a.window > 0 && pos >= a.window) ? pos - a.window + 1 : 0;
+    const int s_lo = start / kChunk, s_hi = pos / kChunk;
+    const float* ml = a.part_ml + (size_t)warp * a.splits * 2;
+    const float* po = a.part_o + (size_t)warp * a.splits * hd;
+    float m = -CUDART_INF_F;
+    for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, ml[2 * s]);
+    float l = 0.f;
+    float acc[kMaxHeadDim / 32];
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
+    for (int s = s_lo; s <= s_hi; ++s) {
+        float w = expf(ml[2 * s] - m);
+        l = fmaf(ml[2 * s + 1], w, l);
+#pragma unroll
+        for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+            int d = lane + 32 * i;
+            if (d < hd) acc[i] = fmaf(po[(size_t)s * hd + d], w, acc[i]);
+        }
+    }
+    float inv = 1.0f / l;
+    __nv_bfloat16* o = a.out + (size_t)warp * hd;
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+        int d = lane + 32 * i;
+        if (d < hd) o[d] = __float2bfloat16_rn(acc[i] * inv);
+    }
+}
+
+}  // namespace
+
+int attention_decode_splits(int max_len) { return (max_len + kChunk - 1) / kChunk; }
+
+size_t attention_decode_workspace_floats(int B, int heads, int head_dim, int splits) {
+    return (size_t)B * heads * splits * (head_dim + 2);
+}
+
+void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
+                      const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
+                      const int32_t* page_table, int table_stride, int ring, int splits, float* workspace,
+                      cudaStream_t stream) {
+    if (B <= 0) return;
+    if (head_dim % 8 || head_dim <= 0 || head_dim > kMaxHeadDim)
+        throw std::invalid_argument("attention_decode: head_dim " + std::to_string(head_dim) +
+                                    " must be a multiple of 8 between 8 and 256");
+    if (heads % kv_heads) throw std::invalid_argument("attention_decode: kv_heads must divide heads");
+    if (splits <= 0 || splits > 65535) throw std::invalid_argument("attention_decode: splits out of range");
+    int group = heads / kv_heads;
+    int half = head_dim / 2;
+    int key_groups = kThreads / half > 0 ? kThreads / half : 1;
+    size_t smem = (size_t)group * head_dim * 4 + (size_t)group * kChunk * 4 + kChunk * 8 +
+                  (size_t)key_groups * kHeadPass * head_dim * 4;
+    if (smem > 200 * 1024)
+        throw std::invalid_argument("attention_decode: " + std::to_string(group) + " heads per kv head with head_dim " +
+                                    std::to_string(head_dim) + " need more shared memory than one SM has");
+    DecodeArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
+                 (const __nv_bfloat16*)v_pool, page_table, table_stride, ring, slots, positions,
+                 B, heads, kv_heads, head_dim, window, splits, scale,
+                 workspace, workspace + (size_t)B * heads * splits * head_dim};
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    dim3 grid(kv_heads, B, splits);
+    decode_partial_kernel<<<grid, kThreads, smem, stream>>>(a);
+    int warps = B * heads;
+    decode_merge_kernel<<<(warps * 32 + 127) / 128, 128, 0, stream>>>(a);
+}
+
+}  // namespace sm

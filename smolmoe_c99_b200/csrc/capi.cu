@@ -112,3 +112,29 @@ SM_API int sm_gemm_tc(const void* x, const void* w, const void* bias, int bias_d
                     (cudaStream_t)stream);
     });
 }
+
+SM_API int sm_attention_prefill_supports(int head_dim) { return sm::attention_prefill_supports(head_dim) ? 1 : 0; }
+
+SM_API int sm_attention_prefill(const void* q, const void* k, const void* v, void* out, const int32_t* tiles,
+                                int n_tiles, int heads, int kv_heads, int head_dim, float scale, int window,
+                                void* stream) {
+    return guarded([&] {
+        sm::attention_prefill(q, k, v, out, tiles, n_tiles, heads, kv_heads, head_dim, scale, window, (cudaStream_t)stream);
+    });
+}
+
+SM_API int sm_attention_decode_splits(int max_len) { return sm::attention_decode_splits(max_len); }
+
+SM_API long long sm_attention_decode_workspace_floats(int B, int heads, int head_dim, int splits) {
+    return (long long)sm::attention_decode_workspace_floats(B, heads, head_dim, splits);
+}
+
+SM_API int sm_attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale,
+                               int window, const int32_t* positions, const int32_t* slots, const void* k_pool,
+                               const void* v_pool, const int32_t* page_table, int table_stride, int ring, int splits,
+                               float* workspace, void* stream) {
+    return guarded([&] {
+        sm::attention_decode(q, out, B, heads, kv_heads, head_dim, scale, window, positions, slots, k_pool, v_pool,
+                             page_table, table_stride, ring, splits, workspace, (cudaStream_t)stream);
+    });
+}

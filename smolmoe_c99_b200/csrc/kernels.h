@@ -90,6 +90,25 @@ struct AttentionArgs {
 // visible key, so the result depends only on the query, the visible keys and the window.
 void attention_plain(const AttentionArgs& a, cudaStream_t stream);
 
+// ---- attention_prefill.cu -------------------------------------------------------------
+// Causal attention of packed whole prompts for bfloat16 on the tensor cores. `tiles` lists
+// the 64-query tiles: [n_tiles, 3] = (packed index of the sequence's first token, the
+// sequence's length, first query of the tile). head_dim: multiples of 16 up to 128.
+bool attention_prefill_supports(int head_dim);
+void attention_prefill(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles,
+                       int heads, int kv_heads, int head_dim, float scale, int window, cudaStream_t stream);
+
+// ---- attention_decode.cu --------------------------------------------------------------
+// One new token per sequence over the paged cache for bfloat16, split along the positions
+// in chunks; `splits` = attention_decode_splits(longest sequence) and the workspace holds
+// attention_decode_workspace_floats() floats.
+int attention_decode_splits(int max_len);
+size_t attention_decode_workspace_floats(int B, int heads, int head_dim, int splits);
+void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
+                      const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
+                      const int32_t* page_table, int table_stride, int ring, int splits, float* workspace,
+                      cudaStream_t stream);
+
 // ---- sampling.cu ----------------------------------------------------------------------
 // out[b] = argmax over the allowed ids of logits[b, :], the lowest id on ties
 // (src/sampler.c:57-63). `banned` (nullable) is one byte per id.

@@ -11,6 +11,9 @@ from typing import List, Optional, Sequence
 import torch
 
 
+QUERY_TILE = 64  # queries per CTA of the prefill attention kernel
+
+
 @dataclass
 class StepBatch:
     mode: str                       # "prefill" or "decode"
@@ -27,6 +30,7 @@ class StepBatch:
     cu_seqlens: torch.Tensor        # int32 [B + 1]
     slot_ids: torch.Tensor          # int32 [B]
     seq_ends: torch.Tensor          # int32 [B] lengths after this step
+    prefill_tiles: Optional[torch.Tensor] = None  # int32 [tiles, 3]: sequence's first packed index, length, first query
 
 
 def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence[Sequence[int]],
@@ -60,9 +64,14 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
         cu.append(first + n)
     host = torch.tensor([tokens, positions, token_slot, token_end, token_seq_start], dtype=torch.int32)
     dev = host.to(device)
+    tiles = None
+    if mode == "prefill":
+        tiles = torch.tensor([[cu[i], n, q0] for i, n in enumerate(lens) for q0 in range(0, n, QUERY_TILE)],
+                             dtype=torch.int32).to(device)
     per_seq = torch.tensor([list(slots), [s + n for s, n in zip(starts, lens)]], dtype=torch.int32).to(device)
     return StepBatch(
         mode=mode, n_seqs=len(slots), n_tokens=len(tokens), slots=list(slots), seq_lens=lens,
         max_seq_len=max(s + n for s, n in zip(starts, lens)),
         tokens=dev[0], positions=dev[1], token_slot=dev[2], token_end=dev[3], token_seq_start=dev[4],
-        cu_seqlens=torch.tensor(cu, dtype=torch.int32).to(device), slot_ids=per_seq[0], seq_ends=per_seq[1])
+        cu_seqlens=torch.tensor(cu, dtype=torch.int32).to(device), slot_ids=per_seq[0], seq_ends=per_seq[1],
+        prefill_tiles=tiles)

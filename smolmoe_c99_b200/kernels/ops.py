@@ -53,7 +53,9 @@ class Ops:
             raise KernelError("no CUDA device: this library runs on an NVIDIA B200 only (no CPU fallback)")
         self.lib = load_library()
         self.lib.sm_gemm_tc_workspace_bytes.restype = ctypes.c_longlong
+        self.lib.sm_attention_decode_workspace_floats.restype = ctypes.c_longlong
         self.use_tensor_cores = True  # False routes bfloat16 products to the CUDA-core kernel
+        self.use_fast_attention = True  # False routes bfloat16 attention to the plain kernel
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
 
     def _check(self, status: int) -> None:
@@ -217,14 +219,50 @@ class Ops:
 
     def attention_prefill(self, q, k_packed, v_packed, step, scale, window):
         """Causal attention of whole prompts over their own keys (sequences start at 0)."""
+        if (self.use_fast_attention and q.dtype == torch.bfloat16 and step.prefill_tiles is not None
+                and self.lib.sm_attention_prefill_supports(q.shape[2])):
+            return self.attention_prefill_tc(q, k_packed, v_packed, step.prefill_tiles, scale, window)
         return self.attention_plain(q, step.positions, scale, window, k_packed=k_packed, v_packed=v_packed,
                                     token_seq_start=step.token_seq_start)
 
+    def attention_prefill_tc(self, q, k_packed, v_packed, tiles, scale, window):
+        _need(q, "q", torch.bfloat16, 3)
+        _need(k_packed, "packed keys", torch.bfloat16, 3)
+        _need(v_packed, "packed values", torch.bfloat16, 3)
+        _need(tiles, "tiles", torch.int32, 2)
+        out = torch.empty_like(q)
+        self._check(self.lib.sm_attention_prefill(_ptr(q), _ptr(k_packed), _ptr(v_packed), _ptr(out), _ptr(tiles),
+                                                  tiles.shape[0], q.shape[1], k_packed.shape[1], q.shape[2],
+                                                  ctypes.c_float(scale), int(window or 0), _stream()))
+        return out
+
     def attention_cached(self, q, step, scale, window, cache, kv_heads):
         """Attention of this step's tokens over the keys and values in the cache."""
+        if self.use_fast_attention and q.dtype == torch.bfloat16 and step.mode == "decode":
+            return self.attention_decode(q, step.positions, step.slot_ids, scale, window, cache.k_pool, cache.v_pool,
+                                         cache.page_table, cache.ring, kv_heads, step.max_seq_len)
         return self.attention_plain(q, step.positions, scale, window, k_pool=cache.k_pool, v_pool=cache.v_pool,
                                     page_table=cache.page_table, ring=cache.ring, token_slot=step.token_slot,
                                     kv_heads=kv_heads)
+
+    def attention_decode(self, q, positions, slots, scale, window, k_pool, v_pool, page_table, ring, kv_heads, max_len):
+        """One new token per sequence (row b of q belongs to slots[b] at positions[b])."""
+        _need(q, "q", torch.bfloat16, 3)
+        B, heads, head_dim = q.shape
+        _need(positions, "positions", torch.int32, 1)
+        _need(slots, "slots", torch.int32, 1)
+        _need(k_pool, "key pool", torch.bfloat16)
+        _need(v_pool, "value pool", torch.bfloat16)
+        _need(page_table, "page table", torch.int32, 2)
+        splits = int(self.lib.sm_attention_decode_splits(int(max_len)))
+        floats = int(self.lib.sm_attention_decode_workspace_floats(B, heads, head_dim, splits))
+        workspace = torch.empty((floats,), dtype=torch.float32, device=q.device)
+        out = torch.empty_like(q)
+        self._check(self.lib.sm_attention_decode(
+            _ptr(q), _ptr(out), B, heads, kv_heads, head_dim, ctypes.c_float(scale), int(window or 0), _ptr(positions),
+            _ptr(slots), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), page_table.shape[1], ring, splits,
+            _ptr(workspace), _stream()))
+        return out
 
     # ---- sampling ----------------------------------------------------------------------
     def argmax(self, logits: torch.Tensor, banned: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):

@@ -74,3 +74,108 @@ def test_gemm_simt(ops, xd, wd, od, T, N, K):
     # each output is one chain over k: more rows in the batch change no bit
     alone = ops.gemm_simt(x[:1].contiguous(), w, b, torch.empty((1, N), dtype=od, device="cuda"))
     assert torch.equal(alone[0], out[0])
+
+
+# ---- attention ---------------------------------------------------------------------------
+def _plain_attention(q, k, v, lens, window, scale):
+    """q [T, H, hd], k/v [T, KH, hd] packed sequences; float64 reference on the CPU."""
+    q, k, v = q.double().cpu(), k.double().cpu(), v.double().cpu()
+    out = torch.zeros_like(q)
+    H, KH = q.shape[1], k.shape[1]
+    at = 0
+    for n in lens:
+        for pos in range(n):
+            start = pos - window + 1 if (window and pos >= window) else 0
+            for h in range(H):
+                kh = h // (H // KH)
+                s = (k[at + start:at + pos + 1, kh] @ q[at + pos, h]) * scale
+                p = torch.softmax(s, dim=0)
+                out[at + pos, h] = p @ v[at + start:at + pos + 1, kh]
+        at += n
+    return out.float()
+
+
+def _packed_step(lens):
+    from smolmoe_c99_b200.engine.batch import pack_step
+    return pack_step(list(range(len(lens))), [0] * len(lens), [[0] * n for n in lens], torch.device("cuda"))
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (5, 5, 48), (14, 2, 64), (6, 3, 80), (8, 2, 128)])
+@pytest.mark.parametrize("window", [None, 37])
+def test_prefill_attention(ops, heads, kv_heads, hd, window):
+    lens = [1, 63, 64, 65, 130]
+    T = sum(lens)
+    q, k, v = (_rand((T, n, hd), torch.bfloat16, s) for n, s in ((heads, 1), (kv_heads, 2), (kv_heads, 3)))
+    scale = 1.0 / math.sqrt(hd)
+    step = _packed_step(lens)
+    want = _plain_attention(q, k, v, lens, window, scale)
+    got = ops.attention_prefill_tc(q, k, v, step.prefill_tiles, scale, window).float().cpu()
+    assert float((got - want).abs().max()) <= 2e-2
+    plain = ops.attention_plain(q, step.positions, scale, window, k_packed=k, v_packed=v,
+                                token_seq_start=step.token_seq_start).float().cpu()
+    assert float((plain - want).abs().max()) <= 1e-2
+    plain32 = ops.attention_plain(q.float(), step.positions, scale, window, k_packed=k.float(), v_packed=v.float(),
+                                  token_seq_start=step.token_seq_start).cpu()
+    assert float((plain32 - want).abs().max()) <= 2e-5
+
+
+def test_prefill_attention_finds_a_far_key(ops):
+    """One key far back among hundreds is made to dominate: its value must come through."""
+    heads, kv_heads, hd, n = 2, 1, 64, 700
+    q, k, v = _rand((n, heads, hd), torch.bfloat16, 1, 0.1), _rand((n, kv_heads, hd), torch.bfloat16, 2, 0.1), \
+        _rand((n, kv_heads, hd), torch.bfloat16, 3)
+    far = 5
+    k[far] = 0
+    k[far, 0, 0] = 40.0
+    q[n - 1, :, 0] = 40.0   # score 1600/8 = 200 for the far key, O(1) for the others
+    step = _packed_step([n])
+    got = ops.attention_prefill_tc(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), None).float()
+    assert float((got[n - 1, 0] - v[far, 0].float()).abs().max()) <= 2e-2
+    # with a window that ends just after it, it is out of sight
+    got_w = ops.attention_prefill_tc(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), n - 1 - far).float()
+    assert float((got_w[n - 1, 0] - v[far, 0].float()).abs().max()) > 0.1
+    got_w1 = ops.attention_prefill_tc(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), n - far).float()
+    assert float((got_w1[n - 1, 0] - v[far, 0].float()).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (5, 5, 48), (14, 2, 64), (9, 1, 128), (4, 2, 256)])
+@pytest.mark.parametrize("window", [None, 100])
+def test_decode_attention_over_pages(ops, heads, kv_heads, hd, window):
+    """Sequences of unequal lengths in scattered pages; the windowed case uses a ring."""
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    lens = [1, 64, 65, 129, 500]
+    B = len(lens)
+    ring = ((window + PAGE_SIZE - 1) // PAGE_SIZE) * PAGE_SIZE if window else 0
+    pages_per_seq = (ring or max(lens) + PAGE_SIZE - 1) // PAGE_SIZE + 1
+    n_pages = B * pages_per_seq + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(7)).tolist()
+    table = torch.zeros((B + 2, pages_per_seq), dtype=torch.int32)
+    slots = [4, 0, 2, 5, 1]
+    for b, slot in enumerate(slots):
+        table[slot] = torch.tensor(perm[b * pages_per_seq:(b + 1) * pages_per_seq], dtype=torch.int32)
+    k_pool = torch.zeros((n_pages, kv_heads, PAGE_SIZE, hd), dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    ks, vs, qs = [], [], []
+    for b, n in enumerate(lens):
+        k, v = _rand((n, kv_heads, hd), torch.bfloat16, 10 + b).cpu(), _rand((n, kv_heads, hd), torch.bfloat16, 20 + b).cpu()
+        ks.append(k); vs.append(v)
+        for p in range(n):
+            idx = p % ring if ring else p
+            page = int(table[slots[b], idx // PAGE_SIZE])
+            k_pool[page, :, idx % PAGE_SIZE] = k[p]
+            v_pool[page, :, idx % PAGE_SIZE] = v[p]
+        qs.append(_rand((1, heads, hd), torch.bfloat16, 30 + b))
+    q = torch.cat(qs, dim=0)
+    scale = 1.0 / math.sqrt(hd)
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    slot_ids = torch.tensor(slots, dtype=torch.int32).cuda()
+    got = ops.attention_decode(q, positions, slot_ids, scale, window, k_pool.cuda(), v_pool.cuda(), table.cuda(), ring,
+                               kv_heads, max(lens)).float().cpu()
+    plain = ops.attention_plain(q, positions, scale, window, k_pool=k_pool.cuda(), v_pool=v_pool.cuda(),
+                                page_table=table.cuda(), ring=ring, token_slot=slot_ids, kv_heads=kv_heads).float().cpu()
+    for b, n in enumerate(lens):
+        qq = torch.zeros((n, heads, hd), dtype=torch.bfloat16)
+        qq[n - 1] = q[b].cpu()
+        want = _plain_attention(qq, ks[b], vs[b], [n], window, scale)[n - 1]
+        assert float((got[b] - want).abs().max()) <= 1e-2, f"split kernel, sequence {b}"
+        assert float((plain[b] - want).abs().max()) <= 1e-2, f"plain kernel, sequence {b}"
