@@ -235,6 +235,7 @@ void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, 
                  workspace, workspace + (size_t)B * heads * splits * head_dim};
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    note_launch(2);
     dim3 grid(kv_heads, B, splits);
     decode_partial_kernel<<<grid, kThreads, smem, stream>>>(a);
     int warps = B * heads;

@@ -124,6 +124,7 @@ void attention_plain(const AttentionArgs& a, cudaStream_t stream) {
     bool paged = a.k_packed == nullptr;
     if (paged && (a.k_pool == nullptr || a.page_table == nullptr))
         throw std::invalid_argument("attention_plain: neither packed keys nor a cache were given");
+    note_launch();
     long long items = (long long)a.T * a.heads;
     unsigned blocks = (unsigned)((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
     int threads = kWarpsPerBlock * 32;

@@ -201,6 +201,7 @@ void attention_prefill(const void* q, const void* k, const void* v, void* out, c
                                     " is not a multiple of 16 between 16 and 128 (the plain kernel takes it)");
     if (heads % kv_heads) throw std::invalid_argument("attention_prefill: kv_heads must divide heads");
     if (heads > 65535) throw std::invalid_argument("attention_prefill: more than 65535 heads");
+    note_launch();
     PrefillArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)out, tiles,
                   heads, kv_heads, window, scale * 1.4426950408889634f};
     switch (head_dim) {

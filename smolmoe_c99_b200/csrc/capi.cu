@@ -5,6 +5,7 @@
 // still works.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <exception>
 #include <string>
 
@@ -34,9 +35,18 @@ int guarded(F&& body) {
 }
 }  // namespace
 
+namespace sm {
+static std::atomic<long long> g_launches{0};
+void note_launch(int kernels) { g_launches.fetch_add(kernels, std::memory_order_relaxed); }
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+}  // namespace sm
+
 #define SM_API extern "C" __attribute__((visibility("default")))
 
 SM_API const char* sm_last_error() { return g_last_error.c_str(); }
+
+// Kernels enqueued by this library since it was loaded.
+SM_API long long sm_launch_count() { return sm::launch_count(); }
 
 SM_API int sm_embedding(const void* table, int table_dt, const int32_t* tokens, float* out, int T, int D, int V,
                         int32_t* status, void* stream) {

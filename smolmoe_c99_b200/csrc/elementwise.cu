@@ -27,6 +27,7 @@ __global__ void embedding_kernel(const TW* __restrict__ table, const int32_t* __
 void embedding(const void* table, DType table_dt, const int32_t* tokens, float* out, int T, int D,
                int V, int32_t* status, cudaStream_t stream) {
     if (T <= 0) return;
+    note_launch();
     int threads = D >= 256 ? 256 : 128;
     if (table_dt == F32)
         embedding_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, out, D, V, status);
@@ -70,6 +71,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
 void rmsnorm(const float* x, const void* w, DType w_dt, float eps, void* out, DType out_dt,
              const int32_t* rows, int n_rows, int D, cudaStream_t stream) {
     if (n_rows <= 0) return;
+    note_launch();
 #define SM_NORM(TW, TO) \
     rmsnorm_kernel<TW, TO><<<n_rows, kNormThreads, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, D)
     if (w_dt == F32 && out_dt == F32) SM_NORM(float, float);
@@ -94,6 +96,7 @@ __global__ void swiglu_kernel(const float* __restrict__ gate_up, TO* __restrict_
 void swiglu(const float* gate_up, void* out, DType out_dt, int T, int H, cudaStream_t stream) {
     size_t total = (size_t)T * H;
     if (!total) return;
+    note_launch();
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (out_dt == F32) swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gate_up, (float*)out, H, total);
     else swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gate_up, (__nv_bfloat16*)out, H, total);
@@ -160,6 +163,7 @@ void rope_store(const RopeStoreArgs& a, cudaStream_t stream) {
     if (a.head_dim % 2 || a.rotary_dim % 2 || a.rotary_dim > a.head_dim)
         throw std::invalid_argument("rope_store: head_dim " + std::to_string(a.head_dim) + " / rotary_dim " +
                                     std::to_string(a.rotary_dim) + " must be even, rotary_dim <= head_dim");
+    note_launch();
     int work = (a.heads + 2 * a.kv_heads) * a.head_dim / 2;
     int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
     if (a.dt == F32) rope_store_kernel<float><<<a.T, threads, 0, stream>>>(a);

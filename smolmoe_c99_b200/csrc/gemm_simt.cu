@@ -100,6 +100,7 @@ void gemm_simt(const void* x, DType x_dt, const void* w, DType w_dt, const void*
     if (T <= 0 || N <= 0) return;
     if (K <= 0) throw std::invalid_argument("gemm_simt: K must be positive");
     if ((T + BM - 1) / BM > 65535) throw std::invalid_argument("gemm_simt: more than 65535*64 rows in one call");
+    note_launch();
     if (x_dt == F32 && w_dt == F32) launch_bias<float, float>(x, w, bias, bias_dt, out, out_dt, T, N, K, accumulate, stream);
     else if (x_dt == F32) launch_bias<float, __nv_bfloat16>(x, w, bias, bias_dt, out, out_dt, T, N, K, accumulate, stream);
     else if (w_dt == F32) launch_bias<__nv_bfloat16, float>(x, w, bias, bias_dt, out, out_dt, T, N, K, accumulate, stream);

@@ -395,6 +395,7 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     });
     dim3 grid((N + kTileM - 1) / kTileM, (T + p.tile_n - 1) / p.tile_n, p.splits);
     gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(map_w, map_x, p);
+    note_launch(p.splits > 1 ? 2 : 1);
     if (p.splits > 1) {
         p.epilogue = final_mode;
         size_t total = (size_t)T * N;

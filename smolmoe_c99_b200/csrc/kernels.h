@@ -11,6 +11,10 @@ namespace sm {
 
 enum DType : int { F32 = 0, BF16 = 1 };
 
+// Every launcher reports the kernels it enqueues (capi.cu keeps the count).
+void note_launch(int kernels = 1);
+long long launch_count();
+
 // ---- elementwise.cu -------------------------------------------------------------------
 // out[t, :] = table[tokens[t], :] as float. A token outside [0, V) sets *status |= 1 and
 // its row is zeroed.

@@ -55,6 +55,7 @@ argmax_kernel(const float* __restrict__ logits, const uint8_t* __restrict__ bann
 void argmax(const float* logits, const uint8_t* banned, int32_t* out, int B, int V, cudaStream_t stream) {
     if (B <= 0) return;
     if (V <= 0 || V > (1 << 24)) throw std::invalid_argument("argmax: vocabulary must be in [1, 2^24]");
+    note_launch();
     argmax_kernel<<<B, kSampleThreads, 0, stream>>>(logits, banned, out, V);
 }
 
@@ -205,6 +206,7 @@ void sample(const float* logits, const uint8_t* banned, int32_t* out, uint32_t* 
     if (V <= 0 || V > (1 << 24)) throw std::invalid_argument("sample: vocabulary must be in [1, 2^24]");
     if (!(temperature > 0.f)) throw std::invalid_argument("sample: temperature must be positive (0 is argmax)");
     if (!(top_p > 0.f && top_p <= 1.0f)) throw std::invalid_argument("sample: top_p must be in (0, 1]");
+    note_launch();
     sample_kernel<<<B, kSampleThreads, 0, stream>>>(logits, banned, out, rng_state, V, temperature, top_k, top_p);
 }
 

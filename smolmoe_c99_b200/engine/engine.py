@@ -6,12 +6,16 @@ lengths, one step) or all go on by one token; it runs only the tokens it is give
 batch, from the cache that earlier steps left, and returns the logits at the wanted places.
 The reference's counterpart is ``model_forward(tokens, n, pos0, mode)`` for its single
 sequence (src/model.h:79-97, src/model.c:664-724).
+
+Steps of one token per sequence are launch-bound, so their kernels are captured once per
+batch size into a CUDA graph and replayed; the step's numbers (tokens, positions, slots)
+live in fixed device buffers that are refilled before each replay.
 """
 from __future__ import annotations
 
-import os
 import tempfile
-from typing import Dict, List, Optional, Sequence, Union
+from collections import OrderedDict
+from typing import Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 
@@ -24,15 +28,46 @@ from .batch import StepBatch, pack_step
 from .model import DecoderModel, cache_needs, model_param_specs
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+SPAN_BUCKET = 1024   # decode graphs are captured for key spans rounded up to this many positions
+MAX_GRAPHS = 24
 
 
 class StepError(ValueError):
     """The step's arguments cannot be run (bad token, unknown slot, no room)."""
 
 
+class _DecodeGraph:
+    """One captured decode step for a batch size and key span."""
+
+    def __init__(self, engine: "Engine", n_seqs: int, span: int):
+        dev = engine.device
+        self.meta = torch.zeros((4, n_seqs), dtype=torch.int32, device=dev)  # tokens, positions, slots, ends
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.rows = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+        self.batch = StepBatch(
+            mode="decode", n_seqs=n_seqs, n_tokens=n_seqs, slots=[], seq_lens=[1] * n_seqs, max_seq_len=span,
+            tokens=self.meta[0], positions=self.meta[1], token_slot=self.meta[2], token_end=self.meta[3],
+            token_seq_start=self.rows, cu_seqlens=torch.arange(n_seqs + 1, dtype=torch.int32, device=dev),
+            slot_ids=self.meta[2], seq_ends=self.meta[3])
+
+    def capture(self, engine: "Engine") -> None:
+        """``meta`` must already hold a real step: the run before the capture loads kernels and
+        sets function attributes, and it writes the same keys and values the replay will."""
+        side = torch.cuda.Stream(device=engine.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            engine.model.forward(self.batch, engine.cache, self.rows, engine._status)
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = engine.model.forward(self.batch, engine.cache, self.rows, engine._status)
+
+
 class Engine:
     def __init__(self, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", *, max_tokens: int = 4096,
-                 max_slots: Optional[int] = None, max_seq_len: Optional[int] = None, device: str = "cuda:0"):
+                 max_slots: Optional[int] = None, max_seq_len: Optional[int] = None, device: str = "cuda:0",
+                 use_graphs: bool = True):
         self.dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
         if self.dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("dtype must be bfloat16 or float32")
@@ -49,7 +84,10 @@ class Engine:
                                    max_slots=max_slots if max_slots is not None else 256,
                                    max_seq_len=self.max_seq_len, dtype=self.dtype, device=self.device)
         self.vocab_size = self.spec.vocab_size
+        self.use_graphs = use_graphs
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._graphs: "OrderedDict[Tuple[int, int], _DecodeGraph]" = OrderedDict()
+        self.kernel_launches = 0   # graph replays and eager steps, for the record
 
     # ---- construction from random weights ------------------------------------------------
     @classmethod
@@ -74,49 +112,105 @@ class Engine:
         return self.cache.length(slot)
 
     # ---- the step function ---------------------------------------------------------------
-    def step(self, slots: Sequence[int], token_lists: Sequence[Sequence[int]],
+    def step(self, slots: Sequence[int], tokens: Union[Sequence[Sequence[int]], torch.Tensor],
              want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
-        """Runs ``token_lists[i]`` as the next tokens of the sequence in ``slots[i]``.
+        """Runs the next tokens of the sequences in ``slots``.
 
-        ``want[i]`` lists the places among these tokens whose logits are asked for (default:
-        the last token of each sequence). Returns float32 ``[wanted, vocab]`` on the device in
-        the order of the sequences and of ``want``, or None if nothing is wanted.
+        ``tokens`` is a list of token lists, one per sequence, or -- for a step of one token
+        each -- an int32 device tensor ``[len(slots)]`` (what the sampler returned; it is not
+        read back to the host). ``want[i]`` lists the places among sequence ``i``'s tokens
+        whose logits are asked for (default: its last token). Returns float32
+        ``[wanted, vocab]`` on the device in the order of the sequences and of ``want``, or
+        None if nothing is wanted. The result may be overwritten by the next step.
         """
-        if len(slots) != len(token_lists) or (want is not None and len(want) != len(slots)):
-            raise StepError("slots, token lists and wanted places must have one entry per sequence")
-        if len(set(slots)) != len(slots):
+        n = len(slots)
+        on_device = isinstance(tokens, torch.Tensor)
+        if on_device:
+            if tokens.dtype != torch.int32 or tokens.dim() != 1 or tokens.numel() != n or not tokens.is_cuda:
+                raise StepError("device tokens must be an int32 CUDA tensor with one token per sequence")
+            lens = [1] * n
+        else:
+            if len(tokens) != n:
+                raise StepError("slots and token lists must have one entry per sequence")
+            lens = [len(t) for t in tokens]
+            for toks in tokens:
+                for t in toks:
+                    if not 0 <= int(t) < self.vocab_size:  # src/model.c:673
+                        raise StepError(f"token {t} out of vocabulary ({self.vocab_size})")
+        if n == 0 or any(k == 0 for k in lens):
+            raise StepError("a step needs at least one sequence, and every sequence at least one token")
+        if want is not None and len(want) != n:
+            raise StepError("wanted places must have one entry per sequence")
+        if len(set(slots)) != n:
             raise StepError("a slot appears twice in one step")
-        starts = []
-        for slot, toks in zip(slots, token_lists):
+        for slot in slots:
             if slot not in self.cache.lengths:
                 raise StepError(f"slot {slot} is not open")
-            for t in toks:
-                if not 0 <= int(t) < self.vocab_size:  # src/model.c:673
-                    raise StepError(f"token {t} out of vocabulary ({self.vocab_size})")
-            starts.append(self.cache.length(slot))
-        try:
-            batch = pack_step(slots, starts, token_lists, self.device)
-        except ValueError as e:
-            raise StepError(str(e)) from None
-        growth = {slot: n for slot, n in zip(slots, batch.seq_lens)}
+        starts = [self.cache.length(slot) for slot in slots]
+        rows: List[int] = []
+        first = 0
+        for i, k in enumerate(lens):
+            for p in ([k - 1] if want is None else want[i]):
+                if not 0 <= p < k:
+                    raise StepError(f"wanted place {p} is outside the {k} tokens of sequence {i}")
+                rows.append(first + p)
+            first += k
+        decode = all(k == 1 for k in lens) and all(s > 0 for s in starts)
+        if not decode and not all(s == 0 for s in starts):
+            raise StepError("the sequences of a step either all start at their first token or all go on by one token")
+        if not decode and on_device:
+            raise StepError("device tokens are for steps of one token per sequence")
+        growth = {slot: k for slot, k in zip(slots, lens)}
         try:
             self.cache.reserve(growth)
         except CacheFull as e:
             raise StepError(f"token batch exceeds the cache: {e}") from None  # src/model.c:669-670
         self.cache.flush_tables()
-        rows: List[int] = []
-        first = 0
-        for i, n in enumerate(batch.seq_lens):
-            places = [n - 1] if want is None else list(want[i])
-            for p in places:
-                if not 0 <= p < n:
-                    raise StepError(f"wanted place {p} is outside the {n} tokens of sequence {i}")
-                rows.append(first + p)
-            first += n
-        want_rows = torch.tensor(rows, dtype=torch.int32).to(self.device) if rows else None
-        logits = self.model.forward(batch, self.cache, want_rows, self._status)
+        if decode and self.use_graphs:
+            logits = self._decode_graph(slots, starts, tokens, on_device)
+            if rows != list(range(n)):
+                logits = logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else None
+        else:
+            if on_device:
+                tokens = [[int(t)] for t in tokens.tolist()]
+            batch = pack_step(slots, starts, tokens, self.device)
+            want_rows = torch.tensor(rows, dtype=torch.int32).to(self.device) if rows else None
+            logits = self.model.forward(batch, self.cache, want_rows, self._status)
+        self.kernel_launches += 1
         self.cache.advance(growth)
         return logits
+
+    def _decode_graph(self, slots, starts, tokens, on_device) -> torch.Tensor:
+        n = len(slots)
+        longest = max(starts) + 1
+        span = min(-(-longest // SPAN_BUCKET) * SPAN_BUCKET, -(-self.max_seq_len // 128) * 128)
+        key = (n, span)
+        g = self._graphs.get(key)
+        if g is None:
+            if len(self._graphs) >= MAX_GRAPHS:
+                self._graphs.popitem(last=False)
+            g = self._graphs[key] = _DecodeGraph(self, n, span)
+        else:
+            self._graphs.move_to_end(key)
+        meta = [[0] * n if on_device else [int(t[0]) for t in tokens], list(starts), list(slots),
+                [s + 1 for s in starts]]
+        g.meta.copy_(torch.tensor(meta, dtype=torch.int32))   # pageable and small: staged at once, no hazard
+        if on_device:
+            g.meta[0].copy_(tokens)
+        if g.graph is None:
+            g.capture(self)
+        g.graph.replay()
+        return g.logits
+
+    def synchronize(self) -> None:
+        torch.cuda.synchronize(self.device)
+
+    def check_status(self) -> None:
+        """Raises if a kernel reported a fault since the last check (synchronises)."""
+        self.runtime.ops.check_error_flag()
+        if int(self._status.item()):
+            self._status.zero_()
+            raise StepError("a token outside the vocabulary reached the device")
 
     # ---- figures -------------------------------------------------------------------------
     def weight_bytes(self) -> int:

@@ -1,0 +1,132 @@
+"""The generation loop above the step function: batches of unequal prompts, stop tokens,
+sequences that end earlier, and as many batches one after another as there are requests.
+
+The reference's loop serves one prompt (src/main.c:571-600; chat: src/engine.c:149-219);
+what carries over: the prompt goes through in one pass, then one token a step; a stop
+token ends the sequence, is reported and is not fed back; the last token that the limit
+allows is not fed back either (src/main.c:590); prompt plus new tokens must fit the context
+(src/main.c:795-796); a sink receives every token and may ask to stop (src/engine_sink.h).
+The loop only decides; the engine and the sampler it is given do the work, so it runs
+unchanged over a stand-in engine in tests.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+
+@dataclass(frozen=True)
+class GenerationOptions:
+    max_new_tokens: int = 64            # --tokens (src/main.c:29)
+    stop_token_ids: Tuple[int, ...] = ()
+    batch: int = 8                      # sequences that start together
+
+
+@dataclass
+class Completion:
+    prompt_tokens: int
+    tokens: List[int] = field(default_factory=list)
+    finish_reason: str = ""             # "stop", "length" or "cancelled"
+
+
+@dataclass
+class GenerationStats:
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    decode_forwards: int = 0
+    prefill_seconds: float = 0.0
+    decode_seconds: float = 0.0
+    batches: int = 0
+
+    def as_dict(self) -> Dict[str, float]:
+        """The reference's keys and definitions (src/main.c:347-382)."""
+        return {
+            "prompt_tokens": self.prompt_tokens, "generated_tokens": self.generated_tokens,
+            "prefill_seconds": self.prefill_seconds, "decode_seconds": self.decode_seconds,
+            "prefill_tokens_per_second": self.prompt_tokens / self.prefill_seconds if self.prefill_seconds > 0 else 0.0,
+            "decode_tokens_per_second": self.decode_forwards / self.decode_seconds if self.decode_seconds > 0 else 0.0,
+            "batches": self.batches,
+        }
+
+
+class TokenSink:
+    """Receives tokens as they are chosen. ``should_stop`` is asked once per step."""
+
+    def on_token(self, request: int, token: int, last: bool) -> None:
+        pass
+
+    def should_stop(self) -> bool:
+        return False
+
+
+def generate(engine, sampler, prompts: Sequence[Sequence[int]], options: GenerationOptions,
+             sink: Optional[TokenSink] = None, stats: Optional[GenerationStats] = None,
+             clock: Callable[[], float] = time.perf_counter) -> List[Completion]:
+    """``engine`` provides open_sequence/close_sequence/step/max_seq_len/synchronize;
+    ``sampler`` provides new_states/choose. Returns one completion per prompt, in order."""
+    if options.batch <= 0 or options.max_new_tokens < 0:
+        raise ValueError("batch must be positive and max_new_tokens must not be negative")
+    for i, p in enumerate(prompts):
+        if len(p) == 0:
+            raise ValueError(f"prompt {i} is empty")
+        if len(p) + options.max_new_tokens > engine.max_seq_len:
+            raise ValueError(f"prompt {i}: {len(p)} prompt tokens and {options.max_new_tokens} new tokens "
+                             f"exceed the context of {engine.max_seq_len}")
+    sink = sink or TokenSink()
+    stats = stats if stats is not None else GenerationStats()
+    stop = set(options.stop_token_ids)
+    results = [Completion(prompt_tokens=len(p)) for p in prompts]
+    cancelled = False
+    for first in range(0, len(prompts), options.batch):
+        ids = list(range(first, min(first + options.batch, len(prompts))))
+        if cancelled or options.max_new_tokens == 0:
+            for r in ids:
+                results[r].finish_reason = "cancelled" if cancelled else "length"
+            continue
+        slots = {r: engine.open_sequence() for r in ids}
+        live = list(ids)
+        try:
+            stats.batches += 1
+            t0 = clock()
+            logits = engine.step([slots[r] for r in live], [list(prompts[r]) for r in live])
+            states = sampler.new_states(live)
+            engine.synchronize()
+            t1 = clock()
+            stats.prefill_seconds += t1 - t0
+            stats.prompt_tokens += sum(len(prompts[r]) for r in live)
+            for produced in range(1, options.max_new_tokens + 1):
+                chosen = sampler.choose(logits, states)
+                tokens = [int(t) for t in chosen.tolist()]   # the one device-to-host read of the step
+                keep = []
+                for i, r in enumerate(live):
+                    tok = tokens[i]
+                    if tok < 0:
+                        raise RuntimeError("every token is banned")  # src/sampler.c:61
+                    results[r].tokens.append(tok)
+                    stats.generated_tokens += 1
+                    done = "stop" if tok in stop else ("length" if produced == options.max_new_tokens else "")
+                    sink.on_token(r, tok, bool(done))
+                    if done:
+                        results[r].finish_reason = done
+                        engine.close_sequence(slots.pop(r))
+                    else:
+                        keep.append(i)
+                if sink.should_stop():
+                    cancelled = True
+                    for i in keep:
+                        results[live[i]].finish_reason = "cancelled"
+                    break
+                if not keep:
+                    break
+                if len(keep) != len(live):   # shorter requests have ended: the batch shrinks
+                    chosen, states = sampler.select(chosen, keep), sampler.select(states, keep)
+                    live = [live[i] for i in keep]
+                logits = engine.step([slots[r] for r in live], chosen)
+                stats.decode_forwards += len(live)
+            engine.synchronize()
+            stats.decode_seconds += clock() - t1
+        finally:
+            for slot in slots.values():
+                engine.close_sequence(slot)
+    return results

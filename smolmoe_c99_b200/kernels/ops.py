@@ -54,6 +54,7 @@ class Ops:
         self.lib = load_library()
         self.lib.sm_gemm_tc_workspace_bytes.restype = ctypes.c_longlong
         self.lib.sm_attention_decode_workspace_floats.restype = ctypes.c_longlong
+        self.lib.sm_launch_count.restype = ctypes.c_longlong
         self.use_tensor_cores = True  # False routes bfloat16 products to the CUDA-core kernel
         self.use_fast_attention = True  # False routes bfloat16 attention to the plain kernel
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
