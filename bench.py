@@ -121,6 +121,9 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--profile-region", choices=["decode", "prefill"], default=None,
+                    help="for ncu --profile-from-start off: run only this region between cudaProfilerStart/Stop "
+                         "(decode: 2 eager steps of the batch; prefill: one 2,048-token prompt) and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -166,6 +169,26 @@ def main() -> int:
     def close(slots):
         for s in slots:
             engine.close_sequence(s)
+
+    if args.profile_region:
+        one = prompts(1)
+        if args.profile_region == "prefill":
+            s = engine.open_sequence(); engine.step([s], one); engine.close_sequence(s)
+            torch.cuda.synchronize()
+            s = engine.open_sequence()
+            torch.cuda.profiler.start(); engine.step([s], one); torch.cuda.synchronize(); torch.cuda.profiler.stop()
+        else:
+            slots = open_and_prefill(B)
+            engine.use_graphs = False
+            tok = torch.zeros(B, dtype=torch.int32, device=engine.device)
+            tok = engine.runtime.ops.argmax(engine.step(slots, tok))
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            for _ in range(2):
+                tok = engine.runtime.ops.argmax(engine.step(slots, tok))
+            torch.cuda.synchronize(); torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": args.profile_region, "batch": B, "layers": raw["num_hidden_layers"]}))
+        return 0
 
     # ---- prefill of one 2,048-token prompt ------------------------------------------------
     one = prompts(1)

@@ -6,10 +6,10 @@
 // heads share every key and value row that is read. Scores for the chunk, their running
 // maximum and sum, and the unnormalised weighted values go to a workspace:
 //   part_o [B, heads, splits, head_dim] float, part_ml [B, heads, splits, 2] float.
-// Kernel 2, one warp per (sequence, head): merges the chunks that hold visible keys in
-// ascending order and writes the normalised result.
-// Chunks without visible keys (beyond the sequence, or before the window) do no work and
-// are not read by the merge.
+// The CTA that finishes last for its (sequence, kv head) -- known from a counter that it
+// then resets -- merges the chunks that hold visible keys in ascending order and writes the
+// normalised result, so the whole attention is one launch. Chunks without visible keys
+// (beyond the sequence, or before the window) do no work and are not read by the merge.
 #include <math_constants.h>
 
 #include <stdexcept>
@@ -40,6 +40,7 @@ struct DecodeArgs {
     float scale;
     float* part_o;
     float* part_ml;
+    int* counters;                // [B, kv_heads], zero between launches
 };
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
@@ -67,6 +68,10 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
     float* sc = qs + group * hd;                                       // [group][kChunk] scores, then weights
     unsigned long long* rows = reinterpret_cast<unsigned long long*>(sc + group * kChunk);  // [kChunk]
     float* red = reinterpret_cast<float*>(rows + kChunk);              // [key groups][kHeadPass][hd]
+    const int half_ = hd / 2;
+    const int key_groups_ = kThreads / half_ > 0 ? kThreads / half_ : 1;
+    float* wts = red + (size_t)key_groups_ * kHeadPass * hd;           // [warps][splits] merge weights
+    __shared__ int is_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const __nv_bfloat16* qb = a.q + ((size_t)b * a.heads + (size_t)kvh * group) * hd;
@@ -168,38 +173,56 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
         }
         __syncthreads();
     }
-}
 
-__global__ void decode_merge_kernel(DecodeArgs a) {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= a.B * a.heads) return;
-    const int b = warp / a.heads, hd = a.head_dim;
-    const int pos = a.positions[b];
-    const int start = (a.window > 0 && pos >= a.window) ? pos - a.window + 1 : 0;
-    const int s_lo = start / kChunk, s_hi = pos / kChunk;
-    const float* ml = a.part_ml + (size_t)warp * a.splits * 2;
-    const float* po = a.part_o + (size_t)warp * a.splits * hd;
-    float m = -CUDART_INF_F;
-    for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, ml[2 * s]);
-    float l = 0.f;
-    float acc[kMaxHeadDim / 32];
+    // the last CTA of this (sequence, kv head) merges the chunks
+    const int s_lo = start / kChunk, s_hi = pos / kChunk, n_active = s_hi - s_lo + 1;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int* counter = a.counters + b * a.kv_heads + kvh;
+        int arrived = atomicAdd(counter, 1);
+        is_last = arrived == n_active - 1;
+        if (is_last) *counter = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    float* my_w = wts + (size_t)warp * a.splits;
+    for (int g = warp; g < group; g += kThreads / 32) {
+        const size_t head = (size_t)b * a.heads + kvh * group + g;
+        const float* ml = a.part_ml + head * a.splits * 2;
+        const float* po = a.part_o + head * a.splits * hd;
+        float m = -CUDART_INF_F;
+        for (int s = s_lo + lane; s <= s_hi; s += 32) m = fmaxf(m, __ldcg(ml + 2 * s));
+        m = warp_max(m);
+        float l = 0.f;
+        for (int s = s_lo + lane; s <= s_hi; s += 32) {
+            float w = expf(__ldcg(ml + 2 * s) - m);
+            my_w[s - s_lo] = w;
+            l = fmaf(__ldcg(ml + 2 * s + 1), w, l);
+        }
+        l = warp_sum(l);
+        __syncwarp();
+        float acc[kMaxHeadDim / 32];
 #pragma unroll
-    for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
-    for (int s = s_lo; s <= s_hi; ++s) {
-        float w = expf(ml[2 * s] - m);
-        l = fmaf(ml[2 * s + 1], w, l);
+        for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
+#pragma unroll 4
+        for (int s = s_lo; s <= s_hi; ++s) {
+            const float w = my_w[s - s_lo];
+#pragma unroll
+            for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+                int d = lane + 32 * i;
+                if (d < hd) acc[i] = fmaf(__ldcg(po + (size_t)s * hd + d), w, acc[i]);
+            }
+        }
+        const float inv = 1.0f / l;
+        __nv_bfloat16* o = a.out + head * hd;
 #pragma unroll
         for (int i = 0; i < kMaxHeadDim / 32; ++i) {
             int d = lane + 32 * i;
-            if (d < hd) acc[i] = fmaf(po[(size_t)s * hd + d], w, acc[i]);
+            if (d < hd) o[d] = __float2bfloat16_rn(acc[i] * inv);
         }
-    }
-    float inv = 1.0f / l;
-    __nv_bfloat16* o = a.out + (size_t)warp * hd;
-#pragma unroll
-    for (int i = 0; i < kMaxHeadDim / 32; ++i) {
-        int d = lane + 32 * i;
-        if (d < hd) o[d] = __float2bfloat16_rn(acc[i] * inv);
+        __syncwarp();
     }
 }
 
@@ -214,7 +237,7 @@ size_t attention_decode_workspace_floats(int B, int heads, int head_dim, int spl
 void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
                       const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
                       const int32_t* page_table, int table_stride, int ring, int splits, float* workspace,
-                      cudaStream_t stream) {
+                      int* counters, cudaStream_t stream) {
     if (B <= 0) return;
     if (head_dim % 8 || head_dim <= 0 || head_dim > kMaxHeadDim)
         throw std::invalid_argument("attention_decode: head_dim " + std::to_string(head_dim) +
@@ -225,21 +248,20 @@ void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, 
     int half = head_dim / 2;
     int key_groups = kThreads / half > 0 ? kThreads / half : 1;
     size_t smem = (size_t)group * head_dim * 4 + (size_t)group * kChunk * 4 + kChunk * 8 +
-                  (size_t)key_groups * kHeadPass * head_dim * 4;
+                  (size_t)key_groups * kHeadPass * head_dim * 4 + (size_t)(kThreads / 32) * splits * 4;
+    if (B * kv_heads > 65536) throw std::invalid_argument("attention_decode: more than 65536 (sequence, kv head) pairs");
     if (smem > 200 * 1024)
         throw std::invalid_argument("attention_decode: " + std::to_string(group) + " heads per kv head with head_dim " +
                                     std::to_string(head_dim) + " need more shared memory than one SM has");
     DecodeArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
                  (const __nv_bfloat16*)v_pool, page_table, table_stride, ring, slots, positions,
                  B, heads, kv_heads, head_dim, window, splits, scale,
-                 workspace, workspace + (size_t)B * heads * splits * head_dim};
+                 workspace, workspace + (size_t)B * heads * splits * head_dim, counters};
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    note_launch(2);
+    note_launch();
     dim3 grid(kv_heads, B, splits);
     decode_partial_kernel<<<grid, kThreads, smem, stream>>>(a);
-    int warps = B * heads;
-    decode_merge_kernel<<<(warps * 32 + 127) / 128, 128, 0, stream>>>(a);
 }
 
 }  // namespace sm

@@ -142,9 +142,33 @@ SM_API long long sm_attention_decode_workspace_floats(int B, int heads, int head
 SM_API int sm_attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale,
                                int window, const int32_t* positions, const int32_t* slots, const void* k_pool,
                                const void* v_pool, const int32_t* page_table, int table_stride, int ring, int splits,
-                               float* workspace, void* stream) {
+                               float* workspace, int* counters, void* stream) {
     return guarded([&] {
         sm::attention_decode(q, out, B, heads, kv_heads, head_dim, scale, window, positions, slots, k_pool, v_pool,
-                             page_table, table_stride, ring, splits, workspace, (cudaStream_t)stream);
+                             page_table, table_stride, ring, splits, workspace, counters, (cudaStream_t)stream);
+    });
+}
+
+SM_API int sm_gemm_skinny_supports(int T, int N, int K) { return sm::gemm_skinny_supports(T, N, K) ? 1 : 0; }
+
+SM_API int sm_gemm_skinny(const void* x, const void* norm_w, int norm_w_dt, float eps, const void* w, int T, int N,
+                          int K, int mode, const void* bias, int bias_dt, void* out, int out_dt, int up_offset,
+                          void* stream) {
+    return guarded([&] {
+        sm::gemm_skinny(x, norm_w, (sm::DType)norm_w_dt, eps, w, T, N, K, mode, bias, (sm::DType)bias_dt, out,
+                        (sm::DType)out_dt, up_offset, nullptr, (cudaStream_t)stream);
+    });
+}
+
+SM_API int sm_gemm_skinny_qkv(const void* x, const void* norm_w, int norm_w_dt, float eps, const void* w, int T, int K,
+                              const void* bias, int bias_dt, int heads, int kv_heads, int head_dim, int rotary_dim,
+                              const int32_t* positions, const float* cos_table, const float* sin_table, void* q_out,
+                              void* k_pool, void* v_pool, const int32_t* page_table, int table_stride, int ring,
+                              const int32_t* token_slot, void* stream) {
+    return guarded([&] {
+        sm::SkinnyRope rope{heads, kv_heads, head_dim, rotary_dim, positions, cos_table, sin_table, q_out,
+                            k_pool, v_pool, page_table, table_stride, ring, token_slot};
+        sm::gemm_skinny(x, norm_w, (sm::DType)norm_w_dt, eps, w, T, (heads + 2 * kv_heads) * head_dim, K, 3, bias,
+                        (sm::DType)bias_dt, nullptr, sm::BF16, 0, &rope, (cudaStream_t)stream);
     });
 }

@@ -69,6 +69,29 @@ size_t gemm_tc_workspace_bytes(int T, int N, int K, bool dual);
 void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N,
              int K, int mode, int up_offset, float* workspace, int* error, cudaStream_t stream);
 
+// ---- gemm_skinny.cu -------------------------------------------------------------------
+// The product for a handful of tokens (T <= 32) and bfloat16 weights, with the layer's
+// surroundings folded in. x is bfloat16 [T, K], or -- when norm_w is given -- the float
+// residual [T, K], normalised on the fly (RMSNorm with norm_w and eps). mode 0: out = x w^T
+// + bias; 1: float out += x w^T; 2: out = act(x w[:N]^T) * (x w[up_offset:up_offset+N]^T);
+// 3: q/k/v rows with bias, rotation of q and k, q written to rope->q_out and k, v to the cache.
+struct SkinnyRope {
+    int heads, kv_heads, head_dim, rotary_dim;
+    const int32_t* positions;   // [T]
+    const float* cos_table;
+    const float* sin_table;
+    void* q_out;                // bfloat16 [T, heads, head_dim]
+    void* k_pool;
+    void* v_pool;
+    const int32_t* page_table;
+    int table_stride, ring;
+    const int32_t* token_slot;  // [T]
+};
+bool gemm_skinny_supports(int T, int N, int K);
+void gemm_skinny(const void* x, const void* norm_w, DType norm_w_dt, float eps, const void* w, int T, int N, int K,
+                 int mode, const void* bias, DType bias_dt, void* out, DType out_dt, int up_offset,
+                 const SkinnyRope* rope, cudaStream_t stream);
+
 // ---- attention_plain.cu ---------------------------------------------------------------
 struct AttentionArgs {
     const void* q;              // [T, heads, head_dim]
@@ -104,14 +127,15 @@ void attention_prefill(const void* q, const void* k, const void* v, void* out, c
 
 // ---- attention_decode.cu --------------------------------------------------------------
 // One new token per sequence over the paged cache for bfloat16, split along the positions
-// in chunks; `splits` = attention_decode_splits(longest sequence) and the workspace holds
-// attention_decode_workspace_floats() floats.
+// in chunks; `splits` = attention_decode_splits(longest sequence), the workspace holds
+// attention_decode_workspace_floats() floats, and `counters` holds B * kv_heads ints that are
+// zero before the first launch (the kernel leaves them zero).
 int attention_decode_splits(int max_len);
 size_t attention_decode_workspace_floats(int B, int heads, int head_dim, int splits);
 void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
                       const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
                       const int32_t* page_table, int table_stride, int ring, int splits, float* workspace,
-                      cudaStream_t stream);
+                      int* counters, cudaStream_t stream);
 
 // ---- sampling.cu ----------------------------------------------------------------------
 // out[b] = argmax over the allowed ids of logits[b, :], the lowest id on ties

@@ -31,6 +31,7 @@ class StepBatch:
     slot_ids: torch.Tensor          # int32 [B]
     seq_ends: torch.Tensor          # int32 [B] lengths after this step
     prefill_tiles: Optional[torch.Tensor] = None  # int32 [tiles, 3]: sequence's first packed index, length, first query
+    wants_every_row: bool = False   # logits are asked for every token of the step, in order
 
 
 def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence[Sequence[int]],

@@ -49,7 +49,7 @@ class _DecodeGraph:
             mode="decode", n_seqs=n_seqs, n_tokens=n_seqs, slots=[], seq_lens=[1] * n_seqs, max_seq_len=span,
             tokens=self.meta[0], positions=self.meta[1], token_slot=self.meta[2], token_end=self.meta[3],
             token_seq_start=self.rows, cu_seqlens=torch.arange(n_seqs + 1, dtype=torch.int32, device=dev),
-            slot_ids=self.meta[2], seq_ends=self.meta[3])
+            slot_ids=self.meta[2], seq_ends=self.meta[3], wants_every_row=True)
 
     def capture(self, engine: "Engine") -> None:
         """``meta`` must already hold a real step: the run before the capture loads kernels and

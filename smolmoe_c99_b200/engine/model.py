@@ -69,7 +69,8 @@ class DecoderModel:
             self.blocks[index].forward(residual, step, cache.run_view(run))
         if want_rows is None or want_rows.numel() == 0:
             return None
-        x = self.final_norm.forward(residual, want_rows)
+        every_row = getattr(step, "wants_every_row", False)   # the wanted rows are 0..T-1 in order
+        x = self.final_norm.forward(residual, None if every_row else want_rows, lazy=True)
         return ops.linear(x, self.head, None, out_dtype=torch.float32)
 
     def weight_bytes(self) -> int:

@@ -45,6 +45,26 @@ def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class NormedRows:
+    """The rows of a float residual under RMSNorm, not computed yet. A product over a handful
+    of tokens takes the norm as its prologue; everything else asks for ``tensor()``, which
+    runs the norm kernel once."""
+
+    def __init__(self, ops: "Ops", residual: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                 rows: Optional[torch.Tensor] = None):
+        self.ops, self.residual, self.weight, self.eps, self.out_dtype, self.rows = ops, residual, weight, eps, out_dtype, rows
+        self.done: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return (self.residual.shape[0] if self.rows is None else self.rows.numel(), self.residual.shape[1])
+
+    def tensor(self) -> torch.Tensor:
+        if self.done is None:
+            self.done = self.ops.rmsnorm(self.residual, self.weight, self.eps, self.out_dtype, self.rows)
+        return self.done
+
+
 class Ops:
     """The kernel library, loaded (and built if needed) at construction."""
 
@@ -57,6 +77,9 @@ class Ops:
         self.lib.sm_launch_count.restype = ctypes.c_longlong
         self.use_tensor_cores = True  # False routes bfloat16 products to the CUDA-core kernel
         self.use_fast_attention = True  # False routes bfloat16 attention to the plain kernel
+        self.use_skinny = True  # False routes products over a handful of tokens to the general kernels
+        # arrival counters of the decode attention kernel: zero between launches
+        self.decode_counters = torch.zeros(65536, dtype=torch.int32, device="cuda")
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
 
     def _check(self, status: int) -> None:
@@ -83,6 +106,10 @@ class Ops:
         self._check(self.lib.sm_rmsnorm(_ptr(x), _ptr(weight), _dt(weight), ctypes.c_float(eps), _ptr(out), _dt(out),
                                         _ptr(rows), n, x.shape[1], _stream()))
         return out
+
+    def rmsnorm_lazy(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                     rows: Optional[torch.Tensor] = None) -> NormedRows:
+        return NormedRows(self, x, weight, eps, out_dtype, rows)
 
     def swiglu(self, gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         _need(gate_up, "gate_up", torch.float32, 2)
@@ -144,18 +171,81 @@ class Ops:
         """out (+)= x @ w.T + bias. float32 operands run on the CUDA cores in float; bfloat16
         operands run on the tensor cores where the shape allows, else on the CUDA cores."""
         if out is None:
-            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or self._dtype_of(x), device=w.device)
+        if self._skinny_ok(x, w) and (not accumulate or out.dtype == torch.float32):
+            return self.gemm_skinny(x, w, bias, out, mode=1 if accumulate else 0)
+        x = self.materialize(x)
         if self._tensor_core_ok(x, w) and (not accumulate or out.dtype == torch.float32):
             return self.gemm_tc(x, w, bias, out, mode=1 if accumulate else 0)
         return self.gemm_simt(x, w, bias, out, accumulate)
 
-    def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor, hidden: int, out_dtype: torch.dtype) -> torch.Tensor:
+    def gated_linear(self, x, w_gate_up: torch.Tensor, hidden: int, out_dtype: torch.dtype) -> torch.Tensor:
         """act(x @ w_gate.T) * (x @ w_up.T) with w_gate_up = [w_gate; w_up]."""
+        if self._skinny_ok(x, w_gate_up):
+            out = torch.empty((x.shape[0], hidden), dtype=out_dtype, device=w_gate_up.device)
+            return self.gemm_skinny(x, w_gate_up, None, out, mode=2, up_offset=hidden)
+        x = self.materialize(x)
         if self._tensor_core_ok(x, w_gate_up):
             out = torch.empty((x.shape[0], hidden), dtype=out_dtype, device=x.device)
             return self.gemm_tc(x, w_gate_up, None, out, mode=2, up_offset=hidden)
         gate_up = self.linear(x, w_gate_up, None, out_dtype=torch.float32)
         return self.swiglu(gate_up, out_dtype)
+
+    # ---- rows under a norm that has not been computed yet -------------------------------
+    @staticmethod
+    def materialize(x) -> torch.Tensor:
+        return x.tensor() if isinstance(x, NormedRows) else x
+
+    @staticmethod
+    def _dtype_of(x) -> torch.dtype:
+        return x.out_dtype if isinstance(x, NormedRows) else x.dtype
+
+    def _skinny_ok(self, x, w: torch.Tensor) -> bool:
+        """A handful of tokens and bfloat16 weights: the weight-streaming kernel, which also
+        takes the norm as its prologue."""
+        if not self.use_skinny or w.dtype != torch.bfloat16:
+            return False
+        if isinstance(x, NormedRows):
+            if x.rows is not None or x.out_dtype != torch.bfloat16 or x.done is not None:
+                return False
+        elif x.dtype != torch.bfloat16:
+            return False
+        return bool(self.lib.sm_gemm_skinny_supports(x.shape[0], w.shape[0], x.shape[1]))
+
+    def gemm_skinny(self, x, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int = 0,
+                    up_offset: int = 0) -> torch.Tensor:
+        """mode 0: out = x w^T + bias; 1: float out += x w^T; 2: gated (see gemm_tc)."""
+        norm_w, eps, src = (x.weight, x.eps, x.residual) if isinstance(x, NormedRows) else (None, 0.0, x)
+        _need(src, "x", torch.float32 if norm_w is not None else torch.bfloat16, 2)
+        _need(w, "w", torch.bfloat16, 2)
+        _need(out, "out", ndim=2)
+        T, K = src.shape
+        N = out.shape[1]
+        if w.shape[1] != K or out.shape[0] != T or w.shape[0] != (up_offset + N if mode == 2 else N):
+            raise KernelError(f"gemm shapes do not agree: x {tuple(src.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if mode == 1 and out.dtype != torch.float32:
+            raise KernelError("accumulation needs a float32 output")
+        self._check(self.lib.sm_gemm_skinny(
+            _ptr(src), _ptr(norm_w), _dt(norm_w) if norm_w is not None else F32, ctypes.c_float(eps), _ptr(w), T, N, K,
+            mode, _ptr(bias), _dt(bias) if bias is not None else F32, _ptr(out), _dt(out), up_offset, _stream()))
+        return out
+
+    def qkv_rope_store_fused(self, x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim,
+                             rotary_dim, k_pool, v_pool, page_table, ring, token_slot) -> Optional[torch.Tensor]:
+        """For a handful of tokens: q/k/v product, bias, rotation and cache write in one launch.
+        Returns q [T, heads, head_dim], or None when the shapes are not the fused kernel's."""
+        if (not self._skinny_ok(x, w_qkv) or head_dim % 16 or rotary_dim != head_dim or k_pool is None
+                or k_pool.dtype != torch.bfloat16):
+            return None
+        norm_w, eps, src = (x.weight, x.eps, x.residual) if isinstance(x, NormedRows) else (None, 0.0, x)
+        T, K = src.shape
+        q = torch.empty((T, heads, head_dim), dtype=torch.bfloat16, device=src.device)
+        self._check(self.lib.sm_gemm_skinny_qkv(
+            _ptr(src), _ptr(norm_w), _dt(norm_w) if norm_w is not None else F32, ctypes.c_float(eps), _ptr(w_qkv), T, K,
+            _ptr(b_qkv), _dt(b_qkv) if b_qkv is not None else F32, heads, kv_heads, head_dim, rotary_dim,
+            _ptr(positions), _ptr(cos_table), _ptr(sin_table), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
+            page_table.shape[1], ring, _ptr(token_slot), _stream()))
+        return q
 
     def _tensor_core_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
         return (self.use_tensor_cores and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -262,7 +352,7 @@ class Ops:
         self._check(self.lib.sm_attention_decode(
             _ptr(q), _ptr(out), B, heads, kv_heads, head_dim, ctypes.c_float(scale), int(window or 0), _ptr(positions),
             _ptr(slots), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), page_table.shape[1], ring, splits,
-            _ptr(workspace), _stream()))
+            _ptr(workspace), _ptr(self.decode_counters), _stream()))
         return out
 
     # ---- sampling ----------------------------------------------------------------------

@@ -19,6 +19,8 @@ from .base import MIXERS, POSITIONS, KVNeed, ParamSpec, Part, Runtime, full_name
 
 @MIXERS.register("attention")
 class Attention(Part):
+    takes_lazy_norm = True
+
     def __init__(self, spec: PartSpec, runtime: Runtime):
         super().__init__(spec, runtime)
         self.hidden = int(spec["hidden_size"])
@@ -69,10 +71,20 @@ class Attention(Part):
         T = x.shape[0]
         cos, sin = self.position.tables(rt.max_positions)
         kv_heads_here = 0 if self.kv_from_cache else self.kv_heads
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
         prefill = step.mode == "prefill"
         if cache.kind != "kv":
             raise RuntimeError("attention needs a key/value cache")
+        q = None
+        if not prefill and not self.kv_from_cache:
+            # one token per sequence: product, bias, rotation and cache write in one launch
+            q = ops.qkv_rope_store_fused(x, self.w_qkv, self.b_qkv, step.positions, cos, sin, self.heads, self.kv_heads,
+                                         self.head_dim, self.position.rotary_dim, cache.k_pool, cache.v_pool,
+                                         cache.page_table, cache.ring, step.token_slot)
+        if q is not None:
+            att = ops.attention_cached(q, step, self.scale, self.window, cache, self.kv_heads)
+            ops.linear(att.view(T, self.heads * self.head_dim), self.w_o, None, out=residual, accumulate=True)
+            return
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
         q, k_packed, v_packed = ops.rope_store(
             qkv, step.positions, cos, sin, self.heads, kv_heads_here, self.head_dim, self.position.rotary_dim,
             rt.dtype, want_packed=prefill and not self.kv_from_cache,

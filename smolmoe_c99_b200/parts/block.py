@@ -44,5 +44,9 @@ class PreNormBlock:
         return mixer.cache_need(spec.mixer) if hasattr(mixer, "cache_need") else None
 
     def forward(self, residual: torch.Tensor, step, cache) -> None:
-        self.mixer.forward(self.mixer_norm.forward(residual), residual, step, cache)
-        self.feed_forward.forward(self.feed_forward_norm.forward(residual), residual, step)
+        # a part that sets ``takes_lazy_norm`` hands its input straight to the kernel library's
+        # products and may receive the norm as a handle; any other part gets a tensor
+        lazy = getattr(self.mixer, "takes_lazy_norm", False)
+        self.mixer.forward(self.mixer_norm.forward(residual, lazy=lazy), residual, step, cache)
+        lazy = getattr(self.feed_forward, "takes_lazy_norm", False)
+        self.feed_forward.forward(self.feed_forward_norm.forward(residual, lazy=lazy), residual, step)

@@ -12,6 +12,8 @@ from .base import FEED_FORWARDS, ParamSpec, Part, Runtime, full_name
 
 @FEED_FORWARDS.register("gated_mlp")
 class GatedMLP(Part):
+    takes_lazy_norm = True
+
     def __init__(self, spec: PartSpec, runtime: Runtime):
         super().__init__(spec, runtime)
         self.hidden = int(spec["hidden_size"])

@@ -26,6 +26,11 @@ class RMSNorm(Part):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
 
-    def forward(self, residual: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``rows`` (int32) picks which rows of ``residual`` are normalised."""
+    def forward(self, residual: torch.Tensor, rows: Optional[torch.Tensor] = None, lazy: bool = False):
+        """``rows`` (int32) picks which rows of ``residual`` are normalised. With ``lazy`` the
+        result is a handle that the kernel library's products accept in place of a tensor (a
+        product over a handful of tokens then computes the norm itself); ``.tensor()`` of the
+        handle gives the values."""
+        if lazy:
+            return self.runtime.ops.rmsnorm_lazy(residual, self.weight, self.eps, self.runtime.dtype, rows)
         return self.runtime.ops.rmsnorm(residual, self.weight, self.eps, self.runtime.dtype, rows)

@@ -179,3 +179,64 @@ def test_decode_attention_over_pages(ops, heads, kv_heads, hd, window):
         want = _plain_attention(qq, ks[b], vs[b], [n], window, scale)[n - 1]
         assert float((got[b] - want).abs().max()) <= 1e-2, f"split kernel, sequence {b}"
         assert float((plain[b] - want).abs().max()) <= 1e-2, f"plain kernel, sequence {b}"
+
+
+# ---- products over a handful of tokens -----------------------------------------------------
+@pytest.mark.parametrize("T", [1, 3, 8, 9, 16, 32])
+@pytest.mark.parametrize("N,K", [(896, 896), (100, 72), (151, 4864), (1000, 136)])
+def test_gemm_skinny_store_and_accumulate(ops, T, N, K):
+    x, w, b = _rand((T, K), torch.bfloat16, 1), _rand((N, K), torch.bfloat16, 2, 0.05), _rand((N,), torch.bfloat16, 3)
+    want = x.float() @ w.float().T
+    out = ops.gemm_skinny(x, w, b, torch.empty((T, N), dtype=torch.float32, device="cuda"))
+    tol = 1e-3 * math.sqrt(K) * 0.05
+    assert float((out - (want + b.float())).abs().max()) <= tol
+    res = _rand((T, N), torch.float32, 4)
+    want_acc = want + res
+    ops.gemm_skinny(x, w, None, res, mode=1)
+    assert float((res - want_acc).abs().max()) <= tol
+    # the same rows alone give the same bits: a row's sum does not depend on the batch
+    alone = ops.gemm_skinny(x[:1].contiguous(), w, b, torch.empty((1, N), dtype=torch.float32, device="cuda"))
+    assert torch.equal(alone[0], out[0])
+
+
+@pytest.mark.parametrize("T,H,K", [(1, 4864, 896), (8, 160, 96), (13, 520, 264)])
+def test_gemm_skinny_norm_prologue_and_gate(ops, T, H, K):
+    from smolmoe_c99_b200.kernels.ops import NormedRows
+    res = _rand((T, K), torch.float32, 7)
+    nw = (_rand((K,), torch.bfloat16, 8, 0.2).float() + 1).to(torch.bfloat16)
+    w = _rand((2 * H, K), torch.bfloat16, 6, 0.05)
+    eps = 1e-5
+    xn = ops.rmsnorm(res, nw, eps, torch.bfloat16)   # the stand-alone kernel
+    ref = res * torch.rsqrt((res * res).mean(dim=1, keepdim=True) + eps) * nw.float()
+    assert float((xn.float() - ref).abs().max()) <= 8e-3 * float(ref.abs().max())
+    g, u = xn.float() @ w[:H].float().T, xn.float() @ w[H:].float().T
+    want = u * (g / (1 + torch.exp(-g)))
+    lazy = NormedRows(ops, res, nw, eps, torch.bfloat16)
+    got = ops.gemm_skinny(lazy, w, None, torch.empty((T, H), dtype=torch.bfloat16, device="cuda"), mode=2, up_offset=H)
+    assert float((got.float() - want).abs().max()) <= 1e-2 * float(want.abs().max()) + 1e-3
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (14, 2, 64), (5, 5, 48)])
+def test_fused_qkv_matches_the_separate_kernels(ops, heads, kv_heads, hd):
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    T, K = 5, 96
+    N = (heads + 2 * kv_heads) * hd
+    x, w, b = _rand((T, K), torch.bfloat16, 1), _rand((N, K), torch.bfloat16, 2, 0.1), _rand((N,), torch.bfloat16, 3)
+    positions = torch.tensor([0, 7, 63, 64, 130], dtype=torch.int32).cuda()
+    slots = torch.tensor([2, 0, 4, 1, 3], dtype=torch.int32).cuda()
+    table = torch.randperm(20, generator=torch.Generator().manual_seed(3)).to(torch.int32).view(5, 4).cuda()
+    half = hd // 2
+    ang = torch.arange(200, dtype=torch.float64)[:, None] * torch.pow(torch.tensor(10000.0, dtype=torch.float64),
+                                                                        -torch.arange(half, dtype=torch.float64) * 2 / hd)
+    cos, sin = torch.cos(ang).float().cuda(), torch.sin(ang).float().cuda()
+    pools = [torch.zeros((20, kv_heads, PAGE_SIZE, hd), dtype=torch.bfloat16, device="cuda") for _ in range(4)]
+    ends = positions + 1
+    qkv = ops.gemm_simt(x, w, b, torch.empty((T, N), dtype=torch.float32, device="cuda"))
+    q_ref, _, _ = ops.rope_store(qkv, positions, cos, sin, heads, kv_heads, hd, hd, torch.bfloat16, False, pools[0], pools[1],
+                                 table, 0, slots, ends)
+    q = ops.qkv_rope_store_fused(x, w, b, positions, cos, sin, heads, kv_heads, hd, hd, pools[2], pools[3], table, 0, slots)
+    assert q is not None
+    assert float((q.float() - q_ref.float()).abs().max()) <= 2e-2
+    assert float((pools[2].float() - pools[0].float()).abs().max()) <= 2e-2
+    assert float((pools[3].float() - pools[1].float()).abs().max()) <= 2e-2
+    assert int((pools[2] != 0).sum()) == int((pools[0] != 0).sum())   # the same cells were written
