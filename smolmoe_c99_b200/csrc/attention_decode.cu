@@ -17,6 +17,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace sm {
 
@@ -43,8 +44,20 @@ struct DecodeArgs {
     int* counters;                // [B, kv_heads], zero between launches
 };
 
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
-    uint4 raw = *reinterpret_cast<const uint4*>(p);
+// Phase timestamps of one CTA, for a timing probe built with -DSM_DECODE_TIMING.
+#ifdef SM_DECODE_TIMING
+__device__ unsigned long long g_decode_timing[32];
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define SM_STAMP(i) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (blockIdx.z == 0 || (i) >= 10)) g_decode_timing[i] = global_ns(); } while (0)
+#else
+#define SM_STAMP(i) do { } while (0)
+#endif
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -56,6 +69,9 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
 
 __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    SM_STAMP(0);
+    pdl_launch_dependents();
+    pdl_wait();   // q and the newest key and value come from the kernel before
     const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
     const int hd = a.head_dim, group = a.heads / a.kv_heads;
     const int pos = a.positions[b];
@@ -68,14 +84,17 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
     float* sc = qs + group * hd;                                       // [group][kChunk] scores, then weights
     unsigned long long* rows = reinterpret_cast<unsigned long long*>(sc + group * kChunk);  // [kChunk]
     float* red = reinterpret_cast<float*>(rows + kChunk);              // [key groups][kHeadPass][hd]
-    const int half_ = hd / 2;
-    const int key_groups_ = kThreads / half_ > 0 ? kThreads / half_ : 1;
-    float* wts = red + (size_t)key_groups_ * kHeadPass * hd;           // [warps][splits] merge weights
+    float* wts = red + (size_t)(kThreads / (hd / 8)) * kHeadPass * hd; // [warps][splits] merge weights
     __shared__ int is_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const __nv_bfloat16* qb = a.q + ((size_t)b * a.heads + (size_t)kvh * group) * hd;
-    for (int i = tid; i < group * hd; i += kThreads) qs[i] = __bfloat162float(qb[i]);
+    for (int i = tid * 8; i < group * hd; i += kThreads * 8) {   // hd is a multiple of 8
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(qb + i), v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qs[i + e] = v[e];
+    }
     const int slot = a.slots[b];
     PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
     const int p = c0 + tid;
@@ -84,6 +103,7 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
     if (valid) row = (unsigned long long)paged.row_offset(slot, p, kvh);
     rows[tid] = row;
     __syncthreads();
+    SM_STAMP(1);
 
     // scores: one key per thread, kHeadPass heads at a time
     for (int g0 = 0; g0 < group; g0 += kHeadPass) {
@@ -92,18 +112,28 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
         for (int g = 0; g < kHeadPass; ++g) s[g] = 0.f;
         if (valid) {
             const __nv_bfloat16* kr = a.k_pool + row;
-            for (int d = 0; d < hd; d += 8) {
-                float kv[8];
-                load8(kr + d, kv);
+            for (int d0 = 0; d0 < hd; d0 += 64) {
+                // up to 64 dims of the key row at once: eight loads in flight, then the arithmetic
+                uint4 raw[8];
 #pragma unroll
-                for (int g = 0; g < kHeadPass; ++g) {
-                    if (g0 + g < group) {
-                        const float4 qa = *reinterpret_cast<const float4*>(qs + (g0 + g) * hd + d);
-                        const float4 qc = *reinterpret_cast<const float4*>(qs + (g0 + g) * hd + d + 4);
-                        s[g] = fmaf(qa.x, kv[0], s[g]); s[g] = fmaf(qa.y, kv[1], s[g]);
-                        s[g] = fmaf(qa.z, kv[2], s[g]); s[g] = fmaf(qa.w, kv[3], s[g]);
-                        s[g] = fmaf(qc.x, kv[4], s[g]); s[g] = fmaf(qc.y, kv[5], s[g]);
-                        s[g] = fmaf(qc.z, kv[6], s[g]); s[g] = fmaf(qc.w, kv[7], s[g]);
+                for (int c = 0; c < 8; ++c)
+                    raw[c] = d0 + c * 8 < hd ? *reinterpret_cast<const uint4*>(kr + d0 + c * 8) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int d = d0 + c * 8;
+                    if (d >= hd) break;
+                    float kv[8];
+                    unpack8(raw[c], kv);
+#pragma unroll
+                    for (int g = 0; g < kHeadPass; ++g) {
+                        if (g0 + g < group) {
+                            const float4 qa = *reinterpret_cast<const float4*>(qs + (g0 + g) * hd + d);
+                            const float4 qc = *reinterpret_cast<const float4*>(qs + (g0 + g) * hd + d + 4);
+                            s[g] = fmaf(qa.x, kv[0], s[g]); s[g] = fmaf(qa.y, kv[1], s[g]);
+                            s[g] = fmaf(qa.z, kv[2], s[g]); s[g] = fmaf(qa.w, kv[3], s[g]);
+                            s[g] = fmaf(qc.x, kv[4], s[g]); s[g] = fmaf(qc.y, kv[5], s[g]);
+                            s[g] = fmaf(qc.z, kv[6], s[g]); s[g] = fmaf(qc.w, kv[7], s[g]);
+                        }
                     }
                 }
             }
@@ -113,6 +143,7 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
             if (g0 + g < group) sc[(g0 + g) * kChunk + tid] = valid ? s[g] * a.scale : -CUDART_INF_F;
     }
     __syncthreads();
+    SM_STAMP(2);
 
     // per head: maximum, weights exp(s - m) and their sum; warps take heads in turn
     for (int g = warp; g < group; g += kThreads / 32) {
@@ -133,34 +164,48 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
         }
     }
     __syncthreads();
+    SM_STAMP(3);
 
-    // weighted values: a thread owns two neighbouring dims; thread groups take keys in turn
-    const int half = hd / 2;
-    const int key_groups = kThreads / half > 0 ? kThreads / half : 1;   // hd <= 256 -> half <= 128
-    const int kg = tid / half, dd = tid - kg * half;
+    // weighted values: a thread owns 8 neighbouring dims (16 bytes) of the rows of its key
+    // group; the groups take keys in turn, four loads in flight each
+    const int cpr = hd / 8;                       // 16-byte chunks per row
+    const int key_groups = kThreads / cpr;        // hd <= 256 -> at least 4
+    const int kg = tid / cpr, ch = tid - kg * cpr;
     const int first = lo - c0, last = hi - c0;
     for (int g0 = 0; g0 < group; g0 += kHeadPass) {
-        float acc[kHeadPass][2];
+        float acc[kHeadPass][8];
 #pragma unroll
-        for (int g = 0; g < kHeadPass; ++g) acc[g][0] = acc[g][1] = 0.f;
+        for (int g = 0; g < kHeadPass; ++g)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
         if (kg < key_groups) {
-            for (int j = first + kg; j <= last; j += key_groups) {
-                const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(a.v_pool + rows[j] + 2 * dd);
-                const float2 v = __bfloat1622float2(v2);
+            for (int j0 = first + kg; j0 <= last; j0 += 8 * key_groups) {
+                uint4 raw[8];
 #pragma unroll
-                for (int g = 0; g < kHeadPass; ++g) {
-                    if (g0 + g < group) {
-                        float w = sc[(g0 + g) * kChunk + j];
-                        acc[g][0] = fmaf(w, v.x, acc[g][0]);
-                        acc[g][1] = fmaf(w, v.y, acc[g][1]);
+                for (int u = 0; u < 8; ++u) {
+                    const int j = j0 + u * key_groups;
+                    raw[u] = j <= last ? *reinterpret_cast<const uint4*>(a.v_pool + rows[j] + 8 * ch) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int j = j0 + u * key_groups;
+                    if (j > last) break;
+                    float v[8];
+                    unpack8(raw[u], v);
+#pragma unroll
+                    for (int g = 0; g < kHeadPass; ++g) {
+                        if (g0 + g < group) {
+                            const float w = sc[(g0 + g) * kChunk + j];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(w, v[e], acc[g][e]);
+                        }
                     }
                 }
             }
 #pragma unroll
-            for (int g = 0; g < kHeadPass; ++g) {
-                red[((size_t)kg * kHeadPass + g) * hd + 2 * dd] = acc[g][0];
-                red[((size_t)kg * kHeadPass + g) * hd + 2 * dd + 1] = acc[g][1];
-            }
+            for (int g = 0; g < kHeadPass; ++g)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) red[((size_t)kg * kHeadPass + g) * hd + 8 * ch + e] = acc[g][e];
         }
         __syncthreads();
         for (int i = tid; i < kHeadPass * hd; i += kThreads) {
@@ -174,6 +219,7 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
         __syncthreads();
     }
 
+    SM_STAMP(4);
     // the last CTA of this (sequence, kv head) merges the chunks
     const int s_lo = start / kChunk, s_hi = pos / kChunk, n_active = s_hi - s_lo + 1;
     __threadfence();
@@ -185,8 +231,10 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
         if (is_last) *counter = 0;
     }
     __syncthreads();
+    SM_STAMP(5);
     if (!is_last) return;
     __threadfence();
+    SM_STAMP(10);
     float* my_w = wts + (size_t)warp * a.splits;
     for (int g = warp; g < group; g += kThreads / 32) {
         const size_t head = (size_t)b * a.heads + kvh * group + g;
@@ -203,16 +251,22 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
         }
         l = warp_sum(l);
         __syncwarp();
+        SM_STAMP(11);
         float acc[kMaxHeadDim / 32];
 #pragma unroll
         for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
-#pragma unroll 4
-        for (int s = s_lo; s <= s_hi; ++s) {
-            const float w = my_w[s - s_lo];
+        for (int s0 = s_lo; s0 <= s_hi; s0 += 16) {
+            // sixteen chunks' partial results in flight per dim, then the sums in chunk order
 #pragma unroll
             for (int i = 0; i < kMaxHeadDim / 32; ++i) {
-                int d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(__ldcg(po + (size_t)s * hd + d), w, acc[i]);
+                const int d = lane + 32 * i;
+                if (d >= hd) break;
+                float v[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) v[u] = s0 + u <= s_hi ? __ldcg(po + (size_t)(s0 + u) * hd + d) : 0.f;
+#pragma unroll
+                for (int u = 0; u < 16; ++u)
+                    if (s0 + u <= s_hi) acc[i] = fmaf(v[u], my_w[s0 + u - s_lo], acc[i]);
             }
         }
         const float inv = 1.0f / l;
@@ -223,6 +277,7 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) 
             if (d < hd) o[d] = __float2bfloat16_rn(acc[i] * inv);
         }
         __syncwarp();
+        SM_STAMP(12);
     }
 }
 
@@ -245,8 +300,7 @@ void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, 
     if (heads % kv_heads) throw std::invalid_argument("attention_decode: kv_heads must divide heads");
     if (splits <= 0 || splits > 65535) throw std::invalid_argument("attention_decode: splits out of range");
     int group = heads / kv_heads;
-    int half = head_dim / 2;
-    int key_groups = kThreads / half > 0 ? kThreads / half : 1;
+    int key_groups = kThreads / (head_dim / 8);
     size_t smem = (size_t)group * head_dim * 4 + (size_t)group * kChunk * 4 + kChunk * 8 +
                   (size_t)key_groups * kHeadPass * head_dim * 4 + (size_t)(kThreads / 32) * splits * 4;
     if (B * kv_heads > 65536) throw std::invalid_argument("attention_decode: more than 65536 (sequence, kv head) pairs");
@@ -261,7 +315,8 @@ void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, 
         cudaFuncSetAttribute(decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     note_launch();
     dim3 grid(kv_heads, B, splits);
-    decode_partial_kernel<<<grid, kThreads, smem, stream>>>(a);
+    launch_kernel("attention_decode", decode_partial_kernel, grid, dim3(kThreads), smem, stream, 1,
+                  dependent_launch_enabled(), a);
 }
 
 }  // namespace sm

@@ -39,11 +39,17 @@ namespace sm {
 static std::atomic<long long> g_launches{0};
 void note_launch(int kernels) { g_launches.fetch_add(kernels, std::memory_order_relaxed); }
 long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+static std::atomic<bool> g_dependent_launch{true};
+bool dependent_launch_enabled() { return g_dependent_launch.load(std::memory_order_relaxed); }
+void set_dependent_launch(bool on) { g_dependent_launch.store(on, std::memory_order_relaxed); }
 }  // namespace sm
 
 #define SM_API extern "C" __attribute__((visibility("default")))
 
 SM_API const char* sm_last_error() { return g_last_error.c_str(); }
+
+// Programmatic dependent launch of the decode chain's kernels: 1 on (default), 0 off.
+SM_API void sm_set_dependent_launch(int on) { sm::set_dependent_launch(on != 0); }
 
 // Kernels enqueued by this library since it was loaded.
 SM_API long long sm_launch_count() { return sm::launch_count(); }
@@ -98,8 +104,9 @@ SM_API int sm_attention_plain(const void* q, void* out, int dt, int T, int heads
     });
 }
 
-SM_API int sm_argmax(const float* logits, const uint8_t* banned, int32_t* out, int B, int V, void* stream) {
-    return guarded([&] { sm::argmax(logits, banned, out, B, V, (cudaStream_t)stream); });
+SM_API int sm_argmax(const float* logits, const uint8_t* banned, int32_t* out, int B, int V,
+                     unsigned long long* scratch, int* counters, void* stream) {
+    return guarded([&] { sm::argmax(logits, banned, out, B, V, scratch, counters, (cudaStream_t)stream); });
 }
 
 SM_API int sm_sample(const float* logits, const uint8_t* banned, int32_t* out, uint32_t* rng_state, int B, int V,

@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace sm {
 
@@ -12,6 +13,8 @@ namespace sm {
 template <typename TW>
 __global__ void embedding_kernel(const TW* __restrict__ table, const int32_t* __restrict__ tokens,
                                  float* __restrict__ out, int D, int V, int32_t* status) {
+    pdl_launch_dependents();
+    pdl_wait();   // the tokens may come from the sampler's kernel
     int t = blockIdx.x;
     int token = tokens[t];
     float* row = out + (size_t)t * D;
@@ -30,9 +33,11 @@ void embedding(const void* table, DType table_dt, const int32_t* tokens, float* 
     note_launch();
     int threads = D >= 256 ? 256 : 128;
     if (table_dt == F32)
-        embedding_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, out, D, V, status);
+        launch_kernel("embedding", embedding_kernel<float>, dim3(T), dim3(threads), 0, stream, 1, dependent_launch_enabled(),
+                      (const float*)table, tokens, out, D, V, status);
     else
-        embedding_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, D, V, status);
+        launch_kernel("embedding", embedding_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, 1,
+                      dependent_launch_enabled(), (const __nv_bfloat16*)table, tokens, out, D, V, status);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -15,6 +15,11 @@ enum DType : int { F32 = 0, BF16 = 1 };
 void note_launch(int kernels = 1);
 long long launch_count();
 
+// Whether the kernels of the decode chain are launched as programmatic dependents of their
+// predecessors (see launch.cuh). On by default.
+bool dependent_launch_enabled();
+void set_dependent_launch(bool on);
+
 // ---- elementwise.cu -------------------------------------------------------------------
 // out[t, :] = table[tokens[t], :] as float. A token outside [0, V) sets *status |= 1 and
 // its row is zeroed.
@@ -139,8 +144,10 @@ void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, 
 
 // ---- sampling.cu ----------------------------------------------------------------------
 // out[b] = argmax over the allowed ids of logits[b, :], the lowest id on ties
-// (src/sampler.c:57-63). `banned` (nullable) is one byte per id.
-void argmax(const float* logits, const uint8_t* banned, int32_t* out, int B, int V, cudaStream_t stream);
+// (src/sampler.c:57-63). `banned` (nullable) is one byte per id. `scratch` holds B words
+// that are all ones and `counters` B zeros before the first launch; the kernel leaves them so.
+void argmax(const float* logits, const uint8_t* banned, int32_t* out, int B, int V, unsigned long long* scratch,
+            int* counters, cudaStream_t stream);
 
 // Temperature sampling with optional top-k (0 or >= V: off) and top-p (1: off), one
 // xorshift32 state per row, advanced once per call (src/sampler.c:103-127). out[b] = -1

@@ -15,6 +15,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace sm {
 
@@ -29,15 +30,39 @@ __device__ __forceinline__ unsigned long long rank_of(float logit, int id) {
     return ((unsigned long long)(~key) << 24) | (unsigned long long)(uint32_t)id;
 }
 
-__global__ void __launch_bounds__(kSampleThreads)
-argmax_kernel(const float* __restrict__ logits, const uint8_t* __restrict__ banned, int32_t* __restrict__ out, int V) {
-    __shared__ unsigned long long best_shared[kSampleThreads / 32];
-    const float* row = logits + (size_t)blockIdx.x * V;
+// Greedy choice in one launch over (chunks of the vocabulary, rows): every CTA finds the
+// best rank of its chunk and lowers the row's 64-bit scratch word with atomicMin (a
+// minimum does not depend on the order of arrival); the CTA that arrives last for a row
+// writes the token and puts the scratch word and the counter back to their idle values.
+constexpr int kArgmaxThreads = 256;
+constexpr int kArgmaxChunks = 32;
+
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_kernel(const float* __restrict__ logits, const uint8_t* __restrict__ banned, int32_t* __restrict__ out, int V,
+              unsigned long long* scratch, int* counters) {
+    __shared__ unsigned long long best_shared[kArgmaxThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y;
+    const float* row = logits + (size_t)b * V;
+    const int per = (V + kArgmaxChunks - 1) / kArgmaxChunks;
+    const int lo = blockIdx.x * per, hi = min(V, lo + per);
     unsigned long long best = kAllRanks;
-    for (int i = threadIdx.x; i < V; i += kSampleThreads) {
-        if (banned && banned[i]) continue;
-        unsigned long long r = rank_of(row[i], i);
-        best = r < best ? r : best;
+    for (int i0 = lo + threadIdx.x; i0 < hi; i0 += 4 * kArgmaxThreads) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            int i = i0 + u * kArgmaxThreads;
+            v[u] = i < hi ? row[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            int i = i0 + u * kArgmaxThreads;
+            if (i < hi && !(banned && banned[i])) {
+                unsigned long long r = rank_of(v[u], i);
+                best = r < best ? r : best;
+            }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -47,16 +72,26 @@ argmax_kernel(const float* __restrict__ logits, const uint8_t* __restrict__ bann
     if ((threadIdx.x & 31) == 0) best_shared[threadIdx.x >> 5] = best;
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int i = 1; i < kSampleThreads / 32; ++i) best = best_shared[i] < best ? best_shared[i] : best;
-        out[blockIdx.x] = best == kAllRanks ? -1 : (int32_t)(best & 0xffffffu);
+        for (int i = 1; i < kArgmaxThreads / 32; ++i) best = best_shared[i] < best ? best_shared[i] : best;
+        atomicMin(&scratch[b], best);
+        __threadfence();
+        if (atomicAdd(&counters[b], 1) == kArgmaxChunks - 1) {
+            __threadfence();
+            unsigned long long final_rank = atomicExch(&scratch[b], kAllRanks);
+            counters[b] = 0;
+            out[b] = final_rank == kAllRanks ? -1 : (int32_t)(final_rank & 0xffffffu);
+        }
     }
 }
 
-void argmax(const float* logits, const uint8_t* banned, int32_t* out, int B, int V, cudaStream_t stream) {
+void argmax(const float* logits, const uint8_t* banned, int32_t* out, int B, int V, unsigned long long* scratch,
+            int* counters, cudaStream_t stream) {
     if (B <= 0) return;
     if (V <= 0 || V > (1 << 24)) throw std::invalid_argument("argmax: vocabulary must be in [1, 2^24]");
+    if (B > 65535) throw std::invalid_argument("argmax: more than 65535 rows");
     note_launch();
-    argmax_kernel<<<B, kSampleThreads, 0, stream>>>(logits, banned, out, V);
+    launch_kernel("argmax", argmax_kernel, dim3(kArgmaxChunks, B), dim3(kArgmaxThreads), 0, stream, 1,
+                  dependent_launch_enabled(), logits, banned, out, V, scratch, counters);
 }
 
 // ---------------------------------------------------------------------------------------

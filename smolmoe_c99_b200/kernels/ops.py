@@ -81,6 +81,9 @@ class Ops:
         # arrival counters of the decode attention kernel: zero between launches
         self.decode_counters = torch.zeros(65536, dtype=torch.int32, device="cuda")
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        # scratch of the greedy choice: one word per row, all ones when idle, and arrival counters
+        self.argmax_scratch = torch.full((4096,), -1, dtype=torch.int64, device="cuda")
+        self.argmax_counters = torch.zeros(4096, dtype=torch.int32, device="cuda")
 
     def _check(self, status: int) -> None:
         if status:
@@ -362,7 +365,10 @@ class Ops:
             _need(banned, "banned", torch.uint8, 1)
         if out is None:
             out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
-        self._check(self.lib.sm_argmax(_ptr(logits), _ptr(banned), _ptr(out), logits.shape[0], logits.shape[1], _stream()))
+        if logits.shape[0] > self.argmax_scratch.numel():
+            raise KernelError(f"argmax takes at most {self.argmax_scratch.numel()} rows a call")
+        self._check(self.lib.sm_argmax(_ptr(logits), _ptr(banned), _ptr(out), logits.shape[0], logits.shape[1],
+                                       _ptr(self.argmax_scratch), _ptr(self.argmax_counters), _stream()))
         return out
 
     def sample(self, logits, rng_state, temperature, top_k, top_p, banned=None, out=None):
