@@ -1,15 +1,20 @@
-// Decode attention over the paged cache for bfloat16: one new token per sequence attends
-// to its sequence's keys, split along the positions so that one long sequence fills many
-// SMs (the reference scans [start, pos] per head on one thread: src/kernels.c:1156-1176).
+// Decode attention over the paged cache for bfloat16: one new token per sequence attends to
+// its sequence's keys (the reference scans [start, pos] per head on one thread:
+// src/kernels.c:1156-1176).
 //
-// Kernel 1, one CTA per (kv head, sequence, chunk of kChunk positions): the group's query
-// heads share every key and value row that is read. Scores for the chunk, their running
-// maximum and sum, and the unnormalised weighted values go to a workspace:
-//   part_o [B, heads, splits, head_dim] float, part_ml [B, heads, splits, 2] float.
-// The CTA that finishes last for its (sequence, kv head) -- known from a counter that it
-// then resets -- merges the chunks that hold visible keys in ascending order and writes the
-// normalised result, so the whole attention is one launch. Chunks without visible keys
-// (beyond the sequence, or before the window) do no work and are not read by the merge.
+// A thread-block cluster of 1 to 8 CTAs serves one (sequence, kv head); its CTAs split the
+// visible positions, and within a CTA the four warps take tiles of 32 positions in turn. The
+// group's query heads are the 16 rows of the tensor-core tile (mma.sync m16n8k16), so every
+// key and value row that is read serves all of them. A warp keeps a running maximum, sum and
+// weighted values over its tiles (the next tile's keys and values are on their way while the
+// current one is used); the warps of a CTA merge through shared memory, the CTAs of the
+// cluster through distributed shared memory in rank order. There is no workspace in global
+// memory and nothing depends on the order in which CTAs finish.
+//
+// Key rows are read straight from the cache into the B fragments (16 bytes a lane; the
+// permutation of the head dimension inside a block of 32 is the same for q and k, so the
+// dot products are unchanged); value rows go through shared memory to be read transposed.
+#include <cooperative_groups.h>
 #include <math_constants.h>
 
 #include <stdexcept>
@@ -23,10 +28,10 @@ namespace sm {
 
 namespace {
 
-constexpr int kChunk = 128;       // positions per CTA
-constexpr int kThreads = 128;
-constexpr int kHeadPass = 8;      // query heads handled per pass over the keys
-constexpr int kMaxHeadDim = 256;
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kTile = 32;           // positions per warp tile
+constexpr int kMaxCluster = 8;
 
 struct DecodeArgs {
     const __nv_bfloat16* q;       // [B, heads, head_dim]
@@ -37,286 +42,301 @@ struct DecodeArgs {
     int table_stride, ring;
     const int32_t* slots;         // [B]
     const int32_t* positions;     // [B] position of the new token (its key is already in the cache)
-    int B, heads, kv_heads, head_dim, window, splits;
-    float scale;
-    float* part_o;
-    float* part_ml;
-    int* counters;                // [B, kv_heads], zero between launches
+    int B, heads, kv_heads, head_dim, window, cluster;
+    float scale_log2;             // scale * log2(e)
 };
 
-// Phase timestamps of one CTA, for a timing probe built with -DSM_DECODE_TIMING.
-#ifdef SM_DECODE_TIMING
-__device__ unsigned long long g_decode_timing[32];
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-#define SM_STAMP(i) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (blockIdx.z == 0 || (i) >= 10)) g_decode_timing[i] = global_ns(); } while (0)
-#else
-#define SM_STAMP(i) do { } while (0)
-#endif
-
-__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float2 f = __bfloat1622float2(h[i]);
-        v[2 * i] = f.x;
-        v[2 * i + 1] = f.y;
-    }
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* p) {
+    uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred) {
+    uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    int bytes = pred ? 16 : 0;   // 0 bytes read: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes));
 }
 
-__global__ void __launch_bounds__(kThreads) decode_partial_kernel(DecodeArgs a) {
+// HDB: blocks of 32 of the head dimension (head_dim <= 32 * HDB, a multiple of 16).
+template <int HDB>
+__global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a) {
+    constexpr int HDP = HDB * 32;            // padded head dimension
+    constexpr int LDV = HDP + 8;             // value row in shared memory: conflict-free transposed reads
+    constexpr int NT = HDP / 8;              // dim tiles of the output
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    SM_STAMP(0);
-    pdl_launch_dependents();
-    pdl_wait();   // q and the newest key and value come from the kernel before
-    const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+    // per warp two value buffers [kTile][LDV]; after the loop the same memory holds the warps' results
+    __nv_bfloat16* vs_all = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+
+    const int rank = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q4 = lane & 3;
     const int hd = a.head_dim, group = a.heads / a.kv_heads;
-    const int pos = a.positions[b];
+    pdl_launch_dependents();
+    // slots, positions and the page table are written before the step's first kernel
+    const int slot = a.slots[b], pos = a.positions[b];
     const int start = (a.window > 0 && pos >= a.window) ? pos - a.window + 1 : 0;
-    const int c0 = split * kChunk;
-    if (c0 > pos || c0 + kChunk <= start) return;   // no visible key in this chunk
-    const int lo = max(c0, start), hi = min(c0 + kChunk - 1, pos);   // visible keys [lo, hi]
-
-    float* qs = reinterpret_cast<float*>(smem_raw);                    // [group][hd]
-    float* sc = qs + group * hd;                                       // [group][kChunk] scores, then weights
-    unsigned long long* rows = reinterpret_cast<unsigned long long*>(sc + group * kChunk);  // [kChunk]
-    float* red = reinterpret_cast<float*>(rows + kChunk);              // [key groups][kHeadPass][hd]
-    float* wts = red + (size_t)(kThreads / (hd / 8)) * kHeadPass * hd; // [warps][splits] merge weights
-    __shared__ int is_last;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const __nv_bfloat16* qb = a.q + ((size_t)b * a.heads + (size_t)kvh * group) * hd;
-    for (int i = tid * 8; i < group * hd; i += kThreads * 8) {   // hd is a multiple of 8
-        float v[8];
-        unpack8(*reinterpret_cast<const uint4*>(qb + i), v);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) qs[i + e] = v[e];
-    }
-    const int slot = a.slots[b];
+    const int n_keys = pos - start + 1;
+    const int per_cta = ((n_keys + a.cluster - 1) / a.cluster + kTile - 1) / kTile * kTile;
+    const int cta_lo = start + rank * per_cta, cta_hi = min(pos + 1, cta_lo + per_cta);   // keys [cta_lo, cta_hi)
+    const int n_tiles = cta_hi > cta_lo ? (cta_hi - cta_lo + kTile - 1) / kTile : 0;
     PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
-    const int p = c0 + tid;
-    const bool valid = p >= lo && p <= hi;
-    unsigned long long row = 0;
-    if (valid) row = (unsigned long long)paged.row_offset(slot, p, kvh);
-    rows[tid] = row;
-    __syncthreads();
-    SM_STAMP(1);
+    __nv_bfloat16* vs = vs_all + (size_t)warp * 2 * kTile * LDV;
 
-    // scores: one key per thread, kHeadPass heads at a time
-    for (int g0 = 0; g0 < group; g0 += kHeadPass) {
-        float s[kHeadPass];
+    // row offset of this lane's key of a tile (lane l <-> key l of the tile); ~0 marks "none"
+    auto tile_offset = [&](int tile) -> unsigned long long {
+        const int key = cta_lo + tile * kTile + lane;
+        return key < cta_hi ? (unsigned long long)paged.row_offset(slot, key, kvh) : ~0ull;
+    };
+    int tile = warp;
+    unsigned long long off = tile < n_tiles ? tile_offset(tile) : ~0ull;
+
+    pdl_wait();   // q and the newest key and value come from the kernel before
+
+    // Q fragments: rows g and g + 8 are heads kvh * group + g (+8); heads beyond the group are zero
+    uint4 qa[HDB], qb[HDB];
+    {
+        const __nv_bfloat16* qrow = a.q + ((size_t)b * a.heads + (size_t)kvh * group) * hd;
 #pragma unroll
-        for (int g = 0; g < kHeadPass; ++g) s[g] = 0.f;
-        if (valid) {
-            const __nv_bfloat16* kr = a.k_pool + row;
-            for (int d0 = 0; d0 < hd; d0 += 64) {
-                // up to 64 dims of the key row at once: eight loads in flight, then the arithmetic
-                uint4 raw[8];
+        for (int kb = 0; kb < HDB; ++kb) {
+            const int d = kb * 32 + q4 * 8;
+            qa[kb] = (g < group && d < hd) ? *reinterpret_cast<const uint4*>(qrow + (size_t)g * hd + d) : make_uint4(0, 0, 0, 0);
+            qb[kb] = (g + 8 < group && d < hd) ? *reinterpret_cast<const uint4*>(qrow + (size_t)(g + 8) * hd + d)
+                                               : make_uint4(0, 0, 0, 0);
+        }
+    }
+    uint4 kf[4][HDB];
+    auto load_k = [&](unsigned long long my_off) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    raw[c] = d0 + c * 8 < hd ? *reinterpret_cast<const uint4*>(kr + d0 + c * 8) : make_uint4(0, 0, 0, 0);
+        for (int j = 0; j < 4; ++j) {
+            const unsigned long long o = __shfl_sync(0xffffffffu, my_off, 8 * j + g);   // key 8j + g of the tile
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int d = d0 + c * 8;
-                    if (d >= hd) break;
-                    float kv[8];
-                    unpack8(raw[c], kv);
-#pragma unroll
-                    for (int g = 0; g < kHeadPass; ++g) {
-                        if (g0 + g < group) {
-                            const float4 qa = *reinterpret_cast<const float4*>(qs + (g0 + g) * hd + d);
-                            const float4 qc = *reinterpret_cast<const float4*>(qs + (g0 + g) * hd + d + 4);
-                            s[g] = fmaf(qa.x, kv[0], s[g]); s[g] = fmaf(qa.y, kv[1], s[g]);
-                            s[g] = fmaf(qa.z, kv[2], s[g]); s[g] = fmaf(qa.w, kv[3], s[g]);
-                            s[g] = fmaf(qc.x, kv[4], s[g]); s[g] = fmaf(qc.y, kv[5], s[g]);
-                            s[g] = fmaf(qc.z, kv[6], s[g]); s[g] = fmaf(qc.w, kv[7], s[g]);
-                        }
-                    }
-                }
+            for (int kb = 0; kb < HDB; ++kb) {
+                const int d = kb * 32 + q4 * 8;
+                kf[j][kb] = (o != ~0ull && d < hd) ? *reinterpret_cast<const uint4*>(a.k_pool + o + d) : make_uint4(0, 0, 0, 0);
             }
         }
+    };
+    auto load_v = [&](unsigned long long my_off, int buf) {
+        __nv_bfloat16* dst = vs + (size_t)buf * kTile * LDV;
+        constexpr int CPR = HDP / 8;   // 16-byte chunks per row
 #pragma unroll
-        for (int g = 0; g < kHeadPass; ++g)
-            if (g0 + g < group) sc[(g0 + g) * kChunk + tid] = valid ? s[g] * a.scale : -CUDART_INF_F;
-    }
-    __syncthreads();
-    SM_STAMP(2);
+        for (int c0 = 0; c0 < kTile * CPR; c0 += 32) {
+            const int c = c0 + lane, row = c / CPR, col = (c % CPR) * 8;
+            const unsigned long long o = __shfl_sync(0xffffffffu, my_off, row);
+            const bool in = o != ~0ull && col < hd;
+            cp_async16(dst + (size_t)row * LDV + col, a.v_pool + (in ? o + col : 0), in);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
 
-    // per head: maximum, weights exp(s - m) and their sum; warps take heads in turn
-    for (int g = warp; g < group; g += kThreads / 32) {
-        float m = -CUDART_INF_F;
-        for (int i = lane; i < kChunk; i += 32) m = fmaxf(m, sc[g * kChunk + i]);
-        m = warp_max(m);
-        float l = 0.f;
-        for (int i = lane; i < kChunk; i += 32) {
-            float e = expf(sc[g * kChunk + i] - m);   // masked keys: exp(-inf) = 0
-            sc[g * kChunk + i] = e;
-            l += e;
-        }
-        l = warp_sum(l);
-        if (lane == 0) {
-            float* ml = a.part_ml + (((size_t)b * a.heads + kvh * group + g) * a.splits + split) * 2;
-            ml[0] = m;
-            ml[1] = l;
-        }
-    }
-    __syncthreads();
-    SM_STAMP(3);
+    float o_acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
 
-    // weighted values: a thread owns 8 neighbouring dims (16 bytes) of the rows of its key
-    // group; the groups take keys in turn, four loads in flight each
-    const int cpr = hd / 8;                       // 16-byte chunks per row
-    const int key_groups = kThreads / cpr;        // hd <= 256 -> at least 4
-    const int kg = tid / cpr, ch = tid - kg * cpr;
-    const int first = lo - c0, last = hi - c0;
-    for (int g0 = 0; g0 < group; g0 += kHeadPass) {
-        float acc[kHeadPass][8];
-#pragma unroll
-        for (int g = 0; g < kHeadPass; ++g)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
-        if (kg < key_groups) {
-            for (int j0 = first + kg; j0 <= last; j0 += 8 * key_groups) {
-                uint4 raw[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int j = j0 + u * key_groups;
-                    raw[u] = j <= last ? *reinterpret_cast<const uint4*>(a.v_pool + rows[j] + 8 * ch) : make_uint4(0, 0, 0, 0);
-                }
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int j = j0 + u * key_groups;
-                    if (j > last) break;
-                    float v[8];
-                    unpack8(raw[u], v);
-#pragma unroll
-                    for (int g = 0; g < kHeadPass; ++g) {
-                        if (g0 + g < group) {
-                            const float w = sc[(g0 + g) * kChunk + j];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(w, v[e], acc[g][e]);
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < kHeadPass; ++g)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) red[((size_t)kg * kHeadPass + g) * hd + 8 * ch + e] = acc[g][e];
+    if (tile < n_tiles) {
+        load_k(off);
+        load_v(off, 0);
+    }
+    int buf = 0;
+    for (; tile < n_tiles; tile += kWarps, buf ^= 1) {
+        const int next = tile + kWarps;
+        const bool has_next = next < n_tiles;
+        unsigned long long next_off = ~0ull;
+        if (has_next) {
+            next_off = tile_offset(next);
+            __syncwarp();                 // the other buffer was read in the previous iteration
+            load_v(next_off, buf ^ 1);
         }
-        __syncthreads();
-        for (int i = tid; i < kHeadPass * hd; i += kThreads) {
-            int g = i / hd, d = i - g * hd;
-            if (g0 + g < group) {
-                float sum = 0.f;
-                for (int k = 0; k < key_groups; ++k) sum += red[((size_t)k * kHeadPass + g) * hd + d];
-                a.part_o[(((size_t)b * a.heads + kvh * group + g0 + g) * a.splits + split) * hd + d] = sum;
+        // S = Q K^T: 16 heads x 32 keys
+        float s[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int kb = 0; kb < HDB; ++kb) {
+                mma_bf16(s[j], qa[kb].x, qb[kb].x, qa[kb].y, qb[kb].y, kf[j][kb].x, kf[j][kb].y);
+                mma_bf16(s[j], qa[kb].z, qb[kb].z, qa[kb].w, qb[kb].w, kf[j][kb].z, kf[j][kb].w);
             }
         }
-        __syncthreads();
-    }
-
-    SM_STAMP(4);
-    // the last CTA of this (sequence, kv head) merges the chunks
-    const int s_lo = start / kChunk, s_hi = pos / kChunk, n_active = s_hi - s_lo + 1;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        int* counter = a.counters + b * a.kv_heads + kvh;
-        int arrived = atomicAdd(counter, 1);
-        is_last = arrived == n_active - 1;
-        if (is_last) *counter = 0;
-    }
-    __syncthreads();
-    SM_STAMP(5);
-    if (!is_last) return;
-    __threadfence();
-    SM_STAMP(10);
-    float* my_w = wts + (size_t)warp * a.splits;
-    for (int g = warp; g < group; g += kThreads / 32) {
-        const size_t head = (size_t)b * a.heads + kvh * group + g;
-        const float* ml = a.part_ml + head * a.splits * 2;
-        const float* po = a.part_o + head * a.splits * hd;
-        float m = -CUDART_INF_F;
-        for (int s = s_lo + lane; s <= s_hi; s += 32) m = fmaxf(m, __ldcg(ml + 2 * s));
-        m = warp_max(m);
-        float l = 0.f;
-        for (int s = s_lo + lane; s <= s_hi; s += 32) {
-            float w = expf(__ldcg(ml + 2 * s) - m);
-            my_w[s - s_lo] = w;
-            l = fmaf(__ldcg(ml + 2 * s + 1), w, l);
+        if (has_next) load_k(next_off);   // the key registers are free again
+        // scale, mask the keys beyond this CTA's range, running maximum
+        const int kbase = cta_lo + tile * kTile;
+        float mx0 = m0, mx1 = m1;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = kbase + j * 8 + q4 * 2 + (e & 1);
+                const float x = key < cta_hi ? s[j][e] * a.scale_log2 : -CUDART_INF_F;
+                s[j][e] = x;
+                if (e & 2) mx1 = fmaxf(mx1, x); else mx0 = fmaxf(mx0, x);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float c0 = exp2f(m0 - mx0), c1 = exp2f(m1 - mx1);   // a tile always holds a visible key: mx is finite
+        m0 = mx0;
+        m1 = mx1;
+        uint32_t pf[2][4];
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float p0 = exp2f(s[j][0] - mx0), p1 = exp2f(s[j][1] - mx0);
+            const float p2 = exp2f(s[j][2] - mx1), p3 = exp2f(s[j][3] - mx1);
+            sum0 += p0 + p1;
+            sum1 += p2 + p3;
+            pf[j / 2][(j & 1) * 2] = pack_bf16(p0, p1);
+            pf[j / 2][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
         }
-        l = warp_sum(l);
+        l0 = l0 * c0 + sum0;
+        l1 = l1 * c1 + sum1;
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            o_acc[i][0] *= c0; o_acc[i][1] *= c0; o_acc[i][2] *= c1; o_acc[i][3] *= c1;
+        }
+        if (has_next) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncwarp();
-        SM_STAMP(11);
-        float acc[kMaxHeadDim / 32];
+        const __nv_bfloat16* vb = vs + (size_t)buf * kTile * LDV;
 #pragma unroll
-        for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
-        for (int s0 = s_lo; s0 <= s_hi; s0 += 16) {
-            // sixteen chunks' partial results in flight per dim, then the sums in chunk order
+        for (int jj = 0; jj < 2; ++jj)
 #pragma unroll
-            for (int i = 0; i < kMaxHeadDim / 32; ++i) {
-                const int d = lane + 32 * i;
-                if (d >= hd) break;
-                float v[16];
+            for (int i = 0; i < NT; ++i) {
+                uint32_t b0, b1;
+                ldmatrix_x2_trans(b0, b1, vb + (size_t)(jj * 16 + (lane & 15)) * LDV + i * 8);
+                mma_bf16(o_acc[i], pf[jj][0], pf[jj][1], pf[jj][2], pf[jj][3], b0, b1);
+            }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // ---- the warps of this CTA, through shared memory (the value buffers are free now) -------
+    __syncthreads();
+    float* wm = reinterpret_cast<float*>(smem_raw);          // [kWarps][16] maxima
+    float* wl = wm + kWarps * 16;                            // [kWarps][16] sums
+    float* wo = wl + kWarps * 16;                            // [kWarps][16][HDP] weighted values
+    // [cluster][group][HDP + 2], the leader's copy is used. It lies behind everything a CTA uses
+    // for itself: other CTAs write here while this one may still be in its loop.
+    constexpr size_t kLoopBytes = (size_t)kWarps * 2 * kTile * LDV * sizeof(__nv_bfloat16);
+    constexpr size_t kLocalBytes = ((size_t)kWarps * 32 + (size_t)kWarps * 16 * HDP) * sizeof(float);
+    float* part = reinterpret_cast<float*>(smem_raw + (kLoopBytes > kLocalBytes ? kLoopBytes : kLocalBytes));
+    if (q4 == 0) {
+        wm[warp * 16 + g] = m0; wm[warp * 16 + g + 8] = m1;
+        wl[warp * 16 + g] = l0; wl[warp * 16 + g + 8] = l1;
+    }
 #pragma unroll
-                for (int u = 0; u < 16; ++u) v[u] = s0 + u <= s_hi ? __ldcg(po + (size_t)(s0 + u) * hd + d) : 0.f;
+    for (int i = 0; i < NT; ++i) {
+        float* r0 = wo + ((size_t)warp * 16 + g) * HDP + i * 8 + q4 * 2;
+        float* r1 = wo + ((size_t)warp * 16 + g + 8) * HDP + i * 8 + q4 * 2;
+        r0[0] = o_acc[i][0]; r0[1] = o_acc[i][1];
+        r1[0] = o_acc[i][2]; r1[1] = o_acc[i][3];
+    }
+    __syncthreads();
+    const int pstride = HDP + 2;
+    float* dst = a.cluster > 1 ? cluster.map_shared_rank(part, 0) : part;
+    for (int idx = threadIdx.x; idx < group * HDP; idx += kThreads) {
+        const int r = idx / HDP, d = idx - r * HDP;
+        float m = -CUDART_INF_F;
 #pragma unroll
-                for (int u = 0; u < 16; ++u)
-                    if (s0 + u <= s_hi) acc[i] = fmaf(v[u], my_w[s0 + u - s_lo], acc[i]);
+        for (int w = 0; w < kWarps; ++w) m = fmaxf(m, wm[w * 16 + r]);
+        float l = 0.f, o = 0.f;
+        if (m != -CUDART_INF_F) {
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float f = exp2f(wm[w * 16 + r] - m);   // a warp without tiles: exp2(-inf) = 0
+                l = fmaf(wl[w * 16 + r], f, l);
+                o = fmaf(wo[((size_t)w * 16 + r) * HDP + d], f, o);
             }
         }
-        const float inv = 1.0f / l;
-        __nv_bfloat16* o = a.out + head * hd;
-#pragma unroll
-        for (int i = 0; i < kMaxHeadDim / 32; ++i) {
-            int d = lane + 32 * i;
-            if (d < hd) o[d] = __float2bfloat16_rn(acc[i] * inv);
-        }
-        __syncwarp();
-        SM_STAMP(12);
+        float* p = dst + ((size_t)rank * group + r) * pstride;
+        p[2 + d] = o;
+        if (d == 0) { p[0] = m; p[1] = l; }
     }
+    if (a.cluster > 1) {
+        cluster.sync();
+        if (rank != 0) return;
+    } else {
+        __syncthreads();
+    }
+    // ---- the CTAs of the cluster, in rank order ---------------------------------------------------
+    for (int idx = threadIdx.x; idx < group * hd; idx += kThreads) {
+        const int r = idx / hd, d = idx - r * hd;
+        float m = -CUDART_INF_F;
+        for (int c = 0; c < a.cluster; ++c) m = fmaxf(m, part[((size_t)c * group + r) * pstride]);
+        float l = 0.f, o = 0.f;
+        for (int c = 0; c < a.cluster; ++c) {
+            const float* p = part + ((size_t)c * group + r) * pstride;
+            const float f = exp2f(p[0] - m);   // a CTA without keys: exp2(-inf) = 0
+            l = fmaf(p[1], f, l);
+            o = fmaf(p[2 + d], f, o);
+        }
+        a.out[((size_t)b * a.heads + (size_t)kvh * group + r) * hd + d] = __float2bfloat16_rn(o / l);
+    }
+}
+
+template <int HDB>
+void launch(const DecodeArgs& a, cudaStream_t stream) {
+    constexpr int HDP = HDB * 32, LDV = HDP + 8;
+    const int group = a.heads / a.kv_heads;
+    const size_t loop_bytes = (size_t)kWarps * 2 * kTile * LDV * sizeof(__nv_bfloat16);
+    const size_t local_bytes = ((size_t)kWarps * 32 + (size_t)kWarps * 16 * HDP) * sizeof(float);
+    const size_t smem = (loop_bytes > local_bytes ? loop_bytes : local_bytes) +
+                        (size_t)a.cluster * group * (HDP + 2) * sizeof(float);
+    auto kernel = decode_attention_kernel<HDB>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) throw std::runtime_error(std::string("attention_decode: ") + cudaGetErrorString(e));
+    }
+    launch_kernel("attention_decode", kernel, dim3(a.cluster, a.kv_heads, a.B), dim3(kThreads), smem, stream, a.cluster,
+                  dependent_launch_enabled(), a);
 }
 
 }  // namespace
 
-int attention_decode_splits(int max_len) { return (max_len + kChunk - 1) / kChunk; }
-
-size_t attention_decode_workspace_floats(int B, int heads, int head_dim, int splits) {
-    return (size_t)B * heads * splits * (head_dim + 2);
+bool attention_decode_supports(int heads, int kv_heads, int head_dim) {
+    return head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128 && kv_heads > 0 && heads % kv_heads == 0 &&
+           heads / kv_heads <= 16;
 }
 
 void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
                       const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
-                      const int32_t* page_table, int table_stride, int ring, int splits, float* workspace,
-                      int* counters, cudaStream_t stream) {
+                      const int32_t* page_table, int table_stride, int ring, int max_len, cudaStream_t stream) {
     if (B <= 0) return;
-    if (head_dim % 8 || head_dim <= 0 || head_dim > kMaxHeadDim)
-        throw std::invalid_argument("attention_decode: head_dim " + std::to_string(head_dim) +
-                                    " must be a multiple of 8 between 8 and 256");
-    if (heads % kv_heads) throw std::invalid_argument("attention_decode: kv_heads must divide heads");
-    if (splits <= 0 || splits > 65535) throw std::invalid_argument("attention_decode: splits out of range");
-    int group = heads / kv_heads;
-    int key_groups = kThreads / (head_dim / 8);
-    size_t smem = (size_t)group * head_dim * 4 + (size_t)group * kChunk * 4 + kChunk * 8 +
-                  (size_t)key_groups * kHeadPass * head_dim * 4 + (size_t)(kThreads / 32) * splits * 4;
-    if (B * kv_heads > 65536) throw std::invalid_argument("attention_decode: more than 65536 (sequence, kv head) pairs");
-    if (smem > 200 * 1024)
-        throw std::invalid_argument("attention_decode: " + std::to_string(group) + " heads per kv head with head_dim " +
-                                    std::to_string(head_dim) + " need more shared memory than one SM has");
-    DecodeArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
-                 (const __nv_bfloat16*)v_pool, page_table, table_stride, ring, slots, positions,
-                 B, heads, kv_heads, head_dim, window, splits, scale,
-                 workspace, workspace + (size_t)B * heads * splits * head_dim, counters};
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (!attention_decode_supports(heads, kv_heads, head_dim))
+        throw std::invalid_argument("attention_decode: head_dim " + std::to_string(head_dim) + " with " +
+                                    std::to_string(heads) + "/" + std::to_string(kv_heads) +
+                                    " heads is outside this kernel (multiples of 16 up to 128, at most 16 heads per "
+                                    "kv head); the plain kernel takes it");
+    if (B > 65535 || kv_heads > 65535) throw std::invalid_argument("attention_decode: more than 65535 sequences or kv heads");
+    // CTAs per (sequence, kv head): fill the machine, but give every warp of every CTA a tile
+    const int visible = window > 0 && window < max_len ? window : max_len;
+    int cluster = 1;
+    while (cluster < kMaxCluster && B * kv_heads * cluster < 296 && visible > cluster * kWarps * kTile) cluster *= 2;
+    DecodeArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
+                 page_table, table_stride, ring, slots, positions, B, heads, kv_heads, head_dim, window, cluster,
+                 scale * 1.4426950408889634f};
     note_launch();
-    dim3 grid(kv_heads, B, splits);
-    launch_kernel("attention_decode", decode_partial_kernel, grid, dim3(kThreads), smem, stream, 1,
-                  dependent_launch_enabled(), a);
+    switch ((head_dim + 31) / 32) {
+        case 1: launch<1>(a, stream); break;
+        case 2: launch<2>(a, stream); break;
+        case 3: launch<3>(a, stream); break;
+        default: launch<4>(a, stream); break;
+    }
 }
 
 }  // namespace sm

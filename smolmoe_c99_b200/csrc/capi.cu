@@ -140,19 +140,17 @@ SM_API int sm_attention_prefill(const void* q, const void* k, const void* v, voi
     });
 }
 
-SM_API int sm_attention_decode_splits(int max_len) { return sm::attention_decode_splits(max_len); }
-
-SM_API long long sm_attention_decode_workspace_floats(int B, int heads, int head_dim, int splits) {
-    return (long long)sm::attention_decode_workspace_floats(B, heads, head_dim, splits);
+SM_API int sm_attention_decode_supports(int heads, int kv_heads, int head_dim) {
+    return sm::attention_decode_supports(heads, kv_heads, head_dim) ? 1 : 0;
 }
 
 SM_API int sm_attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale,
                                int window, const int32_t* positions, const int32_t* slots, const void* k_pool,
-                               const void* v_pool, const int32_t* page_table, int table_stride, int ring, int splits,
-                               float* workspace, int* counters, void* stream) {
+                               const void* v_pool, const int32_t* page_table, int table_stride, int ring, int max_len,
+                               void* stream) {
     return guarded([&] {
         sm::attention_decode(q, out, B, heads, kv_heads, head_dim, scale, window, positions, slots, k_pool, v_pool,
-                             page_table, table_stride, ring, splits, workspace, counters, (cudaStream_t)stream);
+                             page_table, table_stride, ring, max_len, (cudaStream_t)stream);
     });
 }
 

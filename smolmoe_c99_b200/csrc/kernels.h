@@ -131,16 +131,14 @@ void attention_prefill(const void* q, const void* k, const void* v, void* out, c
                        int heads, int kv_heads, int head_dim, float scale, int window, cudaStream_t stream);
 
 // ---- attention_decode.cu --------------------------------------------------------------
-// One new token per sequence over the paged cache for bfloat16, split along the positions
-// in chunks; `splits` = attention_decode_splits(longest sequence), the workspace holds
-// attention_decode_workspace_floats() floats, and `counters` holds B * kv_heads ints that are
-// zero before the first launch (the kernel leaves them zero).
-int attention_decode_splits(int max_len);
-size_t attention_decode_workspace_floats(int B, int heads, int head_dim, int splits);
+// One new token per sequence over the paged cache for bfloat16: a cluster of CTAs per
+// (sequence, kv head) splits the visible positions and merges through distributed shared
+// memory; no workspace. `max_len` (the longest sequence of the batch, or a bound of it) only
+// sizes the clusters. head_dim: multiples of 16 up to 128; at most 16 heads per kv head.
+bool attention_decode_supports(int heads, int kv_heads, int head_dim);
 void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
                       const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
-                      const int32_t* page_table, int table_stride, int ring, int splits, float* workspace,
-                      int* counters, cudaStream_t stream);
+                      const int32_t* page_table, int table_stride, int ring, int max_len, cudaStream_t stream);
 
 // ---- sampling.cu ----------------------------------------------------------------------
 // out[b] = argmax over the allowed ids of logits[b, :], the lowest id on ties

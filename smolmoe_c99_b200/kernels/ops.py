@@ -73,13 +73,10 @@ class Ops:
             raise KernelError("no CUDA device: this library runs on an NVIDIA B200 only (no CPU fallback)")
         self.lib = load_library()
         self.lib.sm_gemm_tc_workspace_bytes.restype = ctypes.c_longlong
-        self.lib.sm_attention_decode_workspace_floats.restype = ctypes.c_longlong
         self.lib.sm_launch_count.restype = ctypes.c_longlong
         self.use_tensor_cores = True  # False routes bfloat16 products to the CUDA-core kernel
         self.use_fast_attention = True  # False routes bfloat16 attention to the plain kernel
         self.use_skinny = True  # False routes products over a handful of tokens to the general kernels
-        # arrival counters of the decode attention kernel: zero between launches
-        self.decode_counters = torch.zeros(65536, dtype=torch.int32, device="cuda")
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
         # scratch of the greedy choice: one word per row, all ones when idle, and arrival counters
         self.argmax_scratch = torch.full((4096,), -1, dtype=torch.int64, device="cuda")
@@ -213,6 +210,8 @@ class Ops:
                 return False
         elif x.dtype != torch.bfloat16:
             return False
+        if w.shape[0] > 32768 and self.use_tensor_cores and self.lib.sm_gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1]):
+            return False   # the output head: thousands of row tiles, where the tcgen05 kernel streams better
         return bool(self.lib.sm_gemm_skinny_supports(x.shape[0], w.shape[0], x.shape[1]))
 
     def gemm_skinny(self, x, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int = 0,
@@ -332,7 +331,8 @@ class Ops:
 
     def attention_cached(self, q, step, scale, window, cache, kv_heads):
         """Attention of this step's tokens over the keys and values in the cache."""
-        if self.use_fast_attention and q.dtype == torch.bfloat16 and step.mode == "decode":
+        if (self.use_fast_attention and q.dtype == torch.bfloat16 and step.mode == "decode"
+                and self.lib.sm_attention_decode_supports(q.shape[1], kv_heads, q.shape[2])):
             return self.attention_decode(q, step.positions, step.slot_ids, scale, window, cache.k_pool, cache.v_pool,
                                          cache.page_table, cache.ring, kv_heads, step.max_seq_len)
         return self.attention_plain(q, step.positions, scale, window, k_pool=cache.k_pool, v_pool=cache.v_pool,
@@ -348,14 +348,10 @@ class Ops:
         _need(k_pool, "key pool", torch.bfloat16)
         _need(v_pool, "value pool", torch.bfloat16)
         _need(page_table, "page table", torch.int32, 2)
-        splits = int(self.lib.sm_attention_decode_splits(int(max_len)))
-        floats = int(self.lib.sm_attention_decode_workspace_floats(B, heads, head_dim, splits))
-        workspace = torch.empty((floats,), dtype=torch.float32, device=q.device)
         out = torch.empty_like(q)
         self._check(self.lib.sm_attention_decode(
             _ptr(q), _ptr(out), B, heads, kv_heads, head_dim, ctypes.c_float(scale), int(window or 0), _ptr(positions),
-            _ptr(slots), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), page_table.shape[1], ring, splits,
-            _ptr(workspace), _ptr(self.decode_counters), _stream()))
+            _ptr(slots), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), page_table.shape[1], ring, int(max_len), _stream()))
         return out
 
     # ---- sampling ----------------------------------------------------------------------

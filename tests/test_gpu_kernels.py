@@ -138,7 +138,8 @@ def test_prefill_attention_finds_a_far_key(ops):
     assert float((got_w1[n - 1, 0] - v[far, 0].float()).abs().max()) <= 2e-2
 
 
-@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (5, 5, 48), (14, 2, 64), (9, 1, 128), (4, 2, 256)])
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (5, 5, 48), (14, 2, 64), (9, 1, 128), (16, 1, 80),
+                                               (4, 2, 256)])
 @pytest.mark.parametrize("window", [None, 100])
 def test_decode_attention_over_pages(ops, heads, kv_heads, hd, window):
     """Sequences of unequal lengths in scattered pages; the windowed case uses a ring."""
@@ -169,15 +170,23 @@ def test_decode_attention_over_pages(ops, heads, kv_heads, hd, window):
     scale = 1.0 / math.sqrt(hd)
     positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
     slot_ids = torch.tensor(slots, dtype=torch.int32).cuda()
-    got = ops.attention_decode(q, positions, slot_ids, scale, window, k_pool.cuda(), v_pool.cuda(), table.cuda(), ring,
-                               kv_heads, max(lens)).float().cpu()
+    if hd > 128:
+        from smolmoe_c99_b200.kernels import KernelError
+        with pytest.raises(KernelError, match="outside this kernel"):   # refused, not wrong: the plain kernel takes it
+            ops.attention_decode(q, positions, slot_ids, scale, window, k_pool.cuda(), v_pool.cuda(), table.cuda(), ring,
+                                 kv_heads, max(lens))
+        got = None
+    else:
+        got = ops.attention_decode(q, positions, slot_ids, scale, window, k_pool.cuda(), v_pool.cuda(), table.cuda(), ring,
+                                   kv_heads, max(lens)).float().cpu()
     plain = ops.attention_plain(q, positions, scale, window, k_pool=k_pool.cuda(), v_pool=v_pool.cuda(),
                                 page_table=table.cuda(), ring=ring, token_slot=slot_ids, kv_heads=kv_heads).float().cpu()
     for b, n in enumerate(lens):
         qq = torch.zeros((n, heads, hd), dtype=torch.bfloat16)
         qq[n - 1] = q[b].cpu()
         want = _plain_attention(qq, ks[b], vs[b], [n], window, scale)[n - 1]
-        assert float((got[b] - want).abs().max()) <= 1e-2, f"split kernel, sequence {b}"
+        if got is not None:
+            assert float((got[b] - want).abs().max()) <= 1e-2, f"cluster kernel, sequence {b}"
         assert float((plain[b] - want).abs().max()) <= 1e-2, f"plain kernel, sequence {b}"
 
 
