@@ -54,11 +54,16 @@ class _DecodeGraph:
     def capture(self, engine: "Engine") -> None:
         """``meta`` must already hold a real step: the run before the capture loads kernels and
         sets function attributes, and it writes the same keys and values the replay will."""
+        # Keys and values are written twice with the same numbers, which is harmless; a state of
+        # fixed size would be advanced twice, so it is put back after the run.
+        saved = [s.clone() for s in engine.cache.states]
         side = torch.cuda.Stream(device=engine.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             engine.model.forward(self.batch, engine.cache, self.rows, engine._status)
         torch.cuda.current_stream().wait_stream(side)
+        for state, before in zip(engine.cache.states, saved):
+            state.copy_(before)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.logits = engine.model.forward(self.batch, engine.cache, self.rows, engine._status)
