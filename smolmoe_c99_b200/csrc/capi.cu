@@ -44,6 +44,11 @@ bool dependent_launch_enabled() { return g_dependent_launch.load(std::memory_ord
 void set_dependent_launch(bool on) { g_dependent_launch.store(on, std::memory_order_relaxed); }
 }  // namespace sm
 
+namespace sm {
+// For entry points that live in other files and report through the same message channel.
+void set_last_error(const std::string& message) { g_last_error = message; }
+}  // namespace sm
+
 #define SM_API extern "C" __attribute__((visibility("default")))
 
 SM_API const char* sm_last_error() { return g_last_error.c_str(); }
