@@ -16,7 +16,6 @@ import json
 import os
 import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -51,36 +50,40 @@ def peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
-class ClockSampler(threading.Thread):
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+class ClockSampler:
+    """Samples SM clocks and throttle reasons while the timed region runs: one nvidia-smi
+    process that prints a line every 100 ms, started before the region and stopped after it."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
-        super().__init__(daemon=True)
-        self.samples, self.stop_flag = [], threading.Event()
+        self.proc = None
 
-    def run(self):
-        while not self.stop_flag.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits"],
-                                     capture_output=True, text=True, timeout=5).stdout.strip().splitlines()
-                if out:
-                    self.samples.append([c.strip() for c in out[0].split(",")])
-            except Exception:
-                pass
-            self.stop_flag.wait(0.2)
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            time.sleep(0.3)   # the first line is out before the timed region begins
+        except OSError:
+            self.proc = None
 
     def summary(self):
-        self.stop_flag.set()
-        self.join(timeout=6)
-        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        samples = []
+        if self.proc is not None:
+            self.proc.terminate()   # the exact process started above
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+                out, _ = self.proc.communicate()
+            samples = [[c.strip() for c in line.split(",")] for line in out.strip().splitlines() if line.count(",") >= 5]
+        mhz = sorted(int(s[0]) for s in samples if s[0].isdigit())
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2:6]) if v.lower().startswith("active")})
+        reasons = sorted({n for s in samples for n, v in zip(names, s[2:6]) if v.lower().startswith("active")})
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
-                "sm_max_mhz": int(self.samples[0][1]) if self.samples and self.samples[0][1].isdigit() else None,
-                "reasons": reasons, "samples": len(self.samples)}
+                "sm_max_mhz": int(samples[0][1]) if samples and samples[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(samples)}
 
 
 def prefill_flops(cfg, T):
@@ -113,8 +116,8 @@ def decode_tokens_per_second(engine, slots, steps, warmup):
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
