@@ -4,15 +4,19 @@
 //
 // The weight rows are the M side of the instruction (128 output features a tile, one per
 // TMEM lane) and the tokens are the N side (16..256 a tile), so the same kernel serves
-// prefill (many tokens) and decode (a handful): with few tokens the instruction shrinks
-// instead of wasting a 128-row tile on them. One CTA computes one 128 x TN tile over a range
-// of K; when K is split over several CTAs the partial sums go to a workspace and a second
-// kernel adds them in split order and applies the epilogue.
+// prefill (many tokens) and decode batches too large for the weight-streaming kernel: with
+// few tokens the instruction shrinks instead of wasting a 128-row tile on them.
 //
-// Roles (192 threads): warp 0 issues the TMA loads, warp 1 allocates tensor memory and
-// issues the MMAs, warps 2-5 read the accumulator back (each its own quarter of the lanes)
-// and write the result. Epilogues: store (+bias), add into a float residual, or
-// act(gate) * up from two accumulators.
+// The kernel is persistent: one CTA per SM takes work units (a 128 x TN tile over a range of
+// K) round-robin. Roles (192 threads): warp 0 issues the TMA loads into a ring of stages,
+// warp 1 allocates tensor memory and issues the MMAs, warps 2-5 are the epilogue (each its
+// own quarter of the TMEM lanes). Tensor memory holds TWO accumulators, so the MMAs of the
+// next unit run while the epilogue drains the previous one. The epilogue reads 32 tokens at a
+// time with tcgen05.ld, applies bias / SwiGLU, transposes through shared memory and hands the
+// chunk to TMA: a bulk tensor store, or a bulk tensor float add for "+= into the residual"
+// (TMA drops what lies outside the matrix, so ragged edges need no code). Outputs whose rows
+// TMA cannot address, and the partial sums of a split K, are written by the threads directly;
+// split partial sums go to a workspace and a second kernel adds them in split order.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in *error and
 // the CTA drains and leaves without writing.
@@ -35,7 +39,7 @@ constexpr int kTileM = 128;          // output features per CTA
 constexpr int kBlockK = 64;          // bf16 elements per 128-byte swizzled row
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 22;
 
 enum Epilogue : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
 
@@ -54,6 +58,9 @@ struct GemmParams {
     int out_dt;
     float* workspace;         // [splits, T, N] for EPI_PARTIAL
     int* error;
+    int tiles_m, tiles_t;     // tile grid: 128 features x tile_n tokens
+    int units;                // tiles_m * tiles_t * splits work units, shared out round-robin
+    int tma_out;              // the epilogue leaves through shared memory and TMA (store or add)
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------
@@ -132,33 +139,78 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
 __device__ __forceinline__ uint32_t instr_desc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Output tile from shared memory to global memory by TMA: plain store, or float add.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(smem_u32(src)) : "memory");
+}
+__device__ __forceinline__ void tma_add_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(smem_u32(src)) : "memory");
+}
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+constexpr int kChunk = 32;                                  // tokens per epilogue chunk
+constexpr int kStagingBytes = kChunk * kTileM * 4;          // one staged chunk (float)
+
+// Which tile and K range a work unit is: units that run side by side share the token tile.
+struct Unit {
+    int n0, t0, kb_begin, kb_end, split;
+};
+__device__ __forceinline__ Unit unit_of(const GemmParams& p, int u) {
+    const int tm = u % p.tiles_m, rest = u / p.tiles_m, tt = rest % p.tiles_t, split = rest / p.tiles_t;
+    const int kb_total = (p.K + kBlockK - 1) / kBlockK;
+    Unit r;
+    r.n0 = tm * kTileM;
+    r.t0 = tt * p.tile_n;
+    r.split = split;
+    r.kb_begin = split * p.kblocks_per_split;
+    r.kb_end = min(kb_total, r.kb_begin + p.kblocks_per_split);
+    return r;
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const __grid_constant__ CUtensorMap map_out, GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles is what the swizzle pattern assumes
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int a_bytes = kTileM * kBlockK * 2 * (p.dual ? 2 : 1);
     const int b_bytes = p.tile_n * kBlockK * 2;
     const int stage_bytes = a_bytes + b_bytes;
-    uint64_t* full_bar = (uint64_t*)(smem + (size_t)p.stages * stage_bytes);
+    uint8_t* staging = smem + (size_t)p.stages * stage_bytes;                 // 2 x kStagingBytes
+    uint64_t* full_bar = (uint64_t*)(staging + 2 * kStagingBytes);
     uint64_t* empty_bar = full_bar + p.stages;
-    uint64_t* tmem_full_bar = empty_bar + p.stages;
-    uint32_t* tmem_slot = (uint32_t*)(tmem_full_bar + 1);
-    int* failed = (int*)(tmem_slot + 1);
+    uint64_t* tfull_bar = empty_bar + p.stages;       // [2] accumulator complete
+    uint64_t* tempty_bar = tfull_bar + 2;             // [2] accumulator drained
+    uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+    volatile int* failed = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kTileM, t0 = blockIdx.y * p.tile_n, split = blockIdx.z;
-    const int kb_total = (p.K + kBlockK - 1) / kBlockK;
-    const int kb_begin = split * p.kblocks_per_split;
-    const int kb_end = min(kb_total, kb_begin + p.kblocks_per_split);
-    const int n_kb = kb_end - kb_begin;   // >= 1 by construction of the grid
+    const int buf_cols = p.tile_n * (p.dual ? 2 : 1);
     uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < p.tile_n * (p.dual ? 2 : 1)) tmem_cols <<= 1;
+    while ((int)tmem_cols < 2 * buf_cols) tmem_cols <<= 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(tmem_full_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -170,85 +222,140 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
-                int s = i % p.stages;
-                uint32_t phase = (uint32_t)(i / p.stages) & 1u;
-                if (!mbar_wait(&empty_bar[s], phase ^ 1u)) { *failed = 1; atomicExch(p.error, 1); break; }
-                uint8_t* a = smem + (size_t)s * stage_bytes;
-                mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
-                int k = (kb_begin + i) * kBlockK;
-                tma_load_2d(a, &map_w, k, n0, &full_bar[s]);
-                if (p.dual) tma_load_2d(a + kTileM * kBlockK * 2, &map_w, k, p.up_offset + n0, &full_bar[s]);
-                tma_load_2d(a + a_bytes, &map_x, k, t0, &full_bar[s]);
+            uint32_t it = 0;
+            for (int u = blockIdx.x; u < p.units && !*failed; u += gridDim.x) {
+                const Unit w = unit_of(p, u);
+                for (int kb = w.kb_begin; kb < w.kb_end; ++kb, ++it) {
+                    const int s = it % p.stages;
+                    const uint32_t phase = (it / p.stages) & 1u;
+                    if (!mbar_wait(&empty_bar[s], phase ^ 1u)) { *failed = 1; atomicExch(p.error, 1); break; }
+                    uint8_t* a = smem + (size_t)s * stage_bytes;
+                    mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
+                    const int k = kb * kBlockK;
+                    tma_load_2d(a, &map_w, k, w.n0, &full_bar[s]);
+                    if (p.dual) tma_load_2d(a + kTileM * kBlockK * 2, &map_w, k, p.up_offset + w.n0, &full_bar[s]);
+                    tma_load_2d(a + a_bytes, &map_x, k, w.t0, &full_bar[s]);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(kTileM, p.tile_n);
-            bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                int s = i % p.stages;
-                uint32_t phase = (uint32_t)(i / p.stages) & 1u;
-                if (!mbar_wait(&full_bar[s], phase)) { *failed = 1; atomicExch(p.error, 2); ok = false; break; }
+            uint32_t it = 0;
+            int i = 0;
+            for (int u = blockIdx.x; u < p.units && !*failed; u += gridDim.x, ++i) {
+                const Unit w = unit_of(p, u);
+                const int b = i & 1;
+                // the epilogue has drained this accumulator (its first use is free)
+                if (!mbar_wait(&tempty_bar[b], (((uint32_t)i >> 1) & 1u) ^ 1u)) { *failed = 1; atomicExch(p.error, 4); break; }
                 tc_fence_after();
-                uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
-                uint32_t b_addr = a_addr + a_bytes;
-                uint64_t da = smem_desc(a_addr), db = smem_desc(b_addr);
-                uint64_t du = smem_desc(a_addr + kTileM * kBlockK * 2);
+                const uint32_t d = tmem_base + (uint32_t)(b * buf_cols);
+                for (int kb = w.kb_begin; kb < w.kb_end; ++kb, ++it) {
+                    const int s = it % p.stages;
+                    const uint32_t phase = (it / p.stages) & 1u;
+                    if (!mbar_wait(&full_bar[s], phase)) { *failed = 1; atomicExch(p.error, 2); break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+                    const uint32_t b_addr = a_addr + a_bytes;
+                    const uint64_t da = smem_desc(a_addr), db = smem_desc(b_addr);
+                    const uint64_t du = smem_desc(a_addr + kTileM * kBlockK * 2);
 #pragma unroll
-                for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                    uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-                    uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);   // 32 bytes a step inside the swizzled row
-                    umma_bf16(tmem_base, da + step, db + step, idesc, acc);
-                    if (p.dual) umma_bf16(tmem_base + (uint32_t)p.tile_n, du + step, db + step, idesc, acc);
+                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                        const uint32_t acc = (kb > w.kb_begin || k > 0) ? 1u : 0u;
+                        const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);   // 32 bytes a step inside the swizzled row
+                        umma_bf16(d, da + step, db + step, idesc, acc);
+                        if (p.dual) umma_bf16(d + (uint32_t)p.tile_n, du + step, db + step, idesc, acc);
+                    }
+                    umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
                 }
-                umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
+                umma_commit(&tfull_bar[b]);        // the accumulator is complete once all MMAs are done
             }
-            umma_commit(tmem_full_bar);        // the accumulator is complete once all MMAs are done
         }
     } else {
-        // epilogue warps 2..5: TMEM lanes of quarter (warp % 4)
+        // epilogue warps 2..5: TMEM lanes of quarter (warp % 4); one output feature per thread
         const int quarter = warp & 3;
-        const int n = n0 + quarter * 32 + lane;
-        bool ok = mbar_wait(tmem_full_bar, 0);
-        if (!ok && lane == 0) { *failed = 1; atomicExch(p.error, 3); }
-        ok = ok && (*(volatile int*)failed == 0);
-        ok = __all_sync(0xffffffffu, ok);
-        tc_fence_after();
-        if (ok) {
-            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const bool issuer = warp == 2 && lane == 0;
+        int i = 0;
+        uint32_t chunk_count = 0;
+        for (int u = blockIdx.x; u < p.units; u += gridDim.x, ++i) {
+            const Unit w = unit_of(p, u);
+            const int b = i & 1;
+            bool ok = mbar_wait(&tfull_bar[b], ((uint32_t)i >> 1) & 1u);
+            if (!ok && lane == 0) { *failed = 1; atomicExch(p.error, 3); }
+            ok = __all_sync(0xffffffffu, ok && *failed == 0);
+            if (!ok) break;
+            tc_fence_after();
+            const int n = w.n0 + quarter * 32 + lane;
+            const uint32_t acc_addr = tmem_base + (uint32_t)(b * buf_cols) + ((uint32_t)(quarter * 32) << 16);
             float bias_v = 0.f;
             if (p.bias && n < p.N)
                 bias_v = p.bias_dt == F32 ? ((const float*)p.bias)[n] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
-            for (int c0 = 0; c0 < p.tile_n; c0 += 16) {
-                if (t0 + c0 >= p.T) break;   // the same for the whole warp
-                float g[16], u[16];
-                tmem_ld16(lane_base + (uint32_t)c0, g);
-                if (p.dual) tmem_ld16(lane_base + (uint32_t)(p.tile_n + c0), u);
-                if (n >= p.N) continue;
+            if (p.tma_out) {
+                for (int c0 = 0; c0 < p.tile_n; c0 += kChunk, ++chunk_count) {
+                    if (w.t0 + c0 >= p.T) break;   // the same for all epilogue threads
+                    uint8_t* stage = staging + (chunk_count & 1u) * kStagingBytes;
+                    // the store that used this buffer two chunks ago has read it
+                    if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    epilogue_barrier();
+                    float g[32], up[32];
+                    tmem_ld32(acc_addr + (uint32_t)c0, g);
+                    if (p.dual) tmem_ld32(acc_addr + (uint32_t)(p.tile_n + c0), up);
+                    const int f = quarter * 32 + lane;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    int t = t0 + c0 + j;
-                    if (t >= p.T) break;
-                    size_t o = (size_t)t * p.N + n;
-                    float v = g[j];
-                    if (p.epilogue == EPI_PARTIAL) {
-                        p.workspace[((size_t)split * p.T + t) * p.N + n] = v;
-                        if (p.dual) p.workspace[(((size_t)p.splits + split) * p.T + t) * p.N + n] = u[j];
-                        continue;
+                    for (int j = 0; j < 32; ++j) {
+                        float v = g[j];
+                        if (p.epilogue == EPI_SWIGLU) v = up[j] * (v / (1.0f + __expf(-v)));
+                        else v += bias_v;
+                        if (p.out_dt == F32) ((float*)stage)[j * kTileM + f] = v;
+                        else ((__nv_bfloat16*)stage)[j * kTileM + f] = __float2bfloat16_rn(v);
                     }
-                    if (p.epilogue == EPI_SWIGLU) v = u[j] * (v / (1.0f + expf(-v)));
-                    else v += bias_v;
-                    if (p.epilogue == EPI_ACCUM) {
-                        ((float*)p.out)[o] += v;
-                    } else if (p.out_dt == F32) {
-                        ((float*)p.out)[o] = v;
-                    } else {
-                        ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    epilogue_barrier();
+                    if (issuer) {
+                        if (p.epilogue == EPI_ACCUM) tma_add_2d(&map_out, stage, w.n0, w.t0 + c0);
+                        else tma_store_2d(&map_out, stage, w.n0, w.t0 + c0);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
+            } else {
+                for (int c0 = 0; c0 < p.tile_n; c0 += 16) {
+                    if (w.t0 + c0 >= p.T) break;   // the same for the whole warp
+                    float g[16], up[16], old[16];
+                    tmem_ld16(acc_addr + (uint32_t)c0, g);
+                    if (p.dual) tmem_ld16(acc_addr + (uint32_t)(p.tile_n + c0), up);
+                    if (n >= p.N) continue;
+                    if (p.epilogue == EPI_ACCUM) {   // all the old values first: the loads overlap
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = w.t0 + c0 + j;
+                            old[j] = t < p.T ? ((const float*)p.out)[(size_t)t * p.N + n] : 0.f;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = w.t0 + c0 + j;
+                        if (t >= p.T) break;
+                        const size_t o = (size_t)t * p.N + n;
+                        float v = g[j];
+                        if (p.epilogue == EPI_PARTIAL) {
+                            p.workspace[((size_t)w.split * p.T + t) * p.N + n] = v;
+                            if (p.dual) p.workspace[(((size_t)p.splits + w.split) * p.T + t) * p.N + n] = up[j];
+                            continue;
+                        }
+                        if (p.epilogue == EPI_SWIGLU) v = up[j] * (v / (1.0f + __expf(-v)));
+                        else v += bias_v;
+                        if (p.epilogue == EPI_ACCUM) ((float*)p.out)[o] = old[j] + v;
+                        else if (p.out_dt == F32) ((float*)p.out)[o] = v;
+                        else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
                     }
                 }
             }
+            // this accumulator may be overwritten by the MMAs of the unit after next
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[b]);
         }
+        if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory stays valid until read
     }
     __syncwarp();
     tc_fence_before();
@@ -269,7 +376,7 @@ __global__ void splitk_reduce_kernel(GemmParams p) {
         if (p.dual) u += p.workspace[((size_t)p.splits + s) * total + i];
     }
     float v = g;
-    if (p.epilogue == EPI_SWIGLU) v = u * (g / (1.0f + expf(-g)));
+    if (p.epilogue == EPI_SWIGLU) v = u * (g / (1.0f + __expf(-g)));
     else if (p.bias) v += p.bias_dt == F32 ? ((const float*)p.bias)[n] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
     if (p.epilogue == EPI_ACCUM) ((float*)p.out)[i] += v;
     else if (p.out_dt == F32) ((float*)p.out)[i] = v;
@@ -311,6 +418,24 @@ CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
     return map;
 }
 
+// The [T, N] row-major output, boxes of kChunk tokens x 128 features, no swizzle. Stores and
+// adds outside the matrix are dropped.
+CUtensorMap make_out_map(void* base, int T, int N, DType dt) {
+    CUtensorMap map;
+    const size_t elem_bytes = dt == F32 ? 4 : 2;
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)T};
+    cuuint64_t strides[1] = {(cuuint64_t)N * elem_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)kTileM, (cuuint32_t)kChunk};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode_fn()(&map, dt == F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
+                             dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        throw std::runtime_error("gemm_tc: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r) +
+                                 " for the " + std::to_string(T) + " x " + std::to_string(N) + " output");
+    return map;
+}
+
 int device_sm_count() {
     static int count = 0;
     if (!count) {
@@ -327,29 +452,29 @@ int device_sm_count() {
 bool gemm_tc_supports(int T, int N, int K) { return T > 0 && N > 0 && K > 0 && K % 8 == 0; }
 
 void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
-    int sms = device_sm_count();
-    int tiles_m = (N + kTileM - 1) / kTileM;
-    int t16 = ((T + 15) / 16) * 16;
-    int max_tile = dual ? 128 : 256;
+    const int sms = device_sm_count();
+    const int tiles_m = (N + kTileM - 1) / kTileM;
+    const int t16 = ((T + 15) / 16) * 16;
+    const int max_tile = dual ? 128 : 256;
     int tn = 16;
-    // the largest token tile that still fills the machine, else the smallest that covers T
+    // the largest token tile that keeps most of the machine busy, else the smallest that covers T
     for (int cand = max_tile; cand >= 16; cand >>= 1) {
         if (cand > t16 && cand > 16) continue;
-        int ctas = tiles_m * ((T + cand - 1) / cand);
+        const int tiles = tiles_m * ((T + cand - 1) / cand);
         tn = cand;
-        if (ctas >= sms) break;
+        if (tiles * 10 >= sms * 7) break;
     }
-    int ctas = tiles_m * ((T + tn - 1) / tn);
-    int kb = (K + kBlockK - 1) / kBlockK;
+    const int tiles = tiles_m * ((T + tn - 1) / tn);
+    const int kb = (K + kBlockK - 1) / kBlockK;
     int sp = 1;
-    if (ctas < sms && kb >= 4) {
-        sp = (2 * sms + ctas - 1) / ctas;
+    if (tiles * 2 < sms && kb >= 4) {
+        sp = (2 * sms + tiles - 1) / tiles;
         if (sp > kb / 2) sp = kb / 2;
         if (sp > 16) sp = 16;
         if (sp < 1) sp = 1;
     }
-    // no empty split: every CTA along K gets at least one block
-    int per = (kb + sp - 1) / sp;
+    // no empty split: every unit along K gets at least one block
+    const int per = (kb + sp - 1) / sp;
     sp = (kb + per - 1) / per;
     *tile_n = tn;
     *splits = sp;
@@ -370,7 +495,7 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     GemmParams p{};
     p.T = T; p.N = N; p.K = K;
     gemm_tc_plan(T, N, K, dual, &p.tile_n, &p.splits);
-    int kb = (K + kBlockK - 1) / kBlockK;
+    const int kb = (K + kBlockK - 1) / kBlockK;
     p.kblocks_per_split = (kb + p.splits - 1) / p.splits;
     p.dual = dual ? 1 : 0;
     p.up_offset = up_offset;
@@ -378,23 +503,33 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     p.out = out; p.out_dt = out_dt;
     p.workspace = workspace;
     p.error = error;
+    p.tiles_m = (N + kTileM - 1) / kTileM;
+    p.tiles_t = (T + p.tile_n - 1) / p.tile_n;
+    p.units = p.tiles_m * p.tiles_t * p.splits;
     const int final_mode = mode;
     p.epilogue = p.splits > 1 ? EPI_PARTIAL : final_mode;
     if (p.splits > 1 && !workspace) throw std::invalid_argument("gemm_tc: this shape splits K and needs a workspace");
-    int stage_bytes = kTileM * kBlockK * 2 * (dual ? 2 : 1) + p.tile_n * kBlockK * 2;
-    int budget = p.tile_n <= 64 ? 100 * 1024 : 200 * 1024;   // small tiles: two CTAs share an SM
+    // the output leaves through shared memory and TMA where TMA can address it: rows that start
+    // on 16 bytes (TMA stores outside the matrix are dropped, so ragged edges need no care)
+    const size_t out_elem = out_dt == F32 ? 4 : 2;
+    // (a chunk is 32 tokens, so the token tile must hold at least one)
+    p.tma_out = p.splits == 1 && p.tile_n >= kChunk && ((size_t)N * out_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0 ? 1 : 0;
+    const int stage_bytes = kTileM * kBlockK * 2 * (dual ? 2 : 1) + p.tile_n * kBlockK * 2;
+    const int budget = 227 * 1024 - 1024 - 2 * kStagingBytes - 512;
     p.stages = budget / stage_bytes;
     if (p.stages > 8) p.stages = 8;
-    if (p.stages < 2) p.stages = 2;
-    size_t smem = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + (2 * p.stages + 1) * 8 + 16;
-    CUtensorMap map_w = make_map(w, dual ? up_offset + N : N, K, kTileM);
-    CUtensorMap map_x = make_map(x, T, K, p.tile_n);
+    if (p.stages < 2) throw std::runtime_error("gemm_tc: a pipeline stage does not fit shared memory twice");
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + 2 * kStagingBytes + (2 * p.stages + 4) * 8 + 16;
+    const CUtensorMap map_w = make_map(w, dual ? up_offset + N : N, K, kTileM);
+    const CUtensorMap map_x = make_map(x, T, K, p.tile_n);
+    const CUtensorMap map_out = p.tma_out ? make_out_map(out, T, N, out_dt) : map_x;
     static std::once_flag attr_once;
     std::call_once(attr_once, [] {
         cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     });
-    dim3 grid((N + kTileM - 1) / kTileM, (T + p.tile_n - 1) / p.tile_n, p.splits);
-    gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(map_w, map_x, p);
+    const int sms = device_sm_count();
+    const int grid = p.units < sms ? p.units : sms;
+    gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(map_w, map_x, map_out, p);
     note_launch(p.splits > 1 ? 2 : 1);
     if (p.splits > 1) {
         p.epilogue = final_mode;
