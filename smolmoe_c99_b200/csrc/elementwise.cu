@@ -73,17 +73,95 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
     for (int d = threadIdx.x; d < D; d += kNormThreads) o[d] = from_float<TO>((xr[d] * inv) * to_float(w[d]));
 }
 
+// Many rows (prefill): one warp per row, the row held in registers (NV float4 a lane), one pass.
+// The sum runs over a lane's elements in ascending order, then the butterfly: again a function
+// of D alone.
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a);
+    raw.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+constexpr int kRowWarps = 8;
+
+template <typename TW, typename TO, int NV>
+__global__ void __launch_bounds__(kRowWarps * 32)
+rmsnorm_rows_kernel(const float* __restrict__ x, const TW* __restrict__ w, float eps, TO* __restrict__ out,
+                    const int32_t* __restrict__ rows, int n_rows, int D) {
+    const int r = blockIdx.x * kRowWarps + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= n_rows) return;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
+    float v[NV][4];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int d = (i * 32 + lane) * 4;
+        if (d < D) load4(xr + d, v[i]);
+        else v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sq = fmaf(v[i][e], v[i][e], sq);
+    sq = warp_sum(sq);
+    const float inv = 1.0f / sqrtf(sq / (float)D + eps);
+    TO* o = out + (size_t)r * D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int d = (i * 32 + lane) * 4;
+        if (d < D) {
+            float wv[4], y[4];
+            load4(w + d, wv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) y[e] = (v[i][e] * inv) * wv[e];
+            store4(o + d, y);
+        }
+    }
+}
+
+template <typename TW, typename TO>
+static void launch_norm(const float* x, const void* w, float eps, void* out, const int32_t* rows, int n_rows, int D,
+                        cudaStream_t stream) {
+    // rows whose length is a multiple of 4 and at most 4096 fit the warp-per-row kernel. The
+    // choice depends on D alone, never on the number of rows: a row's result must not depend on
+    // how many rows come with it
+    if (D % 4 == 0 && D <= 4096) {
+        const unsigned blocks = (unsigned)((n_rows + kRowWarps - 1) / kRowWarps);
+        if (D <= 1024)
+            rmsnorm_rows_kernel<TW, TO, 8><<<blocks, kRowWarps * 32, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
+        else if (D <= 2048)
+            rmsnorm_rows_kernel<TW, TO, 16><<<blocks, kRowWarps * 32, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
+        else
+            rmsnorm_rows_kernel<TW, TO, 32><<<blocks, kRowWarps * 32, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
+        return;
+    }
+    rmsnorm_kernel<TW, TO><<<n_rows, kNormThreads, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, D);
+}
+
 void rmsnorm(const float* x, const void* w, DType w_dt, float eps, void* out, DType out_dt,
              const int32_t* rows, int n_rows, int D, cudaStream_t stream) {
     if (n_rows <= 0) return;
     note_launch();
-#define SM_NORM(TW, TO) \
-    rmsnorm_kernel<TW, TO><<<n_rows, kNormThreads, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, D)
-    if (w_dt == F32 && out_dt == F32) SM_NORM(float, float);
-    else if (w_dt == F32 && out_dt == BF16) SM_NORM(float, __nv_bfloat16);
-    else if (w_dt == BF16 && out_dt == F32) SM_NORM(__nv_bfloat16, float);
-    else SM_NORM(__nv_bfloat16, __nv_bfloat16);
-#undef SM_NORM
+    if (w_dt == F32 && out_dt == F32) launch_norm<float, float>(x, w, eps, out, rows, n_rows, D, stream);
+    else if (w_dt == F32 && out_dt == BF16) launch_norm<float, __nv_bfloat16>(x, w, eps, out, rows, n_rows, D, stream);
+    else if (w_dt == BF16 && out_dt == F32) launch_norm<__nv_bfloat16, float>(x, w, eps, out, rows, n_rows, D, stream);
+    else launch_norm<__nv_bfloat16, __nv_bfloat16>(x, w, eps, out, rows, n_rows, D, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -163,8 +241,66 @@ __global__ void rope_store_kernel(RopeStoreArgs a) {
     }
 }
 
+// The common case (full rotation, head sizes that are multiples of 8): one thread per (token,
+// head, 4 neighbouring pairs), 16-byte loads and 8-byte stores.
+template <typename TO>
+__global__ void rope_store_vec_kernel(RopeStoreArgs a, long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int hd = a.head_dim, half = hd / 2, groups = half / 4;
+    const int n_heads = a.heads + 2 * a.kv_heads;
+    const int grp = (int)(idx % groups);
+    const int head = (int)((idx / groups) % n_heads);
+    const int t = (int)(idx / ((long long)groups * n_heads));
+    const int pos = a.positions[t];
+    const float* x = a.qkv + ((size_t)t * n_heads + head) * hd;
+    const int i0 = grp * 4;
+    float lo[4], hi[4];
+    load4(x + i0, lo);
+    load4(x + half + i0, hi);
+    const bool is_v = head >= a.heads + a.kv_heads;
+    if (!is_v) {
+        float c[4], s[4];
+        load4(a.cos_table + (size_t)pos * half + i0, c);
+        load4(a.sin_table + (size_t)pos * half + i0, s);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float r0 = lo[e] * c[e] - hi[e] * s[e], r1 = lo[e] * s[e] + hi[e] * c[e];
+            lo[e] = r0;
+            hi[e] = r1;
+        }
+    }
+    if (head < a.heads) {
+        TO* q = (TO*)a.q_out + ((size_t)t * a.heads + head) * hd;
+        store4(q + i0, lo);
+        store4(q + half + i0, hi);
+        return;
+    }
+    const int kvh = is_v ? head - a.heads - a.kv_heads : head - a.heads;
+    TO* packed = (TO*)(is_v ? a.v_packed : a.k_packed);
+    if (packed) {
+        TO* p = packed + ((size_t)t * a.kv_heads + kvh) * hd;
+        store4(p + i0, lo);
+        store4(p + half + i0, hi);
+    }
+    if (a.k_pool != nullptr && !(a.ring > 0 && pos < a.token_end[t] - a.ring)) {
+        PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
+        TO* c = (TO*)(is_v ? a.v_pool : a.k_pool) + paged.row_offset(a.token_slot[t], pos, kvh);
+        store4(c + i0, lo);
+        store4(c + half + i0, hi);
+    }
+}
+
 void rope_store(const RopeStoreArgs& a, cudaStream_t stream) {
     if (a.T <= 0) return;
+    if (a.rotary_dim == a.head_dim && a.head_dim % 8 == 0 && a.head_dim > 0) {
+        note_launch();
+        const long long total = (long long)a.T * (a.heads + 2 * a.kv_heads) * (a.head_dim / 8);
+        const unsigned blocks = (unsigned)((total + 255) / 256);
+        if (a.dt == F32) rope_store_vec_kernel<float><<<blocks, 256, 0, stream>>>(a, total);
+        else rope_store_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(a, total);
+        return;
+    }
     if (a.head_dim % 2 || a.rotary_dim % 2 || a.rotary_dim > a.head_dim)
         throw std::invalid_argument("rope_store: head_dim " + std::to_string(a.head_dim) + " / rotary_dim " +
                                     std::to_string(a.rotary_dim) + " must be even, rotary_dim <= head_dim");
