@@ -364,6 +364,141 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
 
+// The kernel for at most 64 tokens (decode batches beyond the weight-streaming kernel, and the
+// output head): one CTA per work unit, few registers, two CTAs to an SM. With so few tokens a
+// unit is nothing but a stream of weight tiles, and two small CTAs keep more of them in flight
+// than one persistent CTA does (measured on the 151,936 x 896 head at 8 tokens: 54 against 75 us).
+__global__ void __launch_bounds__(kThreads, 2)
+gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // 1024-byte alignment of the tiles is what the swizzle pattern assumes
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int a_bytes = kTileM * kBlockK * 2 * (p.dual ? 2 : 1);
+    const int b_bytes = p.tile_n * kBlockK * 2;
+    const int stage_bytes = a_bytes + b_bytes;
+    uint64_t* full_bar = (uint64_t*)(smem + (size_t)p.stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + p.stages;
+    uint64_t* tmem_full_bar = empty_bar + p.stages;
+    uint32_t* tmem_slot = (uint32_t*)(tmem_full_bar + 1);
+    int* failed = (int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kTileM, t0 = blockIdx.y * p.tile_n, split = blockIdx.z;
+    const int kb_total = (p.K + kBlockK - 1) / kBlockK;
+    const int kb_begin = split * p.kblocks_per_split;
+    const int kb_end = min(kb_total, kb_begin + p.kblocks_per_split);
+    const int n_kb = kb_end - kb_begin;   // >= 1 by construction of the grid
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < p.tile_n * (p.dual ? 2 : 1)) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(tmem_full_bar, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < n_kb; ++i) {
+                int s = i % p.stages;
+                uint32_t phase = (uint32_t)(i / p.stages) & 1u;
+                if (!mbar_wait(&empty_bar[s], phase ^ 1u)) { *failed = 1; atomicExch(p.error, 1); break; }
+                uint8_t* a = smem + (size_t)s * stage_bytes;
+                mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
+                int k = (kb_begin + i) * kBlockK;
+                tma_load_2d(a, &map_w, k, n0, &full_bar[s]);
+                if (p.dual) tma_load_2d(a + kTileM * kBlockK * 2, &map_w, k, p.up_offset + n0, &full_bar[s]);
+                tma_load_2d(a + a_bytes, &map_x, k, t0, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(kTileM, p.tile_n);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                int s = i % p.stages;
+                uint32_t phase = (uint32_t)(i / p.stages) & 1u;
+                if (!mbar_wait(&full_bar[s], phase)) { *failed = 1; atomicExch(p.error, 2); ok = false; break; }
+                tc_fence_after();
+                uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+                uint32_t b_addr = a_addr + a_bytes;
+                uint64_t da = smem_desc(a_addr), db = smem_desc(b_addr);
+                uint64_t du = smem_desc(a_addr + kTileM * kBlockK * 2);
+#pragma unroll
+                for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                    uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                    uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);   // 32 bytes a step inside the swizzled row
+                    umma_bf16(tmem_base, da + step, db + step, idesc, acc);
+                    if (p.dual) umma_bf16(tmem_base + (uint32_t)p.tile_n, du + step, db + step, idesc, acc);
+                }
+                umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
+            }
+            umma_commit(tmem_full_bar);        // the accumulator is complete once all MMAs are done
+        }
+    } else {
+        // epilogue warps 2..5: TMEM lanes of quarter (warp % 4)
+        const int quarter = warp & 3;
+        const int n = n0 + quarter * 32 + lane;
+        bool ok = mbar_wait(tmem_full_bar, 0);
+        if (!ok && lane == 0) { *failed = 1; atomicExch(p.error, 3); }
+        ok = ok && (*(volatile int*)failed == 0);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+        if (ok) {
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            float bias_v = 0.f;
+            if (p.bias && n < p.N)
+                bias_v = p.bias_dt == F32 ? ((const float*)p.bias)[n] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
+            for (int c0 = 0; c0 < p.tile_n; c0 += 16) {
+                if (t0 + c0 >= p.T) break;   // the same for the whole warp
+                float g[16], u[16], old[16];
+                tmem_ld16(lane_base + (uint32_t)c0, g);
+                if (p.dual) tmem_ld16(lane_base + (uint32_t)(p.tile_n + c0), u);
+                if (n >= p.N) continue;
+                if (p.epilogue == EPI_ACCUM) {   // all the old values first: the loads overlap
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c0 + j;
+                        old[j] = t < p.T ? ((const float*)p.out)[(size_t)t * p.N + n] : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    int t = t0 + c0 + j;
+                    if (t >= p.T) break;
+                    size_t o = (size_t)t * p.N + n;
+                    float v = g[j];
+                    if (p.epilogue == EPI_PARTIAL) {
+                        p.workspace[((size_t)split * p.T + t) * p.N + n] = v;
+                        if (p.dual) p.workspace[(((size_t)p.splits + split) * p.T + t) * p.N + n] = u[j];
+                        continue;
+                    }
+                    if (p.epilogue == EPI_SWIGLU) v = u[j] * (v / (1.0f + __expf(-v)));
+                    else v += bias_v;
+                    if (p.epilogue == EPI_ACCUM) {
+                        ((float*)p.out)[o] = old[j] + v;
+                    } else if (p.out_dt == F32) {
+                        ((float*)p.out)[o] = v;
+                    } else {
+                        ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
 // Adds the splits in order and applies the epilogue. One thread per output element.
 __global__ void splitk_reduce_kernel(GemmParams p) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -515,6 +650,29 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     // (a chunk is 32 tokens, so the token tile must hold at least one)
     p.tma_out = p.splits == 1 && p.tile_n >= kChunk && ((size_t)N * out_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0 ? 1 : 0;
     const int stage_bytes = kTileM * kBlockK * 2 * (dual ? 2 : 1) + p.tile_n * kBlockK * 2;
+    if (T <= 64) {
+        // few tokens: one CTA per unit, two CTAs to an SM
+        p.tma_out = 0;
+        p.stages = 100 * 1024 / stage_bytes;
+        if (p.stages > 8) p.stages = 8;
+        if (p.stages < 2) p.stages = 2;
+        const size_t smem_small = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + (2 * p.stages + 1) * 8 + 16;
+        const CUtensorMap mw = make_map(w, dual ? up_offset + N : N, K, kTileM);
+        const CUtensorMap mx = make_map(x, T, K, p.tile_n);
+        static std::once_flag small_once;
+        std::call_once(small_once, [] {
+            cudaFuncSetAttribute(gemm_tc_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        });
+        dim3 grid3(p.tiles_m, p.tiles_t, p.splits);
+        gemm_tc_small_kernel<<<grid3, kThreads, smem_small, stream>>>(mw, mx, p);
+        note_launch(p.splits > 1 ? 2 : 1);
+        if (p.splits > 1) {
+            p.epilogue = final_mode;
+            size_t total = (size_t)T * N;
+            splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p);
+        }
+        return;
+    }
     const int budget = 227 * 1024 - 1024 - 2 * kStagingBytes - 512;
     p.stages = budget / stage_bytes;
     if (p.stages > 8) p.stages = 8;

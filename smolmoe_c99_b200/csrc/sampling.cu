@@ -35,7 +35,7 @@ __device__ __forceinline__ unsigned long long rank_of(float logit, int id) {
 // minimum does not depend on the order of arrival); the CTA that arrives last for a row
 // writes the token and puts the scratch word and the counter back to their idle values.
 constexpr int kArgmaxThreads = 256;
-constexpr int kArgmaxChunks = 32;
+constexpr int kArgmaxChunks = 128;   // a vocabulary of 150 k: 1.2 k logits a CTA, one batch of loads a thread
 
 __global__ void __launch_bounds__(kArgmaxThreads)
 argmax_kernel(const float* __restrict__ logits, const uint8_t* __restrict__ banned, int32_t* __restrict__ out, int V,
