@@ -42,6 +42,9 @@ long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 static std::atomic<bool> g_dependent_launch{true};
 bool dependent_launch_enabled() { return g_dependent_launch.load(std::memory_order_relaxed); }
 void set_dependent_launch(bool on) { g_dependent_launch.store(on, std::memory_order_relaxed); }
+static std::atomic<int*> g_error_word{nullptr};
+int* error_word() { return g_error_word.load(std::memory_order_relaxed); }
+void set_error_word(int* word) { g_error_word.store(word, std::memory_order_relaxed); }
 }  // namespace sm
 
 namespace sm {
@@ -55,6 +58,9 @@ SM_API const char* sm_last_error() { return g_last_error.c_str(); }
 
 // Programmatic dependent launch of the decode chain's kernels: 1 on (default), 0 off.
 SM_API void sm_set_dependent_launch(int on) { sm::set_dependent_launch(on != 0); }
+
+// The device int that kernels report a bounded wait that ran out into.
+SM_API void sm_set_error_word(int* word) { sm::set_error_word(word); }
 
 // Kernels enqueued by this library since it was loaded.
 SM_API long long sm_launch_count() { return sm::launch_count(); }

@@ -20,6 +20,11 @@ long long launch_count();
 bool dependent_launch_enabled();
 void set_dependent_launch(bool on);
 
+// A device int that kernels whose bounded waits ran out write a code into (0: nothing
+// happened); null until the host gives one. Kernels skip the write when it is null.
+int* error_word();
+void set_error_word(int* word);
+
 // ---- elementwise.cu -------------------------------------------------------------------
 // out[t, :] = table[tokens[t], :] as float. A token outside [0, V) sets *status |= 1 and
 // its row is zeroed.

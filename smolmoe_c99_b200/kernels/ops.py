@@ -78,6 +78,8 @@ class Ops:
         self.use_fast_attention = True  # False routes bfloat16 attention to the plain kernel
         self.use_skinny = True  # False routes products over a handful of tokens to the general kernels
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.lib.sm_set_error_word.restype = None
+        self.lib.sm_set_error_word(_ptr(self.error_flag))
         # scratch of the greedy choice: one word per row, all ones when idle, and arrival counters
         self.argmax_scratch = torch.full((4096,), -1, dtype=torch.int64, device="cuda")
         self.argmax_counters = torch.zeros(4096, dtype=torch.int32, device="cuda")

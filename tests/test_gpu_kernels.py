@@ -208,7 +208,7 @@ def test_gemm_skinny_store_and_accumulate(ops, T, N, K):
     assert torch.equal(alone[0], out[0])
 
 
-@pytest.mark.parametrize("T,H,K", [(1, 4864, 896), (8, 160, 96), (13, 520, 264)])
+@pytest.mark.parametrize("T,H,K", [(1, 4864, 896), (8, 160, 96), (13, 520, 264), (3, 48, 4104), (32, 40, 2056)])
 def test_gemm_skinny_norm_prologue_and_gate(ops, T, H, K):
     from smolmoe_c99_b200.kernels.ops import NormedRows
     res = _rand((T, K), torch.float32, 7)
