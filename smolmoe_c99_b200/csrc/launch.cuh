@@ -8,7 +8,10 @@
 // successor may be brought in with pdl_launch_dependents().
 //
 // Rules every kernel launched this way keeps: before pdl_wait() it reads only memory that no
-// kernel of the step writes (weights, norm weights, tables), and it writes nothing.
+// kernel of the step writes (weights, norm weights, tables; and the cache rows of positions
+// before the step's own, which only earlier steps wrote), and it writes nothing. A step begins
+// with a copy of its numbers from the host, which the stream orders after every kernel of the
+// step before; so nothing of an earlier step is still in flight when a kernel of this one runs.
 #pragma once
 
 #include <cuda_runtime.h>

@@ -28,8 +28,8 @@ from .batch import StepBatch, pack_step
 from .model import DecoderModel, cache_needs, model_param_specs
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
-SPAN_BUCKET = 1024   # decode graphs are captured for key spans rounded up to this many positions
-MAX_GRAPHS = 24
+SPAN_BUCKET = 256    # decode graphs are captured for key spans rounded up to this, doubling from there on
+MAX_GRAPHS = 32
 
 
 class StepError(ValueError):
@@ -188,7 +188,10 @@ class Engine:
     def _decode_graph(self, slots, starts, tokens, on_device) -> torch.Tensor:
         n = len(slots)
         longest = max(starts) + 1
-        span = min(-(-longest // SPAN_BUCKET) * SPAN_BUCKET, -(-self.max_seq_len // 128) * 128)
+        span = SPAN_BUCKET
+        while span < longest:
+            span *= 2   # a capture costs tens of steps: few spans, each good for as many steps as came before it
+        span = min(span, -(-self.max_seq_len // 128) * 128)
         key = (n, span)
         g = self._graphs.get(key)
         if g is None:
