@@ -2,7 +2,7 @@
 // its sequence's keys (the reference scans [start, pos] per head on one thread:
 // src/kernels.c:1156-1176).
 //
-// A thread-block cluster of 1 to 8 CTAs serves one (sequence, kv head); its CTAs split the
+// A thread-block cluster of 1 to 16 CTAs serves one (sequence, kv head); its CTAs split the
 // visible positions. A CTA brings its keys and values into shared memory with 16-byte
 // asynchronous copies: all of them at once if its share fits a buffer of about 100 KB (two
 // such CTAs fit an SM), else in chunks of a few hundred positions with two chunks in flight.
@@ -34,7 +34,7 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kTile = 32;           // positions per warp tile
-constexpr int kMaxCluster = 8;
+constexpr int kMaxCluster = 16;      // above 8 a kernel has to allow "non-portable" cluster sizes
 
 // positions per chunk for a head dimension of up to 32 * hdb when a share is read in chunks, two in
 // flight: about 36 KB of keys and values each, so that two CTAs fit an SM
@@ -350,6 +350,12 @@ template <int HDB>
 void prepare(size_t smem) {
     // the largest size asked for so far is kept: the attribute is per kernel, not per launch
     static size_t allowed = 48 * 1024;
+    static bool large_clusters = false;
+    if (!large_clusters) {
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<HDB>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) throw std::runtime_error(std::string("attention_decode: ") + cudaGetErrorString(e));
+        large_clusters = true;
+    }
     if (smem > allowed) {
         cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<HDB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) throw std::runtime_error(std::string("attention_decode: ") + cudaGetErrorString(e));
@@ -380,7 +386,7 @@ int resident_clusters(const DecodePlan& p) {
     return n;
 }
 
-// CTAs per (sequence, kv head): the largest cluster, of at most 8, all of whose clusters are resident at once
+// CTAs per (sequence, kv head): the largest cluster, of at most 16, all of whose clusters are resident at once
 // (a second wave doubles the time), and every CTA of which gets a few tiles of positions.
 template <int HDB>
 DecodePlan choose_plan(int pairs, int group, int visible) {
@@ -417,6 +423,19 @@ void launch(DecodeArgs a, int visible, cudaStream_t stream) {
 bool attention_decode_supports(int heads, int kv_heads, int head_dim) {
     return head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128 && kv_heads > 0 && heads % kv_heads == 0 &&
            heads / kv_heads <= 16;
+}
+
+void attention_decode_plan(int B, int heads, int kv_heads, int head_dim, int window, int max_len, int* plan) {
+    if (!attention_decode_supports(heads, kv_heads, head_dim)) throw std::invalid_argument("attention_decode_plan: sizes outside the kernel");
+    const int visible = window > 0 && window < max_len ? window : max_len;
+    DecodePlan p{};
+    switch ((head_dim + 31) / 32) {
+        case 1: p = choose_plan<1>(B * kv_heads, heads / kv_heads, visible); break;
+        case 2: p = choose_plan<2>(B * kv_heads, heads / kv_heads, visible); break;
+        case 3: p = choose_plan<3>(B * kv_heads, heads / kv_heads, visible); break;
+        default: p = choose_plan<4>(B * kv_heads, heads / kv_heads, visible); break;
+    }
+    plan[0] = p.cluster; plan[1] = p.buf_keys; plan[2] = p.n_bufs; plan[3] = (int)p.smem;
 }
 
 void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,

@@ -155,6 +155,10 @@ SM_API int sm_attention_decode_supports(int heads, int kv_heads, int head_dim) {
     return sm::attention_decode_supports(heads, kv_heads, head_dim) ? 1 : 0;
 }
 
+SM_API int sm_attention_decode_plan(int B, int heads, int kv_heads, int head_dim, int window, int max_len, int* plan) {
+    return guarded([&] { sm::attention_decode_plan(B, heads, kv_heads, head_dim, window, max_len, plan); });
+}
+
 SM_API int sm_attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale,
                                int window, const int32_t* positions, const int32_t* slots, const void* k_pool,
                                const void* v_pool, const int32_t* page_table, int table_stride, int ring, int max_len,

@@ -141,6 +141,9 @@ void attention_prefill(const void* q, const void* k, const void* v, void* out, c
 // memory; no workspace. `max_len` (the longest sequence of the batch, or a bound of it) only
 // sizes the clusters. head_dim: multiples of 16 up to 128; at most 16 heads per kv head.
 bool attention_decode_supports(int heads, int kv_heads, int head_dim);
+// How a launch for these sizes would be cut: plan[0..3] = CTAs per (sequence, kv head), positions per
+// buffer, buffers, bytes of shared memory per CTA.
+void attention_decode_plan(int B, int heads, int kv_heads, int head_dim, int window, int max_len, int* plan);
 void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
                       const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
                       const int32_t* page_table, int table_stride, int ring, int max_len, cudaStream_t stream);
