@@ -151,6 +151,19 @@ SM_API int sm_attention_prefill(const void* q, const void* k, const void* v, voi
     });
 }
 
+SM_API int sm_attention_prefill_tc_supports(int heads, int kv_heads, int head_dim) {
+    return sm::attention_prefill_tc_supports(heads, kv_heads, head_dim) ? 1 : 0;
+}
+
+SM_API int sm_attention_prefill_tc(const void* q, const void* k, const void* v, void* out, const int32_t* tiles,
+                                   int n_tiles, int T, int heads, int kv_heads, int head_dim, float scale, int window,
+                                   int* error, void* stream) {
+    return guarded([&] {
+        sm::attention_prefill_tc(q, k, v, out, tiles, n_tiles, T, heads, kv_heads, head_dim, scale, window, error,
+                                 (cudaStream_t)stream);
+    });
+}
+
 SM_API int sm_attention_decode_supports(int heads, int kv_heads, int head_dim) {
     return sm::attention_decode_supports(heads, kv_heads, head_dim) ? 1 : 0;
 }

@@ -135,6 +135,16 @@ bool attention_prefill_supports(int head_dim);
 void attention_prefill(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles,
                        int heads, int kv_heads, int head_dim, float scale, int window, cudaStream_t stream);
 
+// ---- attention_prefill_tc.cu ----------------------------------------------------------
+// The same as attention_prefill on the tcgen05 tensor cores (TMA operands, S and PV in tensor
+// memory) for head sizes 64 and 128. q, k, v are the packed [T, heads or kv_heads, head_dim]
+// tensors; `tiles` is the list attention_prefill takes (tiles of 64 queries; the kernel pairs
+// them). A bounded wait that runs out writes a code into *error (nullable).
+bool attention_prefill_tc_supports(int heads, int kv_heads, int head_dim);
+void attention_prefill_tc(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles, int T,
+                          int heads, int kv_heads, int head_dim, float scale, int window, int* error,
+                          cudaStream_t stream);
+
 // ---- attention_decode.cu --------------------------------------------------------------
 // One new token per sequence over the paged cache for bfloat16: a cluster of CTAs per
 // (sequence, kv head) splits the visible positions and merges through distributed shared

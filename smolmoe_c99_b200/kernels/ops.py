@@ -76,6 +76,7 @@ class Ops:
         self.lib.sm_launch_count.restype = ctypes.c_longlong
         self.use_tensor_cores = True  # False routes bfloat16 products to the CUDA-core kernel
         self.use_fast_attention = True  # False routes bfloat16 attention to the plain kernel
+        self.use_tcgen05_attention = True  # False routes prefill attention to the mma.sync kernel
         self.use_skinny = True  # False routes products over a handful of tokens to the general kernels
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.lib.sm_set_error_word.restype = None
@@ -314,21 +315,36 @@ class Ops:
 
     def attention_prefill(self, q, k_packed, v_packed, step, scale, window):
         """Causal attention of whole prompts over their own keys (sequences start at 0)."""
-        if (self.use_fast_attention and q.dtype == torch.bfloat16 and step.prefill_tiles is not None
-                and self.lib.sm_attention_prefill_supports(q.shape[2])):
-            return self.attention_prefill_tc(q, k_packed, v_packed, step.prefill_tiles, scale, window)
+        if self.use_fast_attention and q.dtype == torch.bfloat16 and step.prefill_tiles is not None:
+            if self.use_tcgen05_attention and self.lib.sm_attention_prefill_tc_supports(q.shape[1], k_packed.shape[1], q.shape[2]):
+                return self.attention_prefill_tcgen05(q, k_packed, v_packed, step.prefill_tiles, scale, window)
+            if self.lib.sm_attention_prefill_supports(q.shape[2]):
+                return self.attention_prefill_mma(q, k_packed, v_packed, step.prefill_tiles, scale, window)
         return self.attention_plain(q, step.positions, scale, window, k_packed=k_packed, v_packed=v_packed,
                                     token_seq_start=step.token_seq_start)
 
-    def attention_prefill_tc(self, q, k_packed, v_packed, tiles, scale, window):
+    def _prefill_operands(self, q, k_packed, v_packed, tiles):
         _need(q, "q", torch.bfloat16, 3)
         _need(k_packed, "packed keys", torch.bfloat16, 3)
         _need(v_packed, "packed values", torch.bfloat16, 3)
         _need(tiles, "tiles", torch.int32, 2)
-        out = torch.empty_like(q)
+        return torch.empty_like(q)
+
+    def attention_prefill_mma(self, q, k_packed, v_packed, tiles, scale, window):
+        """The mma.sync kernel: head sizes in steps of 16 up to 128."""
+        out = self._prefill_operands(q, k_packed, v_packed, tiles)
         self._check(self.lib.sm_attention_prefill(_ptr(q), _ptr(k_packed), _ptr(v_packed), _ptr(out), _ptr(tiles),
                                                   tiles.shape[0], q.shape[1], k_packed.shape[1], q.shape[2],
                                                   ctypes.c_float(scale), int(window or 0), _stream()))
+        return out
+
+    def attention_prefill_tcgen05(self, q, k_packed, v_packed, tiles, scale, window):
+        """The tcgen05 kernel: head sizes 64 and 128."""
+        out = self._prefill_operands(q, k_packed, v_packed, tiles)
+        self._check(self.lib.sm_attention_prefill_tc(_ptr(q), _ptr(k_packed), _ptr(v_packed), _ptr(out), _ptr(tiles),
+                                                     tiles.shape[0], q.shape[0], q.shape[1], k_packed.shape[1], q.shape[2],
+                                                     ctypes.c_float(scale), int(window or 0), _ptr(self.error_flag),
+                                                     _stream()))
         return out
 
     def attention_cached(self, q, step, scale, window, cache, kv_heads):

@@ -109,7 +109,7 @@ def test_prefill_attention(ops, heads, kv_heads, hd, window):
     scale = 1.0 / math.sqrt(hd)
     step = _packed_step(lens)
     want = _plain_attention(q, k, v, lens, window, scale)
-    got = ops.attention_prefill_tc(q, k, v, step.prefill_tiles, scale, window).float().cpu()
+    got = ops.attention_prefill_mma(q, k, v, step.prefill_tiles, scale, window).float().cpu()
     assert float((got - want).abs().max()) <= 2e-2
     plain = ops.attention_plain(q, step.positions, scale, window, k_packed=k, v_packed=v,
                                 token_seq_start=step.token_seq_start).float().cpu()
@@ -119,9 +119,27 @@ def test_prefill_attention(ops, heads, kv_heads, hd, window):
     assert float((plain32 - want).abs().max()) <= 2e-5
 
 
-def test_prefill_attention_finds_a_far_key(ops):
+@pytest.mark.parametrize("heads,kv_heads,hd", [(14, 2, 64), (3, 1, 64), (4, 4, 128), (6, 2, 128)])
+@pytest.mark.parametrize("window", [None, 37, 200])
+def test_prefill_attention_tcgen05(ops, heads, kv_heads, hd, window):
+    """Sequences shorter than, equal to and longer than the tiles of 128; a window inside and across tiles."""
+    lens = [1, 127, 128, 129, 300, 64]
+    T = sum(lens)
+    q, k, v = (_rand((T, n, hd), torch.bfloat16, s) for n, s in ((heads, 1), (kv_heads, 2), (kv_heads, 3)))
+    scale = 1.0 / math.sqrt(hd)
+    step = _packed_step(lens)
+    want = _plain_attention(q, k, v, lens, window, scale)
+    got = ops.attention_prefill_tcgen05(q, k, v, step.prefill_tiles, scale, window).float().cpu()
+    ops.check_error_flag()
+    assert float((got - want).abs().max()) <= 2e-2
+    assert ops.attention_prefill(q, k, v, step, scale, window).float().cpu().equal(got)   # it is the one the engine takes
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+def test_prefill_attention_finds_a_far_key(ops, kernel):
     """One key far back among hundreds is made to dominate: its value must come through."""
     heads, kv_heads, hd, n = 2, 1, 64, 700
+    run = ops.attention_prefill_mma if kernel == "mma" else ops.attention_prefill_tcgen05
     q, k, v = _rand((n, heads, hd), torch.bfloat16, 1, 0.1), _rand((n, kv_heads, hd), torch.bfloat16, 2, 0.1), \
         _rand((n, kv_heads, hd), torch.bfloat16, 3)
     far = 5
@@ -129,12 +147,12 @@ def test_prefill_attention_finds_a_far_key(ops):
     k[far, 0, 0] = 40.0
     q[n - 1, :, 0] = 40.0   # score 1600/8 = 200 for the far key, O(1) for the others
     step = _packed_step([n])
-    got = ops.attention_prefill_tc(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), None).float()
+    got = run(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), None).float()
     assert float((got[n - 1, 0] - v[far, 0].float()).abs().max()) <= 2e-2
     # with a window that ends just after it, it is out of sight
-    got_w = ops.attention_prefill_tc(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), n - 1 - far).float()
+    got_w = run(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), n - 1 - far).float()
     assert float((got_w[n - 1, 0] - v[far, 0].float()).abs().max()) > 0.1
-    got_w1 = ops.attention_prefill_tc(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), n - far).float()
+    got_w1 = run(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), n - far).float()
     assert float((got_w1[n - 1, 0] - v[far, 0].float()).abs().max()) <= 2e-2
 
 
