@@ -4,18 +4,20 @@
 // scans [start, pos] per query and head: src/model.c:459-491, src/kernels.c:1156-1176), for
 // head sizes 64 and 128.
 //
-// One CTA of 128 threads per (tile of 128 queries of one sequence, head). Q, and tiles of 128
+// One CTA per (tile of 128 queries of one sequence, head): 256 threads, two to a query row (64 of a
+// key tile's 128 scores and half of the output's columns each), and a ninth warp whose first thread
+// issues the copies and the MMAs. Q, and tiles of 128
 // keys and values, come into shared memory by TMA (128-byte swizzle). For every key tile:
 //   S = Q K^T   tcgen05.mma 128 x 128 x head_dim, both operands K-major, S (float) in tensor memory;
-//   each thread owns one query row (its lane of tensor memory): it reads the row with
-//   tcgen05.ld, masks, takes the running maximum, writes P = exp2(S - max) as bfloat16 into
-//   shared memory in the swizzled K-major layout an MMA operand needs;
+//   a row's two threads read their halves of it (their lane of tensor memory) with tcgen05.ld,
+//   mask, agree on the running maximum through shared memory, and write P = exp2(S - max) as
+//   bfloat16 into shared memory in the swizzled K-major layout an MMA operand needs;
 //   PV = P V    tcgen05.mma 128 x head_dim x 128 with V as it lies in memory ([key][dim], the
-//   "MN-major" operand form), into a second accumulator; the thread adds its row of PV to the
-//   output it keeps in registers, rescaled when the maximum moved.
-// One thread issues the copies and the MMAs. The MMAs of S for the next tile are issued right
-// behind those of PV, so they run while the threads finish this tile; two CTAs share an SM
-// (head size 64), so one's MMAs also run under the other's softmax.
+//   "MN-major" operand form), into a second accumulator; the threads add their columns of PV to
+//   the output they keep in registers, rescaled when the maximum moved.
+// The row threads and the issuing thread meet only at mbarriers: S of the next tile is issued as
+// soon as the rows of this one are in registers, and PV of a tile is added to the output during
+// the next tile's arithmetic, so the tensor core works under the softmax.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in *error and the
 // CTA leaves without writing.
@@ -34,8 +36,14 @@ namespace {
 
 using namespace tc5;
 
-constexpr int kBM = 128, kBN = 128, kThreads = 128;
+constexpr int kBM = 128, kBN = 128;
+constexpr int kRowThreads = 256;      // two threads per query row (warps w and w + 4 share the rows of lane quarter w)
+constexpr int kIssueWarp = 8;         // the warp whose first thread issues copies and MMAs (and which owns tensor memory)
+constexpr int kThreads = kRowThreads + 32;
 constexpr int kBlockBytes = 128 * 128;      // 128 rows of 128 bytes: one swizzled block of 64 bfloat16 columns
+
+// key tiles, and value tiles, in flight: what fits beside Q and P in an SM's shared memory
+__host__ __device__ constexpr int kv_stages(int head_dim) { return head_dim == 64 ? 4 : 2; }
 
 struct PrefillTcArgs {
     __nv_bfloat16* out;       // [T, heads, HD]
@@ -64,14 +72,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kThreads) prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(kThreads, 1) prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         PrefillTcArgs a) {
     constexpr int DB = HD / 64;                       // blocks of 64 columns of the head dimension
     constexpr int kQBytes = DB * kBlockBytes;         // Q tile, and one K or V tile
+    constexpr int NS = kv_stages(HD);                 // key tiles, and value tiles, in flight
     constexpr uint32_t kTmemCols = 256;               // S: 128 columns, PV: HD columns
-    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;   // late tiles (most keys) first
+    // CTAs start in the order of their index, the heads of one tile together: late tiles (most keys) first, so that
+    // the longest chains of key tiles begin at once and the short ones fill the SMs that become free
+    const int tile = (int)gridDim.y - 1 - (int)blockIdx.y, h = blockIdx.x;
     const int seq_start = a.tiles[3 * tile], seq_len = a.tiles[3 * tile + 1], q0 = a.tiles[3 * tile + 2];
     if (q0 % kBM) return;                             // the second half of a tile of 128 queries
     const int kvh = h / (a.heads / a.kv_heads);
@@ -79,212 +90,245 @@ __global__ void __launch_bounds__(kThreads) prefill_attention_tc_kernel(const __
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = smem;                              // [DB][128 queries][128 B]
-    uint8_t* k_s = q_s + kQBytes;                     // 2 x [DB][128 keys][128 B]
-    uint8_t* v_s = k_s + 2 * kQBytes;                 // [DB][128 keys][128 B]
-    uint8_t* p_s = v_s + kQBytes;                     // [2][128 queries][128 B]: keys 0-63 and 64-127 of the tile
+    uint8_t* k_s = q_s + kQBytes;                     // NS x [DB][128 keys][128 B]
+    uint8_t* v_s = k_s + NS * kQBytes;                // NS x [DB][128 keys][128 B]
+    uint8_t* p_s = v_s + NS * kQBytes;                // [2][128 queries][128 B]: keys 0-63 and 64-127 of the tile
     uint64_t* bars = (uint64_t*)(p_s + 2 * kBlockBytes);
-    uint64_t* q_bar = bars;
-    uint64_t* k_bar = bars + 1;                       // [2]
-    uint64_t* v_bar = bars + 3;
-    uint64_t* s_bar = bars + 4;
-    uint64_t* pv_bar = bars + 5;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 6);
+    uint64_t* q_bar = bars;                           // Q has landed
+    uint64_t* s_full = bars + 1;                      // the MMAs of S are done
+    uint64_t* s_free = bars + 2;                      // all rows of S are in registers
+    uint64_t* p_full = bars + 3;                      // all rows of P are in shared memory (and PV of the tile before is read)
+    uint64_t* pv_full = bars + 4;                     // the MMAs of PV are done
+    uint64_t* pair_bar = bars + 5;                    // [4] the two warps of a lane quarter have both written their halves' figures
+    uint64_t* k_bar = bars + 9;                       // [NS] a key tile has landed
+    uint64_t* v_bar = bars + 9 + NS;                  // [NS] a value tile has landed
+    uint32_t* tmem_slot = (uint32_t*)(bars + 18);
     volatile int* failed = (volatile int*)(tmem_slot + 1);
+    float* half_max = (float*)(bars + 20);            // [2 tiles in flight][2 halves][128 rows]: maxima of the halves of the rows' scores
+    float* half_sum = half_max + 512;                 // [2 halves][128 rows]: the sums, at the end
 
     const int warp = threadIdx.x >> 5;
-    const int row = threadIdx.x;                      // this thread's query row of the tile, and its lane of tensor memory
-    const int qpos = q0 + row;
 
     if (threadIdx.x == 0) {
         mbar_init(q_bar, 1);
-        mbar_init(&k_bar[0], 1);
-        mbar_init(&k_bar[1], 1);
-        mbar_init(v_bar, 1);
-        mbar_init(s_bar, 1);
-        mbar_init(pv_bar, 1);
+        for (int i = 0; i < NS; ++i) { mbar_init(&k_bar[i], 1); mbar_init(&v_bar[i], 1); }
+        mbar_init(s_full, 1);
+        mbar_init(s_free, kRowThreads);
+        mbar_init(p_full, kRowThreads);
+        mbar_init(pv_full, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);   // (not the warp whose first thread has just branched off)
+    if (warp == kIssueWarp) tmem_alloc(tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
 
     // key tiles this query tile sees
     const int q_last = min(q0 + kBM, seq_len) - 1;
     const int first_key = a.window > 0 ? max(0, q0 - a.window + 1) : 0;
     const int kt0 = first_key / kBN;
     const int n_kt = q_last / kBN - kt0 + 1;
-
-    const uint32_t idesc_s = instr_desc(kBM, kBN);
-    const uint32_t idesc_pv = instr_desc(kBM, HD) | (1u << 16);   // B (= V) is MN-major
-
-    auto load_k = [&](int t) {      // key tile t (counted from kt0) into buffer t & 1
-        uint8_t* dst = k_s + (size_t)(t & 1) * kQBytes;
-        mbar_expect_tx(&k_bar[t & 1], (uint32_t)kQBytes);
-#pragma unroll
-        for (int b = 0; b < DB; ++b)
-            tma_load_2d(dst + b * kBlockBytes, &map_k, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &k_bar[t & 1]);
-    };
-    auto load_v = [&](int t) {
-        mbar_expect_tx(v_bar, (uint32_t)kQBytes);
-#pragma unroll
-        for (int b = 0; b < DB; ++b)
-            tma_load_2d(v_s + b * kBlockBytes, &map_v, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, v_bar);
-    };
-    auto issue_s = [&](int t) {     // S = Q K^T for key tile t
-        const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + (size_t)(t & 1) * kQBytes);
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-            const uint32_t off = (uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32;
-            umma_bf16(tmem_s, smem_desc(qa + off), smem_desc(ka + off), idesc_s, ks > 0 ? 1u : 0u);
-        }
-        umma_commit(s_bar);
-    };
-    auto issue_pv = [&]() {         // PV = P V for the tile whose P lies in shared memory
-        const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s);
-#pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks) {
-            const uint32_t p_off = (uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32;
-            const uint32_t v_off = (uint32_t)ks * 16 * 128;          // 16 keys of 128 bytes
-            umma_bf16(tmem_pv, smem_desc(pa + p_off), smem_desc_mn(va + v_off, kBlockBytes, 1024), idesc_pv, ks > 0 ? 1u : 0u);
-        }
-        umma_commit(pv_bar);
-    };
     auto fail = [&](int code) {
         *failed = 1;
         if (a.error) atomicExch(a.error, code);
     };
 
-    if (threadIdx.x == 0) {
-        mbar_expect_tx(q_bar, (uint32_t)kQBytes);
+    if (warp == kIssueWarp) {
+        // ---- one thread issues the copies and the MMAs ----------------------------------------------------
+        if ((threadIdx.x & 31) == 0) {
+            const uint32_t idesc_s = instr_desc(kBM, kBN);
+            const uint32_t idesc_pv = instr_desc(kBM, HD) | (1u << 16);   // B (= V) is MN-major
+            // key or value tile t (counted from kt0) lives in stage t % NS; its barrier has parity (t / NS) & 1
+            auto load_k = [&](int t) {
+                uint8_t* dst = k_s + (size_t)(t % NS) * kQBytes;
+                mbar_expect_tx(&k_bar[t % NS], (uint32_t)kQBytes);
 #pragma unroll
-        for (int b = 0; b < DB; ++b) tma_load_2d(q_s + b * kBlockBytes, &map_q, h * HD + b * 64, seq_start + q0, q_bar);
-        load_k(0);
-        load_v(0);
-        if (n_kt > 1) load_k(1);
-        if (mbar_wait(q_bar, 0) && mbar_wait(&k_bar[0], 0)) {
-            tc_fence_after();
-            issue_s(0);
-        } else {
-            fail(11);
+                for (int b = 0; b < DB; ++b)
+                    tma_load_2d(dst + b * kBlockBytes, &map_k, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &k_bar[t % NS]);
+            };
+            auto load_v = [&](int t) {
+                uint8_t* dst = v_s + (size_t)(t % NS) * kQBytes;
+                mbar_expect_tx(&v_bar[t % NS], (uint32_t)kQBytes);
+#pragma unroll
+                for (int b = 0; b < DB; ++b)
+                    tma_load_2d(dst + b * kBlockBytes, &map_v, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &v_bar[t % NS]);
+            };
+            // The descriptors of a tile's k-steps differ in the start address only (bits 0-13, in units of 16 bytes):
+            // built once, then advanced by an addition; this thread has nobody to hide its arithmetic behind.
+            const uint64_t desc_q = smem_desc(smem_u32(q_s)), desc_k0 = smem_desc(smem_u32(k_s));
+            const uint64_t desc_p = smem_desc(smem_u32(p_s)), desc_v0 = smem_desc_mn(smem_u32(v_s), kBlockBytes, 1024);
+            auto issue_s = [&](int t) {     // S = Q K^T for key tile t
+                const uint64_t desc_k = desc_k0 + (uint64_t)(((uint32_t)(t % NS) * kQBytes) >> 4);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint64_t off = (uint64_t)(((uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32) >> 4);
+                    umma_bf16(tmem_s, desc_q + off, desc_k + off, idesc_s, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full);
+            };
+            auto issue_pv = [&](int t) {    // PV = P V for tile t, whose P lies in shared memory
+                const uint64_t desc_v = desc_v0 + (uint64_t)(((uint32_t)(t % NS) * kQBytes) >> 4);
+#pragma unroll
+                for (int ks = 0; ks < kBN / 16; ++ks) {
+                    const uint64_t p_off = (uint64_t)(((uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32) >> 4);
+                    const uint64_t v_off = (uint64_t)(((uint32_t)ks * 16 * 128) >> 4);   // 16 keys of 128 bytes
+                    umma_bf16(tmem_pv, desc_p + p_off, desc_v + v_off, idesc_pv, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(pv_full);
+            };
+            mbar_expect_tx(q_bar, (uint32_t)kQBytes);
+#pragma unroll
+            for (int b = 0; b < DB; ++b) tma_load_2d(q_s + b * kBlockBytes, &map_q, h * HD + b * 64, seq_start + q0, q_bar);
+            for (int t = 0; t < NS && t < n_kt; ++t) {
+                load_k(t);
+                load_v(t);
+            }
+            bool ok = mbar_wait(q_bar, 0) && mbar_wait(&k_bar[0], 0);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0);
+            } else {
+                fail(11);
+            }
+            for (int it = 0; it < n_kt && ok; ++it) {
+                const uint32_t ph = (uint32_t)it & 1u;
+                // S of tile it is in the threads' registers: S of the next tile may overwrite it, and (S of tile it
+                // being done) the key stage of tile it may take tile it + NS
+                if (!(ok = mbar_wait(s_free, ph))) { fail(12); break; }
+                tc_fence_after();
+                if (it + 1 < n_kt) {
+                    if (!(ok = mbar_wait(&k_bar[(it + 1) % NS], (uint32_t)((it + 1) / NS) & 1u))) { fail(13); break; }
+                    tc_fence_after();
+                    issue_s(it + 1);
+                }
+                if (it + NS < n_kt) load_k(it + NS);
+                // P of tile it is in shared memory, and the threads have read PV of the tile before: that one's
+                // value stage may take tile it - 1 + NS
+                if (!(ok = mbar_wait(p_full, ph))) { fail(14); break; }
+                if (it >= 1 && it - 1 + NS < n_kt) load_v(it - 1 + NS);
+                if (!(ok = mbar_wait(&v_bar[it % NS], (uint32_t)(it / NS) & 1u))) { fail(15); break; }
+                tc_fence_after();
+                issue_pv(it);
+            }
         }
-    }
-
-    float o[HD];
+    } else {
+        // ---- 256 threads, two per query row: its lane of tensor memory, and 64 of the tile's 128 keys ----------
+        const int quarter = warp & 3, half = warp >> 2;
+        const int row = quarter * 32 + (threadIdx.x & 31);
+        const int qpos = q0 + row;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        constexpr int OW = HD / 2;          // columns of the output this thread keeps
+        float o[OW];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
-    float m = -CUDART_INF_F, l = 0.f;
-
-    for (int it = 0; it < n_kt; ++it) {
-        const int n0 = (kt0 + it) * kBN;
-        if (!mbar_wait(s_bar, (uint32_t)it & 1u)) fail(12);
-        tc_fence_after();
-        // every key of the tile visible to every query of the tile: no mask needed
-        const bool full = n0 + kBN - 1 <= q0 && n0 + kBN - 1 < seq_len && (a.window <= 0 || n0 > q0 + kBM - 1 - a.window);
-        // otherwise this row sees the keys n0 + j with vis_lo <= j <= vis_hi
-        const int vis_hi = min(qpos, seq_len - 1) - n0;
-        const int vis_lo = a.window > 0 ? qpos - a.window + 1 - n0 : -(1 << 30);
-        // The row's scores are read from tensor memory SW columns at a time: all 128 at once when the registers
-        // allow it (head size 64), else twice 64, in two passes (maximum first, then the exponentials).
-        constexpr int SW = HD == 64 ? 128 : 64, NS = kBN / SW;
-        float sv[SW];
-        auto read_scores = [&](int part) {
-            if constexpr (SW == 128) tmem_ld128(tmem_s + lane_base, sv);
-            else tmem_ld64(tmem_s + lane_base + (uint32_t)(part * SW), sv);
-            if (!full) {
+        for (int i = 0; i < OW; ++i) o[i] = 0.f;
+        float m = -CUDART_INF_F, l = 0.f;   // the row's running maximum, and the sum over this thread's keys
+        bool ok = true;
+        // adds this thread's columns of PV of tile t (complete when pv_full has its phase t) to the output
+        auto add_pv = [&](int t) {
+            if (!mbar_wait(pv_full, (uint32_t)t & 1u)) { fail(17); ok = false; return; }
+            tc_fence_after();
 #pragma unroll
-                for (int j = 0; j < SW; ++j)
-                    if (part * SW + j > vis_hi || part * SW + j < vis_lo) sv[j] = -CUDART_INF_F;
+            for (int c = 0; c < OW / 32; ++c) {
+                float pv[32];
+                tmem_ld32(tmem_pv + lane_base + (uint32_t)(half * OW + c * 32), pv);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[c * 32 + j] += pv[j];
             }
         };
-        // maximum of the raw scores; the scale is positive, so it can be applied to the maximum
-        float raw = -CUDART_INF_F;
-#pragma unroll 1
-        for (int part = 0; part < NS; ++part) {
-            read_scores(part);
-#pragma unroll
-            for (int j = 0; j < SW; ++j) raw = fmaxf(raw, sv[j]);
-        }
-        const float mx = fmaxf(m, raw * a.scale_log2);
-        // a row that has seen no key yet keeps m = -inf; 0 as its reference avoids inf - inf
-        const float ref = mx == -CUDART_INF_F ? 0.f : mx;
-        const float corr = ex2_approx(m - ref);
-        m = mx;
-        // P = 2^(S * scale - max) as bfloat16 into shared memory, and its sum
-        float sum = 0.f;
-#pragma unroll 1
-        for (int part = 0; part < NS; ++part) {
-            if (NS > 1) read_scores(part);
-#pragma unroll
-            for (int c = 0; c < SW / 8; ++c) {       // pieces of 8 keys (16 bytes)
-                uint32_t pk[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = ex2_approx(fmaf(sv[c * 8 + 2 * e], a.scale_log2, -ref));
-                    const float p1 = ex2_approx(fmaf(sv[c * 8 + 2 * e + 1], a.scale_log2, -ref));
-                    sum += p0 + p1;
-                    pk[e] = pack_bf16(p0, p1);
-                }
-                // the piece's place within its block of 64 keys is swizzled with the row
-                const int piece = part * (SW / 8) + c;
-                uint8_t* prow = p_s + (size_t)(piece / 8) * kBlockBytes + (size_t)row * 128;
-                *reinterpret_cast<uint4*>(prow + (((piece % 8) ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
-        }
-        l = l * corr + sum;
-        // P is written: make it visible to the tensor core's reads, then everyone meets
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        tc_fence_before();
-        if (__syncthreads_or(*failed)) break;   // (evaluated by every thread as it arrives: the same answer for all)
-        if (threadIdx.x == 0) {
-            tc_fence_after();
-            if (mbar_wait(v_bar, (uint32_t)it & 1u)) {
-                tc_fence_after();
-                issue_pv();
-                if (it + 1 < n_kt) {
-                    if (mbar_wait(&k_bar[(it + 1) & 1], (uint32_t)((it + 1) >> 1) & 1u)) {
-                        tc_fence_after();
-                        issue_s(it + 1);
-                    } else {
-                        fail(13);
-                    }
-                }
-                if (it + 2 < n_kt) load_k(it + 2);   // S of this tile is done: its key buffer is free
-            } else {
-                fail(14);
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] *= corr;
-        if (!mbar_wait(pv_bar, (uint32_t)it & 1u)) fail(15);
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-            float pv[32];
-            tmem_ld32(tmem_pv + lane_base + (uint32_t)(c * 32), pv);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) o[c * 32 + j] += pv[j];
-        }
-        if (threadIdx.x == 0 && it + 1 < n_kt && !*failed) load_v(it + 1);   // PV is done: the value buffer is free
-    }
 
-    if (!*failed && qpos < seq_len) {
-        const float inv = 1.0f / l;
-        __nv_bfloat16* orow = a.out + ((size_t)(seq_start + qpos) * a.heads + h) * HD;
+        for (int it = 0; it < n_kt && ok; ++it) {
+            const int n0 = (kt0 + it) * kBN + half * 64;     // this thread's first key of the tile
+            // every key of the tile visible to every query of the tile: no mask needed
+            const int t0 = (kt0 + it) * kBN;
+            const bool full = t0 + kBN - 1 <= q0 && t0 + kBN - 1 < seq_len && (a.window <= 0 || t0 > q0 + kBM - 1 - a.window);
+            // otherwise this row sees the keys n0 + j with vis_lo <= j <= vis_hi
+            const int vis_hi = min(qpos, seq_len - 1) - n0;
+            const int vis_lo = a.window > 0 ? qpos - a.window + 1 - n0 : -(1 << 30);
+            if (!mbar_wait(s_full, (uint32_t)it & 1u)) { fail(18); ok = false; break; }
+            tc_fence_after();
+            // this thread's 64 scores into registers; then S may be overwritten
+            float sv[64];
+            tmem_ld64(tmem_s + lane_base + (uint32_t)(half * 64), sv);
+            tc_fence_before();
+            mbar_arrive(s_free);
+            if (!full) {
 #pragma unroll
-        for (int i = 0; i < HD; i += 8)
-            *reinterpret_cast<uint4*>(orow + i) =
-                make_uint4(pack_bf16(o[i] * inv, o[i + 1] * inv), pack_bf16(o[i + 2] * inv, o[i + 3] * inv),
-                           pack_bf16(o[i + 4] * inv, o[i + 5] * inv), pack_bf16(o[i + 6] * inv, o[i + 7] * inv));
+                for (int j = 0; j < 64; ++j)
+                    if (j > vis_hi || j < vis_lo) sv[j] = -CUDART_INF_F;
+            }
+            // maximum of the raw scores (the scale is positive, so it can be applied afterwards); eight running
+            // maxima and four running sums, not one chain of dependent instructions
+            float raw8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) raw8[e] = sv[e];
+#pragma unroll
+            for (int j = 8; j < 64; ++j) raw8[j & 7] = fmaxf(raw8[j & 7], sv[j]);
+            float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
+                              fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
+            // the other half's maximum, through shared memory; the two warps of a lane quarter meet at their own barrier
+            half_max[(it & 1) * 256 + half * 128 + row] = raw;
+            mbar_arrive(&pair_bar[quarter]);
+            if (!mbar_wait(&pair_bar[quarter], (uint32_t)it & 1u)) { fail(19); ok = false; break; }
+            raw = fmaxf(raw, half_max[(it & 1) * 256 + (half ^ 1) * 128 + row]);
+            const float mx = fmaxf(m, raw * a.scale_log2);
+            // a row that has seen no key yet keeps m = -inf; 0 as its reference avoids inf - inf
+            const float ref = mx == -CUDART_INF_F ? 0.f : mx;
+            const float corr = ex2_approx(m - ref);
+            m = mx;
+            // P = 2^(S * scale - max) as bfloat16, and its sum
+            uint32_t pk[32];
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 64; j += 2) {
+                const float p0 = ex2_approx(fmaf(sv[j], a.scale_log2, -ref));
+                const float p1 = ex2_approx(fmaf(sv[j + 1], a.scale_log2, -ref));
+                sum4[(j / 2) & 3] += p0 + p1;
+                pk[j / 2] = pack_bf16(p0, p1);
+            }
+            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            // the tile before: its PV into the output (it ran under this tile's arithmetic), which also frees P
+            if (it > 0) add_pv(it - 1);
+            if (!ok) break;
+            if (corr != 1.0f) {
+#pragma unroll
+                for (int i = 0; i < OW; ++i) o[i] *= corr;
+            }
+            // this thread's 64 keys are block `half` of P: pieces of 8 keys (16 bytes), swizzled with the row
+            uint8_t* prow = p_s + (size_t)half * kBlockBytes + (size_t)row * 128;
+#pragma unroll
+            for (int piece = 0; piece < 8; ++piece)
+                *reinterpret_cast<uint4*>(prow + ((piece ^ (row & 7)) << 4)) =
+                    make_uint4(pk[4 * piece], pk[4 * piece + 1], pk[4 * piece + 2], pk[4 * piece + 3]);
+            // P is written: make it visible to the tensor core's reads, then tell the issuing thread
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(p_full);
+        }
+        if (ok && n_kt > 0) add_pv(n_kt - 1);
+        // the row's sum is the two halves' (both against the same maximum)
+        half_sum[half * 128 + row] = l;
+        mbar_arrive(&pair_bar[quarter]);
+        if (!mbar_wait(&pair_bar[quarter], (uint32_t)n_kt & 1u)) { fail(20); ok = false; }
+        l += half_sum[(half ^ 1) * 128 + row];
+        if (ok && !*failed && qpos < seq_len) {
+            const float inv = 1.0f / l;
+            __nv_bfloat16* orow = a.out + ((size_t)(seq_start + qpos) * a.heads + h) * HD + half * OW;
+#pragma unroll
+            for (int i = 0; i < OW; i += 8)
+                *reinterpret_cast<uint4*>(orow + i) =
+                    make_uint4(pack_bf16(o[i] * inv, o[i + 1] * inv), pack_bf16(o[i + 2] * inv, o[i + 3] * inv),
+                               pack_bf16(o[i + 4] * inv, o[i + 5] * inv), pack_bf16(o[i + 6] * inv, o[i + 7] * inv));
+        }
     }
+    __syncwarp();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+    if (warp == kIssueWarp) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -325,7 +369,8 @@ template <int HD>
 void launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillTcArgs& a, int n_tiles,
             cudaStream_t stream) {
     constexpr int DB = HD / 64;
-    const size_t smem = 1024 + (size_t)(4 * DB + 2) * kBlockBytes + 64;   // alignment, Q + 2 K + V, P, barriers
+    // alignment; Q, the stages of K and V, P; barriers; maxima and sums
+    const size_t smem = 1024 + (size_t)((1 + 2 * kv_stages(HD)) * DB + 2) * kBlockBytes + 160 + 3 * 256 * sizeof(float);
     auto kernel = prefill_attention_tc_kernel<HD>;
     static bool prepared = false;
     if (!prepared) {
@@ -333,13 +378,13 @@ void launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
         if (e != cudaSuccess) throw std::runtime_error(std::string("attention_prefill_tc: ") + cudaGetErrorString(e));
         prepared = true;
     }
-    kernel<<<dim3(n_tiles, a.heads), kThreads, smem, stream>>>(mq, mk, mv, a);
+    kernel<<<dim3(a.heads, n_tiles), kThreads, smem, stream>>>(mq, mk, mv, a);
 }
 
 }  // namespace
 
 bool attention_prefill_tc_supports(int heads, int kv_heads, int head_dim) {
-    return (head_dim == 64 || head_dim == 128) && kv_heads > 0 && heads % kv_heads == 0 && heads <= 65535;
+    return (head_dim == 64 || head_dim == 128) && kv_heads > 0 && heads % kv_heads == 0;
 }
 
 void attention_prefill_tc(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles, int T,
@@ -349,6 +394,7 @@ void attention_prefill_tc(const void* q, const void* k, const void* v, void* out
     if (!attention_prefill_tc_supports(heads, kv_heads, head_dim))
         throw std::invalid_argument("attention_prefill_tc: head_dim " + std::to_string(head_dim) +
                                     " is not 64 or 128 (the mma.sync kernel takes multiples of 16 up to 128)");
+    if (n_tiles > 65535) throw std::invalid_argument("attention_prefill_tc: more than 65535 tiles of 64 queries");
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
         throw std::invalid_argument("attention_prefill_tc: operands must be 16-byte aligned");
     const CUtensorMap mq = make_map(q, T, heads * head_dim);
