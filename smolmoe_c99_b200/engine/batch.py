@@ -48,22 +48,21 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
         mode = "decode"
     else:
         raise ValueError("the sequences of a step either all start at their first token or all go on by one token")
-    tokens: List[int] = []
-    positions: List[int] = []
-    token_slot: List[int] = []
-    token_end: List[int] = []
-    token_seq_start: List[int] = []
-    cu = [0]
-    for slot, start, toks in zip(slots, starts, token_lists):
-        first = len(tokens)
-        n = len(toks)
-        tokens.extend(int(t) for t in toks)
-        positions.extend(range(start, start + n))
-        token_slot.extend([slot] * n)
-        token_end.extend([start + n] * n)
-        token_seq_start.extend([first] * n)
-        cu.append(first + n)
-    host = torch.tensor([tokens, positions, token_slot, token_end, token_seq_start], dtype=torch.int32)
+    # the step's numbers, one row per quantity, built with tensor operations (a prompt of thousands of tokens
+    # would spend a millisecond in Python loops otherwise)
+    n_seqs = len(slots)
+    lens_t = torch.tensor(lens, dtype=torch.int64)
+    starts_t = torch.tensor(list(starts), dtype=torch.int64)
+    slots_t = torch.tensor(list(slots), dtype=torch.int64)
+    ends = torch.cumsum(lens_t, 0)
+    firsts = ends - lens_t
+    cu = [0] + ends.tolist()
+    n_tokens = cu[-1]
+    flat = [t for toks in token_lists for t in toks] if n_seqs > 1 else token_lists[0]
+    tokens = torch.as_tensor(flat, dtype=torch.int64)
+    seq_of = torch.repeat_interleave(torch.arange(n_seqs), lens_t)
+    positions = torch.arange(n_tokens) - firsts[seq_of] + starts_t[seq_of]
+    host = torch.stack([tokens, positions, slots_t[seq_of], (starts_t + lens_t)[seq_of], firsts[seq_of]]).to(torch.int32)
     dev = host.to(device)
     tiles = None
     if mode == "prefill":
@@ -71,7 +70,7 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
                              dtype=torch.int32).to(device)
     per_seq = torch.tensor([list(slots), [s + n for s, n in zip(starts, lens)]], dtype=torch.int32).to(device)
     return StepBatch(
-        mode=mode, n_seqs=len(slots), n_tokens=len(tokens), slots=list(slots), seq_lens=lens,
+        mode=mode, n_seqs=len(slots), n_tokens=n_tokens, slots=list(slots), seq_lens=lens,
         max_seq_len=max(s + n for s, n in zip(starts, lens)),
         tokens=dev[0], positions=dev[1], token_slot=dev[2], token_end=dev[3], token_seq_start=dev[4],
         cu_seqlens=torch.tensor(cu, dtype=torch.int32).to(device), slot_ids=per_seq[0], seq_ends=per_seq[1],

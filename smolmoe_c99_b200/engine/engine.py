@@ -139,9 +139,9 @@ class Engine:
                 raise StepError("slots and token lists must have one entry per sequence")
             lens = [len(t) for t in tokens]
             for toks in tokens:
-                for t in toks:
-                    if not 0 <= int(t) < self.vocab_size:  # src/model.c:673
-                        raise StepError(f"token {t} out of vocabulary ({self.vocab_size})")
+                if len(toks) and not (0 <= min(toks) and max(toks) < self.vocab_size):  # src/model.c:673
+                    bad = next(t for t in toks if not 0 <= int(t) < self.vocab_size)
+                    raise StepError(f"token {bad} out of vocabulary ({self.vocab_size})")
         if n == 0 or any(k == 0 for k in lens):
             raise StepError("a step needs at least one sequence, and every sequence at least one token")
         if want is not None and len(want) != n:
