@@ -1,6 +1,7 @@
 """Each part alone against the plain implementation; the order list naming a layer twice and a
-layer that reads another layer's cache; and a toy mixer with state of its own, defined here,
-that is registered, built and stepped without a change to the library's files."""
+layer that reads another layer's cache; and toy parts defined here (a mixer with state of its
+own, a feed-forward with routing, another position encoding) that are registered, built and
+stepped without a change to the library's files."""
 import json
 import math
 import os
@@ -300,5 +301,134 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
             "batched": replay.batched(engine, [{r: requests[r] for r in ids[:3]}, {r: requests[r] for r in ids[2:]}],
                                       {r: max(1, len(t) // 3) for r, t in requests.items()})}
     for cut, got in cuts.items():          # the state is carried from step to step and starts at zero in a used slot
+        for r in got:
+            assert float((got[r] - want[r]).abs().max()) <= 2e-5, f"{cut} {r}"
+
+
+# ---- a toy feed-forward with routing, and another position encoding --------------------------------
+def _register_toy_routed():
+    from smolmoe_c99_b200.parts import FEED_FORWARDS, ParamSpec, Part, full_name
+
+    @FEED_FORWARDS.register("toy_routed")
+    class ToyRouted(Part):
+        """Router logits in float over E square experts; each token goes to its best expert, whose
+        output is weighted by that expert's softmax probability."""
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.size, self.experts = int(spec["hidden_size"]), int(spec["experts"])
+            self.router = self.w = None
+
+        @classmethod
+        def param_specs(cls, spec, prefix):
+            d, e = int(spec["hidden_size"]), int(spec["experts"])
+            return [ParamSpec("router", full_name(prefix, spec.names["router"]), (e, d)),
+                    ParamSpec("w", full_name(prefix, spec.names["experts"]), (e * d, d))]
+
+        def bind(self, tensors):
+            self.router, self.w = tensors["router"].float(), tensors["w"]
+
+        def forward(self, x, residual, step):
+            ops = self.runtime.ops
+            logits = x.float() @ self.router.T                           # router logits in 32-bit
+            prob, best = torch.softmax(logits, dim=-1).max(dim=-1)
+            every = ops.linear(x, self.w, None, out_dtype=torch.float32)   # all experts through the library's product
+            every = every.view(x.shape[0], self.experts, self.size)
+            picked = every[torch.arange(x.shape[0], device=x.device), best]
+            residual += picked * prob[:, None]
+    return ToyRouted
+
+
+def _register_toy_position():
+    from smolmoe_c99_b200.parts import POSITIONS, Part
+
+    @POSITIONS.register("toy_scaled_rope")
+    class ScaledRotary(Part):
+        """Rotary tables whose positions are divided by a factor (position interpolation)."""
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.theta, self.rotary_dim, self.factor = float(spec["theta"]), int(spec["rotary_dim"]), float(spec["factor"])
+            self._tables = None
+
+        def tables(self, n_positions):
+            if self._tables is None or self._tables[0].shape[0] < n_positions:
+                half = self.rotary_dim // 2
+                inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64),
+                                -(2.0 * torch.arange(half, dtype=torch.float64)) / self.rotary_dim)
+                angle = (torch.arange(n_positions, dtype=torch.float64) / self.factor)[:, None] * inv[None, :]
+                self._tables = (torch.cos(angle).float().to(self.runtime.device).contiguous(),
+                                torch.sin(angle).float().to(self.runtime.device).contiguous())
+            return self._tables
+    return ScaledRotary
+
+
+class ToyRoutedConfig:
+    """Layer 0: attention under the scaled position encoding; layer 1: the routed feed-forward."""
+    EXPERTS, FACTOR = 3, 4.0
+
+    def __init__(self, base):
+        self.base = base
+
+    @classmethod
+    def from_json(cls, raw):
+        from smolmoe_c99_b200.config import Qwen2Config
+        return cls(Qwen2Config.from_json(raw))
+
+    def to_json(self):
+        return dict(self.base.to_json(), architectures=["ToyRoutedForCausalLM"])
+
+    def model_spec(self):
+        from smolmoe_c99_b200.config import PartSpec
+        spec = self.base.model_spec()
+        l0, l1 = spec.layers
+        old = l0.mixer.params["position"]
+        scaled = PartSpec("toy_scaled_rope", dict(old.params, factor=self.FACTOR), old.names)
+        mixer0 = replace(l0.mixer, params=dict(l0.mixer.params, position=scaled))
+        routed = PartSpec("toy_routed", {"hidden_size": self.base.hidden_size, "experts": self.EXPERTS},
+                          {"router": "toy_ffn.router", "experts": "toy_ffn.experts"})
+        return replace(spec, architecture="ToyRoutedForCausalLM",
+                       layers=(replace(l0, mixer=mixer0), replace(l1, feed_forward=routed)))
+
+
+def _plain_toy_routed(model_dir, tokens):
+    cfg = plain_model.read_config(model_dir)
+    w = plain_model.read_safetensors(os.path.join(model_dir, "model.safetensors"))
+    n, d, e = len(tokens), cfg["hidden_size"], ToyRoutedConfig.EXPERTS
+    hd = plain_model.head_dim_of(cfg)
+    half = hd // 2
+    inv = torch.pow(torch.tensor(cfg["rope_theta"], dtype=torch.float64), -(2.0 * torch.arange(half, dtype=torch.float64)) / hd)
+    angle = (torch.arange(n, dtype=torch.float64) / ToyRoutedConfig.FACTOR)[:, None] * inv[None, :]
+    cos0, sin0 = torch.cos(angle).float(), torch.sin(angle).float()
+    cos1, sin1 = plain_model.rope_tables(n, hd, cfg["rope_theta"])
+    x = plain_model.embed(w["model.embed_tokens.weight"], tokens)
+    x = plain_model.ffn_block(plain_model.attention_block(x, w, "model.layers.0", cfg, 0, cos0, sin0), w, "model.layers.0", cfg, None)
+    x = plain_model.attention_block(x, w, "model.layers.1", cfg, 1, cos1, sin1)
+    y = plain_model.rmsnorm(x, w["model.layers.1.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+    prob, best = torch.softmax(y @ w["model.layers.1.toy_ffn.router"].T, dim=-1).max(dim=-1)
+    experts = w["model.layers.1.toy_ffn.experts"].view(e, d, d)
+    for t in range(n):
+        x[t] = x[t] + prob[t] * (experts[best[t]] @ y[t])
+    return plain_model.rmsnorm(x, w["model.norm.weight"], cfg["rms_norm_eps"]) @ w["model.embed_tokens.weight"].T
+
+
+def test_a_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """Both are defined and registered here; the framework's files do not know them."""
+    from smolmoe_c99_b200.config import config_from_json, register_architecture
+    from smolmoe_c99_b200.engine.engine import Engine
+    from smolmoe_c99_b200.weights import write_random_model
+    _register_toy_routed()
+    _register_toy_position()
+    register_architecture("ToyRoutedForCausalLM", ToyRoutedConfig)
+    cfg = config_from_json(dict(TINY["A"], architectures=["ToyRoutedForCausalLM"]))
+    folder = write_random_model(cfg, str(tmp_path / "routed"), 11)
+    engine = Engine(folder, "float32", max_tokens=1024, max_slots=3)
+    requests = {f"r{i}": random_tokens(n, 256, 40 + i) for i, n in enumerate([3, 35, 50, 70])}
+    want = {r: _plain_toy_routed(folder, t) for r, t in requests.items()}
+    ids = list(requests)
+    cuts = {"whole": replay.whole(engine, requests), "tail": replay.tail_decoded(engine, requests),
+            "batched": replay.batched(engine, [{r: requests[r] for r in ids[:3]}, {r: requests[r] for r in ids[2:]}],
+                                      {r: max(1, len(t) // 3) for r, t in requests.items()})}
+    for cut, got in cuts.items():
         for r in got:
             assert float((got[r] - want[r]).abs().max()) <= 2e-5, f"{cut} {r}"
