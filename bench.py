@@ -39,6 +39,15 @@ def base_config():
     return cfg
 
 
+# BASELINE.json's configs[3] and configs[4], as they state them
+OTHER_SHAPES = {
+    "1.5b": {"num_hidden_layers": 28, "hidden_size": 1536, "num_attention_heads": 12, "num_key_value_heads": 2, "head_dim": 128,
+             "intermediate_size": 8960, "vocab_size": 151936, "tie_word_embeddings": True},
+    "7b": {"num_hidden_layers": 28, "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4, "head_dim": 128,
+           "intermediate_size": 18944, "vocab_size": 152064, "tie_word_embeddings": False},
+}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -123,6 +132,10 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--shape", choices=sorted(OTHER_SHAPES) + ["0.5b"], default="0.5b",
+                    help="layer sizes: BASELINE.json's configs[2] (default), or configs[3] / configs[4] as they state them")
+    ap.add_argument("--prompt-min", type=int, default=None,
+                    help="prompts of unequal lengths, uniform between this and --prompt-len (default: all of --prompt-len)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--profile-region", choices=["decode", "prefill"], default=None,
                     help="for ncu --profile-from-start off: run only this region between cudaProfilerStart/Stop "
@@ -144,6 +157,8 @@ def main() -> int:
     from smolmoe_c99_b200.weights import write_random_model
 
     raw = base_config()
+    if args.shape != "0.5b":
+        raw.update(OTHER_SHAPES[args.shape])
     layers_full = raw["num_hidden_layers"]
     if args.layers:
         raw["num_hidden_layers"] = args.layers
@@ -161,7 +176,8 @@ def main() -> int:
     V = cfg.vocab_size
 
     def prompts(n):
-        return [torch.randint(0, V, (P,), generator=gen).tolist() for _ in range(n)]
+        lens = [P] * n if args.prompt_min is None else torch.randint(args.prompt_min, P + 1, (n,), generator=gen).tolist()
+        return [torch.randint(0, V, (k,), generator=gen).tolist() for k in lens]
 
     def open_and_prefill(n):
         slots = [engine.open_sequence() for _ in range(n)]
@@ -249,14 +265,17 @@ def main() -> int:
     engine.check_status()
 
     line = {
-        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if (args.shape, B, P, C, args.prompt_min) == ("0.5b", 8, 2048, 4096, None) else
+        f"decode tok/s at batch {B} (Qwen2.5-{args.shape.upper()} shape, bf16, prompts of up to {P} tokens, context {C})",
+        "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: uniform random token ids (seed 0), random weights N(0, 0.02) (seed 0)",
-        "config": {"model": "Qwen2.5-0.5B shape", "global_batch": B, "seq_len": C, "prompt_len": P, "parallelism": "none (1 GPU)",
+        "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "global_batch": B, "seq_len": C, "prompt_len": P,
+                   "prompt_min": args.prompt_min if args.prompt_min is not None else P, "parallelism": "none (1 GPU)",
                    "layers": raw["num_hidden_layers"], "layers_of_configuration": layers_full, "hidden": raw["hidden_size"],
                    "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
-                   "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"], "tied_embeddings": True,
-                   "l2": "each step reads ~1 GB of weights plus the cache (> 126 MB L2); no flush"},
+                   "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"], "tied_embeddings": bool(raw["tie_word_embeddings"]),
+                   "l2": f"each step reads {engine.weight_bytes() / 1e9:.2f} GB of weights plus the cache (> 126 MB L2); no flush"},
         "clocks": clock_summary, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
         "launches_per_step": launches_per_step, "prefill": prefill, "roofline": roofline, "points": points,
         "impl": "ours",

@@ -490,6 +490,27 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
     const int sms = device_sm_count();
     const int tiles_m = (N + kTileM - 1) / kTileM;
     const int t16 = ((T + 15) / 16) * 16;
+    const int kb = (K + kBlockK - 1) / kBlockK;
+    if (T <= 64) {
+        // A handful of tokens: the product is bound by reading the weights once. One token tile (so that no
+        // weight row is read twice) and, where the row tiles are too few to fill the machine (two CTAs an SM),
+        // K split among CTAs, at least four blocks of 64 each; the partial sums cost T x N floats a split.
+        int sp = 1;
+        if (tiles_m < 2 * sms && kb >= 8) {
+            sp = (2 * sms + tiles_m - 1) / tiles_m;
+            if (sp > kb / 4) sp = kb / 4;
+            if (sp > 16) sp = 16;
+            if (sp < 1) sp = 1;
+        }
+        const int per = (kb + sp - 1) / sp;
+        sp = (kb + per - 1) / per;
+        if (tiles_m * sp * 2 >= sms) {
+            *tile_n = t16;
+            *splits = sp;
+            return;
+        }
+        // (a matrix this small stays in L2: token tiles that read it again, as below, give more CTAs)
+    }
     const int max_tile = dual ? 128 : 256;
     int tn = 16;
     // the largest token tile that keeps most of the machine busy, else the smallest that covers T
@@ -500,7 +521,6 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
         if (tiles * 10 >= sms * 7) break;
     }
     const int tiles = tiles_m * ((T + tn - 1) / tn);
-    const int kb = (K + kBlockK - 1) / kBlockK;
     int sp = 1;
     if (tiles * 2 < sms && kb >= 4) {
         sp = (2 * sms + tiles - 1) / tiles;
