@@ -138,17 +138,15 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const TW* __restrict__ w, float
 template <typename TW, typename TO>
 static void launch_norm(const float* x, const void* w, float eps, void* out, const int32_t* rows, int n_rows, int D,
                         cudaStream_t stream) {
-    // rows whose length is a multiple of 4 and at most 4096 fit the warp-per-row kernel. The
-    // choice depends on D alone, never on the number of rows: a row's result must not depend on
-    // how many rows come with it
-    if (D % 4 == 0 && D <= 4096) {
+    // rows whose length is a multiple of 4 and at most 2048 go to the warp-per-row kernel; a longer row is
+    // worth a block of its own (at 3,584 a warp a row took 8 us for 64 rows). The choice depends on D alone,
+    // never on the number of rows: a row's result must not depend on how many rows come with it
+    if (D % 4 == 0 && D <= 2048) {
         const unsigned blocks = (unsigned)((n_rows + kRowWarps - 1) / kRowWarps);
         if (D <= 1024)
             rmsnorm_rows_kernel<TW, TO, 8><<<blocks, kRowWarps * 32, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
-        else if (D <= 2048)
-            rmsnorm_rows_kernel<TW, TO, 16><<<blocks, kRowWarps * 32, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
         else
-            rmsnorm_rows_kernel<TW, TO, 32><<<blocks, kRowWarps * 32, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
+            rmsnorm_rows_kernel<TW, TO, 16><<<blocks, kRowWarps * 32, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
         return;
     }
     rmsnorm_kernel<TW, TO><<<n_rows, kNormThreads, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, D);

@@ -405,10 +405,20 @@ __global__ void splitk_reduce_kernel(GemmParams p) {
     size_t total = (size_t)p.T * p.N;
     if (i >= total) return;
     int n = (int)(i % p.N);
+    // all the partial sums first (at most 16 splits: the loads are in flight together), then added in split order
+    float part[16], part_up[16];
+#pragma unroll
+    for (int s = 0; s < 16; ++s) {
+        part[s] = s < p.splits ? p.workspace[(size_t)s * total + i] : 0.f;
+        part_up[s] = p.dual && s < p.splits ? p.workspace[((size_t)p.splits + s) * total + i] : 0.f;
+    }
     float g = 0.f, u = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-        g += p.workspace[(size_t)s * total + i];
-        if (p.dual) u += p.workspace[((size_t)p.splits + s) * total + i];
+#pragma unroll
+    for (int s = 0; s < 16; ++s) {
+        if (s < p.splits) {
+            g += part[s];
+            u += part_up[s];
+        }
     }
     float v = g;
     if (p.epilogue == EPI_SWIGLU) v = u * (g / (1.0f + __expf(-g)));
