@@ -210,6 +210,50 @@ class Engine:
         g.graph.replay()
         return g.logits
 
+    # ---- a one-token step in two halves ----------------------------------------------------
+    def prepare_decode(self, slots: Sequence[int]):
+        """The host's share of the next one-token step of ``slots`` that does not depend on the tokens:
+        room in the cache, and the step's positions and slots copied into the captured graph's buffers
+        (in stream order, so behind the step that may still be running). A generation loop calls this
+        before it waits for the tokens it has just chosen, and ``launch_prepared`` after. Returns None where
+        the plain ``step`` has to do it (no graphs, a graph still to be captured, a sequence at its start)."""
+        n = len(slots)
+        if not self.use_graphs or n == 0 or len(set(slots)) != n or any(s not in self.cache.lengths for s in slots):
+            return None
+        starts = [self.cache.length(slot) for slot in slots]
+        if min(starts) == 0:
+            return None
+        longest = max(starts) + 1
+        span = SPAN_BUCKET
+        while span < longest:
+            span *= 2
+        span = min(span, -(-self.max_seq_len // 128) * 128)
+        g = self._graphs.get((n, span))
+        if g is None or g.graph is None:
+            return None
+        try:
+            self.cache.reserve({slot: 1 for slot in slots})
+        except CacheFull:
+            return None
+        self.cache.flush_tables()
+        self._graphs.move_to_end((n, span))
+        g.meta[1:].copy_(torch.tensor([list(starts), list(slots), [s + 1 for s in starts]], dtype=torch.int32))
+        return g, tuple(slots), tuple(starts)
+
+    def launch_prepared(self, prepared, tokens: torch.Tensor) -> torch.Tensor:
+        """Runs the step that ``prepare_decode`` prepared, with one int32 device token per sequence; returns
+        the logits of every sequence like ``step``."""
+        g, slots, starts = prepared
+        if tokens.dtype != torch.int32 or tokens.dim() != 1 or tokens.numel() != len(slots) or not tokens.is_cuda:
+            raise StepError("device tokens must be an int32 CUDA tensor with one token per sequence")
+        if tuple(self.cache.lengths.get(slot, -1) for slot in slots) != starts:
+            raise StepError("the sequences changed between prepare_decode and launch_prepared")
+        g.meta[0].copy_(tokens)
+        g.graph.replay()
+        self.kernel_launches += 1
+        self.cache.advance({slot: 1 for slot in slots})
+        return g.logits
+
     def synchronize(self) -> None:
         torch.cuda.synchronize(self.device)
 

@@ -97,6 +97,11 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], options: Generat
             stats.prompt_tokens += sum(len(prompts[r]) for r in live)
             for produced in range(1, options.max_new_tokens + 1):
                 chosen = sampler.choose(logits, states)
+                # while the choice is still being computed: the host's share of the next step that does not
+                # depend on it (an engine may offer this; it is redone the plain way if the batch changes)
+                prepared = None
+                if produced < options.max_new_tokens and hasattr(engine, "prepare_decode"):
+                    prepared = engine.prepare_decode([slots[r] for r in live])
                 tokens = [int(t) for t in chosen.tolist()]   # the one device-to-host read of the step
                 keep = []
                 for i, r in enumerate(live):
@@ -122,7 +127,11 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], options: Generat
                 if len(keep) != len(live):   # shorter requests have ended: the batch shrinks
                     chosen, states = sampler.select(chosen, keep), sampler.select(states, keep)
                     live = [live[i] for i in keep]
-                logits = engine.step([slots[r] for r in live], chosen)
+                    prepared = None
+                if prepared is not None:
+                    logits = engine.launch_prepared(prepared, chosen)
+                else:
+                    logits = engine.step([slots[r] for r in live], chosen)
                 stats.decode_forwards += len(live)
             engine.synchronize()
             stats.decode_seconds += clock() - t1

@@ -138,3 +138,33 @@ def test_zero_new_tokens():
     eng = FakeEngine()
     out = generate(eng, FakeSampler(), [[1]], GenerationOptions(max_new_tokens=0))
     assert out[0].tokens == [] and out[0].finish_reason == "length" and not eng.steps
+
+
+class TwoHalfEngine(FakeEngine):
+    """An engine that offers the one-token step in two halves, as the CUDA engine does."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.prepared, self.launched = 0, 0
+
+    def prepare_decode(self, slots):
+        self.prepared += 1
+        return ("handle", tuple(slots), tuple(self.lengths[s] for s in slots))
+
+    def launch_prepared(self, prepared, tokens):
+        _, slots, starts = prepared
+        assert tuple(self.lengths[s] for s in slots) == starts, "the sequences moved between the halves"
+        self.launched += 1
+        return self.step(list(slots), tokens)
+
+
+def test_a_two_half_step_changes_no_decision():
+    prompts = [[1], [7], [20]]
+    opts = GenerationOptions(max_new_tokens=6, stop_token_ids=(9, 23), batch=3)
+    plain, halves = FakeEngine(), TwoHalfEngine()
+    want = generate(plain, FakeSampler(), prompts, opts)
+    got = generate(halves, FakeSampler(), prompts, opts)
+    assert [(c.tokens, c.finish_reason) for c in got] == [(c.tokens, c.finish_reason) for c in want]
+    assert halves.steps == plain.steps                 # the same tokens fed to the same slots: no stop token, no last token
+    assert halves.launched >= 1 and halves.prepared > halves.launched   # a step whose batch shrank was redone the plain way
+    assert not halves.open
