@@ -57,4 +57,6 @@ def main(reference: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_reference_trace.py /path/to/smolmoe-c99")
+    main(sys.argv[1])
