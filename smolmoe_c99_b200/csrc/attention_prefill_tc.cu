@@ -40,10 +40,14 @@ constexpr int kBM = 128, kBN = 128;
 constexpr int kRowThreads = 256;      // two threads per query row (warps w and w + 4 share the rows of lane quarter w)
 constexpr int kIssueWarp = 8;         // the warp whose first thread issues copies and MMAs (and which owns tensor memory)
 constexpr int kThreads = kRowThreads + 32;
+constexpr int kSmCount = 148;            // for the choice between the kernel's two variants only
 constexpr int kBlockBytes = 128 * 128;      // 128 rows of 128 bytes: one swizzled block of 64 bfloat16 columns
 
-// key tiles, and value tiles, in flight: what fits beside Q and P in an SM's shared memory
-__host__ __device__ constexpr int kv_stages(int head_dim) { return head_dim == 64 ? 4 : 2; }
+// Key tiles, and value tiles, in shared memory. One CTA an SM: what fits beside Q and P (four and four at head
+// size 64, two and two at 128). Two CTAs an SM (`two`, head size 64 only): one key stage and two value stages,
+// 100 KB a CTA.
+__host__ __device__ constexpr int key_stages(int head_dim, bool two) { return two ? 1 : (head_dim == 64 ? 4 : 2); }
+__host__ __device__ constexpr int value_stages(int head_dim, bool two) { return two ? 2 : (head_dim == 64 ? 4 : 2); }
 
 struct PrefillTcArgs {
     __nv_bfloat16* out;       // [T, heads, HD]
@@ -71,14 +75,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int HD>
-__global__ void __launch_bounds__(kThreads, 1) prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+// TWO: the variant of which two CTAs share an SM (fewer registers and stages; scores read 32 at a time, in two
+// passes). It wins when every SM has many more key tiles to do than the longest chain of one CTA (long prompts):
+// one CTA's waits are then the other's work. With few tiles an SM (2,048 tokens) the launch waits for the
+// longest chain, which a second CTA on its SM only slows.
+template <int HD, bool TWO>
+__global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         PrefillTcArgs a) {
     constexpr int DB = HD / 64;                       // blocks of 64 columns of the head dimension
     constexpr int kQBytes = DB * kBlockBytes;         // Q tile, and one K or V tile
-    constexpr int NS = kv_stages(HD);                 // key tiles, and value tiles, in flight
+    constexpr int NSK = key_stages(HD, TWO), NSV = value_stages(HD, TWO);
     constexpr uint32_t kTmemCols = 256;               // S: 128 columns, PV: HD columns
     // CTAs start in the order of their index, the heads of one tile together: late tiles (most keys) first, so that
     // the longest chains of key tiles begin at once and the short ones fill the SMs that become free
@@ -90,9 +98,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_attention_tc_kernel(const
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = smem;                              // [DB][128 queries][128 B]
-    uint8_t* k_s = q_s + kQBytes;                     // NS x [DB][128 keys][128 B]
-    uint8_t* v_s = k_s + NS * kQBytes;                // NS x [DB][128 keys][128 B]
-    uint8_t* p_s = v_s + NS * kQBytes;                // [2][128 queries][128 B]: keys 0-63 and 64-127 of the tile
+    uint8_t* k_s = q_s + kQBytes;                     // NSK x [DB][128 keys][128 B]
+    uint8_t* v_s = k_s + NSK * kQBytes;               // NSV x [DB][128 keys][128 B]
+    uint8_t* p_s = v_s + NSV * kQBytes;               // [2][128 queries][128 B]: keys 0-63 and 64-127 of the tile
     uint64_t* bars = (uint64_t*)(p_s + 2 * kBlockBytes);
     uint64_t* q_bar = bars;                           // Q has landed
     uint64_t* s_full = bars + 1;                      // the MMAs of S are done
@@ -100,8 +108,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_attention_tc_kernel(const
     uint64_t* p_full = bars + 3;                      // all rows of P are in shared memory (and PV of the tile before is read)
     uint64_t* pv_full = bars + 4;                     // the MMAs of PV are done
     uint64_t* pair_bar = bars + 5;                    // [4] the two warps of a lane quarter have both written their halves' figures
-    uint64_t* k_bar = bars + 9;                       // [NS] a key tile has landed
-    uint64_t* v_bar = bars + 9 + NS;                  // [NS] a value tile has landed
+    uint64_t* k_bar = bars + 9;                       // [NSK] a key tile has landed
+    uint64_t* v_bar = bars + 9 + NSK;                 // [NSV] a value tile has landed
     uint32_t* tmem_slot = (uint32_t*)(bars + 18);
     volatile int* failed = (volatile int*)(tmem_slot + 1);
     float* half_max = (float*)(bars + 20);            // [2 tiles in flight][2 halves][128 rows]: maxima of the halves of the rows' scores
@@ -111,7 +119,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_attention_tc_kernel(const
 
     if (threadIdx.x == 0) {
         mbar_init(q_bar, 1);
-        for (int i = 0; i < NS; ++i) { mbar_init(&k_bar[i], 1); mbar_init(&v_bar[i], 1); }
+        for (int i = 0; i < NSK; ++i) mbar_init(&k_bar[i], 1);
+        for (int i = 0; i < NSV; ++i) mbar_init(&v_bar[i], 1);
         mbar_init(s_full, 1);
         mbar_init(s_free, kRowThreads);
         mbar_init(p_full, kRowThreads);
@@ -142,27 +151,27 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_attention_tc_kernel(const
         if ((threadIdx.x & 31) == 0) {
             const uint32_t idesc_s = instr_desc(kBM, kBN);
             const uint32_t idesc_pv = instr_desc(kBM, HD) | (1u << 16);   // B (= V) is MN-major
-            // key or value tile t (counted from kt0) lives in stage t % NS; its barrier has parity (t / NS) & 1
+            // key (value) tile t, counted from kt0, lives in stage t % NSK (NSV); its barrier has parity (t / NSK) & 1
             auto load_k = [&](int t) {
-                uint8_t* dst = k_s + (size_t)(t % NS) * kQBytes;
-                mbar_expect_tx(&k_bar[t % NS], (uint32_t)kQBytes);
+                uint8_t* dst = k_s + (size_t)(t % NSK) * kQBytes;
+                mbar_expect_tx(&k_bar[t % NSK], (uint32_t)kQBytes);
 #pragma unroll
                 for (int b = 0; b < DB; ++b)
-                    tma_load_2d(dst + b * kBlockBytes, &map_k, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &k_bar[t % NS]);
+                    tma_load_2d(dst + b * kBlockBytes, &map_k, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &k_bar[t % NSK]);
             };
             auto load_v = [&](int t) {
-                uint8_t* dst = v_s + (size_t)(t % NS) * kQBytes;
-                mbar_expect_tx(&v_bar[t % NS], (uint32_t)kQBytes);
+                uint8_t* dst = v_s + (size_t)(t % NSV) * kQBytes;
+                mbar_expect_tx(&v_bar[t % NSV], (uint32_t)kQBytes);
 #pragma unroll
                 for (int b = 0; b < DB; ++b)
-                    tma_load_2d(dst + b * kBlockBytes, &map_v, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &v_bar[t % NS]);
+                    tma_load_2d(dst + b * kBlockBytes, &map_v, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &v_bar[t % NSV]);
             };
             // The descriptors of a tile's k-steps differ in the start address only (bits 0-13, in units of 16 bytes):
             // built once, then advanced by an addition; this thread has nobody to hide its arithmetic behind.
             const uint64_t desc_q = smem_desc(smem_u32(q_s)), desc_k0 = smem_desc(smem_u32(k_s));
             const uint64_t desc_p = smem_desc(smem_u32(p_s)), desc_v0 = smem_desc_mn(smem_u32(v_s), kBlockBytes, 1024);
             auto issue_s = [&](int t) {     // S = Q K^T for key tile t
-                const uint64_t desc_k = desc_k0 + (uint64_t)(((uint32_t)(t % NS) * kQBytes) >> 4);
+                const uint64_t desc_k = desc_k0 + (uint64_t)(((uint32_t)(t % NSK) * kQBytes) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
                     const uint64_t off = (uint64_t)(((uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32) >> 4);
@@ -171,7 +180,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_attention_tc_kernel(const
                 umma_commit(s_full);
             };
             auto issue_pv = [&](int t) {    // PV = P V for tile t, whose P lies in shared memory
-                const uint64_t desc_v = desc_v0 + (uint64_t)(((uint32_t)(t % NS) * kQBytes) >> 4);
+                const uint64_t desc_v = desc_v0 + (uint64_t)(((uint32_t)(t % NSV) * kQBytes) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < kBN / 16; ++ks) {
                     const uint64_t p_off = (uint64_t)(((uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32) >> 4);
@@ -183,10 +192,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_attention_tc_kernel(const
             mbar_expect_tx(q_bar, (uint32_t)kQBytes);
 #pragma unroll
             for (int b = 0; b < DB; ++b) tma_load_2d(q_s + b * kBlockBytes, &map_q, h * HD + b * 64, seq_start + q0, q_bar);
-            for (int t = 0; t < NS && t < n_kt; ++t) {
-                load_k(t);
-                load_v(t);
-            }
+            for (int t = 0; t < NSK && t < n_kt; ++t) load_k(t);
+            for (int t = 0; t < NSV && t < n_kt; ++t) load_v(t);
             bool ok = mbar_wait(q_bar, 0) && mbar_wait(&k_bar[0], 0);
             if (ok) {
                 tc_fence_after();
@@ -196,21 +203,23 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_attention_tc_kernel(const
             }
             for (int it = 0; it < n_kt && ok; ++it) {
                 const uint32_t ph = (uint32_t)it & 1u;
-                // S of tile it is in the threads' registers: S of the next tile may overwrite it, and (S of tile it
-                // being done) the key stage of tile it may take tile it + NS
+                // S of tile it done: its key stage may take tile it + NSK (with one stage that is the next tile, so
+                // it is asked for as early as this)
+                if (!(ok = mbar_wait(s_full, ph))) { fail(21); break; }
+                if (it + NSK < n_kt) load_k(it + NSK);
+                // S of tile it is in the threads' registers: S of the next tile may overwrite it
                 if (!(ok = mbar_wait(s_free, ph))) { fail(12); break; }
                 tc_fence_after();
                 if (it + 1 < n_kt) {
-                    if (!(ok = mbar_wait(&k_bar[(it + 1) % NS], (uint32_t)((it + 1) / NS) & 1u))) { fail(13); break; }
+                    if (!(ok = mbar_wait(&k_bar[(it + 1) % NSK], (uint32_t)((it + 1) / NSK) & 1u))) { fail(13); break; }
                     tc_fence_after();
                     issue_s(it + 1);
                 }
-                if (it + NS < n_kt) load_k(it + NS);
                 // P of tile it is in shared memory, and the threads have read PV of the tile before: that one's
-                // value stage may take tile it - 1 + NS
+                // value stage may take tile it - 1 + NSV
                 if (!(ok = mbar_wait(p_full, ph))) { fail(14); break; }
-                if (it >= 1 && it - 1 + NS < n_kt) load_v(it - 1 + NS);
-                if (!(ok = mbar_wait(&v_bar[it % NS], (uint32_t)(it / NS) & 1u))) { fail(15); break; }
+                if (it >= 1 && it - 1 + NSV < n_kt) load_v(it - 1 + NSV);
+                if (!(ok = mbar_wait(&v_bar[it % NSV], (uint32_t)(it / NSV) & 1u))) { fail(15); break; }
                 tc_fence_after();
                 issue_pv(it);
             }
@@ -250,59 +259,122 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_attention_tc_kernel(const
             const int vis_lo = a.window > 0 ? qpos - a.window + 1 - n0 : -(1 << 30);
             if (!mbar_wait(s_full, (uint32_t)it & 1u)) { fail(18); ok = false; break; }
             tc_fence_after();
-            // this thread's 64 scores into registers; then S may be overwritten
-            float sv[64];
-            tmem_ld64(tmem_s + lane_base + (uint32_t)(half * 64), sv);
-            tc_fence_before();
-            mbar_arrive(s_free);
-            if (!full) {
-#pragma unroll
-                for (int j = 0; j < 64; ++j)
-                    if (j > vis_hi || j < vis_lo) sv[j] = -CUDART_INF_F;
+            if constexpr (!TWO) {
+                // this thread's 64 scores into registers; then S may be overwritten
+                float sv[64];
+                tmem_ld64(tmem_s + lane_base + (uint32_t)(half * 64), sv);
+                tc_fence_before();
+                mbar_arrive(s_free);
+                if (!full) {
+    #pragma unroll
+                    for (int j = 0; j < 64; ++j)
+                        if (j > vis_hi || j < vis_lo) sv[j] = -CUDART_INF_F;
+                }
+                // maximum of the raw scores (the scale is positive, so it can be applied afterwards); eight running
+                // maxima and four running sums, not one chain of dependent instructions
+                float raw8[8];
+    #pragma unroll
+                for (int e = 0; e < 8; ++e) raw8[e] = sv[e];
+    #pragma unroll
+                for (int j = 8; j < 64; ++j) raw8[j & 7] = fmaxf(raw8[j & 7], sv[j]);
+                float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
+                                  fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
+                // the other half's maximum, through shared memory; the two warps of a lane quarter meet at their own barrier
+                half_max[(it & 1) * 256 + half * 128 + row] = raw;
+                mbar_arrive(&pair_bar[quarter]);
+                if (!mbar_wait(&pair_bar[quarter], (uint32_t)it & 1u)) { fail(19); ok = false; break; }
+                raw = fmaxf(raw, half_max[(it & 1) * 256 + (half ^ 1) * 128 + row]);
+                const float mx = fmaxf(m, raw * a.scale_log2);
+                // a row that has seen no key yet keeps m = -inf; 0 as its reference avoids inf - inf
+                const float ref = mx == -CUDART_INF_F ? 0.f : mx;
+                const float corr = ex2_approx(m - ref);
+                m = mx;
+                // P = 2^(S * scale - max) as bfloat16, and its sum
+                uint32_t pk[32];
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+    #pragma unroll
+                for (int j = 0; j < 64; j += 2) {
+                    const float p0 = ex2_approx(fmaf(sv[j], a.scale_log2, -ref));
+                    const float p1 = ex2_approx(fmaf(sv[j + 1], a.scale_log2, -ref));
+                    sum4[(j / 2) & 3] += p0 + p1;
+                    pk[j / 2] = pack_bf16(p0, p1);
+                }
+                l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+                // the tile before: its PV into the output (it ran under this tile's arithmetic), which also frees P
+                if (it > 0) add_pv(it - 1);
+                if (!ok) break;
+                if (corr != 1.0f) {
+    #pragma unroll
+                    for (int i = 0; i < OW; ++i) o[i] *= corr;
+                }
+                // this thread's 64 keys are block `half` of P: pieces of 8 keys (16 bytes), swizzled with the row
+                uint8_t* prow = p_s + (size_t)half * kBlockBytes + (size_t)row * 128;
+    #pragma unroll
+                for (int piece = 0; piece < 8; ++piece)
+                    *reinterpret_cast<uint4*>(prow + ((piece ^ (row & 7)) << 4)) =
+                        make_uint4(pk[4 * piece], pk[4 * piece + 1], pk[4 * piece + 2], pk[4 * piece + 3]);
+            } else {
+                // This thread's 64 scores are read 32 at a time, in two passes (the maximum, then the exponentials):
+                // holding all of them would leave too few registers for two CTAs on an SM.
+                float sv[32];
+                auto read_scores = [&](int part) {
+                    tmem_ld32(tmem_s + lane_base + (uint32_t)(half * 64 + part * 32), sv);
+                    if (!full) {
+    #pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (part * 32 + j > vis_hi || part * 32 + j < vis_lo) sv[j] = -CUDART_INF_F;
+                    }
+                };
+                float raw8[8];
+    #pragma unroll
+                for (int e = 0; e < 8; ++e) raw8[e] = -CUDART_INF_F;
+    #pragma unroll
+                for (int part = 0; part < 2; ++part) {
+                    read_scores(part);
+    #pragma unroll
+                    for (int j = 0; j < 32; ++j) raw8[j & 7] = fmaxf(raw8[j & 7], sv[j]);
+                }
+                float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
+                                  fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
+                half_max[(it & 1) * 256 + half * 128 + row] = raw;
+                mbar_arrive(&pair_bar[quarter]);
+                if (!mbar_wait(&pair_bar[quarter], (uint32_t)it & 1u)) { fail(19); ok = false; break; }
+                raw = fmaxf(raw, half_max[(it & 1) * 256 + (half ^ 1) * 128 + row]);
+                const float mx = fmaxf(m, raw * a.scale_log2);
+                const float ref = mx == -CUDART_INF_F ? 0.f : mx;
+                const float corr = ex2_approx(m - ref);
+                m = mx;
+                if (it > 0) add_pv(it - 1);   // (it ran under this tile's first pass; this also frees P)
+                if (!ok) break;
+                if (corr != 1.0f) {
+    #pragma unroll
+                    for (int i = 0; i < OW; ++i) o[i] *= corr;
+                }
+                uint8_t* prow = p_s + (size_t)half * kBlockBytes + (size_t)row * 128;
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+    #pragma unroll
+                for (int part = 0; part < 2; ++part) {
+                    read_scores(part);
+                    if (part == 1) {   // S is in registers for the last time: it may be overwritten
+                        tc_fence_before();
+                        mbar_arrive(s_free);
+                    }
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t pk[4];
+    #pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float p0 = ex2_approx(fmaf(sv[c * 8 + 2 * e], a.scale_log2, -ref));
+                            const float p1 = ex2_approx(fmaf(sv[c * 8 + 2 * e + 1], a.scale_log2, -ref));
+                            sum4[e] += p0 + p1;
+                            pk[e] = pack_bf16(p0, p1);
+                        }
+                        const int piece = part * 4 + c;
+                        *reinterpret_cast<uint4*>(prow + ((piece ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                }
+                l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             }
-            // maximum of the raw scores (the scale is positive, so it can be applied afterwards); eight running
-            // maxima and four running sums, not one chain of dependent instructions
-            float raw8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) raw8[e] = sv[e];
-#pragma unroll
-            for (int j = 8; j < 64; ++j) raw8[j & 7] = fmaxf(raw8[j & 7], sv[j]);
-            float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
-                              fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
-            // the other half's maximum, through shared memory; the two warps of a lane quarter meet at their own barrier
-            half_max[(it & 1) * 256 + half * 128 + row] = raw;
-            mbar_arrive(&pair_bar[quarter]);
-            if (!mbar_wait(&pair_bar[quarter], (uint32_t)it & 1u)) { fail(19); ok = false; break; }
-            raw = fmaxf(raw, half_max[(it & 1) * 256 + (half ^ 1) * 128 + row]);
-            const float mx = fmaxf(m, raw * a.scale_log2);
-            // a row that has seen no key yet keeps m = -inf; 0 as its reference avoids inf - inf
-            const float ref = mx == -CUDART_INF_F ? 0.f : mx;
-            const float corr = ex2_approx(m - ref);
-            m = mx;
-            // P = 2^(S * scale - max) as bfloat16, and its sum
-            uint32_t pk[32];
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int j = 0; j < 64; j += 2) {
-                const float p0 = ex2_approx(fmaf(sv[j], a.scale_log2, -ref));
-                const float p1 = ex2_approx(fmaf(sv[j + 1], a.scale_log2, -ref));
-                sum4[(j / 2) & 3] += p0 + p1;
-                pk[j / 2] = pack_bf16(p0, p1);
-            }
-            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            // the tile before: its PV into the output (it ran under this tile's arithmetic), which also frees P
-            if (it > 0) add_pv(it - 1);
-            if (!ok) break;
-            if (corr != 1.0f) {
-#pragma unroll
-                for (int i = 0; i < OW; ++i) o[i] *= corr;
-            }
-            // this thread's 64 keys are block `half` of P: pieces of 8 keys (16 bytes), swizzled with the row
-            uint8_t* prow = p_s + (size_t)half * kBlockBytes + (size_t)row * 128;
-#pragma unroll
-            for (int piece = 0; piece < 8; ++piece)
-                *reinterpret_cast<uint4*>(prow + ((piece ^ (row & 7)) << 4)) =
-                    make_uint4(pk[4 * piece], pk[4 * piece + 1], pk[4 * piece + 2], pk[4 * piece + 3]);
             // P is written: make it visible to the tensor core's reads, then tell the issuing thread
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
@@ -365,13 +437,14 @@ CUtensorMap make_map(const void* base, int T, int width) {
     return map;
 }
 
-template <int HD>
+template <int HD, bool TWO>
 void launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillTcArgs& a, int n_tiles,
             cudaStream_t stream) {
     constexpr int DB = HD / 64;
     // alignment; Q, the stages of K and V, P; barriers; maxima and sums
-    const size_t smem = 1024 + (size_t)((1 + 2 * kv_stages(HD)) * DB + 2) * kBlockBytes + 160 + 3 * 256 * sizeof(float);
-    auto kernel = prefill_attention_tc_kernel<HD>;
+    const size_t smem = 1024 + (size_t)((1 + key_stages(HD, TWO) + value_stages(HD, TWO)) * DB + 2) * kBlockBytes + 160 +
+                        3 * 256 * sizeof(float);
+    auto kernel = prefill_attention_tc_kernel<HD, TWO>;
     static bool prepared = false;
     if (!prepared) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -388,8 +461,8 @@ bool attention_prefill_tc_supports(int heads, int kv_heads, int head_dim) {
 }
 
 void attention_prefill_tc(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles, int T,
-                          int heads, int kv_heads, int head_dim, float scale, int window, int* error,
-                          cudaStream_t stream) {
+                          int heads, int kv_heads, int head_dim, float scale, int window, int longest, int variant,
+                          int* error, cudaStream_t stream) {
     if (n_tiles <= 0) return;
     if (!attention_prefill_tc_supports(heads, kv_heads, head_dim))
         throw std::invalid_argument("attention_prefill_tc: head_dim " + std::to_string(head_dim) +
@@ -402,8 +475,22 @@ void attention_prefill_tc(const void* q, const void* k, const void* v, void* out
     const CUtensorMap mv = make_map(v, T, kv_heads * head_dim);
     PrefillTcArgs a{(__nv_bfloat16*)out, tiles, heads, kv_heads, window, scale * 1.4426950408889634f, error};
     note_launch();
-    if (head_dim == 64) launch<64>(mq, mk, mv, a, n_tiles, stream);
-    else launch<128>(mq, mk, mv, a, n_tiles, stream);
+    if (head_dim == 128) {
+        launch<128, false>(mq, mk, mv, a, n_tiles, stream);
+        return;
+    }
+    bool two = variant == 1;
+    if (variant < 0) {
+        // Two CTAs an SM when every SM has at least as many key tiles to do as the longest chain of one CTA has
+        // (estimated as if every sequence were as long as the longest). Measured on a B200, 14 heads of 64, one
+        // CTA against two: one prompt of 2,048 tokens 34.6 / 39.0 us, of 4,096 95 / 77, of 8,192 305 / 238, of
+        // 16,384 1,115 / 855 (563 TFLOP/s); eight prompts of 2,048 216 / 165; four of 1,024 43 / 41.
+        const long long chain = ((longest > 0 && longest < T ? longest : T) + kBN - 1) / kBN;
+        const long long total = (long long)heads * ((T + kBM - 1) / kBM) * (chain + 1) / 2;
+        two = total >= chain * kSmCount;
+    }
+    if (two) launch<64, true>(mq, mk, mv, a, n_tiles, stream);
+    else launch<64, false>(mq, mk, mv, a, n_tiles, stream);
 }
 
 }  // namespace sm

@@ -157,10 +157,10 @@ SM_API int sm_attention_prefill_tc_supports(int heads, int kv_heads, int head_di
 
 SM_API int sm_attention_prefill_tc(const void* q, const void* k, const void* v, void* out, const int32_t* tiles,
                                    int n_tiles, int T, int heads, int kv_heads, int head_dim, float scale, int window,
-                                   int* error, void* stream) {
+                                   int longest, int variant, int* error, void* stream) {
     return guarded([&] {
-        sm::attention_prefill_tc(q, k, v, out, tiles, n_tiles, T, heads, kv_heads, head_dim, scale, window, error,
-                                 (cudaStream_t)stream);
+        sm::attention_prefill_tc(q, k, v, out, tiles, n_tiles, T, heads, kv_heads, head_dim, scale, window, longest,
+                                 variant, error, (cudaStream_t)stream);
     });
 }
 

@@ -141,9 +141,11 @@ void attention_prefill(const void* q, const void* k, const void* v, void* out, c
 // tensors; `tiles` is the list attention_prefill takes (tiles of 64 queries; the kernel pairs
 // them). A bounded wait that runs out writes a code into *error (nullable).
 bool attention_prefill_tc_supports(int heads, int kv_heads, int head_dim);
+// `longest`: the longest sequence (0: unknown); `variant`: -1 lets the launcher choose between one CTA an SM
+// (0) and two (1, head size 64 only; it wins on long prompts).
 void attention_prefill_tc(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles, int T,
-                          int heads, int kv_heads, int head_dim, float scale, int window, int* error,
-                          cudaStream_t stream);
+                          int heads, int kv_heads, int head_dim, float scale, int window, int longest, int variant,
+                          int* error, cudaStream_t stream);
 
 // ---- attention_decode.cu --------------------------------------------------------------
 // One new token per sequence over the paged cache for bfloat16: a cluster of CTAs per

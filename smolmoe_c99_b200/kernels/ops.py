@@ -317,7 +317,8 @@ class Ops:
         """Causal attention of whole prompts over their own keys (sequences start at 0)."""
         if self.use_fast_attention and q.dtype == torch.bfloat16 and step.prefill_tiles is not None:
             if self.use_tcgen05_attention and self.lib.sm_attention_prefill_tc_supports(q.shape[1], k_packed.shape[1], q.shape[2]):
-                return self.attention_prefill_tcgen05(q, k_packed, v_packed, step.prefill_tiles, scale, window)
+                return self.attention_prefill_tcgen05(q, k_packed, v_packed, step.prefill_tiles, scale, window,
+                                                      longest=step.max_seq_len)
             if self.lib.sm_attention_prefill_supports(q.shape[2]):
                 return self.attention_prefill_mma(q, k_packed, v_packed, step.prefill_tiles, scale, window)
         return self.attention_plain(q, step.positions, scale, window, k_packed=k_packed, v_packed=v_packed,
@@ -338,13 +339,14 @@ class Ops:
                                                   ctypes.c_float(scale), int(window or 0), _stream()))
         return out
 
-    def attention_prefill_tcgen05(self, q, k_packed, v_packed, tiles, scale, window):
-        """The tcgen05 kernel: head sizes 64 and 128."""
+    def attention_prefill_tcgen05(self, q, k_packed, v_packed, tiles, scale, window, longest=0, variant=-1):
+        """The tcgen05 kernel: head sizes 64 and 128. ``longest``: the longest sequence, if known; ``variant``:
+        0 one CTA an SM, 1 two (head size 64), -1 the launcher's choice."""
         out = self._prefill_operands(q, k_packed, v_packed, tiles)
         self._check(self.lib.sm_attention_prefill_tc(_ptr(q), _ptr(k_packed), _ptr(v_packed), _ptr(out), _ptr(tiles),
                                                      tiles.shape[0], q.shape[0], q.shape[1], k_packed.shape[1], q.shape[2],
-                                                     ctypes.c_float(scale), int(window or 0), _ptr(self.error_flag),
-                                                     _stream()))
+                                                     ctypes.c_float(scale), int(window or 0), int(longest), int(variant),
+                                                     _ptr(self.error_flag), _stream()))
         return out
 
     def attention_cached(self, q, step, scale, window, cache, kv_heads):

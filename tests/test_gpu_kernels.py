@@ -119,9 +119,10 @@ def test_prefill_attention(ops, heads, kv_heads, hd, window):
     assert float((plain32 - want).abs().max()) <= 2e-5
 
 
-@pytest.mark.parametrize("heads,kv_heads,hd", [(14, 2, 64), (3, 1, 64), (4, 4, 128), (6, 2, 128)])
+@pytest.mark.parametrize("heads,kv_heads,hd,variant", [(14, 2, 64, 0), (14, 2, 64, 1), (3, 1, 64, 0), (3, 1, 64, 1),
+                                                       (4, 4, 128, -1), (6, 2, 128, -1)])
 @pytest.mark.parametrize("window", [None, 37, 200])
-def test_prefill_attention_tcgen05(ops, heads, kv_heads, hd, window):
+def test_prefill_attention_tcgen05(ops, heads, kv_heads, hd, variant, window):
     """Sequences shorter than, equal to and longer than the tiles of 128; a window inside and across tiles."""
     lens = [1, 127, 128, 129, 300, 64]
     T = sum(lens)
@@ -129,10 +130,11 @@ def test_prefill_attention_tcgen05(ops, heads, kv_heads, hd, window):
     scale = 1.0 / math.sqrt(hd)
     step = _packed_step(lens)
     want = _plain_attention(q, k, v, lens, window, scale)
-    got = ops.attention_prefill_tcgen05(q, k, v, step.prefill_tiles, scale, window).float().cpu()
+    got = ops.attention_prefill_tcgen05(q, k, v, step.prefill_tiles, scale, window, variant=variant).float().cpu()
     ops.check_error_flag()
     assert float((got - want).abs().max()) <= 2e-2
-    assert ops.attention_prefill(q, k, v, step, scale, window).float().cpu().equal(got)   # it is the one the engine takes
+    # it is the one the engine takes (whichever variant: they agree to rounding)
+    assert float((ops.attention_prefill(q, k, v, step, scale, window).float().cpu() - got).abs().max()) <= 1e-2
 
 
 @pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
