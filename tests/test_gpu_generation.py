@@ -93,8 +93,27 @@ def test_long_decoding(model_dirs, dtype):
     engine.close_sequence(slot)
 
 
+def test_long_prompt_then_long_decoding_at_head_size_64(model_dirs):
+    """A prompt of 1,500 positions through the tcgen05 prefill attention, then 120 tokens one at a time: the decode
+    graph's span doubles on the way (2,048 is crossed at no point, 1,536 positions are in one span) and the cluster's
+    CTAs hold their shares in one buffer."""
+    from smolmoe_c99_b200.engine.engine import Engine
+    toks = random_tokens(1620, 331, 77)
+    want = plain_model.forward(model_dirs["D"], toks, round_like_bf16_engine=True)
+    engine = Engine(model_dirs["D"], "bfloat16", max_tokens=4096)
+    slot = engine.open_sequence()
+    rows = [engine.step([slot], [toks[:1500]], [list(range(1500))]).cpu()]
+    for t in toks[1500:]:
+        rows.append(engine.step([slot], [[t]], [[0]]).cpu())
+    engine.check_status()
+    got = torch.cat(rows)
+    diff = (got - want).abs().max(dim=1).values
+    assert float(diff.max()) <= TOL["bfloat16"], f"first position over tolerance: {int((diff > TOL['bfloat16']).nonzero()[0])}"
+    engine.close_sequence(slot)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
     from smolmoe_c99_b200.engine.engine import Engine
     engine = Engine(model_dirs[name], dtype, max_tokens=512)

@@ -210,6 +210,47 @@ def test_decode_attention_over_pages(ops, heads, kv_heads, hd, window):
         assert float((plain[b] - want).abs().max()) <= 1e-2, f"plain kernel, sequence {b}"
 
 
+@pytest.mark.parametrize("heads,kv_heads,hd", [(14, 2, 64), (8, 2, 128), (3, 1, 32)])
+@pytest.mark.parametrize("lens,max_len", [([3000, 2500, 64, 1, 700], 4096), ([1500] * 3 + [40] * 37, 2048), ([4090], 4096)])
+def test_decode_attention_long_contexts(ops, heads, kv_heads, hd, lens, max_len):
+    """Shares of a cluster's CTAs that do not fit one buffer (chunks in flight), many sequences with one CTA each,
+    and one sequence over the largest cluster: against the float64 formula for the newest position."""
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    B = len(lens)
+    pages_per_seq = max_len // PAGE_SIZE
+    g = torch.Generator().manual_seed(5)
+    table = torch.randperm(B * pages_per_seq, generator=g).to(torch.int32).view(B, pages_per_seq)
+    k_pool = torch.zeros((B * pages_per_seq, kv_heads, PAGE_SIZE, hd), dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    q = _rand((B, heads, hd), torch.bfloat16, 1).cpu()
+    want = torch.zeros((B, heads, hd), dtype=torch.float64)
+    scale = 1.0 / math.sqrt(hd)
+    for b, n in enumerate(lens):
+        k, v = _rand((n, kv_heads, hd), torch.bfloat16, 10 + b).cpu(), _rand((n, kv_heads, hd), torch.bfloat16, 50 + b).cpu()
+        if n > 300:      # a far key that matters, so that a lost chunk shows
+            k[7] = 0
+            k[7, :, 0] = 30.0
+            q[b, :, 0] = 2.0
+        pages = table[b, :(n + PAGE_SIZE - 1) // PAGE_SIZE].long()
+        padded = torch.zeros((len(pages) * PAGE_SIZE, kv_heads, hd), dtype=torch.bfloat16)
+        padded[:n] = k
+        k_pool[pages] = padded.view(len(pages), PAGE_SIZE, kv_heads, hd).permute(0, 2, 1, 3)
+        padded = torch.zeros_like(padded)
+        padded[:n] = v
+        v_pool[pages] = padded.view(len(pages), PAGE_SIZE, kv_heads, hd).permute(0, 2, 1, 3)
+        for h in range(heads):
+            kh = h // (heads // kv_heads)
+            p = torch.softmax((k[:, kh].double() @ q[b, h].double()) * scale, dim=0)
+            want[b, h] = p @ v[:, kh].double()
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    slot_ids = torch.arange(B, dtype=torch.int32).cuda()
+    got = ops.attention_decode(q.cuda(), positions, slot_ids, scale, None, k_pool.cuda(), v_pool.cuda(), table.cuda(), 0,
+                               kv_heads, max_len).double().cpu()
+    ops.check_error_flag()
+    for b in range(B):
+        assert float((got[b] - want[b]).abs().max()) <= 1e-2, f"sequence {b} of {lens[b]} positions"
+
+
 # ---- products over a handful of tokens -----------------------------------------------------
 @pytest.mark.parametrize("T", [1, 3, 8, 9, 16, 32])
 @pytest.mark.parametrize("N,K", [(896, 896), (100, 72), (151, 4864), (1000, 136)])

@@ -39,11 +39,12 @@ def _check(got, want, tol, what):
             f"{int((diff > tol).nonzero()[0])}, worst {float(diff.max()):.3g} at position {worst} of {len(diff)}"
 
 
-LENGTHS = {"A": [5, 11, 17, 64, 65, 100, 128], "B": [1, 23, 40, 41, 64, 96], "C": [3, 99, 100, 101, 129, 300]}
+LENGTHS = {"A": [5, 11, 17, 64, 65, 100, 128], "B": [1, 23, 40, 41, 64, 96], "C": [3, 99, 100, 101, 129, 300],
+           "D": [2, 127, 128, 129, 260, 700]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_all_cuts_agree_with_plain(model_dirs, name, dtype):
     requests = _requests(name, LENGTHS[name], 10)
     want = _plain(model_dirs[name], requests, dtype)

@@ -1,6 +1,7 @@
 """Tiny configurations of the Qwen2 decoder for the tests. They differ in every size and
 option: head counts and groups, sizes that are no power of two, layers, vocabulary, eps,
-rope base, tied or untied head, an explicit head size, and the window."""
+rope base, tied or untied head, an explicit head size, the window, and the head sizes that
+the different attention kernels take."""
 import torch
 
 _BASE = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu"}
@@ -21,8 +22,13 @@ TINY = {
               num_key_value_heads=5, head_dim=48, vocab_size=300, max_position_embeddings=2048,
               rms_norm_eps=3e-6, rope_theta=50000.0, tie_word_embeddings=True, use_sliding_window=True,
               sliding_window=100, max_window_layers=1),
+    # head size 64 (the size the tcgen05 prefill attention takes), 6 heads on 3 kv heads, bias-free rotary base,
+    # untied head, a context long enough for prompts of several key tiles and decoding over several chunks
+    "D": dict(_BASE, hidden_size=384, intermediate_size=272, num_hidden_layers=2, num_attention_heads=6,
+              num_key_value_heads=3, vocab_size=331, max_position_embeddings=4096, rms_norm_eps=1e-5,
+              rope_theta=500000.0, tie_word_embeddings=False),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
 
 
 def make_model_dir(name: str, path: str) -> str:
