@@ -6,6 +6,7 @@ unequal lengths) or all go on by one token (``decode``)."""
 from __future__ import annotations
 
 from dataclasses import dataclass
+from array import array
 from typing import List, Optional, Sequence
 
 import torch
@@ -51,18 +52,29 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
     # the step's numbers, one row per quantity, built with tensor operations (a prompt of thousands of tokens
     # would spend a millisecond in Python loops otherwise)
     n_seqs = len(slots)
-    lens_t = torch.tensor(lens, dtype=torch.int64)
-    starts_t = torch.tensor(list(starts), dtype=torch.int64)
-    slots_t = torch.tensor(list(slots), dtype=torch.int64)
-    ends = torch.cumsum(lens_t, 0)
-    firsts = ends - lens_t
-    cu = [0] + ends.tolist()
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
     n_tokens = cu[-1]
-    flat = [t for toks in token_lists for t in toks] if n_seqs > 1 else token_lists[0]
-    tokens = torch.as_tensor(flat, dtype=torch.int64)
-    seq_of = torch.repeat_interleave(torch.arange(n_seqs), lens_t)
-    positions = torch.arange(n_tokens) - firsts[seq_of] + starts_t[seq_of]
-    host = torch.stack([tokens, positions, slots_t[seq_of], (starts_t + lens_t)[seq_of], firsts[seq_of]]).to(torch.int32)
+    host = torch.empty((5, n_tokens), dtype=torch.int32)
+    flat = token_lists[0] if n_seqs == 1 else [t for toks in token_lists for t in toks]
+    host[0] = torch.frombuffer(array("i", flat), dtype=torch.int32) if n_tokens else host[0]
+    if n_seqs <= 4:
+        for i, (slot, start, n) in enumerate(zip(slots, starts, lens)):
+            a, b = cu[i], cu[i + 1]
+            torch.arange(start, start + n, dtype=torch.int32, out=host[1, a:b])
+            host[2, a:b] = slot
+            host[3, a:b] = start + n
+            host[4, a:b] = a
+    else:
+        lens_t = torch.tensor(lens, dtype=torch.int32)
+        starts_t = torch.tensor(list(starts), dtype=torch.int32)
+        firsts = torch.tensor(cu[:-1], dtype=torch.int32)
+        seq_of = torch.repeat_interleave(torch.arange(n_seqs), lens_t.long())
+        host[1] = torch.arange(n_tokens, dtype=torch.int32) - firsts[seq_of] + starts_t[seq_of]
+        host[2] = torch.tensor(list(slots), dtype=torch.int32)[seq_of]
+        host[3] = (starts_t + lens_t)[seq_of]
+        host[4] = firsts[seq_of]
     dev = host.to(device)
     tiles = None
     if mode == "prefill":
