@@ -184,6 +184,8 @@ SM_API int sm_attention_decode(const void* q, void* out, int B, int heads, int k
 
 SM_API int sm_gemm_skinny_supports(int T, int N, int K) { return sm::gemm_skinny_supports(T, N, K) ? 1 : 0; }
 
+SM_API int sm_gemm_skinny_rounds(int T, int N, int K, int gated) { return sm::gemm_skinny_rounds(T, N, K, gated != 0); }
+
 SM_API int sm_gemm_skinny(const void* x, const void* norm_w, int norm_w_dt, float eps, const void* w, int T, int N,
                           int K, int mode, const void* bias, int bias_dt, void* out, int out_dt, int up_offset,
                           void* stream) {

@@ -511,6 +511,15 @@ int pick_cluster(int tiles, int K, int round_limit) {
 
 bool gemm_skinny_supports(int T, int N, int K) { return T > 0 && T <= 32 && N > 0 && K > 0 && K % 8 == 0; }
 
+int gemm_skinny_rounds(int T, int N, int K, bool gated) {
+    const int nt = T <= 8 ? 1 : (T <= 16 ? 2 : 4);
+    const int weight_rows = gated ? 32 : 16;
+    const int cluster = pick_cluster((N + 15) / 16, K, max_round_k(weight_rows + 8));
+    const int kblocks = (K + 31) / 32, per_cta = (kblocks + cluster - 1) / cluster;
+    const int limit = max_round_k(weight_rows + nt * 8);
+    return (per_cta * 32 + limit - 1) / limit;
+}
+
 void gemm_skinny(const void* x, const void* norm_w, DType norm_w_dt, float eps, const void* w, int T, int N, int K,
                  int mode, const void* bias, DType bias_dt, void* out, DType out_dt, int up_offset,
                  const SkinnyRope* rope, cudaStream_t stream) {

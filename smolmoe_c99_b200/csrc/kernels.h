@@ -98,6 +98,9 @@ struct SkinnyRope {
     const int32_t* token_slot;  // [T]
 };
 bool gemm_skinny_supports(int T, int N, int K);
+// Rounds in which a CTA of the kernel takes its share of K for these sizes (1: all of its weights are in
+// flight at once, which is what the kernel is good at).
+int gemm_skinny_rounds(int T, int N, int K, bool gated);
 void gemm_skinny(const void* x, const void* norm_w, DType norm_w_dt, float eps, const void* w, int T, int N, int K,
                  int mode, const void* bias, DType bias_dt, void* out, DType out_dt, int up_offset,
                  const SkinnyRope* rope, cudaStream_t stream);

@@ -78,6 +78,10 @@ class Ops:
         self.use_fast_attention = True  # False routes bfloat16 attention to the plain kernel
         self.use_tcgen05_attention = True  # False routes prefill attention to the mma.sync kernel
         self.use_skinny = True  # False routes products over a handful of tokens to the general kernels
+        # more tokens than this go to the tcgen05 kernel (the weight-streaming kernel itself takes up to 32; measured
+        # on a B200 at 24 and 32 tokens it is 20-35% behind on every shape from 0.5B to 7B)
+        self.skinny_max_tokens = 16
+        self.skinny_single_round_above_8 = True
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.lib.sm_set_error_word.restype = None
         self.lib.sm_set_error_word(_ptr(self.error_flag))
@@ -184,7 +188,7 @@ class Ops:
 
     def gated_linear(self, x, w_gate_up: torch.Tensor, hidden: int, out_dtype: torch.dtype) -> torch.Tensor:
         """act(x @ w_gate.T) * (x @ w_up.T) with w_gate_up = [w_gate; w_up]."""
-        if self._skinny_ok(x, w_gate_up):
+        if self._skinny_ok(x, w_gate_up, gated=True):
             out = torch.empty((x.shape[0], hidden), dtype=out_dtype, device=w_gate_up.device)
             return self.gemm_skinny(x, w_gate_up, None, out, mode=2, up_offset=hidden)
         x = self.materialize(x)
@@ -203,11 +207,14 @@ class Ops:
     def _dtype_of(x) -> torch.dtype:
         return x.out_dtype if isinstance(x, NormedRows) else x.dtype
 
-    def _skinny_ok(self, x, w: torch.Tensor) -> bool:
+    def _skinny_ok(self, x, w: torch.Tensor, gated: bool = False) -> bool:
         """A handful of tokens and bfloat16 weights: the weight-streaming kernel, which also
         takes the norm as its prologue."""
-        if not self.use_skinny or w.dtype != torch.bfloat16:
+        if not self.use_skinny or w.dtype != torch.bfloat16 or x.shape[0] > self.skinny_max_tokens:
             return False
+        if x.shape[0] > 8 and self.skinny_single_round_above_8 and self.lib.sm_gemm_skinny_rounds(
+                x.shape[0], w.shape[0] // 2 if gated else w.shape[0], x.shape[1], int(gated)) > 1:
+            return False   # its CTAs would take their weights in rounds: the tcgen05 kernel streams them better
         if isinstance(x, NormedRows):
             if x.rows is not None or x.out_dtype != torch.bfloat16 or x.done is not None:
                 return False
