@@ -39,6 +39,7 @@ namespace {
 constexpr int kTileM = 128;          // output features per CTA
 constexpr int kBlockK = 64;          // bf16 elements per 128-byte swizzled row
 constexpr int kUmmaK = 16;
+constexpr int kBoxRows = 64;         // rows of one TMA box (a token tile below 64 rows is one box of its own size)
 constexpr int kThreads = 192;
 
 enum Epilogue : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
@@ -71,6 +72,39 @@ constexpr int kChunk = 32;                                  // tokens per epilog
 constexpr int kStagingBytes = kChunk * kTileM * 4;          // one staged chunk (float)
 
 // Which tile and K range a work unit is: units that run side by side share the token tile.
+// What lane `lane` of the loading warp brings of every stage: the weight tile (and the second one of a gated
+// product) goes as 128 / kBoxRows boxes, the token tile as ceil(tile_n / kBoxRows) boxes, one box a lane. A box is
+// kBoxRows rows of 128 bytes: a multiple of the 1,024-byte swizzle atom, so boxes side by side are the same bytes as
+// one large box.
+// up * gate / (1 + e^-gate) with the hardware's exponential and reciprocal (a few ulp of float; the result is
+// stored as bfloat16). The epilogue's four warps have a scheduler each, so every instruction saved is time.
+__device__ __forceinline__ float gated(float gate, float up) { return up * __fdividef(gate, 1.0f + __expf(-gate)); }
+
+struct StageBox {
+    bool active, from_x;    // this lane loads something; from the token matrix (else from the weights)
+    int offset;             // bytes from the stage's start
+    int row;                // first row, relative to the tile's first row (for the second weight tile: + up_offset)
+};
+__device__ __forceinline__ StageBox stage_box(int lane, int a_bytes, const GemmParams& p) {
+    constexpr int kPerTile = kTileM / kBoxRows;
+    constexpr int kBoxBytes = kBoxRows * kBlockK * 2;
+    const int w_boxes = kPerTile * (p.dual ? 2 : 1);
+    const int x_boxes = (p.tile_n + kBoxRows - 1) / kBoxRows;
+    StageBox b{false, false, 0, 0};
+    if (lane < w_boxes) {
+        const int tile = lane / kPerTile, part = lane - tile * kPerTile;
+        b.active = true;
+        b.offset = lane * kBoxBytes;
+        b.row = (tile ? p.up_offset : 0) + part * kBoxRows;
+    } else if (lane < w_boxes + x_boxes) {
+        const int part = lane - w_boxes;
+        b.active = b.from_x = true;
+        b.offset = a_bytes + part * kBoxBytes;
+        b.row = part * kBoxRows;
+    }
+    return b;
+}
+
 struct Unit {
     int n0, t0, kb_begin, kb_end, split;
 };
@@ -121,27 +155,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (int u = blockIdx.x; u < p.units && !*failed; u += gridDim.x) {
-                const Unit w = unit_of(p, u);
-                for (int kb = w.kb_begin; kb < w.kb_end; ++kb, ++it) {
-                    const int s = it % p.stages;
-                    const uint32_t phase = (it / p.stages) & 1u;
-                    if (!mbar_wait(&empty_bar[s], phase ^ 1u)) { *failed = 1; atomicExch(p.error, 1); break; }
-                    uint8_t* a = smem + (size_t)s * stage_bytes;
-                    mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
-                    const int k = kb * kBlockK;
-                    tma_load_2d(a, &map_w, k, w.n0, &full_bar[s]);
-                    if (p.dual) tma_load_2d(a + kTileM * kBlockK * 2, &map_w, k, p.up_offset + w.n0, &full_bar[s]);
-                    tma_load_2d(a + a_bytes, &map_x, k, w.t0, &full_bar[s]);
+        // The whole warp runs the loop; a stage's tiles are loaded as boxes of kBoxRows rows, one box a lane.
+        // (One thread's TMA copies are taken one after another, ~0.35 us each whatever their size: measured on a
+        // B200 with bulk copies from L2, a thread moves 16 KB copies at 6.5 TB/s over 148 SMs, two lanes at 12,
+        // four at 18. With one issuing thread this kernel sat at 5.4 TB/s of operand traffic.)
+        // (The loops of this warp and of the issuing thread below are kept free of divisions and of anything else
+        // that can be counted up: a thread alone on its scheduler waits out the latency of every instruction, and at
+        // ~1,000 cycles a block of K these two loops, not memory or the tensor core, bounded the kernel.)
+        const StageBox box = stage_box(lane, a_bytes, p);
+        int s = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < p.units && ok && !*failed; u += gridDim.x) {
+            const Unit w = unit_of(p, u);
+            const int row = box.from_x ? w.t0 + box.row : w.n0 + box.row;
+            for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u));
+                if (!ok) {
+                    if (lane == 0) { *failed = 1; atomicExch(p.error, 1); }
+                    break;
                 }
+                if (lane == 0) mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
+                __syncwarp();
+                if (box.active)
+                    tma_load_2d(smem + (size_t)s * stage_bytes + box.offset, box.from_x ? &map_x : &map_w, kb * kBlockK, row, &full_bar[s]);
+                if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(kTileM, p.tile_n);
-            uint32_t it = 0;
+            // descriptors differ in the start address only (bits 0-13, in units of 16 bytes): one per stage's first
+            // tile is kept running, the others are a constant away
+            const uint64_t desc_first = smem_desc(smem_u32(smem));
+            const uint64_t stage_step = (uint64_t)(stage_bytes >> 4), b_off = (uint64_t)(a_bytes >> 4);
+            const uint64_t up_off = (uint64_t)((kTileM * kBlockK * 2) >> 4);
+            uint64_t da = desc_first;
+            int s = 0;
+            uint32_t phase = 0;
             int i = 0;
             for (int u = blockIdx.x; u < p.units && !*failed; u += gridDim.x, ++i) {
                 const Unit w = unit_of(p, u);
@@ -150,23 +201,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (!mbar_wait(&tempty_bar[b], (((uint32_t)i >> 1) & 1u) ^ 1u)) { *failed = 1; atomicExch(p.error, 4); break; }
                 tc_fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(b * buf_cols);
-                for (int kb = w.kb_begin; kb < w.kb_end; ++kb, ++it) {
-                    const int s = it % p.stages;
-                    const uint32_t phase = (it / p.stages) & 1u;
+                const uint32_t d_up = d + (uint32_t)p.tile_n;
+                uint32_t acc = 0;
+                for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
                     if (!mbar_wait(&full_bar[s], phase)) { *failed = 1; atomicExch(p.error, 2); break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
-                    const uint32_t b_addr = a_addr + a_bytes;
-                    const uint64_t da = smem_desc(a_addr), db = smem_desc(b_addr);
-                    const uint64_t du = smem_desc(a_addr + kTileM * kBlockK * 2);
+                    const uint64_t db = da + b_off, du = da + up_off;
 #pragma unroll
                     for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                        const uint32_t acc = (kb > w.kb_begin || k > 0) ? 1u : 0u;
                         const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);   // 32 bytes a step inside the swizzled row
                         umma_bf16(d, da + step, db + step, idesc, acc);
-                        if (p.dual) umma_bf16(d + (uint32_t)p.tile_n, du + step, db + step, idesc, acc);
+                        if (p.dual) umma_bf16(d_up, du + step, db + step, idesc, acc);
+                        acc = 1;
                     }
                     umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
+                    da += stage_step;
+                    if (++s == p.stages) { s = 0; phase ^= 1u; da = desc_first; }
                 }
                 umma_commit(&tfull_bar[b]);        // the accumulator is complete once all MMAs are done
             }
@@ -204,7 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         float v = g[j];
-                        if (p.epilogue == EPI_SWIGLU) v = up[j] * (v / (1.0f + __expf(-v)));
+                        if (p.epilogue == EPI_SWIGLU) v = gated(v, up[j]);
                         else v += bias_v;
                         if (p.out_dt == F32) ((float*)stage)[j * kTileM + f] = v;
                         else ((__nv_bfloat16*)stage)[j * kTileM + f] = __float2bfloat16_rn(v);
@@ -242,7 +292,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             if (p.dual) p.workspace[(((size_t)p.splits + w.split) * p.T + t) * p.N + n] = up[j];
                             continue;
                         }
-                        if (p.epilogue == EPI_SWIGLU) v = up[j] * (v / (1.0f + __expf(-v)));
+                        if (p.epilogue == EPI_SWIGLU) v = gated(v, up[j]);
                         else v += bias_v;
                         if (p.epilogue == EPI_ACCUM) ((float*)p.out)[o] = old[j] + v;
                         else if (p.out_dt == F32) ((float*)p.out)[o] = v;
@@ -304,40 +354,47 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
-                int s = i % p.stages;
-                uint32_t phase = (uint32_t)(i / p.stages) & 1u;
-                if (!mbar_wait(&empty_bar[s], phase ^ 1u)) { *failed = 1; atomicExch(p.error, 1); break; }
-                uint8_t* a = smem + (size_t)s * stage_bytes;
-                mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
-                int k = (kb_begin + i) * kBlockK;
-                tma_load_2d(a, &map_w, k, n0, &full_bar[s]);
-                if (p.dual) tma_load_2d(a + kTileM * kBlockK * 2, &map_w, k, p.up_offset + n0, &full_bar[s]);
-                tma_load_2d(a + a_bytes, &map_x, k, t0, &full_bar[s]);
+        // the whole warp: one box of a stage's tiles a lane (see the persistent kernel)
+        const StageBox box = stage_box(lane, a_bytes, p);
+        const int row = box.from_x ? t0 + box.row : n0 + box.row;
+        int s = 0;
+        uint32_t phase = 0;
+        for (int i = 0; i < n_kb; ++i) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u))) {
+                if (lane == 0) { *failed = 1; atomicExch(p.error, 1); }
+                break;
             }
+            if (lane == 0) mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
+            __syncwarp();
+            if (box.active)
+                tma_load_2d(smem + (size_t)s * stage_bytes + box.offset, box.from_x ? &map_x : &map_w, (kb_begin + i) * kBlockK, row, &full_bar[s]);
+            if (++s == p.stages) { s = 0; phase ^= 1u; }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(kTileM, p.tile_n);
+            const uint64_t desc_first = smem_desc(smem_u32(smem));
+            const uint64_t stage_step = (uint64_t)(stage_bytes >> 4), b_off = (uint64_t)(a_bytes >> 4);
+            const uint64_t up_off = (uint64_t)((kTileM * kBlockK * 2) >> 4);
+            const uint32_t d_up = tmem_base + (uint32_t)p.tile_n;
+            uint64_t da = desc_first;
+            int s = 0;
+            uint32_t phase = 0, acc = 0;
             bool ok = true;
             for (int i = 0; i < n_kb && ok; ++i) {
-                int s = i % p.stages;
-                uint32_t phase = (uint32_t)(i / p.stages) & 1u;
                 if (!mbar_wait(&full_bar[s], phase)) { *failed = 1; atomicExch(p.error, 2); ok = false; break; }
                 tc_fence_after();
-                uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
-                uint32_t b_addr = a_addr + a_bytes;
-                uint64_t da = smem_desc(a_addr), db = smem_desc(b_addr);
-                uint64_t du = smem_desc(a_addr + kTileM * kBlockK * 2);
+                const uint64_t db = da + b_off, du = da + up_off;
 #pragma unroll
                 for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                    uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-                    uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);   // 32 bytes a step inside the swizzled row
+                    const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);   // 32 bytes a step inside the swizzled row
                     umma_bf16(tmem_base, da + step, db + step, idesc, acc);
-                    if (p.dual) umma_bf16(tmem_base + (uint32_t)p.tile_n, du + step, db + step, idesc, acc);
+                    if (p.dual) umma_bf16(d_up, du + step, db + step, idesc, acc);
+                    acc = 1;
                 }
                 umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
+                da += stage_step;
+                if (++s == p.stages) { s = 0; phase ^= 1u; da = desc_first; }
             }
             umma_commit(tmem_full_bar);        // the accumulator is complete once all MMAs are done
         }
@@ -379,7 +436,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         if (p.dual) p.workspace[(((size_t)p.splits + split) * p.T + t) * p.N + n] = u[j];
                         continue;
                     }
-                    if (p.epilogue == EPI_SWIGLU) v = u[j] * (v / (1.0f + __expf(-v)));
+                    if (p.epilogue == EPI_SWIGLU) v = gated(v, u[j]);
                     else v += bias_v;
                     if (p.epilogue == EPI_ACCUM) {
                         ((float*)p.out)[o] = old[j] + v;
@@ -421,7 +478,7 @@ __global__ void splitk_reduce_kernel(GemmParams p) {
         }
     }
     float v = g;
-    if (p.epilogue == EPI_SWIGLU) v = u * (g / (1.0f + __expf(-g)));
+    if (p.epilogue == EPI_SWIGLU) v = gated(g, u);
     else if (p.bias) v += p.bias_dt == F32 ? ((const float*)p.bias)[n] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
     if (p.epilogue == EPI_ACCUM) ((float*)p.out)[i] += v;
     else if (p.out_dt == F32) ((float*)p.out)[i] = v;
@@ -587,8 +644,8 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
         if (p.stages > 8) p.stages = 8;
         if (p.stages < 2) p.stages = 2;
         const size_t smem_small = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + (2 * p.stages + 1) * 8 + 16;
-        const CUtensorMap mw = make_map(w, dual ? up_offset + N : N, K, kTileM);
-        const CUtensorMap mx = make_map(x, T, K, p.tile_n);
+        const CUtensorMap mw = make_map(w, dual ? up_offset + N : N, K, kBoxRows);
+        const CUtensorMap mx = make_map(x, T, K, p.tile_n < kBoxRows ? p.tile_n : kBoxRows);
         static std::once_flag small_once;
         std::call_once(small_once, [] {
             cudaFuncSetAttribute(gemm_tc_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -608,8 +665,8 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     if (p.stages > 8) p.stages = 8;
     if (p.stages < 2) throw std::runtime_error("gemm_tc: a pipeline stage does not fit shared memory twice");
     const size_t smem = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + 2 * kStagingBytes + (2 * p.stages + 4) * 8 + 16;
-    const CUtensorMap map_w = make_map(w, dual ? up_offset + N : N, K, kTileM);
-    const CUtensorMap map_x = make_map(x, T, K, p.tile_n);
+    const CUtensorMap map_w = make_map(w, dual ? up_offset + N : N, K, kBoxRows);
+    const CUtensorMap map_x = make_map(x, T, K, p.tile_n < kBoxRows ? p.tile_n : kBoxRows);
     const CUtensorMap map_out = p.tma_out ? make_out_map(out, T, N, out_dt) : map_x;
     static std::once_flag attr_once;
     std::call_once(attr_once, [] {
