@@ -38,6 +38,8 @@ namespace {
 
 constexpr int kTileM = 128;          // output features per CTA
 constexpr int kBlockK = 64;          // bf16 elements per 128-byte swizzled row
+constexpr int kAtoms = 2;            // swizzled blocks of K per pipeline stage: a stage holds kStageK = 128 elements of K,
+constexpr int kStageK = kAtoms * kBlockK;   // so that the issuing thread's wait and commit are paid once per 8 MMAs
 constexpr int kUmmaK = 16;
 constexpr int kBoxRows = 64;         // rows of one TMA box (a token tile below 64 rows is one box of its own size)
 constexpr int kThreads = 192;
@@ -80,27 +82,32 @@ constexpr int kStagingBytes = kChunk * kTileM * 4;          // one staged chunk 
 // stored as bfloat16). The epilogue's four warps have a scheduler each, so every instruction saved is time.
 __device__ __forceinline__ float gated(float gate, float up) { return up * __fdividef(gate, 1.0f + __expf(-gate)); }
 
+// A stage lies in shared memory as [weight tile][block of K][128 rows], [second weight tile ...], then
+// [block of K][tile_n token rows], every row 128 bytes.
 struct StageBox {
     bool active, from_x;    // this lane loads something; from the token matrix (else from the weights)
     int offset;             // bytes from the stage's start
     int row;                // first row, relative to the tile's first row (for the second weight tile: + up_offset)
+    int k;                  // first element of K, relative to the stage's
 };
 __device__ __forceinline__ StageBox stage_box(int lane, int a_bytes, const GemmParams& p) {
     constexpr int kPerTile = kTileM / kBoxRows;
     constexpr int kBoxBytes = kBoxRows * kBlockK * 2;
-    const int w_boxes = kPerTile * (p.dual ? 2 : 1);
-    const int x_boxes = (p.tile_n + kBoxRows - 1) / kBoxRows;
-    StageBox b{false, false, 0, 0};
+    const int w_boxes = kPerTile * kAtoms * (p.dual ? 2 : 1);
+    const int x_parts = (p.tile_n + kBoxRows - 1) / kBoxRows;
+    StageBox b{false, false, 0, 0, 0};
     if (lane < w_boxes) {
-        const int tile = lane / kPerTile, part = lane - tile * kPerTile;
+        const int part = lane % kPerTile, atom = (lane / kPerTile) % kAtoms, tile = lane / (kPerTile * kAtoms);
         b.active = true;
         b.offset = lane * kBoxBytes;
         b.row = (tile ? p.up_offset : 0) + part * kBoxRows;
-    } else if (lane < w_boxes + x_boxes) {
-        const int part = lane - w_boxes;
+        b.k = atom * kBlockK;
+    } else if (lane < w_boxes + x_parts * kAtoms) {
+        const int idx = lane - w_boxes, atom = idx / x_parts, part = idx - atom * x_parts;
         b.active = b.from_x = true;
-        b.offset = a_bytes + part * kBoxBytes;
+        b.offset = a_bytes + (atom * p.tile_n + part * kBoxRows) * kBlockK * 2;
         b.row = part * kBoxRows;
+        b.k = atom * kBlockK;
     }
     return b;
 }
@@ -110,7 +117,7 @@ struct Unit {
 };
 __device__ __forceinline__ Unit unit_of(const GemmParams& p, int u) {
     const int tm = u % p.tiles_m, rest = u / p.tiles_m, tt = rest % p.tiles_t, split = rest / p.tiles_t;
-    const int kb_total = (p.K + kBlockK - 1) / kBlockK;
+    const int kb_total = (p.K + kStageK - 1) / kStageK;
     Unit r;
     r.n0 = tm * kTileM;
     r.t0 = tt * p.tile_n;
@@ -126,8 +133,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles is what the swizzle pattern assumes
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int a_bytes = kTileM * kBlockK * 2 * (p.dual ? 2 : 1);
-    const int b_bytes = p.tile_n * kBlockK * 2;
+    const int a_bytes = kTileM * kStageK * 2 * (p.dual ? 2 : 1);
+    const int b_bytes = p.tile_n * kStageK * 2;
     const int stage_bytes = a_bytes + b_bytes;
     uint8_t* staging = smem + (size_t)p.stages * stage_bytes;                 // 2 x kStagingBytes
     uint64_t* full_bar = (uint64_t*)(staging + 2 * kStagingBytes);
@@ -178,7 +185,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (lane == 0) mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
                 __syncwarp();
                 if (box.active)
-                    tma_load_2d(smem + (size_t)s * stage_bytes + box.offset, box.from_x ? &map_x : &map_w, kb * kBlockK, row, &full_bar[s]);
+                    tma_load_2d(smem + (size_t)s * stage_bytes + box.offset, box.from_x ? &map_x : &map_w, kb * kStageK + box.k, row, &full_bar[s]);
                 if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
         }
@@ -189,7 +196,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             // tile is kept running, the others are a constant away
             const uint64_t desc_first = smem_desc(smem_u32(smem));
             const uint64_t stage_step = (uint64_t)(stage_bytes >> 4), b_off = (uint64_t)(a_bytes >> 4);
-            const uint64_t up_off = (uint64_t)((kTileM * kBlockK * 2) >> 4);
+            const uint64_t up_off = (uint64_t)((kTileM * kStageK * 2) >> 4);
+            // a step of 16 elements of K: 32 bytes on inside its swizzled block, the blocks a tile's rows apart
+            const uint64_t a_atom = (uint64_t)((kTileM * kBlockK * 2) >> 4), b_atom = (uint64_t)((p.tile_n * kBlockK * 2) >> 4);
             uint64_t da = desc_first;
             int s = 0;
             uint32_t phase = 0;
@@ -208,10 +217,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     tc_fence_after();
                     const uint64_t db = da + b_off, du = da + up_off;
 #pragma unroll
-                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                        const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);   // 32 bytes a step inside the swizzled row
-                        umma_bf16(d, da + step, db + step, idesc, acc);
-                        if (p.dual) umma_bf16(d_up, du + step, db + step, idesc, acc);
+                    for (int k = 0; k < kStageK / kUmmaK; ++k) {
+                        const uint64_t sub = (uint64_t)(((k % (kBlockK / kUmmaK)) * kUmmaK * 2) >> 4);
+                        const uint64_t a_step = (k / (kBlockK / kUmmaK)) * a_atom + sub, b_step = (k / (kBlockK / kUmmaK)) * b_atom + sub;
+                        umma_bf16(d, da + a_step, db + b_step, idesc, acc);
+                        if (p.dual) umma_bf16(d_up, du + a_step, db + b_step, idesc, acc);
                         acc = 1;
                     }
                     umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
@@ -323,8 +333,8 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles is what the swizzle pattern assumes
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int a_bytes = kTileM * kBlockK * 2 * (p.dual ? 2 : 1);
-    const int b_bytes = p.tile_n * kBlockK * 2;
+    const int a_bytes = kTileM * kStageK * 2 * (p.dual ? 2 : 1);
+    const int b_bytes = p.tile_n * kStageK * 2;
     const int stage_bytes = a_bytes + b_bytes;
     uint64_t* full_bar = (uint64_t*)(smem + (size_t)p.stages * stage_bytes);
     uint64_t* empty_bar = full_bar + p.stages;
@@ -334,7 +344,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kTileM, t0 = blockIdx.y * p.tile_n, split = blockIdx.z;
-    const int kb_total = (p.K + kBlockK - 1) / kBlockK;
+    const int kb_total = (p.K + kStageK - 1) / kStageK;
     const int kb_begin = split * p.kblocks_per_split;
     const int kb_end = min(kb_total, kb_begin + p.kblocks_per_split);
     const int n_kb = kb_end - kb_begin;   // >= 1 by construction of the grid
@@ -367,7 +377,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             if (lane == 0) mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
             __syncwarp();
             if (box.active)
-                tma_load_2d(smem + (size_t)s * stage_bytes + box.offset, box.from_x ? &map_x : &map_w, (kb_begin + i) * kBlockK, row, &full_bar[s]);
+                tma_load_2d(smem + (size_t)s * stage_bytes + box.offset, box.from_x ? &map_x : &map_w, (kb_begin + i) * kStageK + box.k, row, &full_bar[s]);
             if (++s == p.stages) { s = 0; phase ^= 1u; }
         }
     } else if (warp == 1) {
@@ -375,7 +385,8 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             const uint32_t idesc = instr_desc(kTileM, p.tile_n);
             const uint64_t desc_first = smem_desc(smem_u32(smem));
             const uint64_t stage_step = (uint64_t)(stage_bytes >> 4), b_off = (uint64_t)(a_bytes >> 4);
-            const uint64_t up_off = (uint64_t)((kTileM * kBlockK * 2) >> 4);
+            const uint64_t up_off = (uint64_t)((kTileM * kStageK * 2) >> 4);
+            const uint64_t a_atom = (uint64_t)((kTileM * kBlockK * 2) >> 4), b_atom = (uint64_t)((p.tile_n * kBlockK * 2) >> 4);
             const uint32_t d_up = tmem_base + (uint32_t)p.tile_n;
             uint64_t da = desc_first;
             int s = 0;
@@ -386,10 +397,11 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 tc_fence_after();
                 const uint64_t db = da + b_off, du = da + up_off;
 #pragma unroll
-                for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                    const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);   // 32 bytes a step inside the swizzled row
-                    umma_bf16(tmem_base, da + step, db + step, idesc, acc);
-                    if (p.dual) umma_bf16(d_up, du + step, db + step, idesc, acc);
+                for (int k = 0; k < kStageK / kUmmaK; ++k) {
+                    const uint64_t sub = (uint64_t)(((k % (kBlockK / kUmmaK)) * kUmmaK * 2) >> 4);
+                    const uint64_t a_step = (k / (kBlockK / kUmmaK)) * a_atom + sub, b_step = (k / (kBlockK / kUmmaK)) * b_atom + sub;
+                    umma_bf16(tmem_base, da + a_step, db + b_step, idesc, acc);
+                    if (p.dual) umma_bf16(d_up, du + a_step, db + b_step, idesc, acc);
                     acc = 1;
                 }
                 umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
@@ -557,15 +569,15 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
     const int sms = device_sm_count();
     const int tiles_m = (N + kTileM - 1) / kTileM;
     const int t16 = ((T + 15) / 16) * 16;
-    const int kb = (K + kBlockK - 1) / kBlockK;
+    const int kb = (K + kStageK - 1) / kStageK;   // stages of K
     if (T <= 64) {
         // A handful of tokens: the product is bound by reading the weights once. One token tile (so that no
         // weight row is read twice) and, where the row tiles are too few to fill the machine (two CTAs an SM),
-        // K split among CTAs, at least four blocks of 64 each; the partial sums cost T x N floats a split.
+        // K split among CTAs, at least two stages of 128 each; the partial sums cost T x N floats a split.
         int sp = 1;
-        if (tiles_m < 2 * sms && kb >= 8) {
+        if (tiles_m < 2 * sms && kb >= 4) {
             sp = (2 * sms + tiles_m - 1) / tiles_m;
-            if (sp > kb / 4) sp = kb / 4;
+            if (sp > kb / 2) sp = kb / 2;
             if (sp > 16) sp = 16;
             if (sp < 1) sp = 1;
         }
@@ -589,9 +601,9 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
     }
     const int tiles = tiles_m * ((T + tn - 1) / tn);
     int sp = 1;
-    if (tiles * 2 < sms && kb >= 4) {
+    if (tiles * 2 < sms && kb >= 2) {
         sp = (2 * sms + tiles - 1) / tiles;
-        if (sp > kb / 2) sp = kb / 2;
+        if (sp > kb) sp = kb;
         if (sp > 16) sp = 16;
         if (sp < 1) sp = 1;
     }
@@ -617,7 +629,7 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     GemmParams p{};
     p.T = T; p.N = N; p.K = K;
     gemm_tc_plan(T, N, K, dual, &p.tile_n, &p.splits);
-    const int kb = (K + kBlockK - 1) / kBlockK;
+    const int kb = (K + kStageK - 1) / kStageK;
     p.kblocks_per_split = (kb + p.splits - 1) / p.splits;
     p.dual = dual ? 1 : 0;
     p.up_offset = up_offset;
@@ -636,7 +648,7 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     const size_t out_elem = out_dt == F32 ? 4 : 2;
     // (a chunk is 32 tokens, so the token tile must hold at least one)
     p.tma_out = p.splits == 1 && p.tile_n >= kChunk && ((size_t)N * out_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0 ? 1 : 0;
-    const int stage_bytes = kTileM * kBlockK * 2 * (dual ? 2 : 1) + p.tile_n * kBlockK * 2;
+    const int stage_bytes = kTileM * kStageK * 2 * (dual ? 2 : 1) + p.tile_n * kStageK * 2;
     if (T <= 64) {
         // few tokens: one CTA per unit, two CTAs to an SM
         p.tma_out = 0;
