@@ -56,7 +56,12 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
     for n in lens:
         cu.append(cu[-1] + n)
     n_tokens = cu[-1]
-    host = torch.empty((5, n_tokens), dtype=torch.int32)
+    # everything the device needs of this step goes up in ONE copy: five rows of n_tokens numbers, then the
+    # prefill tiles, the slots, the sequences' ends and the sequences' first packed indices
+    tile_rows = [[cu[i], n, q0] for i, n in enumerate(lens) for q0 in range(0, n, QUERY_TILE)] if mode == "prefill" else []
+    extra = 3 * len(tile_rows) + 2 * n_seqs + (n_seqs + 1)
+    flat_host = torch.empty(5 * n_tokens + extra, dtype=torch.int32)
+    host = flat_host[:5 * n_tokens].view(5, n_tokens)
     flat = token_lists[0] if n_seqs == 1 else [t for toks in token_lists for t in toks]
     host[0] = torch.frombuffer(array("i", flat), dtype=torch.int32) if n_tokens else host[0]
     if n_seqs <= 4:
@@ -75,15 +80,20 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
         host[2] = torch.tensor(list(slots), dtype=torch.int32)[seq_of]
         host[3] = (starts_t + lens_t)[seq_of]
         host[4] = firsts[seq_of]
-    dev = host.to(device)
+    tail = [x for row in tile_rows for x in row] + list(slots) + [s + n for s, n in zip(starts, lens)] + cu
+    flat_host[5 * n_tokens:] = torch.tensor(tail, dtype=torch.int32)
+    flat_dev = flat_host.to(device)
+    dev = flat_dev[:5 * n_tokens].view(5, n_tokens)
+    at = 5 * n_tokens
     tiles = None
     if mode == "prefill":
-        tiles = torch.tensor([[cu[i], n, q0] for i, n in enumerate(lens) for q0 in range(0, n, QUERY_TILE)],
-                             dtype=torch.int32).to(device)
-    per_seq = torch.tensor([list(slots), [s + n for s, n in zip(starts, lens)]], dtype=torch.int32).to(device)
+        tiles = flat_dev[at:at + 3 * len(tile_rows)].view(len(tile_rows), 3)
+        at += 3 * len(tile_rows)
+    per_seq = flat_dev[at:at + 2 * n_seqs].view(2, n_seqs)
+    cu_dev = flat_dev[at + 2 * n_seqs:at + 3 * n_seqs + 1]
     return StepBatch(
         mode=mode, n_seqs=len(slots), n_tokens=n_tokens, slots=list(slots), seq_lens=lens,
         max_seq_len=max(s + n for s, n in zip(starts, lens)),
         tokens=dev[0], positions=dev[1], token_slot=dev[2], token_end=dev[3], token_seq_start=dev[4],
-        cu_seqlens=torch.tensor(cu, dtype=torch.int32).to(device), slot_ids=per_seq[0], seq_ends=per_seq[1],
+        cu_seqlens=cu_dev, slot_ids=per_seq[0], seq_ends=per_seq[1],
         prefill_tiles=tiles)
