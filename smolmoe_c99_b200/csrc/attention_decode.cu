@@ -3,18 +3,21 @@
 // src/kernels.c:1156-1176).
 //
 // A thread-block cluster of 1 to 16 CTAs serves one (sequence, kv head); its CTAs split the
-// visible positions. A CTA brings its keys and values into shared memory with 16-byte
-// asynchronous copies: all of them at once if its share fits a buffer of about 100 KB (two
-// such CTAs fit an SM), else in chunks of a few hundred positions with two chunks in flight.
-// The step is bound by the latency of that one trip to memory, so everything is asked for at
-// once and as early as possible: the rows of all earlier positions do not depend on the kernel before (only the
-// newest position's row was written by it), so they are requested BEFORE the wait for that
-// kernel. Within a chunk the eight warps take tiles of 32 positions. The group's query heads
-// are the 16 rows of the tensor-core tile (mma.sync m16n8k16, operands by ldmatrix), so every
-// key and value row that is read serves all of them. A warp keeps a running maximum, sum and
-// weighted values over its tiles; the warps of a CTA merge through shared memory, the CTAs of
-// the cluster through distributed shared memory in rank order. There is no workspace in
-// global memory and nothing depends on the order in which CTAs finish.
+// visible positions. The group's query heads are the 16 rows of the tensor-core tile (mma.sync
+// m16n8k16, operands by ldmatrix), so every key and value row that is read serves all of them. A
+// warp keeps a running maximum, sum and weighted values over its tiles; the warps of a CTA merge
+// through shared memory, the CTAs of the cluster through distributed shared memory in rank order.
+// There is no workspace in global memory and nothing depends on the order in which CTAs finish.
+//
+// Two kernels, by how long a CTA's share is at the largest cluster whose clusters are all
+// resident at once:
+//  - up to about 100 KB of keys and values (decode_attention_kernel): the step is bound by the
+//    latency of one trip to memory, so the whole share is asked for at once (16-byte asynchronous
+//    copies) and as early as possible: the rows of all earlier positions do not depend on the
+//    kernel before (only the newest position's row was written by it), so they are requested
+//    BEFORE the wait for that kernel. Eight warps take tiles of 32 positions.
+//  - longer shares (decode_attention_stream_kernel) are bound by bandwidth: every warp streams
+//    tiles of its own through a ring of shared memory filled by the TMA engine.
 #include <cooperative_groups.h>
 #include <math_constants.h>
 
@@ -26,6 +29,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.cuh"
+#include "tcgen05.cuh"
 
 namespace sm {
 
@@ -36,10 +40,7 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kTile = 32;           // positions per warp tile
 constexpr int kMaxCluster = 16;      // above 8 a kernel has to allow "non-portable" cluster sizes
 
-// positions per chunk for a head dimension of up to 32 * hdb when a share is read in chunks, two in
-// flight: about 36 KB of keys and values each, so that two CTAs fit an SM
-constexpr int chunk_keys(int hdb) { return hdb == 1 ? 224 : (hdb == 2 ? 128 : 64); }
-// the most positions of a CTA's share that are held in one buffer instead (about 96 KB)
+// the most positions of a CTA's share that are held in one buffer (about 96 KB); longer shares are streamed
 constexpr int single_buffer_keys(int hdb) { return 96 * 1024 / ((hdb * 32 + 8) * 4) / kTile * kTile; }
 
 struct DecodeArgs {
@@ -53,8 +54,10 @@ struct DecodeArgs {
     const int32_t* positions;     // [B] position of the new token (its key is already in the cache)
     int B, heads, kv_heads, head_dim, window, cluster;
     float scale_log2;             // scale * log2(e)
-    int buf_keys, n_bufs;         // positions per buffer (a multiple of the tile) and buffers (1 or 2)
+    int buf_keys;                 // one-buffer kernel: positions the buffer holds (a multiple of the tile)
     int own_bytes;                // shared memory a CTA uses for itself: the buffers, later the warps' results
+    int stages;                   // streaming kernel: tiles a warp keeps in flight
+    int* error;                   // streaming kernel: where a wait that ran out is recorded
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -85,6 +88,84 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 
+// What a warp holds after its tiles (running maxima, sums and weighted values of heads g and g + 8) is merged over
+// the CTA's warps through shared memory, then over the cluster's CTAs through the leader's shared memory, in warp
+// and rank order; the leader writes the output. `smem_raw` is free for the warps' results when this is called
+// (the first __syncthreads below separates it from the last tile's reads).
+template <int HDB, int WARPS>
+__device__ __forceinline__ void merge_and_store(const DecodeArgs& a, unsigned char* smem_raw, float* part,
+                                                const float (&o_acc)[HDB * 4][4], float m0, float m1, float l0, float l1,
+                                                int rank, int kvh, int b) {
+    constexpr int HDP = HDB * 32, NT = HDP / 8;
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q4 = lane & 3;
+    const int hd = a.head_dim, group = a.heads / a.kv_heads;
+    constexpr int kThreadsHere = WARPS * 32;
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // ---- the warps of this CTA, through shared memory (the chunk buffers are free now) -------
+    __syncthreads();
+    float* wm = reinterpret_cast<float*>(smem_raw);          // [WARPS][16] maxima
+    float* wl = wm + WARPS * 16;                            // [WARPS][16] sums
+    float* wo = wl + WARPS * 16;                            // [WARPS][16][HDP] weighted values
+    if (q4 == 0) {
+        wm[warp * 16 + g] = m0; wm[warp * 16 + g + 8] = m1;
+        wl[warp * 16 + g] = l0; wl[warp * 16 + g + 8] = l1;
+    }
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+        float* r0 = wo + ((size_t)warp * 16 + g) * HDP + i * 8 + q4 * 2;
+        float* r1 = wo + ((size_t)warp * 16 + g + 8) * HDP + i * 8 + q4 * 2;
+        r0[0] = o_acc[i][0]; r0[1] = o_acc[i][1];
+        r1[0] = o_acc[i][2]; r1[1] = o_acc[i][3];
+    }
+    __syncthreads();
+    const int pstride = HDP + 2;
+    float* dst = a.cluster > 1 ? cluster.map_shared_rank(part, 0) : part;
+    for (int idx = threadIdx.x; idx < group * HDP; idx += kThreadsHere) {
+        const int r = idx / HDP, d = idx - r * HDP;
+        float m = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, wm[w * 16 + r]);
+        float l = 0.f, o = 0.f;
+        if (m != -CUDART_INF_F) {
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float f = exp2f(wm[w * 16 + r] - m);   // a warp without tiles: exp2(-inf) = 0
+                l = fmaf(wl[w * 16 + r], f, l);
+                o = fmaf(wo[((size_t)w * 16 + r) * HDP + d], f, o);
+            }
+        }
+        float* p = dst + ((size_t)rank * group + r) * pstride;
+        p[2 + d] = o;
+        if (d == 0) { p[0] = m; p[1] = l; }
+    }
+    if (a.cluster > 1) {
+        cluster.sync();
+        if (rank != 0) return;
+    } else {
+        __syncthreads();
+    }
+    // ---- the CTAs of the cluster, in rank order ---------------------------------------------------
+    for (int idx = threadIdx.x; idx < group * hd; idx += kThreadsHere) {
+        const int r = idx / hd, d = idx - r * hd;
+        float m = -CUDART_INF_F;
+        for (int c = 0; c < a.cluster; ++c) m = fmaxf(m, part[((size_t)c * group + r) * pstride]);
+        float l = 0.f, o = 0.f;
+        for (int c = 0; c < a.cluster; ++c) {
+            const float* p = part + ((size_t)c * group + r) * pstride;
+            const float f = exp2f(p[0] - m);   // a CTA without keys: exp2(-inf) = 0
+            l = fmaf(p[1], f, l);
+            o = fmaf(p[2 + d], f, o);
+        }
+        a.out[((size_t)b * a.heads + (size_t)kvh * group + r) * hd + d] = __float2bfloat16_rn(o / l);
+    }
+}
+
 // HDB: blocks of 32 of the head dimension (head_dim <= 32 * HDB, a multiple of 16).
 template <int HDB>
 __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a) {
@@ -93,8 +174,8 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
     constexpr int NT = HDP / 8;              // dim tiles of the output
     constexpr int CPR = HDP / 8;             // 16-byte pieces per row
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    // n_bufs buffers of keys, then as many of values, [buf_keys][LD] each; after the loop the same memory holds
-    // the warps' results
+    // the share's keys, then its values, [buf_keys][LD] each; after the loop the same memory holds the warps'
+    // results
     __nv_bfloat16* kv_all = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     const size_t buf_elems = (size_t)a.buf_keys * LD;
     const size_t kOwnBytes = (size_t)a.own_bytes;
@@ -106,7 +187,7 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
     cg::cluster_group cluster = cg::this_cluster();
 
     const int rank = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q4 = lane & 3;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q4 = lane & 3;
     const int hd = a.head_dim, group = a.heads / a.kv_heads;
     pdl_launch_dependents();
     // slots, positions and the page table are written before the step's first kernel
@@ -116,38 +197,31 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
     const int per_cta = ((n_keys + a.cluster - 1) / a.cluster + kTile - 1) / kTile * kTile;
     const int cta_lo = start + rank * per_cta, cta_hi = min(pos + 1, cta_lo + per_cta);   // keys [cta_lo, cta_hi)
     const int cta_keys = cta_hi > cta_lo ? cta_hi - cta_lo : 0;
-    const int n_chunks = (cta_keys + a.buf_keys - 1) / a.buf_keys;
-    // chunks of equal length (a multiple of the tile), so that a short second chunk does not cost a whole pass
-    const int chunk_len = n_chunks ? ((cta_keys + kTile - 1) / kTile + n_chunks - 1) / n_chunks * kTile : kTile;
     PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
 
-    // Requests chunk `ch` into its buffer: thread -> (row, 16-byte piece) in turn. `skip_newest` leaves out
-    // the row of position `pos`, which the kernel before this one writes.
-    auto request_chunk = [&](int ch, bool skip_newest) {
-        __nv_bfloat16* kb = kv_all + (size_t)(ch % a.n_bufs) * buf_elems;
-        __nv_bfloat16* vb = kv_all + (size_t)(a.n_bufs + ch % a.n_bufs) * buf_elems;
-        const int lo = cta_lo + ch * chunk_len;
-        const int rows = min(chunk_len, (cta_hi - lo + kTile - 1) / kTile * kTile);   // whole tiles; rows past the end are zeros
+    // The whole share is asked for at once: thread -> (row, 16-byte piece) in turn, whole tiles (rows past the end
+    // are zeros). The row of position `pos`, which the kernel before this one writes, is left out.
+    {
+        __nv_bfloat16* kb = kv_all;
+        __nv_bfloat16* vb = kv_all + buf_elems;
+        const int rows = (cta_keys + kTile - 1) / kTile * kTile;
         for (int idx = threadIdx.x; idx < rows * CPR; idx += kThreads) {
             const int row = idx / CPR, col = (idx - row * CPR) * 8;
-            const int key = lo + row;
-            if (skip_newest && key == pos) continue;
+            const int key = cta_lo + row;
+            if (key == pos) continue;
             const bool in = key < cta_hi && col < hd;
             const size_t o = in ? paged.row_offset(slot, key, kvh) + col : 0;
             cp_async16(kb + (size_t)row * LD + col, a.k_pool + o, in);
             cp_async16(vb + (size_t)row * LD + col, a.v_pool + o, in);
         }
-    };
-    if (n_chunks > 0) request_chunk(0, true);
-    cp_async_commit();
-    if (a.n_bufs > 1 && n_chunks > 1) request_chunk(1, true);
+    }
     cp_async_commit();
 
     pdl_wait();   // q and the newest key and value come from the kernel before
 
     {
-        // q of the group's heads, and the newest position's row if its chunk has been asked for already: plain
-        // loads and stores, which the barrier before the first chunk's use makes visible
+        // q of the group's heads, and the newest position's row: plain loads and stores, which the barrier
+        // before the tiles' use makes visible
         const __nv_bfloat16* qrow = a.q + ((size_t)b * a.heads + (size_t)kvh * group) * hd;
         for (int idx = threadIdx.x; idx < 16 * CPR; idx += kThreads) {
             const int row = idx / CPR, col = (idx - row * CPR) * 8;
@@ -156,13 +230,13 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
                 in ? *reinterpret_cast<const uint4*>(qrow + (size_t)row * hd + col) : make_uint4(0, 0, 0, 0);
         }
         if (pos >= cta_lo && pos < cta_hi) {
-            const int ch = (pos - cta_lo) / chunk_len, row = (pos - cta_lo) - ch * chunk_len;
-            if (ch < a.n_bufs && threadIdx.x < 2 * CPR) {
+            const int row = pos - cta_lo;
+            if (threadIdx.x < 2 * CPR) {
                 const int which = threadIdx.x / CPR, col = (threadIdx.x - which * CPR) * 8;   // 0: key, 1: value
                 const bool in = col < hd;
                 const size_t o = in ? paged.row_offset(slot, pos, kvh) + col : 0;
                 const __nv_bfloat16* src = (which ? a.v_pool : a.k_pool) + o;
-                *reinterpret_cast<uint4*>(kv_all + (size_t)(which * a.n_bufs + ch) * buf_elems + (size_t)row * LD + col) =
+                *reinterpret_cast<uint4*>(kv_all + (size_t)which * buf_elems + (size_t)row * LD + col) =
                     in ? *reinterpret_cast<const uint4*>(src) : make_uint4(0, 0, 0, 0);
             }
         }
@@ -173,17 +247,13 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
     for (int i = 0; i < NT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
     float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
 
-    for (int ch = 0; ch < n_chunks; ++ch) {
-        // Groups of copies in the order they were committed: chunk 0, chunk 1 (or nothing), then one after every
-        // chunk's use (chunk ch + n_bufs, or nothing). Chunk ch is in group ch; with two buffers one later group
-        // may still be on its way.
-        if (a.n_bufs == 1) asm volatile("cp.async.wait_group 0;" ::: "memory");
-        else asm volatile("cp.async.wait_group 1;" ::: "memory");
-        __syncthreads();
-        const __nv_bfloat16* kb = kv_all + (size_t)(ch % a.n_bufs) * buf_elems;
-        const __nv_bfloat16* vb = kv_all + (size_t)(a.n_bufs + ch % a.n_bufs) * buf_elems;
-        const int lo = cta_lo + ch * chunk_len;
-        const int tiles = (min(chunk_len, cta_hi - lo) + kTile - 1) / kTile;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    {
+        const __nv_bfloat16* kb = kv_all;
+        const __nv_bfloat16* vb = kv_all + buf_elems;
+        const int lo = cta_lo;
+        const int tiles = (cta_keys + kTile - 1) / kTile;
         for (int tile = warp; tile < tiles; tile += kWarps) {
             const __nv_bfloat16* kt = kb + (size_t)tile * kTile * LD;
             const __nv_bfloat16* vt = vb + (size_t)tile * kTile * LD;
@@ -251,79 +321,265 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
                     mma_bf16(o_acc[i + 1], pf[jj][0], pf[jj][1], pf[jj][2], pf[jj][3], vf[2], vf[3]);
                 }
         }
-        __syncthreads();   // the buffer is free again
-        if (ch + a.n_bufs < n_chunks) request_chunk(ch + a.n_bufs, false);
-        cp_async_commit();
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    merge_and_store<HDB, kWarps>(a, smem_raw, part, o_acc, m0, m1, l0, l1, rank, kvh, b);
+}
 
-    // ---- the warps of this CTA, through shared memory (the chunk buffers are free now) -------
-    __syncthreads();
-    float* wm = reinterpret_cast<float*>(smem_raw);          // [kWarps][16] maxima
-    float* wl = wm + kWarps * 16;                            // [kWarps][16] sums
-    float* wo = wl + kWarps * 16;                            // [kWarps][16][HDP] weighted values
-    if (q4 == 0) {
-        wm[warp * 16 + g] = m0; wm[warp * 16 + g + 8] = m1;
-        wl[warp * 16 + g] = l0; wl[warp * 16 + g + 8] = l1;
+// ---- shares that do not fit one buffer: every warp streams tiles of its own ------------------------------------
+//
+// A CTA of four warps; warp w takes the tiles w, w + 4, ... of the CTA's share (KT positions a tile) and keeps
+// `stages` of them in flight in a ring of its own, each slot with an mbarrier that counts the bytes as they land.
+// Nothing in the loop synchronises the CTA: a warp waits for its tile, uses it, and asks for the tile `stages`
+// ahead into the same slot. The query fragments stay in registers for the whole share.
+//
+// How a tile comes in. A page of the cache holds 64 positions of one kv head as one contiguous block, so with
+// head sizes of 64 and 128 (BOX) a tile that lies on a multiple of KT positions is one box of a 2-D tensor map over
+// the pool [pages * kv heads * 64 rows, head_dim]: one TMA copy per 64 columns of keys and of values, written with
+// the 128-byte swizzle that keeps ldmatrix free of bank conflicts. (Copies of single rows, the other way, are bound
+// by the number of copies: a B200 takes about one per 16 cycles and SM, 2.3 to 3.8 TB/s at 128 to 256 bytes a row.)
+// Other head sizes are copied row by row (cp.async.bulk, one lane a row) into rows padded by 16 bytes.
+constexpr int kStreamWarps = 4;
+constexpr int kStreamThreads = kStreamWarps * 32;
+
+template <int HDB, int KT, bool BOX>
+__global__ void __launch_bounds__(kStreamThreads)
+decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeArgs a) {
+    using namespace tc5;
+    constexpr int HDP = HDB * 32;
+    constexpr int LD = HDP + 8;                  // row by row: elements of a padded row
+    constexpr int NT = HDP / 8;
+    constexpr int CPR = HDP / 8;                 // 16-byte pieces of a row
+    constexpr int HALVES = BOX ? HDP / 64 : 1;   // BOX: blocks of 64 columns, each [KT][64] with rows of 128 bytes
+    constexpr int kTileElems = BOX ? KT * HDP : KT * LD;                  // keys of a tile; as many values behind them
+    constexpr int kTileBytes = 2 * kTileElems * (int)sizeof(__nv_bfloat16);
+    static_assert(KT == 16 || KT == 32, "a tile is 16 or 32 positions");
+    static_assert(!BOX || HDP % 64 == 0, "boxes are 64 columns wide");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    // [warp][stage][keys | values] (on 1,024 bytes for the swizzle), later the warps' results from smem_raw on;
+    // then q, the cluster's partial results, the barriers
+    const int group = a.heads / a.kv_heads, hd = a.head_dim, S = a.stages;
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw + a.own_bytes);
+    float* part = reinterpret_cast<float*>(smem_raw + a.own_bytes + (size_t)16 * LD * sizeof(__nv_bfloat16));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(part + (size_t)a.cluster * group * (HDP + 2));   // [warp][stage]
+
+    const int rank = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q4 = lane & 3;
+    pdl_launch_dependents();
+    // slots, positions and the page table are written before the step's first kernel
+    const int slot = a.slots[b], pos = a.positions[b];
+    const int start = (a.window > 0 && pos >= a.window) ? pos - a.window + 1 : 0;
+    // BOX: tiles lie on multiples of KT positions, so that each is inside one page; what lies before `start` in
+    // the first of them is masked
+    const int base0 = BOX ? start / KT * KT : start;
+    const int n_keys = pos - base0 + 1;
+    const int per_cta = ((n_keys + a.cluster - 1) / a.cluster + kTile - 1) / kTile * kTile;
+    const int cta_lo = base0 + rank * per_cta, cta_hi = min(pos + 1, cta_lo + per_cta);
+    const int first_key = max(start, cta_lo);                                        // this CTA's keys: [first_key, cta_hi)
+    const int n_tiles = cta_hi > cta_lo ? (cta_hi - cta_lo + KT - 1) / KT : 0;
+    const int my_tiles = n_tiles > warp ? (n_tiles - warp + kStreamWarps - 1) / kStreamWarps : 0;
+    PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
+    unsigned char* ring_base = BOX ? reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023) : smem_raw;
+    unsigned char* ring = ring_base + (size_t)warp * S * kTileBytes;
+    uint64_t* my_bars = bars + warp * S;
+    const uint32_t row_bytes = (uint32_t)hd * sizeof(__nv_bfloat16);
+
+    if (lane == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(&my_bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-#pragma unroll
-    for (int i = 0; i < NT; ++i) {
-        float* r0 = wo + ((size_t)warp * 16 + g) * HDP + i * 8 + q4 * 2;
-        float* r1 = wo + ((size_t)warp * 16 + g + 8) * HDP + i * 8 + q4 * 2;
-        r0[0] = o_acc[i][0]; r0[1] = o_acc[i][1];
-        r1[0] = o_acc[i][2]; r1[1] = o_acc[i][3];
+    if (!BOX && hd != HDP) {
+        // the columns between head_dim and its padded size are never copied: zeros, so that they add nothing
+        for (int i = lane; i < S * kTileBytes / 16; i += 32) reinterpret_cast<uint4*>(ring)[i] = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    __syncthreads();
-    const int pstride = HDP + 2;
-    float* dst = a.cluster > 1 ? cluster.map_shared_rank(part, 0) : part;
-    for (int idx = threadIdx.x; idx < group * HDP; idx += kThreads) {
-        const int r = idx / HDP, d = idx - r * HDP;
-        float m = -CUDART_INF_F;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) m = fmaxf(m, wm[w * 16 + r]);
-        float l = 0.f, o = 0.f;
-        if (m != -CUDART_INF_F) {
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
-                const float f = exp2f(wm[w * 16 + r] - m);   // a warp without tiles: exp2(-inf) = 0
-                l = fmaf(wl[w * 16 + r], f, l);
-                o = fmaf(wo[((size_t)w * 16 + r) * HDP + d], f, o);
+    __syncwarp();
+
+    // Byte offset in a tile of the 16-byte piece `piece` of row `row`.
+    auto piece_at = [&](int row, int piece) -> int {
+        if (BOX) return (piece >> 3) * (KT * 128) + row * 128 + (((piece & 7) ^ (row & 7)) << 4);
+        return (row * LD + piece * 8) * (int)sizeof(__nv_bfloat16);
+    };
+    // Whether this warp's tile number i holds the newest position, whose row the kernel before this one writes.
+    auto holds_newest = [&](int i) -> bool {
+        const int lo = cta_lo + (warp + kStreamWarps * i) * KT;
+        return pos >= lo && pos < lo + KT;
+    };
+    // Asks for this warp's tile number i into slot s. Row by row: before the wait on the kernel before this one
+    // the newest position's row is left out; rows behind the share's end are not copied, and the value rows among
+    // them are zeroed, since they are multiplied (by zero weights).
+    auto request = [&](int i, int s, bool before_wait) {
+        const int lo = cta_lo + (warp + kStreamWarps * i) * KT;
+        unsigned char* kt = ring + (size_t)s * kTileBytes;
+        unsigned char* vt = kt + kTileBytes / 2;
+        if (BOX) {
+            if (lane == 0) mbar_expect_tx(&my_bars[s], (uint32_t)kTileBytes);
+            __syncwarp();
+            if (lane < 2 * HALVES) {
+                const int which = lane / HALVES, half = lane - which * HALVES;   // 0: keys, 1: values
+                const int idx = a.ring > 0 ? lo % a.ring : lo;
+                const int page = a.page_table[(size_t)slot * a.table_stride + idx / kPageSize];
+                const int row = (page * a.kv_heads + kvh) * kPageSize + idx % kPageSize;
+                tma_load_2d((which ? vt : kt) + half * (KT * 128), which ? &map_v : &map_k, half * 64, row, &my_bars[s]);
+            }
+            return;
+        }
+        const int rows = min(KT, cta_hi - lo);
+        const bool without_newest = before_wait && pos >= lo && pos < lo + rows;
+        if (lane == 0) mbar_expect_tx(&my_bars[s], (uint32_t)(rows - (without_newest ? 1 : 0)) * 2u * row_bytes);
+        if (rows < KT) {
+            for (int i16 = lane; i16 < (KT - rows) * (LD / 8); i16 += 32)
+                reinterpret_cast<uint4*>(vt + (size_t)rows * LD * sizeof(__nv_bfloat16))[i16] = make_uint4(0, 0, 0, 0);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+        const int row = KT == 32 ? lane : (lane & 15), key = lo + row;
+        if (row < rows && !(before_wait && key == pos)) {
+            const size_t o = paged.row_offset(slot, key, kvh);
+            const int at = row * LD * (int)sizeof(__nv_bfloat16);
+            if (KT == 32 || lane < 16) bulk_load(kt + at, a.k_pool + o, row_bytes, &my_bars[s]);
+            if (KT == 32 || lane >= 16) bulk_load(vt + at, a.v_pool + o, row_bytes, &my_bars[s]);
+        }
+    };
+    const int ahead = min(S, my_tiles);
+    for (int i = 0; i < ahead; ++i)
+        if (!(BOX && holds_newest(i))) request(i, i, true);
+
+    pdl_wait();   // q and the newest key and value come from the kernel before
+
+    {
+        // q of the group's heads into shared memory (heads beyond the group zero): plain loads and stores
+        const __nv_bfloat16* qrow = a.q + ((size_t)b * a.heads + (size_t)kvh * group) * hd;
+        for (int idx = threadIdx.x; idx < 16 * CPR; idx += kStreamThreads) {
+            const int row = idx / CPR, col = (idx - row * CPR) * 8;
+            const bool in = row < group && col < hd;
+            *reinterpret_cast<uint4*>(qs + (size_t)row * LD + col) =
+                in ? *reinterpret_cast<const uint4*>(qrow + (size_t)row * hd + col) : make_uint4(0, 0, 0, 0);
+        }
+        // the newest position, if its tile is among those asked for above: as a whole tile now (BOX), else its
+        // row by plain loads and stores into the tile
+        if (pos >= cta_lo && pos < cta_hi) {
+            const int t = (pos - cta_lo) / KT, row = (pos - cta_lo) - t * KT;
+            const int i = t / kStreamWarps;
+            if (t % kStreamWarps == warp && i < ahead) {
+                if (BOX) {
+                    request(i, i, false);
+                } else if (lane < 2 * CPR) {
+                    const int which = lane / CPR, piece = lane - which * CPR;   // 0: key, 1: value
+                    if (piece * 8 < hd) {
+                        const size_t o = paged.row_offset(slot, pos, kvh) + piece * 8;
+                        const __nv_bfloat16* src = (which ? a.v_pool : a.k_pool) + o;
+                        unsigned char* tile = ring + (size_t)i * kTileBytes + which * (kTileBytes / 2);
+                        *reinterpret_cast<uint4*>(tile + piece_at(row, piece)) = *reinterpret_cast<const uint4*>(src);
+                    }
+                }
             }
         }
-        float* p = dst + ((size_t)rank * group + r) * pstride;
-        p[2 + d] = o;
-        if (d == 0) { p[0] = m; p[1] = l; }
     }
-    if (a.cluster > 1) {
-        cluster.sync();
-        if (rank != 0) return;
-    } else {
-        __syncthreads();
+    __syncthreads();
+
+    uint32_t qa[HDB][4], qb[HDB][4];   // heads x dims [0, 16) and [16, 32) of each block of 32
+#pragma unroll
+    for (int kb32 = 0; kb32 < HDB; ++kb32) {
+        ldmatrix_x4(qa[kb32], qs + (size_t)(lane & 15) * LD + kb32 * 32 + (lane >> 4) * 8);
+        ldmatrix_x4(qb[kb32], qs + (size_t)(lane & 15) * LD + kb32 * 32 + 16 + (lane >> 4) * 8);
     }
-    // ---- the CTAs of the cluster, in rank order ---------------------------------------------------
-    for (int idx = threadIdx.x; idx < group * hd; idx += kThreads) {
-        const int r = idx / hd, d = idx - r * hd;
-        float m = -CUDART_INF_F;
-        for (int c = 0; c < a.cluster; ++c) m = fmaxf(m, part[((size_t)c * group + r) * pstride]);
-        float l = 0.f, o = 0.f;
-        for (int c = 0; c < a.cluster; ++c) {
-            const float* p = part + ((size_t)c * group + r) * pstride;
-            const float f = exp2f(p[0] - m);   // a CTA without keys: exp2(-inf) = 0
-            l = fmaf(p[1], f, l);
-            o = fmaf(p[2 + d], f, o);
+    float o_acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+    int s = 0;
+    uint32_t parity = 0;
+    for (int i = 0; i < my_tiles; ++i) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&my_bars[s], parity))) {
+            if (lane == 0 && a.error) atomicExch(a.error, 6);
+            break;
         }
-        a.out[((size_t)b * a.heads + (size_t)kvh * group + r) * hd + d] = __float2bfloat16_rn(o / l);
+        const unsigned char* kt = ring + (size_t)s * kTileBytes;
+        unsigned char* vt = ring + (size_t)s * kTileBytes + kTileBytes / 2;
+        const int lo = cta_lo + (warp + kStreamWarps * i) * KT;
+        if (BOX && (lo < first_key || lo + KT > cta_hi)) {
+            // a box brings whole rows of the page: the value rows outside the share are zeroed (zero weights times
+            // whatever lies there must stay zero)
+            for (int idx = lane; idx < KT * CPR; idx += 32) {
+                const int row = idx / CPR, piece = idx - row * CPR;
+                if (lo + row < first_key || lo + row >= cta_hi) *reinterpret_cast<uint4*>(vt + piece_at(row, piece)) = make_uint4(0, 0, 0, 0);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+        }
+        // S = Q K^T: 16 heads x KT keys
+        float sc[KT / 8][4];
+#pragma unroll
+        for (int j = 0; j < KT / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+        for (int kb32 = 0; kb32 < HDB; ++kb32)
+#pragma unroll
+            for (int j = 0; j < KT / 8; ++j) {
+                uint32_t kf[4];      // keys 8j.. x dims 0-7, 8-15, 16-23, 24-31 of the block
+                ldmatrix_x4(kf, kt + piece_at(j * 8 + (lane & 7), kb32 * 4 + (lane >> 3)));
+                mma_bf16(sc[j], qa[kb32][0], qa[kb32][1], qa[kb32][2], qa[kb32][3], kf[0], kf[1]);
+                mma_bf16(sc[j], qb[kb32][0], qb[kb32][1], qb[kb32][2], qb[kb32][3], kf[2], kf[3]);
+            }
+        // scale, mask the keys outside this CTA's range, running maximum
+        float mx0 = m0, mx1 = m1;
+#pragma unroll
+        for (int j = 0; j < KT / 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = lo + j * 8 + q4 * 2 + (e & 1);
+                const float x = (key >= first_key && key < cta_hi) ? sc[j][e] * a.scale_log2 : -CUDART_INF_F;
+                sc[j][e] = x;
+                if (e & 2) mx1 = fmaxf(mx1, x); else mx0 = fmaxf(mx0, x);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        // a tile always holds a visible key (the first one holds the window's start): mx is finite
+        const float c0 = exp2f(m0 - mx0), c1 = exp2f(m1 - mx1);
+        const float sub0 = mx0, sub1 = mx1;
+        m0 = mx0;
+        m1 = mx1;
+        uint32_t pf[KT / 16][4];
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < KT / 8; ++j) {
+            const float p0 = exp2f(sc[j][0] - sub0), p1 = exp2f(sc[j][1] - sub0);
+            const float p2 = exp2f(sc[j][2] - sub1), p3 = exp2f(sc[j][3] - sub1);
+            sum0 += p0 + p1;
+            sum1 += p2 + p3;
+            pf[j / 2][(j & 1) * 2] = pack_bf16(p0, p1);
+            pf[j / 2][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        l0 = l0 * c0 + sum0;
+        l1 = l1 * c1 + sum1;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            o_acc[t][0] *= c0; o_acc[t][1] *= c0; o_acc[t][2] *= c1; o_acc[t][3] *= c1;
+        }
+        // O += P V: keys 16jj.. x two dim tiles per ldmatrix
+#pragma unroll
+        for (int jj = 0; jj < KT / 16; ++jj)
+#pragma unroll
+            for (int t = 0; t < NT; t += 2) {
+                uint32_t vf[4];
+                ldmatrix_x4_trans(vf, vt + piece_at(jj * 16 + (lane & 15), t + (lane >> 4)));
+                mma_bf16(o_acc[t], pf[jj][0], pf[jj][1], pf[jj][2], pf[jj][3], vf[0], vf[1]);
+                mma_bf16(o_acc[t + 1], pf[jj][0], pf[jj][1], pf[jj][2], pf[jj][3], vf[2], vf[3]);
+            }
+        __syncwarp();   // every lane has read the slot
+        if (i + S < my_tiles) request(i + S, s, false);
+        if (++s == S) { s = 0; parity ^= 1u; }
     }
+    merge_and_store<HDB, kStreamWarps>(a, smem_raw, part, o_acc, m0, m1, l0, l1, rank, kvh, b);
 }
 
 // Shared memory of a CTA and how it is cut, for a cluster size and the most positions a CTA can get.
 struct DecodePlan {
-    int cluster, buf_keys, n_bufs, own_bytes;
+    int cluster, buf_keys, own_bytes;
     size_t smem;
+    bool fits;   // a CTA's share fits the buffer; else the share is streamed (StreamPlan)
 };
 
 DecodePlan make_plan(int hdb, int group, int cluster, int visible) {
@@ -331,14 +587,9 @@ DecodePlan make_plan(int hdb, int group, int cluster, int visible) {
     const int per_cta = ((visible + cluster - 1) / cluster + kTile - 1) / kTile * kTile;
     DecodePlan p{};
     p.cluster = cluster;
-    if (per_cta <= single_buffer_keys(hdb)) {
-        p.n_bufs = 1;
-        p.buf_keys = per_cta;
-    } else {
-        p.n_bufs = 2;
-        p.buf_keys = chunk_keys(hdb);
-    }
-    const size_t loop_bytes = (size_t)2 * p.n_bufs * p.buf_keys * ld * sizeof(__nv_bfloat16);
+    p.fits = per_cta <= single_buffer_keys(hdb);
+    p.buf_keys = p.fits ? per_cta : kTile;
+    const size_t loop_bytes = (size_t)2 * p.buf_keys * ld * sizeof(__nv_bfloat16);
     const size_t local_bytes = ((size_t)kWarps * 32 + (size_t)kWarps * 16 * hdb * 32) * sizeof(float);
     p.own_bytes = (int)(((loop_bytes > local_bytes ? loop_bytes : local_bytes) + 15) / 16 * 16);
     p.smem = (size_t)p.own_bytes + (size_t)16 * ld * sizeof(__nv_bfloat16) +
@@ -386,6 +637,142 @@ int resident_clusters(const DecodePlan& p) {
     return n;
 }
 
+// ---- the streaming kernel's plan -------------------------------------------------------------------------------
+constexpr int stream_tile_keys(int hdb) { return hdb >= 3 ? 16 : 32; }
+constexpr size_t kStreamSmemShared = 112 * 1024;   // two CTAs to an SM
+constexpr size_t kStreamSmemAlone = 208 * 1024;    // one CTA to an SM: more tiles in flight when the CTAs are few
+
+struct StreamPlan {
+    int cluster, stages, own_bytes;
+    size_t smem;
+};
+
+// Shared memory for a cluster size: as many tiles in flight per warp (2 to 6) as fit `target` bytes a CTA.
+StreamPlan make_stream_plan(int hdb, bool box, int group, int cluster, size_t target) {
+    const int hdp = hdb * 32, ld = hdp + 8;
+    const size_t tile_bytes = (size_t)2 * stream_tile_keys(hdb) * (box ? hdp : ld) * sizeof(__nv_bfloat16);
+    const size_t fixed = (size_t)16 * ld * sizeof(__nv_bfloat16) + (size_t)cluster * group * (hdp + 2) * sizeof(float) +
+                         (size_t)kStreamWarps * 6 * sizeof(uint64_t) + (box ? 1024 : 0) /*the ring starts on 1,024 bytes*/;
+    int stages = target > fixed ? (int)((target - fixed) / (kStreamWarps * tile_bytes)) : 2;
+    stages = stages < 2 ? 2 : (stages > 6 ? 6 : stages);
+    const size_t ring_bytes = (size_t)kStreamWarps * stages * tile_bytes + (box ? 1024 : 0);
+    const size_t local_bytes = ((size_t)kStreamWarps * 32 + (size_t)kStreamWarps * 16 * hdp) * sizeof(float);
+    StreamPlan p{};
+    p.cluster = cluster;
+    p.stages = stages;
+    p.own_bytes = (int)(((ring_bytes > local_bytes ? ring_bytes : local_bytes) + 15) / 16 * 16);
+    p.smem = (size_t)p.own_bytes + fixed - (box ? 1024 : 0);
+    return p;
+}
+
+template <int HDB, bool BOX>
+void prepare_stream(size_t smem) {
+    constexpr int KT = stream_tile_keys(HDB);
+    static size_t allowed = 48 * 1024;
+    static bool large_clusters = false;
+    if (!large_clusters) {
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_stream_kernel<HDB, KT, BOX>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) throw std::runtime_error(std::string("attention_decode: ") + cudaGetErrorString(e));
+        large_clusters = true;
+    }
+    if (smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_stream_kernel<HDB, KT, BOX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) throw std::runtime_error(std::string("attention_decode: ") + cudaGetErrorString(e));
+        allowed = smem;
+    }
+}
+
+template <int HDB, bool BOX>
+int resident_stream_clusters(const StreamPlan& p) {
+    prepare_stream<HDB, BOX>(p.smem);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(p.cluster, 1, 1);
+    cfg.blockDim = dim3(kStreamThreads);
+    cfg.dynamicSmemBytes = p.smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)p.cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, decode_attention_stream_kernel<HDB, stream_tile_keys(HDB), BOX>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+// The largest cluster all of whose clusters are resident at once and every warp of which gets two tiles or more.
+template <int HDB, bool BOX>
+StreamPlan choose_stream_plan(int pairs, int group, int visible) {
+    struct Known { int pairs, group, visible; StreamPlan plan; };
+    static std::mutex lock;
+    static std::vector<Known> known;
+    std::lock_guard<std::mutex> hold(lock);
+    for (const Known& k : known)
+        if (k.pairs == pairs && k.group == group && k.visible == visible) return k.plan;
+    StreamPlan chosen = make_stream_plan(HDB, BOX, group, 1, kStreamSmemShared);
+    for (int cluster = kMaxCluster; cluster > 1; cluster /= 2) {
+        if (visible < cluster * kStreamWarps * 2 * stream_tile_keys(HDB)) continue;
+        const StreamPlan p = make_stream_plan(HDB, BOX, group, cluster, kStreamSmemShared);
+        if (pairs <= resident_stream_clusters<HDB, BOX>(p)) { chosen = p; break; }
+    }
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (pairs * chosen.cluster <= sms) {
+        // no SM gets a second CTA: each takes the shared memory of two
+        const StreamPlan alone = make_stream_plan(HDB, BOX, group, chosen.cluster, kStreamSmemAlone);
+        if (pairs <= resident_stream_clusters<HDB, BOX>(alone)) chosen = alone;
+    }
+    if (known.size() < 4096) known.push_back({pairs, group, visible, chosen});
+    return chosen;
+}
+
+// Whether tiles can come in as boxes of a tensor map over the pool: whole blocks of 64 columns, a pool TMA can
+// address (16-byte base, row numbers that fit 31 bits).
+bool boxes_possible(int head_dim, int kv_heads, long long pool_pages, const void* k_pool, const void* v_pool) {
+    return head_dim % 64 == 0 && pool_pages > 0 && pool_pages * kv_heads * kPageSize < (1ll << 31) &&
+           (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
+}
+
+// The pool [pages, kv heads, 64 positions, head_dim] as rows of head_dim, boxes of `rows` rows x 64 columns with
+// the 128-byte swizzle.
+CUtensorMap make_pool_map(const void* pool, long long pool_pages, int kv_heads, int head_dim, int rows) {
+    CUtensorMap map;
+    cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)(pool_pages * kv_heads * kPageSize)};
+    cuuint64_t strides[1] = {(cuuint64_t)head_dim * sizeof(__nv_bfloat16)};
+    cuuint32_t box[2] = {64, (cuuint32_t)rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = tc5::tensor_map_encoder()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box,
+                                           elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        throw std::runtime_error("attention_decode: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r) +
+                                 " for a pool of " + std::to_string(pool_pages) + " pages");
+    return map;
+}
+
+template <int HDB, bool BOX>
+void launch_stream(DecodeArgs a, int visible, long long pool_pages, cudaStream_t stream) {
+    constexpr int KT = stream_tile_keys(HDB);
+    const StreamPlan sp = choose_stream_plan<HDB, BOX>(a.B * a.kv_heads, a.heads / a.kv_heads, visible);
+    a.cluster = sp.cluster;
+    a.stages = sp.stages;
+    a.own_bytes = sp.own_bytes;
+    a.error = error_word();
+    CUtensorMap map_k{}, map_v{};
+    if (BOX) {
+        map_k = make_pool_map(a.k_pool, pool_pages, a.kv_heads, a.head_dim, KT);
+        map_v = make_pool_map(a.v_pool, pool_pages, a.kv_heads, a.head_dim, KT);
+    }
+    prepare_stream<HDB, BOX>(sp.smem);
+    launch_kernel("attention_decode", decode_attention_stream_kernel<HDB, KT, BOX>, dim3(a.cluster, a.kv_heads, a.B),
+                  dim3(kStreamThreads), sp.smem, stream, a.cluster, dependent_launch_enabled(), map_k, map_v, a);
+}
+
 // CTAs per (sequence, kv head): the largest cluster, of at most 16, all of whose clusters are resident at once
 // (a second wave doubles the time), and every CTA of which gets a few tiles of positions.
 template <int HDB>
@@ -407,11 +794,18 @@ DecodePlan choose_plan(int pairs, int group, int visible) {
 }
 
 template <int HDB>
-void launch(DecodeArgs a, int visible, cudaStream_t stream) {
+void launch(DecodeArgs a, int visible, long long pool_pages, cudaStream_t stream) {
     const DecodePlan p = choose_plan<HDB>(a.B * a.kv_heads, a.heads / a.kv_heads, visible);
+    if (!p.fits) {
+        // a share that does not fit one buffer is streamed
+        if (HDB % 2 == 0 && boxes_possible(a.head_dim, a.kv_heads, pool_pages, a.k_pool, a.v_pool))
+            launch_stream<HDB, HDB % 2 == 0>(a, visible, pool_pages, stream);
+        else
+            launch_stream<HDB, false>(a, visible, pool_pages, stream);
+        return;
+    }
     a.cluster = p.cluster;
     a.buf_keys = p.buf_keys;
-    a.n_bufs = p.n_bufs;
     a.own_bytes = p.own_bytes;
     prepare<HDB>(p.smem);
     launch_kernel("attention_decode", decode_attention_kernel<HDB>, dim3(a.cluster, a.kv_heads, a.B), dim3(kThreads), p.smem,
@@ -435,12 +829,25 @@ void attention_decode_plan(int B, int heads, int kv_heads, int head_dim, int win
         case 3: p = choose_plan<3>(B * kv_heads, heads / kv_heads, visible); break;
         default: p = choose_plan<4>(B * kv_heads, heads / kv_heads, visible); break;
     }
-    plan[0] = p.cluster; plan[1] = p.buf_keys; plan[2] = p.n_bufs; plan[3] = (int)p.smem;
+    plan[0] = p.cluster; plan[1] = p.buf_keys; plan[2] = 1; plan[3] = (int)p.smem;
+    if (!p.fits) {   // streamed: the cluster, 0, the tiles a warp keeps in flight, the shared memory
+        StreamPlan sp{};
+        switch ((head_dim + 31) / 32) {
+            case 1: sp = choose_stream_plan<1, false>(B * kv_heads, heads / kv_heads, visible); break;
+            case 2: sp = head_dim == 64 ? choose_stream_plan<2, true>(B * kv_heads, heads / kv_heads, visible)
+                                        : choose_stream_plan<2, false>(B * kv_heads, heads / kv_heads, visible); break;
+            case 3: sp = choose_stream_plan<3, false>(B * kv_heads, heads / kv_heads, visible); break;
+            default: sp = head_dim == 128 ? choose_stream_plan<4, true>(B * kv_heads, heads / kv_heads, visible)
+                                          : choose_stream_plan<4, false>(B * kv_heads, heads / kv_heads, visible); break;
+        }
+        plan[0] = sp.cluster; plan[1] = 0; plan[2] = sp.stages; plan[3] = (int)sp.smem;
+    }
 }
 
 void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
                       const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
-                      const int32_t* page_table, int table_stride, int ring, int max_len, cudaStream_t stream) {
+                      const int32_t* page_table, int table_stride, int ring, int max_len, long long pool_pages,
+                      cudaStream_t stream) {
     if (B <= 0) return;
     if (!attention_decode_supports(heads, kv_heads, head_dim))
         throw std::invalid_argument("attention_decode: head_dim " + std::to_string(head_dim) + " with " +
@@ -451,13 +858,13 @@ void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, 
     const int visible = window > 0 && window < max_len ? window : max_len;
     DecodeArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
                  page_table, table_stride, ring, slots, positions, B, heads, kv_heads, head_dim, window, 1,
-                 scale * 1.4426950408889634f, 0, 0, 0};
+                 scale * 1.4426950408889634f, 0, 0, 0, nullptr};
     note_launch();
     switch ((head_dim + 31) / 32) {
-        case 1: launch<1>(a, visible, stream); break;
-        case 2: launch<2>(a, visible, stream); break;
-        case 3: launch<3>(a, visible, stream); break;
-        default: launch<4>(a, visible, stream); break;
+        case 1: launch<1>(a, visible, pool_pages, stream); break;
+        case 2: launch<2>(a, visible, pool_pages, stream); break;
+        case 3: launch<3>(a, visible, pool_pages, stream); break;
+        default: launch<4>(a, visible, pool_pages, stream); break;
     }
 }
 

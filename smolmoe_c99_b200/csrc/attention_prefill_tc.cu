@@ -403,23 +403,6 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     if (warp == kIssueWarp) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult res;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
-            res == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)sym;
-    }
-    if (!fn) throw std::runtime_error("attention_prefill_tc: the driver does not provide cuTensorMapEncodeTiled");
-    return fn;
-}
-
 // A [T, width] row-major bfloat16 matrix, boxes of 128 rows x 64 elements, 128-byte swizzle; rows and columns
 // outside the matrix read as zero.
 CUtensorMap make_map(const void* base, int T, int width) {
@@ -428,7 +411,7 @@ CUtensorMap make_map(const void* base, int T, int width) {
     cuuint64_t strides[1] = {(cuuint64_t)width * 2};
     cuuint32_t box[2] = {64, 128};
     cuuint32_t elem[2] = {1, 1};
-    CUresult r = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+    CUresult r = tensor_map_encoder()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)

@@ -497,24 +497,6 @@ __global__ void splitk_reduce_kernel(GemmParams p) {
     else ((__nv_bfloat16*)p.out)[i] = __float2bfloat16_rn(v);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult res;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
-            res == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)sym;
-    });
-    if (!fn) throw std::runtime_error("gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
-    return fn;
-}
-
 // A [rows, K] row-major bfloat16 matrix, boxes of box_rows x 64 elements, 128-byte swizzle.
 // Rows and columns outside the matrix read as zero.
 CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
@@ -523,7 +505,7 @@ CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
     cuuint64_t strides[1] = {(cuuint64_t)K * 2};
     cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
-    CUresult r = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+    CUresult r = tensor_map_encoder()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -541,7 +523,7 @@ CUtensorMap make_out_map(void* base, int T, int N, DType dt) {
     cuuint64_t strides[1] = {(cuuint64_t)N * elem_bytes};
     cuuint32_t box[2] = {(cuuint32_t)kTileM, (cuuint32_t)kChunk};
     cuuint32_t elem[2] = {1, 1};
-    CUresult r = encode_fn()(&map, dt == F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
+    CUresult r = tensor_map_encoder()(&map, dt == F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
                              dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)

@@ -154,14 +154,17 @@ void attention_prefill_tc(const void* q, const void* k, const void* v, void* out
 // One new token per sequence over the paged cache for bfloat16: a cluster of CTAs per
 // (sequence, kv head) splits the visible positions and merges through distributed shared
 // memory; no workspace. `max_len` (the longest sequence of the batch, or a bound of it) only
-// sizes the clusters. head_dim: multiples of 16 up to 128; at most 16 heads per kv head.
+// sizes the clusters; `pool_pages` is the number of pages of the two pools (long shares of head sizes 64 and 128
+// come in through a tensor map over them). head_dim: multiples of 16 up to 128; at most 16 heads per kv head.
 bool attention_decode_supports(int heads, int kv_heads, int head_dim);
 // How a launch for these sizes would be cut: plan[0..3] = CTAs per (sequence, kv head), positions per
-// buffer, buffers, bytes of shared memory per CTA.
+// buffer, buffers, bytes of shared memory per CTA; for shares that are streamed tile by tile: CTAs, 0, tiles a
+// warp keeps in flight, bytes of shared memory.
 void attention_decode_plan(int B, int heads, int kv_heads, int head_dim, int window, int max_len, int* plan);
 void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
                       const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
-                      const int32_t* page_table, int table_stride, int ring, int max_len, cudaStream_t stream);
+                      const int32_t* page_table, int table_stride, int ring, int max_len, long long pool_pages,
+                      cudaStream_t stream);
 
 // ---- sampling.cu ----------------------------------------------------------------------
 // out[b] = argmax over the allowed ids of logits[b, :], the lowest id on ties

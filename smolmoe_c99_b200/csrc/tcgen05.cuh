@@ -8,6 +8,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+#include <stdexcept>
+
 namespace sm {
 namespace tc5 {
 
@@ -35,6 +38,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     for (uint32_t i = 0; i < kSpinLimit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
+}
+// One contiguous run of bytes (a multiple of 16, both ends on 16 bytes) from global to shared memory; its bytes are
+// counted on `bar` as they land.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
     asm volatile(
@@ -174,5 +183,25 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+// Host side: the driver's cuTensorMapEncodeTiled, looked up through the runtime (nothing links against the driver
+// library).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn tensor_map_encoder() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    });
+    if (!fn) throw std::runtime_error("the driver does not provide cuTensorMapEncodeTiled");
+    return fn;
+}
+
 }  // namespace tc5
 }  // namespace sm

@@ -378,7 +378,8 @@ class Ops:
         out = torch.empty_like(q)
         self._check(self.lib.sm_attention_decode(
             _ptr(q), _ptr(out), B, heads, kv_heads, head_dim, ctypes.c_float(scale), int(window or 0), _ptr(positions),
-            _ptr(slots), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), page_table.shape[1], ring, int(max_len), _stream()))
+            _ptr(slots), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), page_table.shape[1], ring, int(max_len),
+            ctypes.c_longlong(k_pool.shape[0]), _stream()))
         return out
 
     # ---- sampling ----------------------------------------------------------------------

@@ -251,6 +251,56 @@ def test_decode_attention_long_contexts(ops, heads, kv_heads, hd, lens, max_len)
         assert float((got[b] - want[b]).abs().max()) <= 1e-2, f"sequence {b} of {lens[b]} positions"
 
 
+@pytest.mark.parametrize("heads,kv_heads,hd", [(3, 1, 32), (10, 5, 48), (14, 2, 64), (6, 3, 96), (8, 2, 128)])
+@pytest.mark.parametrize("window", [None, 700])
+def test_decode_attention_streamed_shares(ops, heads, kv_heads, hd, window):
+    """More (sequence, kv head) pairs than the GPU holds clusters, each with hundreds of positions: every CTA streams
+    its share tile by tile. Unequal lengths, scattered pages, a ring for the window (tiles then straddle pages and the
+    ring's end), head sizes below their padded size; the newest position's row is the one read after the wait."""
+    import ctypes
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    g = torch.Generator().manual_seed(11)
+    B = 320 // kv_heads
+    lens = [int(x) for x in torch.randint(650, 1000, (B,), generator=g)]
+    lens[0], lens[1], lens[2] = 1, 33, 999
+    max_len = 1024
+    ring = ((window + PAGE_SIZE - 1) // PAGE_SIZE) * PAGE_SIZE if window else 0
+    pages_per_seq = (ring or max_len) // PAGE_SIZE
+    plan = (ctypes.c_int * 4)()
+    ops._check(ops.lib.sm_attention_decode_plan(B, heads, kv_heads, hd, int(window or 0), max_len, plan))
+    assert plan[1] == 0, f"this case is meant for the streaming kernel, the plan is {list(plan)}"
+    table = torch.randperm(B * pages_per_seq, generator=g).to(torch.int32).view(B, pages_per_seq)
+    k_pool = torch.zeros((B * pages_per_seq, kv_heads, PAGE_SIZE, hd), dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    q = _rand((B, heads, hd), torch.bfloat16, 1).cpu()
+    want = torch.zeros((B, heads, hd), dtype=torch.float64)
+    scale = 1.0 / math.sqrt(hd)
+    for b, n in enumerate(lens):
+        k = torch.randn((n, kv_heads, hd), generator=g).to(torch.bfloat16)
+        v = torch.randn((n, kv_heads, hd), generator=g).to(torch.bfloat16)
+        first = max(0, n - window) if window else 0
+        if n - first > 300:      # a far key that matters, so that a lost tile shows
+            k[first + 5] = 0
+            k[first + 5, :, 0] = 30.0
+            q[b, :, 0] = 2.0
+        where = torch.arange(first, n)
+        idx = where % ring if ring else where
+        pages = table[b, idx // PAGE_SIZE].long()
+        k_pool[pages, :, idx % PAGE_SIZE] = k[first:]
+        v_pool[pages, :, idx % PAGE_SIZE] = v[first:]
+        for h in range(heads):
+            kh = h // (heads // kv_heads)
+            p = torch.softmax((k[first:, kh].double() @ q[b, h].double()) * scale, dim=0)
+            want[b, h] = p @ v[first:, kh].double()
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    slot_ids = torch.arange(B, dtype=torch.int32).cuda()
+    got = ops.attention_decode(q.cuda(), positions, slot_ids, scale, window, k_pool.cuda(), v_pool.cuda(), table.cuda(), ring,
+                               kv_heads, max_len).double().cpu()
+    ops.check_error_flag()
+    worst = (got - want).abs().amax(dim=(1, 2))
+    assert float(worst.max()) <= 1e-2, f"sequence {int(worst.argmax())} of {lens[int(worst.argmax())]} positions: {float(worst.max())}"
+
+
 # ---- products over a handful of tokens -----------------------------------------------------
 @pytest.mark.parametrize("T", [1, 3, 8, 9, 16, 32])
 @pytest.mark.parametrize("N,K", [(896, 896), (100, 72), (151, 4864), (1000, 136)])
