@@ -133,6 +133,10 @@ SM_API long long sm_gemm_tc_workspace_bytes(int T, int N, int K, int dual) {
     return (long long)sm::gemm_tc_workspace_bytes(T, N, K, dual != 0);
 }
 
+SM_API int sm_gemm_tc_plan(int T, int N, int K, int dual, int* tile_n, int* splits) {
+    return guarded([&] { sm::gemm_tc_plan(T, N, K, dual != 0, tile_n, splits); });
+}
+
 SM_API int sm_gemm_tc(const void* x, const void* w, const void* bias, int bias_dt, void* out, int out_dt, int T,
                       int N, int K, int mode, int up_offset, float* workspace, int* error, void* stream) {
     return guarded([&] {

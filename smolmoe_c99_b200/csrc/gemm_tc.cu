@@ -27,9 +27,11 @@
 #include <mutex>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 #include "tcgen05.cuh"
 
 namespace sm {
@@ -64,6 +66,8 @@ struct GemmParams {
     int tiles_m, tiles_t;     // tile grid: 128 features x tile_n tokens
     int units;                // tiles_m * tiles_t * splits work units, shared out round-robin
     int tma_out;              // the epilogue leaves through shared memory and TMA (store or add)
+    int final_epilogue;       // what the epilogue is once the splits are added up
+    int cluster_reduce;       // small kernel: the CTAs along K are one cluster and add their sums up among themselves
 };
 
 using namespace tc5;   // the PTX wrappers (tcgen05.cuh)
@@ -328,6 +332,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // output head): one CTA per work unit, few registers, two CTAs to an SM. With so few tokens a
 // unit is nothing but a stream of weight tiles, and two small CTAs keep more of them in flight
 // than one persistent CTA does (measured on the 151,936 x 896 head at 8 tokens: 54 against 75 us).
+//
+// Where K is split, the CTAs of a tile are one thread-block cluster (grid x = the split): each leaves
+// its partial sums in its own shared memory, and after a cluster barrier CTA r adds up the r-th part
+// of the tile from all of them, in split order, through distributed shared memory, applies the
+// epilogue and writes it. No partial sum goes to global memory and no second kernel runs (that
+// kernel and the workspace's round trip cost 6 to 16 us a product at 64 tokens).
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr, uint32_t cta) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(cta));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote));
+    return v;
+}
+
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -343,7 +365,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     int* failed = (int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kTileM, t0 = blockIdx.y * p.tile_n, split = blockIdx.z;
+    const int split = blockIdx.x, n0 = blockIdx.y * kTileM, t0 = blockIdx.z * p.tile_n;
     const int kb_total = (p.K + kStageK - 1) / kStageK;
     const int kb_begin = split * p.kblocks_per_split;
     const int kb_end = min(kb_total, kb_begin + p.kblocks_per_split);
@@ -429,6 +451,17 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 float g[16], u[16], old[16];
                 tmem_ld16(lane_base + (uint32_t)c0, g);
                 if (p.dual) tmem_ld16(lane_base + (uint32_t)(p.tile_n + c0), u);
+                if (p.cluster_reduce) {
+                    // [gate | up][token][128 features] floats over the pipeline's stages, which are free: the
+                    // accumulator is complete, so every MMA has read its operands
+                    float* mine = reinterpret_cast<float*>(smem);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        mine[(c0 + j) * kTileM + quarter * 32 + lane] = g[j];
+                        if (p.dual) mine[(p.tile_n + c0 + j) * kTileM + quarter * 32 + lane] = u[j];
+                    }
+                    continue;
+                }
                 if (n >= p.N) continue;
                 if (p.epilogue == EPI_ACCUM) {   // all the old values first: the loads overlap
 #pragma unroll
@@ -462,6 +495,71 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         }
     }
     __syncwarp();
+    if (p.cluster_reduce) {
+        // every thread of every CTA of the cluster comes here, whatever happened above
+        cluster_barrier();
+        if (warp >= 2) {
+            const int pieces = p.tile_n * (kTileM / 4);                 // float4s of one accumulator
+            const int per = (pieces + p.splits - 1) / p.splits;
+            const int hi = min(pieces, (split + 1) * per);
+            const uint32_t base = smem_u32(smem);
+            // four features at a time where the output's rows allow it (then n + 3 < N whenever n < N)
+            const bool vec = (p.N & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
+            for (int c = split * per + (int)threadIdx.x - 64; c < hi; c += 128) {
+                const int t = t0 + c / (kTileM / 4), n = n0 + (c % (kTileM / 4)) * 4;
+                if (t >= p.T || n >= p.N) continue;
+                const size_t o = (size_t)t * p.N + n;
+                float old[4] = {0.f, 0.f, 0.f, 0.f};
+                if (p.final_epilogue == EPI_ACCUM) {   // asked for before the sums: the trips overlap
+                    if (vec) {
+                        const float4 r = *reinterpret_cast<const float4*>((const float*)p.out + o);
+                        old[0] = r.x; old[1] = r.y; old[2] = r.z; old[3] = r.w;
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) old[e] = n + e < p.N ? ((const float*)p.out)[o + e] : 0.f;
+                    }
+                }
+                float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+#pragma unroll 4
+                for (int sp = 0; sp < p.splits; ++sp) {
+                    const float4 a = ld_cluster_f4(base + (uint32_t)c * 16u, (uint32_t)sp);
+                    g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+                    if (p.dual) {
+                        const float4 b = ld_cluster_f4(base + (uint32_t)(pieces + c) * 16u, (uint32_t)sp);
+                        u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+                    }
+                }
+                float v[4] = {g.x, g.y, g.z, g.w};
+                const float ups[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (p.final_epilogue == EPI_SWIGLU) v[e] = gated(v[e], ups[e]);
+                    else if (p.bias && n + e < p.N)
+                        v[e] += p.bias_dt == F32 ? ((const float*)p.bias)[n + e] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n + e]);
+                    v[e] += old[e];
+                }
+                if (vec) {
+                    if (p.out_dt == F32) {
+                        *reinterpret_cast<float4*>((float*)p.out + o) = make_float4(v[0], v[1], v[2], v[3]);
+                    } else {
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi2 = __floats2bfloat162_rn(v[2], v[3]);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<uint32_t*>(&hi2);
+                        *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + o) = packed;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (n + e >= p.N) break;
+                        if (p.out_dt == F32) ((float*)p.out)[o + e] = v[e];
+                        else ((__nv_bfloat16*)p.out)[o + e] = __float2bfloat16_rn(v[e]);
+                    }
+                }
+            }
+        }
+        cluster_barrier();   // no CTA leaves while another reads its shared memory
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -545,6 +643,59 @@ int device_sm_count() {
 
 }  // namespace
 
+namespace {
+
+// The small kernel's launch for a plan: pipeline stages, shared memory, and whether the CTAs along K can be one
+// cluster (at most 8 CTAs, and the GPU can hold such a cluster).
+struct SmallLaunch {
+    int stages;
+    size_t smem;
+    bool cluster;
+};
+SmallLaunch small_launch(int tile_n, int splits, bool dual) {
+    const int stage_bytes = kTileM * kStageK * 2 * (dual ? 2 : 1) + tile_n * kStageK * 2;
+    SmallLaunch l{};
+    l.stages = 100 * 1024 / stage_bytes;
+    if (l.stages > 8) l.stages = 8;
+    if (l.stages < 2) l.stages = 2;
+    l.smem = (size_t)l.stages * stage_bytes + 1024 /*alignment*/ + (2 * l.stages + 1) * 8 + 16;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        cudaFuncSetAttribute(gemm_tc_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    });
+    l.cluster = false;
+    // the partial sums (tile_n x 128 floats, twice for a gated product) lie over the stages
+    if (splits >= 2 && splits <= 8 && (size_t)tile_n * kTileM * 4 * (dual ? 2 : 1) <= (size_t)l.stages * stage_bytes) {
+        struct Known { int splits; size_t smem; bool ok; };
+        static std::mutex lock;
+        static std::vector<Known> known;
+        std::lock_guard<std::mutex> hold(lock);
+        for (const Known& k : known)
+            if (k.splits == splits && k.smem == l.smem) { l.cluster = k.ok; return l; }
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(splits, 1, 1);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = l.smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_small_kernel, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        l.cluster = n >= 1;
+        known.push_back({splits, l.smem, l.cluster});
+    }
+    return l;
+}
+
+}  // namespace
+
 bool gemm_tc_supports(int T, int N, int K) { return T > 0 && N > 0 && K > 0 && K % 8 == 0; }
 
 void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
@@ -554,15 +705,18 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
     const int kb = (K + kStageK - 1) / kStageK;   // stages of K
     if (T <= 64) {
         // A handful of tokens: the product is bound by reading the weights once. One token tile (so that no
-        // weight row is read twice) and, where the row tiles are too few to fill the machine (two CTAs an SM),
-        // K split among CTAs, at least two stages of 128 each; the partial sums cost T x N floats a split.
-        int sp = 1;
-        if (tiles_m < 2 * sms && kb >= 4) {
-            sp = (2 * sms + tiles_m - 1) / tiles_m;
-            if (sp > kb / 2) sp = kb / 2;
-            if (sp > 16) sp = 16;
-            if (sp < 1) sp = 1;
-        }
+        // weight row is read twice) and, where the row tiles are too few to fill the machine, K split among the
+        // CTAs of a cluster: as many as still run in ONE wave (measured at 64 tokens: 38 row tiles of a gated
+        // product x 3 splits 12.7 us, x 4 splits = 152 CTAs on 148 SMs 19.0 us), at most 8 (clusters of 10 to 16
+        // cost 1.3 to 4 times as much as clusters of 8) and about two stages of 128 of K each or more.
+        const SmallLaunch l = small_launch(t16, 2, dual);
+        int per_sm = (int)((size_t)227 * 1024 / l.smem);
+        if (per_sm > 2) per_sm = 2;
+        if (per_sm < 1) per_sm = 1;
+        int sp = sms * per_sm / tiles_m;
+        if (sp > (kb + 1) / 2) sp = (kb + 1) / 2;
+        if (sp > 8) sp = 8;
+        if (sp < 1) sp = 1;
         const int per = (kb + sp - 1) / sp;
         sp = (kb + per - 1) / per;
         if (tiles_m * sp * 2 >= sms) {
@@ -599,6 +753,7 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
 size_t gemm_tc_workspace_bytes(int T, int N, int K, bool dual) {
     int tn, sp;
     gemm_tc_plan(T, N, K, dual, &tn, &sp);
+    if (sp > 1 && T <= 64 && small_launch(tn, sp, dual).cluster) return 0;   // the splits are added up inside a cluster
     return sp > 1 ? (size_t)sp * (dual ? 2 : 1) * T * N * sizeof(float) : 0;
 }
 
@@ -624,7 +779,8 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     p.units = p.tiles_m * p.tiles_t * p.splits;
     const int final_mode = mode;
     p.epilogue = p.splits > 1 ? EPI_PARTIAL : final_mode;
-    if (p.splits > 1 && !workspace) throw std::invalid_argument("gemm_tc: this shape splits K and needs a workspace");
+    if (p.splits > 1 && !workspace && !(T <= 64 && small_launch(p.tile_n, p.splits, dual).cluster))
+        throw std::invalid_argument("gemm_tc: this shape splits K and needs a workspace");
     // the output leaves through shared memory and TMA where TMA can address it: rows that start
     // on 16 bytes (TMA stores outside the matrix are dropped, so ragged edges need no care)
     const size_t out_elem = out_dt == F32 ? 4 : 2;
@@ -633,21 +789,19 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     const int stage_bytes = kTileM * kStageK * 2 * (dual ? 2 : 1) + p.tile_n * kStageK * 2;
     if (T <= 64) {
         // few tokens: one CTA per unit, two CTAs to an SM
+        const SmallLaunch l = small_launch(p.tile_n, p.splits, dual);
         p.tma_out = 0;
-        p.stages = 100 * 1024 / stage_bytes;
-        if (p.stages > 8) p.stages = 8;
-        if (p.stages < 2) p.stages = 2;
-        const size_t smem_small = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + (2 * p.stages + 1) * 8 + 16;
+        p.stages = l.stages;
+        p.final_epilogue = final_mode;
+        p.cluster_reduce = l.cluster ? 1 : 0;
+        if (p.tiles_m > 65535 || p.tiles_t > 65535) throw std::invalid_argument("gemm_tc: more than 65535 tiles along a side");
         const CUtensorMap mw = make_map(w, dual ? up_offset + N : N, K, kBoxRows);
         const CUtensorMap mx = make_map(x, T, K, p.tile_n < kBoxRows ? p.tile_n : kBoxRows);
-        static std::once_flag small_once;
-        std::call_once(small_once, [] {
-            cudaFuncSetAttribute(gemm_tc_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        });
-        dim3 grid3(p.tiles_m, p.tiles_t, p.splits);
-        gemm_tc_small_kernel<<<grid3, kThreads, smem_small, stream>>>(mw, mx, p);
-        note_launch(p.splits > 1 ? 2 : 1);
-        if (p.splits > 1) {
+        dim3 grid3(p.splits, p.tiles_m, p.tiles_t);
+        launch_kernel("gemm_tc", gemm_tc_small_kernel, grid3, dim3(kThreads), l.smem, stream, l.cluster ? p.splits : 1, false,
+                      mw, mx, p);
+        note_launch(p.splits > 1 && !l.cluster ? 2 : 1);
+        if (p.splits > 1 && !l.cluster) {
             p.epilogue = final_mode;
             size_t total = (size_t)T * N;
             splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p);

@@ -76,6 +76,8 @@ void gemm_simt(const void* x, DType x_dt, const void* w, DType w_dt, const void*
 // of gemm_tc_workspace_bytes(). *error becomes non-zero if a bounded wait ran out.
 bool gemm_tc_supports(int T, int N, int K);
 size_t gemm_tc_workspace_bytes(int T, int N, int K, bool dual);
+// How a product of these sizes is cut: tokens per tile and CTAs along K.
+void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits);
 void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N,
              int K, int mode, int up_offset, float* workspace, int* error, cudaStream_t stream);
 

@@ -21,7 +21,8 @@ def _rand(shape, dtype, seed, scale=1.0):
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 896, 896), (8, 1152, 896), (64, 896, 4864), (3, 100, 72), (130, 300, 200),
-                                   (2048, 896, 896), (500, 1000, 136), (17, 128, 64), (256, 256, 8)])
+                                   (2048, 896, 896), (500, 1000, 136), (17, 128, 64), (256, 256, 8), (33, 150, 1024),
+                                   (64, 3584, 18944), (100, 896, 4864)])
 @pytest.mark.parametrize("mode", ["store_f32", "store_bf16", "accumulate"])
 def test_gemm_tc(ops, T, N, K, mode):
     x, w = _rand((T, K), torch.bfloat16, 1), _rand((N, K), torch.bfloat16, 2, 0.05)
@@ -40,7 +41,8 @@ def test_gemm_tc(ops, T, N, K, mode):
     assert float((out.float() - want).abs().max()) <= tol
 
 
-@pytest.mark.parametrize("T,H,K", [(1, 4864, 896), (8, 4864, 896), (64, 160, 96), (300, 520, 264), (2048, 1024, 128)])
+@pytest.mark.parametrize("T,H,K", [(1, 4864, 896), (8, 4864, 896), (64, 160, 96), (300, 520, 264), (2048, 1024, 128),
+                                   (40, 202, 2048), (64, 18944, 3584), (70, 160, 1024)])
 def test_gemm_tc_gated(ops, T, H, K):
     x, w = _rand((T, K), torch.bfloat16, 5), _rand((2 * H, K), torch.bfloat16, 6, 0.05)
     g, u = x.float() @ w[:H].float().T, x.float() @ w[H:].float().T
