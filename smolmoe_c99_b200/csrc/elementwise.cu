@@ -51,6 +51,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
                                TO* __restrict__ out, const int32_t* __restrict__ rows, int D) {
     __shared__ float warp_part[kNormThreads / 32];
     __shared__ float inv_shared;
+    pdl_launch_dependents();
+    pdl_wait();   // x comes from the kernel before
     int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
     float sq = 0.f;
@@ -105,6 +107,8 @@ __global__ void __launch_bounds__(kRowWarps * 32)
 rmsnorm_rows_kernel(const float* __restrict__ x, const TW* __restrict__ w, float eps, TO* __restrict__ out,
                     const int32_t* __restrict__ rows, int n_rows, int D) {
     const int r = blockIdx.x * kRowWarps + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();   // x comes from the kernel before
     if (r >= n_rows) return;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
     float v[NV][4];
@@ -144,12 +148,15 @@ static void launch_norm(const float* x, const void* w, float eps, void* out, con
     if (D % 4 == 0 && D <= 2048) {
         const unsigned blocks = (unsigned)((n_rows + kRowWarps - 1) / kRowWarps);
         if (D <= 1024)
-            rmsnorm_rows_kernel<TW, TO, 8><<<blocks, kRowWarps * 32, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
+            launch_kernel("rmsnorm", rmsnorm_rows_kernel<TW, TO, 8>, dim3(blocks), dim3(kRowWarps * 32), 0, stream, 1,
+                          dependent_launch_enabled(), x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
         else
-            rmsnorm_rows_kernel<TW, TO, 16><<<blocks, kRowWarps * 32, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
+            launch_kernel("rmsnorm", rmsnorm_rows_kernel<TW, TO, 16>, dim3(blocks), dim3(kRowWarps * 32), 0, stream, 1,
+                          dependent_launch_enabled(), x, (const TW*)w, eps, (TO*)out, rows, n_rows, D);
         return;
     }
-    rmsnorm_kernel<TW, TO><<<n_rows, kNormThreads, 0, stream>>>(x, (const TW*)w, eps, (TO*)out, rows, D);
+    launch_kernel("rmsnorm", rmsnorm_kernel<TW, TO>, dim3((unsigned)n_rows), dim3(kNormThreads), 0, stream, 1,
+                  dependent_launch_enabled(), x, (const TW*)w, eps, (TO*)out, rows, D);
 }
 
 void rmsnorm(const float* x, const void* w, DType w_dt, float eps, void* out, DType out_dt,
@@ -244,6 +251,8 @@ __global__ void rope_store_kernel(RopeStoreArgs a) {
 template <typename TO>
 __global__ void rope_store_vec_kernel(RopeStoreArgs a, long long total) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();   // q, k and v come from the kernel before
     if (idx >= total) return;
     const int hd = a.head_dim, half = hd / 2, groups = half / 4;
     const int n_heads = a.heads + 2 * a.kv_heads;
@@ -295,8 +304,10 @@ void rope_store(const RopeStoreArgs& a, cudaStream_t stream) {
         note_launch();
         const long long total = (long long)a.T * (a.heads + 2 * a.kv_heads) * (a.head_dim / 8);
         const unsigned blocks = (unsigned)((total + 255) / 256);
-        if (a.dt == F32) rope_store_vec_kernel<float><<<blocks, 256, 0, stream>>>(a, total);
-        else rope_store_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(a, total);
+        if (a.dt == F32)
+            launch_kernel("rope_store", rope_store_vec_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, dependent_launch_enabled(), a, total);
+        else
+            launch_kernel("rope_store", rope_store_vec_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1, dependent_launch_enabled(), a, total);
         return;
     }
     if (a.head_dim % 2 || a.rotary_dim % 2 || a.rotary_dim > a.head_dim)

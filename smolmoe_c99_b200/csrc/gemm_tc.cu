@@ -366,6 +366,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, n0 = blockIdx.y * kTileM, t0 = blockIdx.z * p.tile_n;
+    pdl_launch_dependents();
     const int kb_total = (p.K + kStageK - 1) / kStageK;
     const int kb_begin = split * p.kblocks_per_split;
     const int kb_end = min(kb_total, kb_begin + p.kblocks_per_split);
@@ -389,9 +390,22 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         // the whole warp: one box of a stage's tiles a lane (see the persistent kernel)
         const StageBox box = stage_box(lane, a_bytes, p);
         const int row = box.from_x ? t0 + box.row : n0 + box.row;
-        int s = 0;
-        uint32_t phase = 0;
-        for (int i = 0; i < n_kb; ++i) {
+        // The weights do not depend on the kernel before this one: the first stages' weight tiles are asked for
+        // before the wait for it, their token tiles after.
+        const int early = min(p.stages, n_kb);
+        for (int i = 0; i < early; ++i) {
+            if (lane == 0) mbar_expect_tx(&full_bar[i], (uint32_t)stage_bytes);
+            __syncwarp();
+            if (box.active && !box.from_x)
+                tma_load_2d(smem + (size_t)i * stage_bytes + box.offset, &map_w, (kb_begin + i) * kStageK + box.k, row, &full_bar[i]);
+        }
+        pdl_wait();
+        for (int i = 0; i < early; ++i)
+            if (box.active && box.from_x)
+                tma_load_2d(smem + (size_t)i * stage_bytes + box.offset, &map_x, (kb_begin + i) * kStageK + box.k, row, &full_bar[i]);
+        int s = early == p.stages ? 0 : early;
+        uint32_t phase = early == p.stages ? 1u : 0u;
+        for (int i = early; i < n_kb; ++i) {
             if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u))) {
                 if (lane == 0) { *failed = 1; atomicExch(p.error, 1); }
                 break;
@@ -436,6 +450,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         // epilogue warps 2..5: TMEM lanes of quarter (warp % 4)
         const int quarter = warp & 3;
         const int n = n0 + quarter * 32 + lane;
+        pdl_wait();   // the output (read for "+=") and everything written below come after the kernel before
         bool ok = mbar_wait(tmem_full_bar, 0);
         if (!ok && lane == 0) { *failed = 1; atomicExch(p.error, 3); }
         ok = ok && (*(volatile int*)failed == 0);
@@ -798,8 +813,8 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
         const CUtensorMap mw = make_map(w, dual ? up_offset + N : N, K, kBoxRows);
         const CUtensorMap mx = make_map(x, T, K, p.tile_n < kBoxRows ? p.tile_n : kBoxRows);
         dim3 grid3(p.splits, p.tiles_m, p.tiles_t);
-        launch_kernel("gemm_tc", gemm_tc_small_kernel, grid3, dim3(kThreads), l.smem, stream, l.cluster ? p.splits : 1, false,
-                      mw, mx, p);
+        launch_kernel("gemm_tc", gemm_tc_small_kernel, grid3, dim3(kThreads), l.smem, stream, l.cluster ? p.splits : 1,
+                      dependent_launch_enabled(), mw, mx, p);
         note_launch(p.splits > 1 && !l.cluster ? 2 : 1);
         if (p.splits > 1 && !l.cluster) {
             p.epilogue = final_mode;
