@@ -28,6 +28,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 #include "tcgen05.cuh"
 
 namespace sm {
@@ -91,6 +92,7 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     // CTAs start in the order of their index, the heads of one tile together: late tiles (most keys) first, so that
     // the longest chains of key tiles begin at once and the short ones fill the SMs that become free
     const int tile = (int)gridDim.y - 1 - (int)blockIdx.y, h = blockIdx.x;
+    pdl_launch_dependents();
     const int seq_start = a.tiles[3 * tile], seq_len = a.tiles[3 * tile + 1], q0 = a.tiles[3 * tile + 2];
     if (q0 % kBM) return;                             // the second half of a tile of 128 queries
     const int kvh = h / (a.heads / a.kv_heads);
@@ -135,6 +137,7 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
+    pdl_wait();   // q, k and v come from the kernel before; the tiles' list was written before the step's first kernel
 
     // key tiles this query tile sees
     const int q_last = min(q0 + kBM, seq_len) - 1;
@@ -434,7 +437,7 @@ void launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
         if (e != cudaSuccess) throw std::runtime_error(std::string("attention_prefill_tc: ") + cudaGetErrorString(e));
         prepared = true;
     }
-    kernel<<<dim3(a.heads, n_tiles), kThreads, smem, stream>>>(mq, mk, mv, a);
+    launch_kernel("attention_prefill_tc", kernel, dim3(a.heads, n_tiles), dim3(kThreads), smem, stream, 1, dependent_launch_enabled(), mq, mk, mv, a);
 }
 
 }  // namespace

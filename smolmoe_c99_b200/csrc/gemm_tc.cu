@@ -149,6 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int* failed = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
     const int buf_cols = p.tile_n * (p.dual ? 2 : 1);
     uint32_t tmem_cols = 32;
     while ((int)tmem_cols < 2 * buf_cols) tmem_cols <<= 1;
@@ -174,13 +175,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // that can be counted up: a thread alone on its scheduler waits out the latency of every instruction, and at
         // ~1,000 cycles a block of K these two loops, not memory or the tensor core, bounded the kernel.)
         const StageBox box = stage_box(lane, a_bytes, p);
-        int s = 0;
-        uint32_t phase = 0;
+        // The weights do not depend on the kernel before this one: the weight tiles of the first unit's first
+        // stages are asked for before the wait for it, their token tiles after.
+        int early = 0;
+        {
+            const Unit w = unit_of(p, blockIdx.x);   // the grid is never larger than the number of units
+            early = min(p.stages, w.kb_end - w.kb_begin);
+            for (int i = 0; i < early; ++i) {
+                if (lane == 0) mbar_expect_tx(&full_bar[i], (uint32_t)stage_bytes);
+                __syncwarp();
+                if (box.active && !box.from_x)
+                    tma_load_2d(smem + (size_t)i * stage_bytes + box.offset, &map_w, (w.kb_begin + i) * kStageK + box.k, w.n0 + box.row, &full_bar[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                if (box.active && box.from_x)
+                    tma_load_2d(smem + (size_t)i * stage_bytes + box.offset, &map_x, (w.kb_begin + i) * kStageK + box.k, w.t0 + box.row, &full_bar[i]);
+        }
+        int s = early == p.stages ? 0 : early;
+        uint32_t phase = early == p.stages ? 1u : 0u;
         bool ok = true;
         for (int u = blockIdx.x; u < p.units && ok && !*failed; u += gridDim.x) {
             const Unit w = unit_of(p, u);
             const int row = box.from_x ? w.t0 + box.row : w.n0 + box.row;
-            for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
+            for (int kb = w.kb_begin + (u == (int)blockIdx.x ? early : 0); kb < w.kb_end; ++kb) {
                 ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u));
                 if (!ok) {
                     if (lane == 0) { *failed = 1; atomicExch(p.error, 1); }
@@ -241,6 +259,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const bool issuer = warp == 2 && lane == 0;
         int i = 0;
         uint32_t chunk_count = 0;
+        pdl_wait();   // the output (read for "+=") and everything written below come after the kernel before
         for (int u = blockIdx.x; u < p.units; u += gridDim.x, ++i) {
             const Unit w = unit_of(p, u);
             const int b = i & 1;
@@ -837,7 +856,7 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     });
     const int sms = device_sm_count();
     const int grid = p.units < sms ? p.units : sms;
-    gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(map_w, map_x, map_out, p);
+    launch_kernel("gemm_tc", gemm_tc_kernel, dim3(grid), dim3(kThreads), smem, stream, 1, dependent_launch_enabled(), map_w, map_x, map_out, p);
     note_launch(p.splits > 1 ? 2 : 1);
     if (p.splits > 1) {
         p.epilogue = final_mode;
