@@ -60,7 +60,8 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
     # prefill tiles, the slots, the sequences' ends and the sequences' first packed indices
     tile_rows = [[cu[i], n, q0] for i, n in enumerate(lens) for q0 in range(0, n, QUERY_TILE)] if mode == "prefill" else []
     extra = 3 * len(tile_rows) + 2 * n_seqs + (n_seqs + 1)
-    flat_host = torch.empty(5 * n_tokens + extra, dtype=torch.int32)
+    # (pinned memory on a GPU box: the copy below is then asynchronous and the allocator keeps the buffer until it is done)
+    flat_host = torch.empty(5 * n_tokens + extra, dtype=torch.int32, pin_memory=device.type == "cuda")
     host = flat_host[:5 * n_tokens].view(5, n_tokens)
     flat = token_lists[0] if n_seqs == 1 else [t for toks in token_lists for t in toks]
     host[0] = torch.frombuffer(array("i", flat), dtype=torch.int32) if n_tokens else host[0]
@@ -82,7 +83,7 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
         host[4] = firsts[seq_of]
     tail = [x for row in tile_rows for x in row] + list(slots) + [s + n for s, n in zip(starts, lens)] + cu
     flat_host[5 * n_tokens:] = torch.tensor(tail, dtype=torch.int32)
-    flat_dev = flat_host.to(device)
+    flat_dev = flat_host.to(device, non_blocking=True)
     dev = flat_dev[:5 * n_tokens].view(5, n_tokens)
     at = 5 * n_tokens
     tiles = None

@@ -50,6 +50,24 @@ class _DecodeGraph:
             tokens=self.meta[0], positions=self.meta[1], token_slot=self.meta[2], token_end=self.meta[3],
             token_seq_start=self.rows, cu_seqlens=torch.arange(n_seqs + 1, dtype=torch.int32, device=dev),
             slot_ids=self.meta[2], seq_ends=self.meta[3], wants_every_row=True)
+        # The step's numbers go up from pinned host memory, asynchronously. A few buffers take turns; an event says
+        # when the copy that last read a buffer is done, so that it can be written again.
+        self._staging = [torch.empty((4, n_seqs), dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._staged: List[Optional[torch.cuda.Event]] = [None] * len(self._staging)
+        self._turn = 0
+
+    def upload(self, first_row: int, rows: List[List[int]]) -> None:
+        """``meta[first_row:first_row + len(rows)] = rows`` in stream order, through pinned memory."""
+        i = self._turn
+        self._turn = (i + 1) % len(self._staging)
+        if self._staged[i] is not None:
+            self._staged[i].synchronize()
+        else:
+            self._staged[i] = torch.cuda.Event()
+        host = self._staging[i][first_row:first_row + len(rows)]
+        host.copy_(torch.tensor(rows, dtype=torch.int32))
+        self.meta[first_row:first_row + len(rows)].copy_(host, non_blocking=True)
+        self._staged[i].record()
 
     def capture(self, engine: "Engine") -> None:
         """``meta`` must already hold a real step: the run before the capture loads kernels and
@@ -200,9 +218,8 @@ class Engine:
             g = self._graphs[key] = _DecodeGraph(self, n, span)
         else:
             self._graphs.move_to_end(key)
-        meta = [[0] * n if on_device else [int(t[0]) for t in tokens], list(starts), list(slots),
-                [s + 1 for s in starts]]
-        g.meta.copy_(torch.tensor(meta, dtype=torch.int32))   # pageable and small: staged at once, no hazard
+        g.upload(0, [[0] * n if on_device else [int(t[0]) for t in tokens], list(starts), list(slots),
+                     [s + 1 for s in starts]])
         if on_device:
             g.meta[0].copy_(tokens)
         if g.graph is None:
@@ -237,7 +254,7 @@ class Engine:
             return None
         self.cache.flush_tables()
         self._graphs.move_to_end((n, span))
-        g.meta[1:].copy_(torch.tensor([list(starts), list(slots), [s + 1 for s in starts]], dtype=torch.int32))
+        g.upload(1, [list(starts), list(slots), [s + 1 for s in starts]])
         return g, tuple(slots), tuple(starts)
 
     def launch_prepared(self, prepared, tokens: torch.Tensor) -> torch.Tensor:
