@@ -112,6 +112,41 @@ def test_long_prompt_then_long_decoding_at_head_size_64(model_dirs):
     engine.close_sequence(slot)
 
 
+def test_many_long_sequences_decode_with_streamed_attention(model_dirs):
+    """More (sequence, kv head) pairs than the GPU holds clusters, hundreds of positions each: the decode attention
+    streams every CTA's share tile by tile (TMA boxes of the paged pool). One sequence of the 110 is checked against
+    the plain implementation through its prompt's end and 12 tokens one at a time; the others only share the batch."""
+    import ctypes
+    from smolmoe_c99_b200.engine.engine import Engine
+    cfg = TINY["D"]
+    n_seqs, n_prompt, n_more = 110, 890, 12
+    engine = Engine(model_dirs["D"], "bfloat16", max_tokens=n_seqs * 960, max_slots=n_seqs)
+    plan = (ctypes.c_int * 4)()
+    ops = engine.runtime.ops
+    ops._check(ops.lib.sm_attention_decode_plan(n_seqs, cfg["num_attention_heads"], cfg["num_key_value_heads"], 64, 0, 1024, plan))
+    assert plan[1] == 0, f"this batch is meant for the streaming kernel, the plan is {list(plan)}"
+    toks = random_tokens(n_prompt + n_more, cfg["vocab_size"], 91)
+    want = plain_model.forward(model_dirs["D"], toks, round_like_bf16_engine=True)
+    g = torch.Generator().manual_seed(4)
+    others = [random_tokens(int(n), cfg["vocab_size"], 200 + i)
+              for i, n in enumerate(torch.randint(300, 900, (n_seqs - 1,), generator=g))]
+    slots = [engine.open_sequence() for _ in range(n_seqs)]
+    at = 37                                           # the checked sequence sits in the middle of the batch
+    prompts = others[:at] + [toks[:n_prompt]] + others[at:]
+    first = engine.step(slots, prompts)               # the last position of every prompt
+    rows = [first[at:at + 1].cpu()]
+    feed = [[1 + (i % 7)] for i in range(n_seqs)]
+    for t in toks[n_prompt:-1]:
+        feed[at] = [t]
+        rows.append(engine.step(slots, feed)[at:at + 1].cpu())
+    engine.check_status()
+    got = torch.cat(rows)
+    diff = (got - want[n_prompt - 1:n_prompt - 1 + len(rows)]).abs().max(dim=1).values
+    assert float(diff.max()) <= TOL["bfloat16"], f"first step over tolerance: {int((diff > TOL['bfloat16']).nonzero()[0])}"
+    for s in slots:
+        engine.close_sequence(s)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
