@@ -81,6 +81,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
 }
+// The 8 x 8 matrix of 16-bit elements that the warp holds as an MMA fragment (row lane / 4, columns 2 * (lane % 4) and
+// + 1 in one register), transposed.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred) {
     uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
     int bytes = pred ? 16 : 0;   // 0 bytes read: the 16 bytes are filled with zeros
@@ -88,41 +95,27 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 
-// What a warp holds after its tiles (running maxima, sums and weighted values of heads g and g + 8) is merged over
-// the CTA's warps through shared memory, then over the cluster's CTAs through the leader's shared memory, in warp
-// and rank order; the leader writes the output. `smem_raw` is free for the warps' results when this is called
-// (the first __syncthreads below separates it from the last tile's reads).
+// The end of both kernels. Every warp has left what it holds after its tiles in shared memory, from smem_raw on:
+// [WARPS][16] running maxima, [WARPS][16] sums, [WARPS][16][HDP] weighted values, per head of the group. They are
+// merged over the CTA's warps, then over the cluster's CTAs through the leader's shared memory, in warp and rank
+// order; the leader writes the output.
+template <int WARPS>
+__device__ __forceinline__ float* warp_maxima(unsigned char* smem_raw) { return reinterpret_cast<float*>(smem_raw); }
+template <int WARPS>
+__device__ __forceinline__ float* warp_sums(unsigned char* smem_raw) { return reinterpret_cast<float*>(smem_raw) + WARPS * 16; }
+template <int WARPS>
+__device__ __forceinline__ float* warp_values(unsigned char* smem_raw) { return reinterpret_cast<float*>(smem_raw) + 2 * WARPS * 16; }
+
 template <int HDB, int WARPS>
-__device__ __forceinline__ void merge_and_store(const DecodeArgs& a, unsigned char* smem_raw, float* part,
-                                                const float (&o_acc)[HDB * 4][4], float m0, float m1, float l0, float l1,
-                                                int rank, int kvh, int b) {
-    constexpr int HDP = HDB * 32, NT = HDP / 8;
+__device__ __forceinline__ void merge_and_store(const DecodeArgs& a, unsigned char* smem_raw, float* part, int rank, int kvh, int b) {
+    constexpr int HDP = HDB * 32;
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q4 = lane & 3;
     const int hd = a.head_dim, group = a.heads / a.kv_heads;
     constexpr int kThreadsHere = WARPS * 32;
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-
-    // ---- the warps of this CTA, through shared memory (the chunk buffers are free now) -------
-    __syncthreads();
-    float* wm = reinterpret_cast<float*>(smem_raw);          // [WARPS][16] maxima
-    float* wl = wm + WARPS * 16;                            // [WARPS][16] sums
-    float* wo = wl + WARPS * 16;                            // [WARPS][16][HDP] weighted values
-    if (q4 == 0) {
-        wm[warp * 16 + g] = m0; wm[warp * 16 + g + 8] = m1;
-        wl[warp * 16 + g] = l0; wl[warp * 16 + g + 8] = l1;
-    }
-#pragma unroll
-    for (int i = 0; i < NT; ++i) {
-        float* r0 = wo + ((size_t)warp * 16 + g) * HDP + i * 8 + q4 * 2;
-        float* r1 = wo + ((size_t)warp * 16 + g + 8) * HDP + i * 8 + q4 * 2;
-        r0[0] = o_acc[i][0]; r0[1] = o_acc[i][1];
-        r1[0] = o_acc[i][2]; r1[1] = o_acc[i][3];
-    }
+    const float* wm = warp_maxima<WARPS>(smem_raw);
+    const float* wl = warp_sums<WARPS>(smem_raw);
+    const float* wo = warp_values<WARPS>(smem_raw);
     __syncthreads();
     const int pstride = HDP + 2;
     float* dst = a.cluster > 1 ? cluster.map_shared_rank(part, 0) : part;
@@ -163,6 +156,33 @@ __device__ __forceinline__ void merge_and_store(const DecodeArgs& a, unsigned ch
             o = fmaf(p[2 + d], f, o);
         }
         a.out[((size_t)b * a.heads + (size_t)kvh * group + r) * hd + d] = __float2bfloat16_rn(o / l);
+    }
+}
+
+// A warp whose tiles had the heads as the 16 rows of the tensor-core tile (heads g and g + 8 per thread, NT tiles
+// of 8 dimensions) leaves its state for the merge. The shared memory must be free (a barrier after its last use).
+template <int HDB, int WARPS>
+__device__ __forceinline__ void leave_rows_state(unsigned char* smem_raw, const float (&o_acc)[HDB * 4][4], float m0, float m1,
+                                                 float l0, float l1) {
+    constexpr int HDP = HDB * 32, NT = HDP / 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q4 = lane & 3;
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    float* wm = warp_maxima<WARPS>(smem_raw);
+    float* wl = warp_sums<WARPS>(smem_raw);
+    float* wo = warp_values<WARPS>(smem_raw);
+    if (q4 == 0) {
+        wm[warp * 16 + g] = m0; wm[warp * 16 + g + 8] = m1;
+        wl[warp * 16 + g] = l0; wl[warp * 16 + g + 8] = l1;
+    }
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+        float* r0 = wo + ((size_t)warp * 16 + g) * HDP + i * 8 + q4 * 2;
+        float* r1 = wo + ((size_t)warp * 16 + g + 8) * HDP + i * 8 + q4 * 2;
+        r0[0] = o_acc[i][0]; r0[1] = o_acc[i][1];
+        r1[0] = o_acc[i][2]; r1[1] = o_acc[i][3];
     }
 }
 
@@ -322,7 +342,9 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
                 }
         }
     }
-    merge_and_store<HDB, kWarps>(a, smem_raw, part, o_acc, m0, m1, l0, l1, rank, kvh, b);
+    __syncthreads();   // the buffer is free for the warps' results
+    leave_rows_state<HDB, kWarps>(smem_raw, o_acc, m0, m1, l0, l1);
+    merge_and_store<HDB, kWarps>(a, smem_raw, part, rank, kvh, b);
 }
 
 // ---- shares that do not fit one buffer: every warp streams tiles of its own ------------------------------------
@@ -341,13 +363,12 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
 constexpr int kStreamWarps = 4;
 constexpr int kStreamThreads = kStreamWarps * 32;
 
-template <int HDB, int KT, bool BOX>
+template <int HDB, int KT, bool BOX, int NHT>
 __global__ void __launch_bounds__(kStreamThreads)
 decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeArgs a) {
     using namespace tc5;
     constexpr int HDP = HDB * 32;
     constexpr int LD = HDP + 8;                  // row by row: elements of a padded row
-    constexpr int NT = HDP / 8;
     constexpr int CPR = HDP / 8;                 // 16-byte pieces of a row
     constexpr int HALVES = BOX ? HDP / 64 : 1;   // BOX: blocks of 64 columns, each [KT][64] with rows of 128 bytes
     constexpr int kTileElems = BOX ? KT * HDP : KT * LD;                  // keys of a tile; as many values behind them
@@ -356,7 +377,10 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     static_assert(!BOX || HDP % 64 == 0, "boxes are 64 columns wide");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // [warp][stage][keys | values] (on 1,024 bytes for the swizzle), later the warps' results from smem_raw on;
-    // then q, the cluster's partial results, the barriers
+    // then q, the cluster's partial results, the barriers. (The partial results have memory of their own, although
+    // they are written only when the rings are free: a CTA that is done hands its result to the leader at once,
+    // while others still stream. Measured with them laid over the rings, which takes a cluster barrier after the
+    // loop but leaves room for a third tile in flight: 16.6 -> 19.4 us at 8 x 16,384 positions.)
     const int group = a.heads / a.kv_heads, hd = a.head_dim, S = a.stages;
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw + a.own_bytes);
     float* part = reinterpret_cast<float*>(smem_raw + a.own_bytes + (size_t)16 * LD * sizeof(__nv_bfloat16));
@@ -407,6 +431,14 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     // Asks for this warp's tile number i into slot s. Row by row: before the wait on the kernel before this one
     // the newest position's row is left out; rows behind the share's end are not copied, and the value rows among
     // them are zeroed, since they are multiplied (by zero weights).
+    // BOX: the page of this warp's tile number i (looked up ahead of the request, so that the trip to the table
+    // is not waited for when the request is made)
+    auto page_of = [&](int i) -> int {
+        const int lo = cta_lo + (warp + kStreamWarps * i) * KT;
+        const int idx = a.ring > 0 ? lo % a.ring : lo;
+        return a.page_table[(size_t)slot * a.table_stride + idx / kPageSize];
+    };
+    int next_page = 0;
     auto request = [&](int i, int s, bool before_wait) {
         const int lo = cta_lo + (warp + kStreamWarps * i) * KT;
         unsigned char* kt = ring + (size_t)s * kTileBytes;
@@ -417,7 +449,7 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
             if (lane < 2 * HALVES) {
                 const int which = lane / HALVES, half = lane - which * HALVES;   // 0: keys, 1: values
                 const int idx = a.ring > 0 ? lo % a.ring : lo;
-                const int page = a.page_table[(size_t)slot * a.table_stride + idx / kPageSize];
+                const int page = before_wait || i < S ? page_of(i) : next_page;
                 const int row = (page * a.kv_heads + kvh) * kPageSize + idx % kPageSize;
                 tma_load_2d((which ? vt : kt) + half * (KT * 128), which ? &map_v : &map_k, half * 64, row, &my_bars[s]);
             }
@@ -477,16 +509,29 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     }
     __syncthreads();
 
-    uint32_t qa[HDB][4], qb[HDB][4];   // heads x dims [0, 16) and [16, 32) of each block of 32
+    // The tiles are computed transposed: S^T = K Q^T has the tile's positions as the 16 rows of the tensor-core tile
+    // and the group's heads as its 8 columns (NHT = 2 column tiles for groups of 9 to 16 heads), O^T = V^T P^T the
+    // head dimension as rows. A group of up to 8 heads then costs half the MMAs of the untransposed form, where
+    // the heads are padded to 16 rows; and with one warp a scheduler the MMAs are what a long share's time is.
+    // A thread holds, per column tile, the heads 2 * q4 and 2 * q4 + 1 (of positions g and g + 8 in S^T, of
+    // dimensions g and g + 8 in O^T).
+    constexpr int MT = KT / 16;        // tiles of 16 positions
+    constexpr int DT = HDP / 16;       // tiles of 16 dimensions
+    const int g = lane >> 2;
+    uint32_t qf[HDB][NHT][4];          // Q^T as the B operand: per block of 32 dimensions, two steps of 16
 #pragma unroll
-    for (int kb32 = 0; kb32 < HDB; ++kb32) {
-        ldmatrix_x4(qa[kb32], qs + (size_t)(lane & 15) * LD + kb32 * 32 + (lane >> 4) * 8);
-        ldmatrix_x4(qb[kb32], qs + (size_t)(lane & 15) * LD + kb32 * 32 + 16 + (lane >> 4) * 8);
-    }
-    float o_acc[NT][4];
+    for (int kb32 = 0; kb32 < HDB; ++kb32)
 #pragma unroll
-    for (int i = 0; i < NT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
-    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+        for (int nh = 0; nh < NHT; ++nh)
+            ldmatrix_x4(qf[kb32][nh], qs + (size_t)(nh * 8 + (lane & 7)) * LD + kb32 * 32 + (lane >> 3) * 8);
+    float ot[DT][NHT][4];
+#pragma unroll
+    for (int d = 0; d < DT; ++d)
+#pragma unroll
+        for (int nh = 0; nh < NHT; ++nh) ot[d][nh][0] = ot[d][nh][1] = ot[d][nh][2] = ot[d][nh][3] = 0.f;
+    float run_m[NHT][2], run_l[NHT][2];   // per head: running maximum (the same in all lanes of a q4), this thread's part of the sum
+#pragma unroll
+    for (int nh = 0; nh < NHT; ++nh) { run_m[nh][0] = run_m[nh][1] = -CUDART_INF_F; run_l[nh][0] = run_l[nh][1] = 0.f; }
 
     int s = 0;
     uint32_t parity = 0;
@@ -498,6 +543,7 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         const unsigned char* kt = ring + (size_t)s * kTileBytes;
         unsigned char* vt = ring + (size_t)s * kTileBytes + kTileBytes / 2;
         const int lo = cta_lo + (warp + kStreamWarps * i) * KT;
+        if (BOX && lane < 2 * HALVES && i + S < my_tiles) next_page = page_of(i + S);
         if (BOX && (lo < first_key || lo + KT > cta_hi)) {
             // a box brings whole rows of the page: the value rows outside the share are zeroed (zero weights times
             // whatever lies there must stay zero)
@@ -508,71 +554,116 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
         }
-        // S = Q K^T: 16 heads x KT keys
-        float sc[KT / 8][4];
+        // S^T = K Q^T
+        float st[MT][NHT][4];
 #pragma unroll
-        for (int j = 0; j < KT / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int kb32 = 0; kb32 < HDB; ++kb32)
+            for (int nh = 0; nh < NHT; ++nh) st[mt][nh][0] = st[mt][nh][1] = st[mt][nh][2] = st[mt][nh][3] = 0.f;
 #pragma unroll
-            for (int j = 0; j < KT / 8; ++j) {
-                uint32_t kf[4];      // keys 8j.. x dims 0-7, 8-15, 16-23, 24-31 of the block
-                ldmatrix_x4(kf, kt + piece_at(j * 8 + (lane & 7), kb32 * 4 + (lane >> 3)));
-                mma_bf16(sc[j], qa[kb32][0], qa[kb32][1], qa[kb32][2], qa[kb32][3], kf[0], kf[1]);
-                mma_bf16(sc[j], qb[kb32][0], qb[kb32][1], qb[kb32][2], qb[kb32][3], kf[2], kf[3]);
+        for (int kk = 0; kk < HDP / 16; ++kk)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint32_t kf[4];      // positions 16mt.. x dimensions 16kk..: rows g / g + 8, columns 0-7 / 8-15
+                ldmatrix_x4(kf, kt + piece_at(mt * 16 + (lane & 15), kk * 2 + (lane >> 4)));
+#pragma unroll
+                for (int nh = 0; nh < NHT; ++nh)
+                    mma_bf16(st[mt][nh], kf[0], kf[1], kf[2], kf[3], qf[kk / 2][nh][(kk & 1) * 2], qf[kk / 2][nh][(kk & 1) * 2 + 1]);
             }
-        // scale, mask the keys outside this CTA's range, running maximum
-        float mx0 = m0, mx1 = m1;
+        // scale, mask the positions outside this CTA's range, running maximum per head
+        float mx[NHT][2];
 #pragma unroll
-        for (int j = 0; j < KT / 8; ++j)
+        for (int nh = 0; nh < NHT; ++nh) { mx[nh][0] = run_m[nh][0]; mx[nh][1] = run_m[nh][1]; }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = lo + j * 8 + q4 * 2 + (e & 1);
-                const float x = (key >= first_key && key < cta_hi) ? sc[j][e] * a.scale_log2 : -CUDART_INF_F;
-                sc[j][e] = x;
-                if (e & 2) mx1 = fmaxf(mx1, x); else mx0 = fmaxf(mx0, x);
+        for (int mt = 0; mt < MT; ++mt) {
+            const int key0 = lo + mt * 16 + g, key1 = key0 + 8;
+            const bool in0 = key0 >= first_key && key0 < cta_hi, in1 = key1 >= first_key && key1 < cta_hi;
+#pragma unroll
+            for (int nh = 0; nh < NHT; ++nh)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float x = ((e & 2) ? in1 : in0) ? st[mt][nh][e] * a.scale_log2 : -CUDART_INF_F;
+                    st[mt][nh][e] = x;
+                    mx[nh][e & 1] = fmaxf(mx[nh][e & 1], x);
+                }
+        }
+        float rescale[NHT][2];
+#pragma unroll
+        for (int nh = 0; nh < NHT; ++nh)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float v = mx[nh][e];
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+                mx[nh][e] = v;       // a tile always holds a visible key (the first one holds the window's start): finite
+                rescale[nh][e] = exp2f(run_m[nh][e] - v);
+                run_m[nh][e] = v;
             }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        // a tile always holds a visible key (the first one holds the window's start): mx is finite
-        const float c0 = exp2f(m0 - mx0), c1 = exp2f(m1 - mx1);
-        const float sub0 = mx0, sub1 = mx1;
-        m0 = mx0;
-        m1 = mx1;
-        uint32_t pf[KT / 16][4];
-        float sum0 = 0.f, sum1 = 0.f;
+        // P^T as the B operand: an 8 x 8 block (positions x heads) of the accumulator is transposed among the lanes
+        uint32_t pb[MT][NHT][2];
 #pragma unroll
-        for (int j = 0; j < KT / 8; ++j) {
-            const float p0 = exp2f(sc[j][0] - sub0), p1 = exp2f(sc[j][1] - sub0);
-            const float p2 = exp2f(sc[j][2] - sub1), p3 = exp2f(sc[j][3] - sub1);
-            sum0 += p0 + p1;
-            sum1 += p2 + p3;
-            pf[j / 2][(j & 1) * 2] = pack_bf16(p0, p1);
-            pf[j / 2][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+        for (int nh = 0; nh < NHT; ++nh) {
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const float p0 = exp2f(st[mt][nh][0] - mx[nh][0]), p1 = exp2f(st[mt][nh][1] - mx[nh][1]);
+                const float p2 = exp2f(st[mt][nh][2] - mx[nh][0]), p3 = exp2f(st[mt][nh][3] - mx[nh][1]);
+                sum0 += p0 + p2;
+                sum1 += p1 + p3;
+                pb[mt][nh][0] = movmatrix_trans(pack_bf16(p0, p1));
+                pb[mt][nh][1] = movmatrix_trans(pack_bf16(p2, p3));
+            }
+            run_l[nh][0] = run_l[nh][0] * rescale[nh][0] + sum0;
+            run_l[nh][1] = run_l[nh][1] * rescale[nh][1] + sum1;
         }
-        l0 = l0 * c0 + sum0;
-        l1 = l1 * c1 + sum1;
 #pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            o_acc[t][0] *= c0; o_acc[t][1] *= c0; o_acc[t][2] *= c1; o_acc[t][3] *= c1;
-        }
-        // O += P V: keys 16jj.. x two dim tiles per ldmatrix
+        for (int d = 0; d < DT; ++d)
 #pragma unroll
-        for (int jj = 0; jj < KT / 16; ++jj)
+            for (int nh = 0; nh < NHT; ++nh) {
+                ot[d][nh][0] *= rescale[nh][0]; ot[d][nh][1] *= rescale[nh][1];
+                ot[d][nh][2] *= rescale[nh][0]; ot[d][nh][3] *= rescale[nh][1];
+            }
+        // O^T += V^T P^T
 #pragma unroll
-            for (int t = 0; t < NT; t += 2) {
-                uint32_t vf[4];
-                ldmatrix_x4_trans(vf, vt + piece_at(jj * 16 + (lane & 15), t + (lane >> 4)));
-                mma_bf16(o_acc[t], pf[jj][0], pf[jj][1], pf[jj][2], pf[jj][3], vf[0], vf[1]);
-                mma_bf16(o_acc[t + 1], pf[jj][0], pf[jj][1], pf[jj][2], pf[jj][3], vf[2], vf[3]);
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int d = 0; d < DT; ++d) {
+                uint32_t vf[4];      // dimensions 16d.. x positions 16mt..: rows g / g + 8, columns 0-7 / 8-15, transposed on the way
+                ldmatrix_x4_trans(vf, vt + piece_at(mt * 16 + (lane & 7) + ((lane >> 4) << 3), d * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+                for (int nh = 0; nh < NHT; ++nh) mma_bf16(ot[d][nh], vf[0], vf[1], vf[2], vf[3], pb[mt][nh][0], pb[mt][nh][1]);
             }
         __syncwarp();   // every lane has read the slot
         if (i + S < my_tiles) request(i + S, s, false);
         if (++s == S) { s = 0; parity ^= 1u; }
     }
-    merge_and_store<HDB, kStreamWarps>(a, smem_raw, part, o_acc, m0, m1, l0, l1, rank, kvh, b);
+
+    // the warp's state for the merge: [16 heads] maxima and sums, [16 heads][HDP] weighted values
+    __syncthreads();   // every warp is through its tiles: the rings are free
+    {
+        float* wm = warp_maxima<kStreamWarps>(smem_raw);
+        float* wl = warp_sums<kStreamWarps>(smem_raw);
+        float* wo = warp_values<kStreamWarps>(smem_raw);
+#pragma unroll
+        for (int nh = 0; nh < NHT; ++nh)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float l = run_l[nh][e];
+                l += __shfl_xor_sync(0xffffffffu, l, 4);
+                l += __shfl_xor_sync(0xffffffffu, l, 8);
+                l += __shfl_xor_sync(0xffffffffu, l, 16);
+                const int head = nh * 8 + q4 * 2 + e;
+                if (g == 0) { wm[warp * 16 + head] = run_m[nh][e]; wl[warp * 16 + head] = l; }
+#pragma unroll
+                for (int d = 0; d < DT; ++d) {
+                    float* row = wo + ((size_t)warp * 16 + head) * HDP + d * 16 + g;
+                    row[0] = ot[d][nh][e];
+                    row[8] = ot[d][nh][2 + e];
+                }
+            }
+    }
+    merge_and_store<HDB, kStreamWarps>(a, smem_raw, part, rank, kvh, b);
 }
 
 // Shared memory of a CTA and how it is cut, for a cluster size and the most positions a CTA can get.
@@ -665,26 +756,26 @@ StreamPlan make_stream_plan(int hdb, bool box, int group, int cluster, size_t ta
     return p;
 }
 
-template <int HDB, bool BOX>
+template <int HDB, bool BOX, int NHT>
 void prepare_stream(size_t smem) {
     constexpr int KT = stream_tile_keys(HDB);
     static size_t allowed = 48 * 1024;
     static bool large_clusters = false;
     if (!large_clusters) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_stream_kernel<HDB, KT, BOX>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_stream_kernel<HDB, KT, BOX, NHT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) throw std::runtime_error(std::string("attention_decode: ") + cudaGetErrorString(e));
         large_clusters = true;
     }
     if (smem > allowed) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_stream_kernel<HDB, KT, BOX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_stream_kernel<HDB, KT, BOX, NHT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) throw std::runtime_error(std::string("attention_decode: ") + cudaGetErrorString(e));
         allowed = smem;
     }
 }
 
-template <int HDB, bool BOX>
+template <int HDB, bool BOX, int NHT>
 int resident_stream_clusters(const StreamPlan& p) {
-    prepare_stream<HDB, BOX>(p.smem);
+    prepare_stream<HDB, BOX, NHT>(p.smem);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(p.cluster, 1, 1);
     cfg.blockDim = dim3(kStreamThreads);
@@ -697,7 +788,7 @@ int resident_stream_clusters(const StreamPlan& p) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, decode_attention_stream_kernel<HDB, stream_tile_keys(HDB), BOX>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n, decode_attention_stream_kernel<HDB, stream_tile_keys(HDB), BOX, NHT>, &cfg) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -705,7 +796,7 @@ int resident_stream_clusters(const StreamPlan& p) {
 }
 
 // The largest cluster all of whose clusters are resident at once and every warp of which gets two tiles or more.
-template <int HDB, bool BOX>
+template <int HDB, bool BOX, int NHT>
 StreamPlan choose_stream_plan(int pairs, int group, int visible) {
     struct Known { int pairs, group, visible; StreamPlan plan; };
     static std::mutex lock;
@@ -717,7 +808,7 @@ StreamPlan choose_stream_plan(int pairs, int group, int visible) {
     for (int cluster = kMaxCluster; cluster > 1; cluster /= 2) {
         if (visible < cluster * kStreamWarps * 2 * stream_tile_keys(HDB)) continue;
         const StreamPlan p = make_stream_plan(HDB, BOX, group, cluster, kStreamSmemShared);
-        if (pairs <= resident_stream_clusters<HDB, BOX>(p)) { chosen = p; break; }
+        if (pairs <= resident_stream_clusters<HDB, BOX, NHT>(p)) { chosen = p; break; }
     }
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
@@ -725,7 +816,7 @@ StreamPlan choose_stream_plan(int pairs, int group, int visible) {
     if (pairs * chosen.cluster <= sms) {
         // no SM gets a second CTA: each takes the shared memory of two
         const StreamPlan alone = make_stream_plan(HDB, BOX, group, chosen.cluster, kStreamSmemAlone);
-        if (pairs <= resident_stream_clusters<HDB, BOX>(alone)) chosen = alone;
+        if (pairs <= resident_stream_clusters<HDB, BOX, NHT>(alone)) chosen = alone;
     }
     if (known.size() < 4096) known.push_back({pairs, group, visible, chosen});
     return chosen;
@@ -755,10 +846,10 @@ CUtensorMap make_pool_map(const void* pool, long long pool_pages, int kv_heads, 
     return map;
 }
 
-template <int HDB, bool BOX>
+template <int HDB, bool BOX, int NHT>
 void launch_stream(DecodeArgs a, int visible, long long pool_pages, cudaStream_t stream) {
     constexpr int KT = stream_tile_keys(HDB);
-    const StreamPlan sp = choose_stream_plan<HDB, BOX>(a.B * a.kv_heads, a.heads / a.kv_heads, visible);
+    const StreamPlan sp = choose_stream_plan<HDB, BOX, NHT>(a.B * a.kv_heads, a.heads / a.kv_heads, visible);
     a.cluster = sp.cluster;
     a.stages = sp.stages;
     a.own_bytes = sp.own_bytes;
@@ -768,8 +859,8 @@ void launch_stream(DecodeArgs a, int visible, long long pool_pages, cudaStream_t
         map_k = make_pool_map(a.k_pool, pool_pages, a.kv_heads, a.head_dim, KT);
         map_v = make_pool_map(a.v_pool, pool_pages, a.kv_heads, a.head_dim, KT);
     }
-    prepare_stream<HDB, BOX>(sp.smem);
-    launch_kernel("attention_decode", decode_attention_stream_kernel<HDB, KT, BOX>, dim3(a.cluster, a.kv_heads, a.B),
+    prepare_stream<HDB, BOX, NHT>(sp.smem);
+    launch_kernel("attention_decode", decode_attention_stream_kernel<HDB, KT, BOX, NHT>, dim3(a.cluster, a.kv_heads, a.B),
                   dim3(kStreamThreads), sp.smem, stream, a.cluster, dependent_launch_enabled(), map_k, map_v, a);
 }
 
@@ -798,10 +889,13 @@ void launch(DecodeArgs a, int visible, long long pool_pages, cudaStream_t stream
     const DecodePlan p = choose_plan<HDB>(a.B * a.kv_heads, a.heads / a.kv_heads, visible);
     if (!p.fits) {
         // a share that does not fit one buffer is streamed
-        if (HDB % 2 == 0 && boxes_possible(a.head_dim, a.kv_heads, pool_pages, a.k_pool, a.v_pool))
-            launch_stream<HDB, HDB % 2 == 0>(a, visible, pool_pages, stream);
-        else
-            launch_stream<HDB, false>(a, visible, pool_pages, stream);
+        // (a group of up to 8 heads is one column tile of the transposed product, up to 16 heads two)
+        const bool box = HDB % 2 == 0 && boxes_possible(a.head_dim, a.kv_heads, pool_pages, a.k_pool, a.v_pool);
+        const bool wide = a.heads / a.kv_heads > 8;
+        if (box && wide) launch_stream<HDB, HDB % 2 == 0, 2>(a, visible, pool_pages, stream);
+        else if (box) launch_stream<HDB, HDB % 2 == 0, 1>(a, visible, pool_pages, stream);
+        else if (wide) launch_stream<HDB, false, 2>(a, visible, pool_pages, stream);
+        else launch_stream<HDB, false, 1>(a, visible, pool_pages, stream);
         return;
     }
     a.cluster = p.cluster;
@@ -832,13 +926,19 @@ void attention_decode_plan(int B, int heads, int kv_heads, int head_dim, int win
     plan[0] = p.cluster; plan[1] = p.buf_keys; plan[2] = 1; plan[3] = (int)p.smem;
     if (!p.fits) {   // streamed: the cluster, 0, the tiles a warp keeps in flight, the shared memory
         StreamPlan sp{};
+        const int pairs = B * kv_heads, group = heads / kv_heads;
+        const bool wide = group > 8;
         switch ((head_dim + 31) / 32) {
-            case 1: sp = choose_stream_plan<1, false>(B * kv_heads, heads / kv_heads, visible); break;
-            case 2: sp = head_dim == 64 ? choose_stream_plan<2, true>(B * kv_heads, heads / kv_heads, visible)
-                                        : choose_stream_plan<2, false>(B * kv_heads, heads / kv_heads, visible); break;
-            case 3: sp = choose_stream_plan<3, false>(B * kv_heads, heads / kv_heads, visible); break;
-            default: sp = head_dim == 128 ? choose_stream_plan<4, true>(B * kv_heads, heads / kv_heads, visible)
-                                          : choose_stream_plan<4, false>(B * kv_heads, heads / kv_heads, visible); break;
+            case 1: sp = wide ? choose_stream_plan<1, false, 2>(pairs, group, visible) : choose_stream_plan<1, false, 1>(pairs, group, visible); break;
+            case 2:
+                if (head_dim == 64) sp = wide ? choose_stream_plan<2, true, 2>(pairs, group, visible) : choose_stream_plan<2, true, 1>(pairs, group, visible);
+                else sp = wide ? choose_stream_plan<2, false, 2>(pairs, group, visible) : choose_stream_plan<2, false, 1>(pairs, group, visible);
+                break;
+            case 3: sp = wide ? choose_stream_plan<3, false, 2>(pairs, group, visible) : choose_stream_plan<3, false, 1>(pairs, group, visible); break;
+            default:
+                if (head_dim == 128) sp = wide ? choose_stream_plan<4, true, 2>(pairs, group, visible) : choose_stream_plan<4, true, 1>(pairs, group, visible);
+                else sp = wide ? choose_stream_plan<4, false, 2>(pairs, group, visible) : choose_stream_plan<4, false, 1>(pairs, group, visible);
+                break;
         }
         plan[0] = sp.cluster; plan[1] = 0; plan[2] = sp.stages; plan[3] = (int)sp.smem;
     }

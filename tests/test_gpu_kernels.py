@@ -253,7 +253,8 @@ def test_decode_attention_long_contexts(ops, heads, kv_heads, hd, lens, max_len)
         assert float((got[b] - want[b]).abs().max()) <= 1e-2, f"sequence {b} of {lens[b]} positions"
 
 
-@pytest.mark.parametrize("heads,kv_heads,hd", [(3, 1, 32), (10, 5, 48), (14, 2, 64), (6, 3, 96), (8, 2, 128)])
+@pytest.mark.parametrize("heads,kv_heads,hd", [(3, 1, 32), (10, 5, 48), (14, 2, 64), (6, 3, 96), (8, 2, 128), (12, 1, 64),
+                                               (16, 1, 128), (9, 1, 80)])
 @pytest.mark.parametrize("window", [None, 700])
 def test_decode_attention_streamed_shares(ops, heads, kv_heads, hd, window):
     """More (sequence, kv head) pairs than the GPU holds clusters, each with hundreds of positions: every CTA streams
@@ -262,7 +263,7 @@ def test_decode_attention_streamed_shares(ops, heads, kv_heads, hd, window):
     import ctypes
     from smolmoe_c99_b200.kernels import PAGE_SIZE
     g = torch.Generator().manual_seed(11)
-    B = 320 // kv_heads
+    B = 320 // kv_heads      # (the groups of more than 8 heads take two column tiles of the transposed product)
     lens = [int(x) for x in torch.randint(650, 1000, (B,), generator=g)]
     lens[0], lens[1], lens[2] = 1, 33, 999
     max_len = 1024
