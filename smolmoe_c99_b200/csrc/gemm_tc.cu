@@ -46,7 +46,7 @@ constexpr int kUmmaK = 16;
 constexpr int kBoxRows = 64;         // rows of one TMA box (a token tile below 64 rows is one box of its own size)
 constexpr int kThreads = 192;
 
-enum Epilogue : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
+enum Epilogue : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_QKV_ROPE = 4 };
 
 struct GemmParams {
     int T, N, K;              // tokens, output features, reduction
@@ -68,6 +68,7 @@ struct GemmParams {
     int tma_out;              // the epilogue leaves through shared memory and TMA (store or add)
     int final_epilogue;       // what the epilogue is once the splits are added up
     int cluster_reduce;       // small kernel: the CTAs along K are one cluster and add their sums up among themselves
+    SkinnyRope rope;          // EPI_QKV_ROPE: where q goes and where the cache is (out is unused)
 };
 
 using namespace tc5;   // the PTX wrappers (tcgen05.cuh)
@@ -537,57 +538,120 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             const int per = (pieces + p.splits - 1) / p.splits;
             const int hi = min(pieces, (split + 1) * per);
             const uint32_t base = smem_u32(smem);
-            // four features at a time where the output's rows allow it (then n + 3 < N whenever n < N)
-            const bool vec = (p.N & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
-            for (int c = split * per + (int)threadIdx.x - 64; c < hi; c += 128) {
-                const int t = t0 + c / (kTileM / 4), n = n0 + (c % (kTileM / 4)) * 4;
-                if (t >= p.T || n >= p.N) continue;
-                const size_t o = (size_t)t * p.N + n;
-                float old[4] = {0.f, 0.f, 0.f, 0.f};
-                if (p.final_epilogue == EPI_ACCUM) {   // asked for before the sums: the trips overlap
-                    if (vec) {
-                        const float4 r = *reinterpret_cast<const float4*>((const float*)p.out + o);
-                        old[0] = r.x; old[1] = r.y; old[2] = r.z; old[3] = r.w;
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) old[e] = n + e < p.N ? ((const float*)p.out)[o + e] : 0.f;
-                    }
-                }
-                float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+            if (p.final_epilogue == EPI_QKV_ROPE) {
+                // q/k/v rows: bias, rotation of (d, d + head_dim / 2) with the position's angles, q to its matrix,
+                // keys and values into the paged cache (src/model.c:501-526 of the reference: bias before the
+                // rotation, the rotated key into the cache). The head size divides the tile's 128 rows, so both
+                // halves of a head are in this tile; a thread takes four neighbouring dimensions and their partners.
+                const SkinnyRope& r = p.rope;
+                const int hd = r.head_dim, half = hd / 2, hp = hd / 8;       // hp: float4s of half a head
+                const int pairs = p.tile_n * (kTileM / 8);
+                const int per_pairs = (pairs + p.splits - 1) / p.splits;
+                const int hi_pair = min(pairs, (split + 1) * per_pairs);
+                PagedKV paged{r.page_table, r.table_stride, r.ring, r.kv_heads, hd};
+                for (int pp = split * per_pairs + (int)threadIdx.x - 64; pp < hi_pair; pp += 128) {
+                    const int tcol = pp / (kTileM / 8), q = pp - tcol * (kTileM / 8);
+                    const int lo_piece = (q / hp) * (2 * hp) + q % hp, hi_piece = lo_piece + hp;
+                    const int t = t0 + tcol, n_lo = n0 + lo_piece * 4;
+                    if (t >= p.T || n_lo >= p.N) continue;
+                    float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo;
 #pragma unroll 4
-                for (int sp = 0; sp < p.splits; ++sp) {
-                    const float4 a = ld_cluster_f4(base + (uint32_t)c * 16u, (uint32_t)sp);
-                    g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-                    if (p.dual) {
-                        const float4 b = ld_cluster_f4(base + (uint32_t)(pieces + c) * 16u, (uint32_t)sp);
-                        u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        const float4 a = ld_cluster_f4(base + (uint32_t)(tcol * (kTileM / 4) + lo_piece) * 16u, (uint32_t)sp);
+                        const float4 b = ld_cluster_f4(base + (uint32_t)(tcol * (kTileM / 4) + hi_piece) * 16u, (uint32_t)sp);
+                        lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+                        hi4.x += b.x; hi4.y += b.y; hi4.z += b.z; hi4.w += b.w;
                     }
-                }
-                float v[4] = {g.x, g.y, g.z, g.w};
-                const float ups[4] = {u.x, u.y, u.z, u.w};
+                    float vl[4] = {lo.x, lo.y, lo.z, lo.w}, vh[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+                    const int head = n_lo / hd, d = n_lo - head * hd;
+                    if (p.bias) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    if (p.final_epilogue == EPI_SWIGLU) v[e] = gated(v[e], ups[e]);
-                    else if (p.bias && n + e < p.N)
-                        v[e] += p.bias_dt == F32 ? ((const float*)p.bias)[n + e] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n + e]);
-                    v[e] += old[e];
-                }
-                if (vec) {
-                    if (p.out_dt == F32) {
-                        *reinterpret_cast<float4*>((float*)p.out + o) = make_float4(v[0], v[1], v[2], v[3]);
+                        for (int e = 0; e < 4; ++e) {
+                            vl[e] += p.bias_dt == F32 ? ((const float*)p.bias)[n_lo + e] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n_lo + e]);
+                            vh[e] += p.bias_dt == F32 ? ((const float*)p.bias)[n_lo + half + e] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n_lo + half + e]);
+                        }
+                    }
+                    const int pos = r.positions[t];
+                    const bool is_v = head >= r.heads + r.kv_heads;
+                    if (!is_v) {
+                        const float4 c4 = *reinterpret_cast<const float4*>(r.cos_table + (size_t)pos * half + d);
+                        const float4 s4 = *reinterpret_cast<const float4*>(r.sin_table + (size_t)pos * half + d);
+                        const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float r0 = vl[e] * cs[e] - vh[e] * sn[e], r1 = vl[e] * sn[e] + vh[e] * cs[e];
+                            vl[e] = r0;
+                            vh[e] = r1;
+                        }
+                    }
+                    __nv_bfloat16* dst;
+                    if (head < r.heads) {
+                        dst = (__nv_bfloat16*)r.q_out + ((size_t)t * r.heads + head) * hd + d;
                     } else {
-                        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi2 = __floats2bfloat162_rn(v[2], v[3]);
-                        uint2 packed;
-                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
-                        packed.y = *reinterpret_cast<uint32_t*>(&hi2);
-                        *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + o) = packed;
+                        const int kvh = is_v ? head - r.heads - r.kv_heads : head - r.heads;
+                        dst = (__nv_bfloat16*)(is_v ? r.v_pool : r.k_pool) + paged.row_offset(r.token_slot[t], pos, kvh) + d;
                     }
-                } else {
-#pragma unroll
+                    __nv_bfloat162 a0 = __floats2bfloat162_rn(vl[0], vl[1]), a1 = __floats2bfloat162_rn(vl[2], vl[3]);
+                    __nv_bfloat162 b0 = __floats2bfloat162_rn(vh[0], vh[1]), b1 = __floats2bfloat162_rn(vh[2], vh[3]);
+                    uint2 pl, ph;
+                    pl.x = *reinterpret_cast<uint32_t*>(&a0); pl.y = *reinterpret_cast<uint32_t*>(&a1);
+                    ph.x = *reinterpret_cast<uint32_t*>(&b0); ph.y = *reinterpret_cast<uint32_t*>(&b1);
+                    *reinterpret_cast<uint2*>(dst) = pl;
+                    *reinterpret_cast<uint2*>(dst + half) = ph;
+                }
+            } else {
+                // four features at a time where the output's rows allow it (then n + 3 < N whenever n < N)
+                const bool vec = (p.N & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
+                for (int c = split * per + (int)threadIdx.x - 64; c < hi; c += 128) {
+                    const int t = t0 + c / (kTileM / 4), n = n0 + (c % (kTileM / 4)) * 4;
+                    if (t >= p.T || n >= p.N) continue;
+                    const size_t o = (size_t)t * p.N + n;
+                    float old[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (p.final_epilogue == EPI_ACCUM) {   // asked for before the sums: the trips overlap
+                        if (vec) {
+                            const float4 r = *reinterpret_cast<const float4*>((const float*)p.out + o);
+                            old[0] = r.x; old[1] = r.y; old[2] = r.z; old[3] = r.w;
+                        } else {
+    #pragma unroll
+                            for (int e = 0; e < 4; ++e) old[e] = n + e < p.N ? ((const float*)p.out)[o + e] : 0.f;
+                        }
+                    }
+                    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+    #pragma unroll 4
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        const float4 a = ld_cluster_f4(base + (uint32_t)c * 16u, (uint32_t)sp);
+                        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+                        if (p.dual) {
+                            const float4 b = ld_cluster_f4(base + (uint32_t)(pieces + c) * 16u, (uint32_t)sp);
+                            u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+                        }
+                    }
+                    float v[4] = {g.x, g.y, g.z, g.w};
+                    const float ups[4] = {u.x, u.y, u.z, u.w};
+    #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        if (n + e >= p.N) break;
-                        if (p.out_dt == F32) ((float*)p.out)[o + e] = v[e];
-                        else ((__nv_bfloat16*)p.out)[o + e] = __float2bfloat16_rn(v[e]);
+                        if (p.final_epilogue == EPI_SWIGLU) v[e] = gated(v[e], ups[e]);
+                        else if (p.bias && n + e < p.N)
+                            v[e] += p.bias_dt == F32 ? ((const float*)p.bias)[n + e] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n + e]);
+                        v[e] += old[e];
+                    }
+                    if (vec) {
+                        if (p.out_dt == F32) {
+                            *reinterpret_cast<float4*>((float*)p.out + o) = make_float4(v[0], v[1], v[2], v[3]);
+                        } else {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi2 = __floats2bfloat162_rn(v[2], v[3]);
+                            uint2 packed;
+                            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                            packed.y = *reinterpret_cast<uint32_t*>(&hi2);
+                            *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + o) = packed;
+                        }
+                    } else {
+    #pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (n + e >= p.N) break;
+                            if (p.out_dt == F32) ((float*)p.out)[o + e] = v[e];
+                            else ((__nv_bfloat16*)p.out)[o + e] = __float2bfloat16_rn(v[e]);
+                        }
                     }
                 }
             }
@@ -791,8 +855,19 @@ size_t gemm_tc_workspace_bytes(int T, int N, int K, bool dual) {
     return sp > 1 ? (size_t)sp * (dual ? 2 : 1) * T * N * sizeof(float) : 0;
 }
 
-void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N,
-             int K, int mode, int up_offset, float* workspace, int* error, cudaStream_t stream) {
+namespace {
+
+// Whether the fused q/k/v epilogue can take this product: the small kernel (at most 64 tokens) with its sums added up
+// inside the CTA or the cluster, and heads that do not straddle the tiles of 128 rows.
+bool qkv_rope_possible(int T, int N, int K, const SkinnyRope& r) {
+    if (T > 64 || !gemm_tc_supports(T, N, K) || r.head_dim < 16 || kTileM % r.head_dim || r.rotary_dim != r.head_dim) return false;
+    int tn, sp;
+    gemm_tc_plan(T, N, K, false, &tn, &sp);
+    return sp == 1 || small_launch(tn, sp, false).cluster;
+}
+
+void gemm_tc_impl(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N,
+                  int K, int mode, int up_offset, float* workspace, int* error, const SkinnyRope* rope, cudaStream_t stream) {
     if (!gemm_tc_supports(T, N, K))
         throw std::invalid_argument("gemm_tc: K = " + std::to_string(K) + " must be a positive multiple of 8 (TMA rows start on 16 bytes)");
     if (((uintptr_t)x | (uintptr_t)w) & 15) throw std::invalid_argument("gemm_tc: operands must be 16-byte aligned");
@@ -811,10 +886,13 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
     p.tiles_m = (N + kTileM - 1) / kTileM;
     p.tiles_t = (T + p.tile_n - 1) / p.tile_n;
     p.units = p.tiles_m * p.tiles_t * p.splits;
-    const int final_mode = mode;
+    const int final_mode = rope ? (int)EPI_QKV_ROPE : mode;
+    if (rope) p.rope = *rope;
     p.epilogue = p.splits > 1 ? EPI_PARTIAL : final_mode;
     if (p.splits > 1 && !workspace && !(T <= 64 && small_launch(p.tile_n, p.splits, dual).cluster))
         throw std::invalid_argument("gemm_tc: this shape splits K and needs a workspace");
+    if (rope && !qkv_rope_possible(T, N, K, *rope))
+        throw std::invalid_argument("gemm_tc: the fused q/k/v epilogue does not take this shape");
     // the output leaves through shared memory and TMA where TMA can address it: rows that start
     // on 16 bytes (TMA stores outside the matrix are dropped, so ragged edges need no care)
     const size_t out_elem = out_dt == F32 ? 4 : 2;
@@ -827,7 +905,8 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
         p.tma_out = 0;
         p.stages = l.stages;
         p.final_epilogue = final_mode;
-        p.cluster_reduce = l.cluster ? 1 : 0;
+        // (the fused q/k/v epilogue lives in the code that adds the splits up: a single split goes the same way)
+        p.cluster_reduce = l.cluster || rope ? 1 : 0;
         if (p.tiles_m > 65535 || p.tiles_t > 65535) throw std::invalid_argument("gemm_tc: more than 65535 tiles along a side");
         const CUtensorMap mw = make_map(w, dual ? up_offset + N : N, K, kBoxRows);
         const CUtensorMap mx = make_map(x, T, K, p.tile_n < kBoxRows ? p.tile_n : kBoxRows);
@@ -863,6 +942,21 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
         size_t total = (size_t)T * N;
         splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p);
     }
+}
+
+}  // namespace
+
+void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N,
+             int K, int mode, int up_offset, float* workspace, int* error, cudaStream_t stream) {
+    gemm_tc_impl(x, w, bias, bias_dt, out, out_dt, T, N, K, mode, up_offset, workspace, error, nullptr, stream);
+}
+
+bool gemm_tc_qkv_rope(const void* x, const void* w, const void* bias, DType bias_dt, int T, int K, const SkinnyRope& rope,
+                      int* error, cudaStream_t stream) {
+    const int N = (rope.heads + 2 * rope.kv_heads) * rope.head_dim;
+    if (!qkv_rope_possible(T, N, K, rope)) return false;
+    gemm_tc_impl(x, w, bias, bias_dt, nullptr, BF16, T, N, K, EPI_STORE, 0, nullptr, error, &rope, stream);
+    return true;
 }
 
 }  // namespace sm

@@ -76,6 +76,13 @@ void gemm_simt(const void* x, DType x_dt, const void* w, DType w_dt, const void*
 // of gemm_tc_workspace_bytes(). *error becomes non-zero if a bounded wait ran out.
 bool gemm_tc_supports(int T, int N, int K);
 size_t gemm_tc_workspace_bytes(int T, int N, int K, bool dual);
+// q/k/v rows of up to 64 tokens with bias, rotation and the cache write in the product's epilogue (q to rope.q_out,
+// rotated keys and values into the paged pools): x [T, K] bfloat16, w [(heads + 2 kv_heads) * head_dim, K]. Returns
+// false, having done nothing, where the shape is not taken (heads that straddle tiles of 128 rows, K split more
+// than a cluster's ways): the caller then runs the product and rope_store().
+struct SkinnyRope;
+bool gemm_tc_qkv_rope(const void* x, const void* w, const void* bias, DType bias_dt, int T, int K, const SkinnyRope& rope,
+                      int* error, cudaStream_t stream);
 // How a product of these sizes is cut: tokens per tile and CTAs along K.
 void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits);
 void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N,

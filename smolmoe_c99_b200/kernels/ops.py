@@ -246,9 +246,11 @@ class Ops:
                              rotary_dim, k_pool, v_pool, page_table, ring, token_slot) -> Optional[torch.Tensor]:
         """For a handful of tokens: q/k/v product, bias, rotation and cache write in one launch.
         Returns q [T, heads, head_dim], or None when the shapes are not the fused kernel's."""
-        if (not self._skinny_ok(x, w_qkv) or head_dim % 16 or rotary_dim != head_dim or k_pool is None
-                or k_pool.dtype != torch.bfloat16):
+        if head_dim % 16 or rotary_dim != head_dim or k_pool is None or k_pool.dtype != torch.bfloat16:
             return None
+        if not self._skinny_ok(x, w_qkv):
+            return self._qkv_rope_store_tc(x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim,
+                                           k_pool, v_pool, page_table, ring, token_slot)
         norm_w, eps, src = (x.weight, x.eps, x.residual) if isinstance(x, NormedRows) else (None, 0.0, x)
         T, K = src.shape
         q = torch.empty((T, heads, head_dim), dtype=torch.bfloat16, device=src.device)
@@ -258,6 +260,24 @@ class Ops:
             _ptr(positions), _ptr(cos_table), _ptr(sin_table), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
             page_table.shape[1], ring, _ptr(token_slot), _stream()))
         return q
+
+    def _qkv_rope_store_tc(self, x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim, k_pool, v_pool,
+                           page_table, ring, token_slot) -> Optional[torch.Tensor]:
+        """The same for up to 64 tokens on the tcgen05 kernel, whose split-K clusters do bias, rotation and cache
+        write where they add their sums up. None when the shape is not taken."""
+        T, K = x.shape
+        if (T > 64 or 128 % head_dim or not self.use_tensor_cores or w_qkv.dtype != torch.bfloat16
+                or self._dtype_of(x) != torch.bfloat16 or not self.lib.sm_gemm_tc_supports(T, w_qkv.shape[0], K)):
+            return None
+        rows = self.materialize(x)
+        q = torch.empty((T, heads, head_dim), dtype=torch.bfloat16, device=rows.device)
+        taken = ctypes.c_int(0)
+        self._check(self.lib.sm_gemm_tc_qkv(
+            _ptr(rows), _ptr(w_qkv), T, K, _ptr(b_qkv), _dt(b_qkv) if b_qkv is not None else F32, heads, kv_heads,
+            head_dim, head_dim, _ptr(positions), _ptr(cos_table), _ptr(sin_table), _ptr(q), _ptr(k_pool), _ptr(v_pool),
+            _ptr(page_table), page_table.shape[1], ring, _ptr(token_slot), _ptr(self.error_flag), ctypes.byref(taken),
+            _stream()))
+        return q if taken.value else None
 
     def _tensor_core_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
         return (self.use_tensor_cores and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16

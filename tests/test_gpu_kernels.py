@@ -380,3 +380,55 @@ def test_fused_qkv_matches_the_separate_kernels(ops, heads, kv_heads, hd):
     assert float((pools[2].float() - pools[0].float()).abs().max()) <= 2e-2
     assert float((pools[3].float() - pools[1].float()).abs().max()) <= 2e-2
     assert int((pools[2] != 0).sum()) == int((pools[0] != 0).sum())   # the same cells were written
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (14, 2, 64), (8, 2, 128), (28, 4, 128)])
+@pytest.mark.parametrize("T,K", [(17, 96), (40, 896), (64, 3584)])
+def test_fused_qkv_on_the_tcgen05_kernel_matches_the_separate_kernels(ops, heads, kv_heads, hd, T, K):
+    """17 to 64 tokens: bias, rotation and the cache write happen where the split-K cluster of the tcgen05 kernel adds
+    its sums up (one split included). Unequal positions, scattered pages, row counts that are no multiple of 128."""
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    N = (heads + 2 * kv_heads) * hd
+    x, w, b = _rand((T, K), torch.bfloat16, 1), _rand((N, K), torch.bfloat16, 2, 0.05), _rand((N,), torch.bfloat16, 3)
+    g = torch.Generator().manual_seed(9)
+    positions = torch.randint(0, 4 * PAGE_SIZE, (T,), generator=g).to(torch.int32).cuda()
+    slots = torch.randperm(T, generator=g).to(torch.int32).cuda()
+    table = torch.randperm(T * 4, generator=g).to(torch.int32).view(T, 4).cuda()
+    half = hd // 2
+    ang = torch.arange(4 * PAGE_SIZE, dtype=torch.float64)[:, None] * torch.pow(
+        torch.tensor(10000.0, dtype=torch.float64), -torch.arange(half, dtype=torch.float64) * 2 / hd)
+    cos, sin = torch.cos(ang).float().cuda(), torch.sin(ang).float().cuda()
+    pools = [torch.zeros((T * 4, kv_heads, PAGE_SIZE, hd), dtype=torch.bfloat16, device="cuda") for _ in range(4)]
+    qkv = ops.gemm_simt(x, w, b, torch.empty((T, N), dtype=torch.float32, device="cuda"))
+    q_ref, _, _ = ops.rope_store(qkv, positions, cos, sin, heads, kv_heads, hd, hd, torch.bfloat16, False, pools[0], pools[1],
+                                 table, 0, slots, positions + 1)
+    q = ops.qkv_rope_store_fused(x, w, b, positions, cos, sin, heads, kv_heads, hd, hd, pools[2], pools[3], table, 0, slots)
+    ops.check_error_flag()
+    import ctypes
+    tile_n, splits = ctypes.c_int(), ctypes.c_int()
+    ops._check(ops.lib.sm_gemm_tc_plan(T, N, K, 0, ctypes.byref(tile_n), ctypes.byref(splits)))
+    if splits.value > 8:      # K split more ways than a cluster has CTAs (a few rows, a long K): left to the separate kernels
+        assert q is None and float(pools[2].abs().max()) == 0.0
+        return
+    assert q is not None, "the fused tcgen05 path did not take this shape"
+    tol = 1e-3 * math.sqrt(K) * 0.05 + 8e-3 * float(q_ref.float().abs().max())
+    assert float((q.float() - q_ref.float()).abs().max()) <= tol
+    assert float((pools[2].float() - pools[0].float()).abs().max()) <= tol
+    assert float((pools[3].float() - pools[1].float()).abs().max()) <= tol
+    assert int((pools[2] != 0).sum()) == int((pools[0] != 0).sum())   # the same cells were written
+    assert int((pools[3] != 0).sum()) == int((pools[1] != 0).sum())
+
+
+def test_fused_qkv_refuses_heads_that_straddle_tiles(ops):
+    """Head sizes that do not divide 128 are left to the separate kernels."""
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    heads, kv_heads, hd, T, K = 5, 5, 48, 20, 96
+    N = (heads + 2 * kv_heads) * hd
+    x, w = _rand((T, K), torch.bfloat16, 1), _rand((N, K), torch.bfloat16, 2, 0.05)
+    positions = torch.arange(T, dtype=torch.int32).cuda()
+    table = torch.arange(T, dtype=torch.int32).view(T, 1).cuda()
+    cos = torch.ones((PAGE_SIZE, hd // 2), device="cuda"); sin = torch.zeros_like(cos)
+    pool = torch.zeros((T, kv_heads, PAGE_SIZE, hd), dtype=torch.bfloat16, device="cuda")
+    assert ops.qkv_rope_store_fused(x, w, None, positions, cos, sin, heads, kv_heads, hd, hd, pool, pool.clone(), table, 0,
+                                    positions) is None
+    assert float(pool.abs().max()) == 0.0
