@@ -69,6 +69,8 @@ struct GemmParams {
     int final_epilogue;       // what the epilogue is once the splits are added up
     int cluster_reduce;       // small kernel: the CTAs along K are one cluster and add their sums up among themselves
     SkinnyRope rope;          // EPI_QKV_ROPE: where q goes and where the cache is (out is unused)
+    int halves;               // small kernel, gated product: a tile is 64 gate rows and their 64 up rows in ONE accumulator
+                              // (dual = 0); gate and up meet where the splits are added up
 };
 
 using namespace tc5;   // the PTX wrappers (tcgen05.cuh)
@@ -105,7 +107,7 @@ __device__ __forceinline__ StageBox stage_box(int lane, int a_bytes, const GemmP
         const int part = lane % kPerTile, atom = (lane / kPerTile) % kAtoms, tile = lane / (kPerTile * kAtoms);
         b.active = true;
         b.offset = lane * kBoxBytes;
-        b.row = (tile ? p.up_offset : 0) + part * kBoxRows;
+        b.row = p.halves ? (part ? p.up_offset : 0) : (tile ? p.up_offset : 0) + part * kBoxRows;
         b.k = atom * kBlockK;
     } else if (lane < w_boxes + x_parts * kAtoms) {
         const int idx = lane - w_boxes, atom = idx / x_parts, part = idx - atom * x_parts;
@@ -385,7 +387,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     int* failed = (int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int split = blockIdx.x, n0 = blockIdx.y * kTileM, t0 = blockIdx.z * p.tile_n;
+    const int split = blockIdx.x, n0 = blockIdx.y * (p.halves ? kTileM / 2 : kTileM), t0 = blockIdx.z * p.tile_n;
     pdl_launch_dependents();
     const int kb_total = (p.K + kStageK - 1) / kStageK;
     const int kb_begin = split * p.kblocks_per_split;
@@ -599,6 +601,41 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     *reinterpret_cast<uint2*>(dst) = pl;
                     *reinterpret_cast<uint2*>(dst + half) = ph;
                 }
+            } else if (p.halves) {
+                // the tile's rows 0-63 are gate rows n0.., rows 64-127 the up rows of the same features
+                const int pieces_h = p.tile_n * (kTileM / 8);
+                const int per_h = (pieces_h + p.splits - 1) / p.splits;
+                const int hi_h = min(pieces_h, (split + 1) * per_h);
+                const bool vec = (p.N & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
+                for (int c = split * per_h + (int)threadIdx.x - 64; c < hi_h; c += 128) {
+                    const int tcol = c / (kTileM / 8), f4 = c - tcol * (kTileM / 8);
+                    const int t = t0 + tcol, n = n0 + f4 * 4;
+                    if (t >= p.T || n >= p.N) continue;
+                    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+#pragma unroll 4
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        const float4 a = ld_cluster_f4(base + (uint32_t)(tcol * (kTileM / 4) + f4) * 16u, (uint32_t)sp);
+                        const float4 b = ld_cluster_f4(base + (uint32_t)(tcol * (kTileM / 4) + kTileM / 8 + f4) * 16u, (uint32_t)sp);
+                        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+                        u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+                    }
+                    const float v[4] = {gated(g.x, u.x), gated(g.y, u.y), gated(g.z, u.z), gated(g.w, u.w)};
+                    const size_t o = (size_t)t * p.N + n;
+                    if (vec && p.out_dt != F32) {
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi2 = __floats2bfloat162_rn(v[2], v[3]);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<uint32_t*>(&hi2);
+                        *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + o) = packed;
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (n + e >= p.N) break;
+                            if (p.out_dt == F32) ((float*)p.out)[o + e] = v[e];
+                            else ((__nv_bfloat16*)p.out)[o + e] = __float2bfloat16_rn(v[e]);
+                        }
+                    }
+                }
             } else {
                 // four features at a time where the output's rows allow it (then n + 3 < N whenever n < N)
                 const bool vec = (p.N & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
@@ -796,7 +833,39 @@ SmallLaunch small_launch(int tile_n, int splits, bool dual) {
 
 bool gemm_tc_supports(int T, int N, int K) { return T > 0 && N > 0 && K > 0 && K % 8 == 0; }
 
+namespace {
+
+// A gated product over up to 64 tokens as tiles of 64 gate rows + their 64 up rows in one accumulator: half the
+// shared memory of two accumulators, so two CTAs to an SM and twice the tiles. Gate and up meet where the
+// cluster adds its sums up, so the plan needs that path (one split included). Returns the CTAs along K.
+bool gated_halves_plan(int T, int N, int K, int* splits) {
+    if (T > 64) return false;
+    const int sms = device_sm_count();
+    const int tiles = (N + kTileM / 2 - 1) / (kTileM / 2);
+    const int t16 = ((T + 15) / 16) * 16;
+    const int kb = (K + kStageK - 1) / kStageK;
+    const SmallLaunch l = small_launch(t16, 2, false);
+    int per_sm = (int)((size_t)227 * 1024 / l.smem);
+    per_sm = per_sm > 2 ? 2 : (per_sm < 1 ? 1 : per_sm);
+    int sp = sms * per_sm / tiles;
+    if (sp > (kb + 1) / 2) sp = (kb + 1) / 2;
+    if (sp > 8) sp = 8;
+    if (sp < 1) sp = 1;
+    const int per = (kb + sp - 1) / sp;
+    sp = (kb + per - 1) / per;
+    if (tiles * sp * 2 < sms) return false;
+    if (sp > 1 && !small_launch(t16, sp, false).cluster) return false;
+    *splits = sp;
+    return true;
+}
+
+}  // namespace
+
 void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
+    if (dual && gated_halves_plan(T, N, K, splits)) {
+        *tile_n = ((T + 15) / 16) * 16;
+        return;
+    }
     const int sms = device_sm_count();
     const int tiles_m = (N + kTileM - 1) / kTileM;
     const int t16 = ((T + 15) / 16) * 16;
@@ -851,6 +920,7 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
 size_t gemm_tc_workspace_bytes(int T, int N, int K, bool dual) {
     int tn, sp;
     gemm_tc_plan(T, N, K, dual, &tn, &sp);
+    if (dual && gated_halves_plan(T, N, K, &sp)) return 0;
     if (sp > 1 && T <= 64 && small_launch(tn, sp, dual).cluster) return 0;   // the splits are added up inside a cluster
     return sp > 1 ? (size_t)sp * (dual ? 2 : 1) * T * N * sizeof(float) : 0;
 }
@@ -871,10 +941,14 @@ void gemm_tc_impl(const void* x, const void* w, const void* bias, DType bias_dt,
     if (!gemm_tc_supports(T, N, K))
         throw std::invalid_argument("gemm_tc: K = " + std::to_string(K) + " must be a positive multiple of 8 (TMA rows start on 16 bytes)");
     if (((uintptr_t)x | (uintptr_t)w) & 15) throw std::invalid_argument("gemm_tc: operands must be 16-byte aligned");
-    const bool dual = mode == EPI_SWIGLU;
+    const bool gated_mode = mode == EPI_SWIGLU;
     GemmParams p{};
     p.T = T; p.N = N; p.K = K;
-    gemm_tc_plan(T, N, K, dual, &p.tile_n, &p.splits);
+    gemm_tc_plan(T, N, K, gated_mode, &p.tile_n, &p.splits);
+    int halves_splits = 0;
+    const bool halves = gated_mode && gated_halves_plan(T, N, K, &halves_splits);
+    p.halves = halves ? 1 : 0;
+    const bool dual = gated_mode && !halves;   // two accumulators
     const int kb = (K + kStageK - 1) / kStageK;
     p.kblocks_per_split = (kb + p.splits - 1) / p.splits;
     p.dual = dual ? 1 : 0;
@@ -883,7 +957,7 @@ void gemm_tc_impl(const void* x, const void* w, const void* bias, DType bias_dt,
     p.out = out; p.out_dt = out_dt;
     p.workspace = workspace;
     p.error = error;
-    p.tiles_m = (N + kTileM - 1) / kTileM;
+    p.tiles_m = halves ? (N + kTileM / 2 - 1) / (kTileM / 2) : (N + kTileM - 1) / kTileM;
     p.tiles_t = (T + p.tile_n - 1) / p.tile_n;
     p.units = p.tiles_m * p.tiles_t * p.splits;
     const int final_mode = rope ? (int)EPI_QKV_ROPE : mode;
@@ -906,9 +980,9 @@ void gemm_tc_impl(const void* x, const void* w, const void* bias, DType bias_dt,
         p.stages = l.stages;
         p.final_epilogue = final_mode;
         // (the fused q/k/v epilogue lives in the code that adds the splits up: a single split goes the same way)
-        p.cluster_reduce = l.cluster || rope ? 1 : 0;
+        p.cluster_reduce = l.cluster || rope || halves ? 1 : 0;
         if (p.tiles_m > 65535 || p.tiles_t > 65535) throw std::invalid_argument("gemm_tc: more than 65535 tiles along a side");
-        const CUtensorMap mw = make_map(w, dual ? up_offset + N : N, K, kBoxRows);
+        const CUtensorMap mw = make_map(w, gated_mode ? up_offset + N : N, K, kBoxRows);
         const CUtensorMap mx = make_map(x, T, K, p.tile_n < kBoxRows ? p.tile_n : kBoxRows);
         dim3 grid3(p.splits, p.tiles_m, p.tiles_t);
         launch_kernel("gemm_tc", gemm_tc_small_kernel, grid3, dim3(kThreads), l.smem, stream, l.cluster ? p.splits : 1,
