@@ -75,6 +75,7 @@ class Ops:
         self.lib.sm_gemm_tc_workspace_bytes.restype = ctypes.c_longlong
         self.lib.sm_launch_count.restype = ctypes.c_longlong
         self.use_tensor_cores = True  # False routes bfloat16 products to the CUDA-core kernel
+        self.skinny_most_rounds = 2   # plain rows over a longer K go to the tcgen05 kernel (see _skinny_ok)
         self.use_fast_attention = True  # False routes bfloat16 attention to the plain kernel
         self.use_tcgen05_attention = True  # False routes prefill attention to the mma.sync kernel
         self.use_skinny = True  # False routes products over a handful of tokens to the general kernels
@@ -219,6 +220,13 @@ class Ops:
             if x.rows is not None or x.out_dtype != torch.bfloat16 or x.done is not None:
                 return False
         elif x.dtype != torch.bfloat16:
+            return False
+        elif (self.use_tensor_cores and self.lib.sm_gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1])
+              and self.lib.sm_gemm_skinny_rounds(x.shape[0], w.shape[0] // 2 if gated else w.shape[0], x.shape[1],
+                                                 int(gated)) >= self.skinny_most_rounds + 1):
+            # rows that need no norm and a K so long that a CTA takes its weights in three rounds or more: the tcgen05
+            # kernel's clusters stream them better (3,584 x 18,944 at 8 tokens: 26 against 39 us; at two rounds the
+            # weight-streaming kernel still wins, 1,536 x 8,960: 8 against 11 us)
             return False
         if w.shape[0] > 32768 and self.use_tensor_cores and self.lib.sm_gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1]):
             return False   # the output head: thousands of row tiles, where the tcgen05 kernel streams better

@@ -323,14 +323,15 @@ def test_gemm_skinny_store_and_accumulate(ops, T, N, K):
 
 
 def test_which_kernel_takes_a_product_over_few_tokens(ops):
-    """Up to 8 tokens: the weight-streaming kernel. 9 to 16: only if its CTAs hold their share of K at once.
-    More: the tcgen05 kernel. The output head (thousands of row tiles): the tcgen05 kernel."""
+    """Up to 8 tokens: the weight-streaming kernel, unless plain rows would take three rounds or more. 9 to 16: only
+    if its CTAs hold their share of K at once. More: the tcgen05 kernel. The output head (thousands of row tiles): the tcgen05 kernel."""
     def x(T, K):
         return torch.zeros((T, K), dtype=torch.bfloat16, device="cuda")
 
     def w(N, K):
         return torch.empty((N, K), dtype=torch.bfloat16, device="cuda")
-    assert ops._skinny_ok(x(8, 896), w(896, 896)) and ops._skinny_ok(x(8, 18944), w(3584, 18944))
+    assert ops._skinny_ok(x(8, 896), w(896, 896)) and ops._skinny_ok(x(8, 8960), w(1536, 8960))   # one round, two rounds
+    assert not ops._skinny_ok(x(8, 18944), w(3584, 18944))                # four rounds of plain rows: the tcgen05 kernel
     assert ops._skinny_ok(x(16, 896), w(1152, 896))                       # one round at 16 tokens
     assert not ops._skinny_ok(x(16, 896), w(2 * 4864, 896), gated=True)   # two rounds: 32 weight rows beside 16 tokens
     assert not ops._skinny_ok(x(16, 3584), w(4608, 3584))
