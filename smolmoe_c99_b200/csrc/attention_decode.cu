@@ -428,9 +428,6 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         const int lo = cta_lo + (warp + kStreamWarps * i) * KT;
         return pos >= lo && pos < lo + KT;
     };
-    // Asks for this warp's tile number i into slot s. Row by row: before the wait on the kernel before this one
-    // the newest position's row is left out; rows behind the share's end are not copied, and the value rows among
-    // them are zeroed, since they are multiplied (by zero weights).
     // BOX: the page of this warp's tile number i (looked up ahead of the request, so that the trip to the table
     // is not waited for when the request is made)
     auto page_of = [&](int i) -> int {
@@ -439,6 +436,9 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         return a.page_table[(size_t)slot * a.table_stride + idx / kPageSize];
     };
     int next_page = 0;
+    // Asks for this warp's tile number i into slot s. Row by row: before the wait on the kernel before this one
+    // the newest position's row is left out; rows behind the share's end are not copied, and the value rows among
+    // them are zeroed, since they are multiplied (by zero weights).
     auto request = [&](int i, int s, bool before_wait) {
         const int lo = cta_lo + (warp + kStreamWarps * i) * KT;
         unsigned char* kt = ring + (size_t)s * kTileBytes;
