@@ -1,8 +1,8 @@
 // Attention of one query against its visible keys, one warp per (token, head), for any
 // head size that is a multiple of 8 up to 256 and any number of heads and groups.
 //
-// It is the attention of the true 32-bit path (prefill and decode alike) and the fallback
-// of the bfloat16 path. Keys are visited in ascending order in groups of 32 counted from
+// It is the attention of the true 32-bit path (whole prompts, prompts in portions, single
+// tokens and any mix of them in one step) and the fallback of the bfloat16 path. Keys are visited in ascending order in groups of 32 counted from
 // the first visible key, with a running maximum and sum (the reference's two-pass softmax,
 // src/kernels.c:1138-1176, gives the same value up to rounding). What a query's result
 // depends on: the query, its visible keys and values, the scale and the window -- not the
@@ -40,7 +40,9 @@ template <> struct Load8<__nv_bfloat16> {
     }
 };
 
-template <typename T, bool PAGED>
+// SRC says where keys and values lie: 0 packed beside the queries (the step's own tokens), 1 in the cache, 2 both
+// (positions before the first one the sequence brings in this step in the cache, the step's own packed).
+template <typename T, int SRC>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(AttentionArgs a) {
     __shared__ __align__(16) float q_shared[kWarpsPerBlock][kMaxHeadDim];
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -57,11 +59,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(At
     for (int d = lane; d < hd; d += 32) qs[d] = to_float(q[d]);
     __syncwarp();
 
-    const T* kbase = (const T*)(PAGED ? a.k_pool : a.k_packed);
-    const T* vbase = (const T*)(PAGED ? a.v_pool : a.v_packed);
+    constexpr unsigned long long kPackedBit = 1ull << 63;   // marks a row offset into the packed tensors
     PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
-    int slot = PAGED ? a.token_slot[t] : 0;
-    int seq_start = PAGED ? 0 : a.token_seq_start[t];
+    int slot = SRC != 0 ? a.token_slot[t] : 0;
+    int seq_first = SRC != 1 ? a.token_seq_start[t] : 0;   // packed index of the sequence's first token of this step
+    int pos0 = SRC != 1 ? pos - (t - seq_first) : 0;        // ... and its position
 
     float m = -CUDART_INF_F, l = 0.f;
     float acc[kMaxHeadDim / 32];
@@ -74,9 +76,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(At
         unsigned long long row = 0;
         float s = -CUDART_INF_F;
         if (valid) {
-            row = PAGED ? (unsigned long long)paged.row_offset(slot, p, kvh)
-                        : ((unsigned long long)(seq_start + p) * a.kv_heads + kvh) * hd;
-            const T* kr = kbase + row;
+            bool packed = SRC == 0 || (SRC == 2 && p >= pos0);
+            row = packed ? (((unsigned long long)(seq_first + p - pos0) * a.kv_heads + kvh) * hd) | kPackedBit
+                         : (unsigned long long)paged.row_offset(slot, p, kvh);
+            const T* kr = (const T*)(packed ? a.k_packed : a.k_pool) + (row & ~kPackedBit);
             float dot = 0.f;
             for (int d = 0; d < hd; d += 8) {
                 float kv[8];
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(At
         for (int j = 0; j < n_valid; ++j) {
             float pj = __shfl_sync(0xffffffffu, e, j);
             unsigned long long rj = __shfl_sync(0xffffffffu, row, j);
-            const T* vr = vbase + rj;
+            const T* vr = (const T*)((rj & kPackedBit) ? a.v_packed : a.v_pool) + (rj & ~kPackedBit);
 #pragma unroll
             for (int i = 0; i < kMaxHeadDim / 32; ++i) {
                 int d = lane + 32 * i;
@@ -121,19 +124,23 @@ void attention_plain(const AttentionArgs& a, cudaStream_t stream) {
                                     " must be a multiple of 8 between 8 and 256");
     if (a.heads % a.kv_heads)
         throw std::invalid_argument("attention_plain: kv_heads must divide heads");
-    bool paged = a.k_packed == nullptr;
-    if (paged && (a.k_pool == nullptr || a.page_table == nullptr))
+    int src = a.k_packed == nullptr ? 1 : (a.k_pool == nullptr ? 0 : 2);
+    if (src != 0 && (a.k_pool == nullptr || a.page_table == nullptr || a.token_slot == nullptr))
         throw std::invalid_argument("attention_plain: neither packed keys nor a cache were given");
+    if (src != 1 && (a.v_packed == nullptr || a.token_seq_start == nullptr))
+        throw std::invalid_argument("attention_plain: packed keys need packed values and each token's sequence start");
     note_launch();
     long long items = (long long)a.T * a.heads;
     unsigned blocks = (unsigned)((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
     int threads = kWarpsPerBlock * 32;
     if (a.dt == F32) {
-        if (paged) attention_plain_kernel<float, true><<<blocks, threads, 0, stream>>>(a);
-        else attention_plain_kernel<float, false><<<blocks, threads, 0, stream>>>(a);
+        if (src == 0) attention_plain_kernel<float, 0><<<blocks, threads, 0, stream>>>(a);
+        else if (src == 1) attention_plain_kernel<float, 1><<<blocks, threads, 0, stream>>>(a);
+        else attention_plain_kernel<float, 2><<<blocks, threads, 0, stream>>>(a);
     } else {
-        if (paged) attention_plain_kernel<__nv_bfloat16, true><<<blocks, threads, 0, stream>>>(a);
-        else attention_plain_kernel<__nv_bfloat16, false><<<blocks, threads, 0, stream>>>(a);
+        if (src == 0) attention_plain_kernel<__nv_bfloat16, 0><<<blocks, threads, 0, stream>>>(a);
+        else if (src == 1) attention_plain_kernel<__nv_bfloat16, 1><<<blocks, threads, 0, stream>>>(a);
+        else attention_plain_kernel<__nv_bfloat16, 2><<<blocks, threads, 0, stream>>>(a);
     }
 }
 

@@ -3,6 +3,12 @@
 // score matrix is stored (the reference scans [start, pos] per query and head:
 // src/model.c:459-491, src/kernels.c:1156-1176).
 //
+// A second form of the same kernel serves sequences that go on from the cache with any number of
+// tokens (a prompt in portions, a later message of a conversation, single tokens mixed with prompts:
+// the reference's model_forward(tokens, n, pos0), src/model.c:664-690): keys and values of positions
+// before the first one a sequence brings in this step are read from the paged cache, the step's own
+// from the packed tensors.
+//
 // One CTA per (tile of 64 queries of one sequence, head); 4 warps of 16 queries each. Keys
 // and values come through shared memory in tiles of 64 positions; both products run on
 // the tensor cores (mma.sync m16n8k16, bfloat16 in, float accumulate); maximum, sum and
@@ -26,9 +32,15 @@ struct PrefillArgs {
     const __nv_bfloat16* k;   // [T, kv_heads, HD]
     const __nv_bfloat16* v;
     __nv_bfloat16* out;       // [T, heads, HD]
-    const int32_t* tiles;     // [n_tiles, 3]: packed index of the sequence's first token, its length, first query
+    const int32_t* tiles;     // [n_tiles, 3]: packed index of the sequence's first token, its length, first query;
+                              // going on from the cache [n_tiles, 5]: ... its tokens in this step, first query among
+                              // them, the position of its first token of this step, its slot
     int heads, kv_heads, window;
     float scale_log2;         // scale * log2(e)
+    const __nv_bfloat16* k_pool;   // one layer's page pools (null: whole prompts)
+    const __nv_bfloat16* v_pool;
+    const int32_t* page_table;
+    int table_stride, ring;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -51,7 +63,7 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes));
 }
 
-template <int HD>
+template <int HD, bool CACHED>
 __global__ void __launch_bounds__(kWarps * 32) prefill_attention_kernel(PrefillArgs a) {
     constexpr int LD = HD + 8;            // padded row: conflict-free fragment loads
     constexpr int KT = HD / 16;           // k-steps of Q K^T
@@ -59,8 +71,13 @@ __global__ void __launch_bounds__(kWarps * 32) prefill_attention_kernel(PrefillA
     __shared__ __align__(16) __nv_bfloat16 ks[kBN][LD];
     __shared__ __align__(16) __nv_bfloat16 vs[kBN][LD];
 
+    // Queries are counted among the sequence's tokens of this step (0 .. seq_len-1), keys by their absolute
+    // position; the two differ by pos0, the position of the step's first token of the sequence.
     const int tile = blockIdx.x, h = blockIdx.y;
-    const int seq_start = a.tiles[3 * tile], seq_len = a.tiles[3 * tile + 1], q0 = a.tiles[3 * tile + 2];
+    constexpr int TS = CACHED ? 5 : 3;
+    const int seq_start = a.tiles[TS * tile], seq_len = a.tiles[TS * tile + 1], q0 = a.tiles[TS * tile + 2];
+    const int pos0 = CACHED ? a.tiles[TS * tile + 3] : 0, slot = CACHED ? a.tiles[TS * tile + 4] : 0;
+    const int seq_end = pos0 + seq_len;   // the sequence's length after this step
     const int kvh = h / (a.heads / a.kv_heads);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int quad = lane >> 2, tq = lane & 3;
@@ -85,8 +102,9 @@ __global__ void __launch_bounds__(kWarps * 32) prefill_attention_kernel(PrefillA
     for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
 
-    const int q_last = min(q0 + kBM, seq_len) - 1;
-    const int first_key = a.window > 0 ? max(0, q0 - a.window + 1) : 0;
+    const int q_last = pos0 + min(q0 + kBM, seq_len) - 1;
+    const int first_key = a.window > 0 ? max(0, pos0 + q0 - a.window + 1) : 0;
+    PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, HD};
     const __nv_bfloat16* kb = a.k + ((size_t)seq_start * a.kv_heads + kvh) * HD;
     const __nv_bfloat16* vb = a.v + ((size_t)seq_start * a.kv_heads + kvh) * HD;
     const size_t kv_stride = (size_t)a.kv_heads * HD;
@@ -95,8 +113,16 @@ __global__ void __launch_bounds__(kWarps * 32) prefill_attention_kernel(PrefillA
         __syncthreads();   // the previous tile has been read
         for (int c = threadIdx.x; c < kBN * (HD / 8); c += kWarps * 32) {
             int row = c / (HD / 8), col = (c % (HD / 8)) * 8;
-            bool in = n0 + row < seq_len;
-            size_t g = in ? (size_t)(n0 + row) * kv_stride + col : 0;
+            const int p = n0 + row;
+            bool in = p < seq_end;
+            if (CACHED && p < pos0) {
+                in = in && p >= first_key;   // older rows of a ring may be gone; they are masked below anyway
+                size_t g = in ? paged.row_offset(slot, p, kvh) + col : 0;
+                cp_async16(&ks[row][col], a.k_pool + g, in);
+                cp_async16(&vs[row][col], a.v_pool + g, in);
+                continue;
+            }
+            size_t g = in ? (size_t)(p - pos0) * kv_stride + col : 0;
             cp_async16(&ks[row][col], kb + g, in);
             cp_async16(&vs[row][col], vb + g, in);
         }
@@ -123,8 +149,8 @@ __global__ void __launch_bounds__(kWarps * 32) prefill_attention_kernel(PrefillA
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 int key = n0 + j * 8 + tq * 2 + (e & 1);
-                int qp = (e & 2) ? r1 : r0;
-                bool vis = key <= qp && key < seq_len && (a.window <= 0 || key > qp - a.window);
+                int qp = pos0 + ((e & 2) ? r1 : r0);
+                bool vis = key <= qp && key < seq_end && (a.window <= 0 || key > qp - a.window);
                 float x = vis ? s[j][e] * a.scale_log2 : -CUDART_INF_F;
                 s[j][e] = x;
                 if (e & 2) mx1 = fmaxf(mx1, x); else mx0 = fmaxf(mx0, x);
@@ -186,24 +212,11 @@ __global__ void __launch_bounds__(kWarps * 32) prefill_attention_kernel(PrefillA
 template <int HD>
 void launch(const PrefillArgs& a, int n_tiles, cudaStream_t stream) {
     dim3 grid(n_tiles, a.heads);
-    prefill_attention_kernel<HD><<<grid, kWarps * 32, 0, stream>>>(a);
+    if (a.k_pool != nullptr) prefill_attention_kernel<HD, true><<<grid, kWarps * 32, 0, stream>>>(a);
+    else prefill_attention_kernel<HD, false><<<grid, kWarps * 32, 0, stream>>>(a);
 }
 
-}  // namespace
-
-bool attention_prefill_supports(int head_dim) { return head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128; }
-
-void attention_prefill(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles,
-                       int heads, int kv_heads, int head_dim, float scale, int window, cudaStream_t stream) {
-    if (n_tiles <= 0) return;
-    if (!attention_prefill_supports(head_dim))
-        throw std::invalid_argument("attention_prefill: head_dim " + std::to_string(head_dim) +
-                                    " is not a multiple of 16 between 16 and 128 (the plain kernel takes it)");
-    if (heads % kv_heads) throw std::invalid_argument("attention_prefill: kv_heads must divide heads");
-    if (heads > 65535) throw std::invalid_argument("attention_prefill: more than 65535 heads");
-    note_launch();
-    PrefillArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)out, tiles,
-                  heads, kv_heads, window, scale * 1.4426950408889634f};
+void dispatch(const PrefillArgs& a, int n_tiles, int head_dim, cudaStream_t stream) {
     switch (head_dim) {
         case 16: launch<16>(a, n_tiles, stream); break;
         case 32: launch<32>(a, n_tiles, stream); break;
@@ -214,6 +227,42 @@ void attention_prefill(const void* q, const void* k, const void* v, void* out, c
         case 112: launch<112>(a, n_tiles, stream); break;
         default: launch<128>(a, n_tiles, stream); break;
     }
+}
+
+void check(const char* what, int heads, int kv_heads, int head_dim) {
+    if (!attention_prefill_supports(head_dim))
+        throw std::invalid_argument(std::string(what) + ": head_dim " + std::to_string(head_dim) +
+                                    " is not a multiple of 16 between 16 and 128 (the plain kernel takes it)");
+    if (heads % kv_heads) throw std::invalid_argument(std::string(what) + ": kv_heads must divide heads");
+    if (heads > 65535) throw std::invalid_argument(std::string(what) + ": more than 65535 heads");
+}
+
+}  // namespace
+
+bool attention_prefill_supports(int head_dim) { return head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128; }
+
+void attention_prefill(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles,
+                       int heads, int kv_heads, int head_dim, float scale, int window, cudaStream_t stream) {
+    if (n_tiles <= 0) return;
+    check("attention_prefill", heads, kv_heads, head_dim);
+    note_launch();
+    PrefillArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)out, tiles,
+                  heads, kv_heads, window, scale * 1.4426950408889634f, nullptr, nullptr, nullptr, 0, 0};
+    dispatch(a, n_tiles, head_dim, stream);
+}
+
+void attention_extend(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles,
+                      int heads, int kv_heads, int head_dim, float scale, int window, const void* k_pool,
+                      const void* v_pool, const int32_t* page_table, int table_stride, int ring, cudaStream_t stream) {
+    if (n_tiles <= 0) return;
+    check("attention_extend", heads, kv_heads, head_dim);
+    if (k_pool == nullptr || v_pool == nullptr || page_table == nullptr)
+        throw std::invalid_argument("attention_extend: the cache's pools and page table are needed");
+    note_launch();
+    PrefillArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)out, tiles,
+                  heads, kv_heads, window, scale * 1.4426950408889634f, (const __nv_bfloat16*)k_pool,
+                  (const __nv_bfloat16*)v_pool, page_table, table_stride, ring};
+    dispatch(a, n_tiles, head_dim, stream);
 }
 
 }  // namespace sm

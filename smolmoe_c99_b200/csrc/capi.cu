@@ -94,6 +94,15 @@ SM_API int sm_rope_store(const float* qkv, int T, int heads, int kv_heads, int h
     });
 }
 
+SM_API int sm_kv_store(const void* k_packed, const void* v_packed, int dt, int T, int kv_heads, int head_dim,
+                       void* k_pool, void* v_pool, const int32_t* positions, const int32_t* page_table,
+                       int table_stride, int ring, const int32_t* token_slot, const int32_t* token_end, void* stream) {
+    return guarded([&] {
+        sm::kv_store(k_packed, v_packed, (sm::DType)dt, T, kv_heads, head_dim, k_pool, v_pool, positions, page_table,
+                     table_stride, ring, token_slot, token_end, (cudaStream_t)stream);
+    });
+}
+
 SM_API int sm_gemm_simt(const void* x, int x_dt, const void* w, int w_dt, const void* bias, int bias_dt, void* out,
                         int out_dt, int T, int N, int K, int accumulate, void* stream) {
     return guarded([&] {
@@ -152,6 +161,16 @@ SM_API int sm_attention_prefill(const void* q, const void* k, const void* v, voi
                                 void* stream) {
     return guarded([&] {
         sm::attention_prefill(q, k, v, out, tiles, n_tiles, heads, kv_heads, head_dim, scale, window, (cudaStream_t)stream);
+    });
+}
+
+SM_API int sm_attention_extend(const void* q, const void* k, const void* v, void* out, const int32_t* tiles,
+                               int n_tiles, int heads, int kv_heads, int head_dim, float scale, int window,
+                               const void* k_pool, const void* v_pool, const int32_t* page_table, int table_stride,
+                               int ring, void* stream) {
+    return guarded([&] {
+        sm::attention_extend(q, k, v, out, tiles, n_tiles, heads, kv_heads, head_dim, scale, window, k_pool, v_pool,
+                             page_table, table_stride, ring, (cudaStream_t)stream);
     });
 }
 

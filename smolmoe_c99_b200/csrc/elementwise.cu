@@ -298,6 +298,40 @@ __global__ void rope_store_vec_kernel(RopeStoreArgs a, long long total) {
     }
 }
 
+// Copies this step's packed keys and values into the cache: one thread per 16 bytes of a (token, kv head) row.
+__global__ void kv_store_kernel(const uint4* __restrict__ k_packed, const uint4* __restrict__ v_packed, uint4* k_pool,
+                                uint4* v_pool, int kv_heads, int chunks, const int32_t* positions,
+                                const int32_t* page_table, int table_stride, int ring, const int32_t* token_slot,
+                                const int32_t* token_end, long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int c = (int)(idx % chunks);
+    const int kvh = (int)((idx / chunks) % kv_heads);
+    const int t = (int)(idx / ((long long)chunks * kv_heads));
+    const int pos = positions[t];
+    if (ring > 0 && pos < token_end[t] - ring) return;   // a later token of this step takes the same place
+    PagedKV paged{page_table, table_stride, ring, kv_heads, chunks};   // offsets counted in 16-byte units
+    const size_t dst = paged.row_offset(token_slot[t], pos, kvh) + c;
+    const size_t src = ((size_t)t * kv_heads + kvh) * chunks + c;
+    k_pool[dst] = k_packed[src];
+    v_pool[dst] = v_packed[src];
+}
+
+void kv_store(const void* k_packed, const void* v_packed, DType dt, int T, int kv_heads, int head_dim, void* k_pool,
+              void* v_pool, const int32_t* positions, const int32_t* page_table, int table_stride, int ring,
+              const int32_t* token_slot, const int32_t* token_end, cudaStream_t stream) {
+    if (T <= 0) return;
+    const int elem = dt == F32 ? 4 : 2;
+    if (head_dim <= 0 || (head_dim * elem) % 16)
+        throw std::invalid_argument("kv_store: a row of head_dim " + std::to_string(head_dim) + " is no multiple of 16 bytes");
+    note_launch();
+    const int chunks = head_dim * elem / 16;
+    const long long total = (long long)T * kv_heads * chunks;
+    kv_store_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+        (const uint4*)k_packed, (const uint4*)v_packed, (uint4*)k_pool, (uint4*)v_pool, kv_heads, chunks, positions,
+        page_table, table_stride, ring, token_slot, token_end, total);
+}
+
 void rope_store(const RopeStoreArgs& a, cudaStream_t stream) {
     if (a.T <= 0) return;
     if (a.rotary_dim == a.head_dim && a.head_dim % 8 == 0 && a.head_dim > 0) {

@@ -62,6 +62,13 @@ struct RopeStoreArgs {
 // permutation undone), writes q, and writes k and v to the packed buffers and the cache.
 void rope_store(const RopeStoreArgs& a, cudaStream_t stream);
 
+// Writes packed keys and values [T, kv_heads, head_dim] (already rotated) to the cache, for steps whose attention
+// must still read what the new rows replace in a windowed group's ring. A token whose place a later token of the
+// same step takes (position < token_end - ring) is not stored.
+void kv_store(const void* k_packed, const void* v_packed, DType dt, int T, int kv_heads, int head_dim, void* k_pool,
+              void* v_pool, const int32_t* positions, const int32_t* page_table, int table_stride, int ring,
+              const int32_t* token_slot, const int32_t* token_end, cudaStream_t stream);
+
 // ---- gemm_simt.cu ---------------------------------------------------------------------
 // out[t, n] (+)= sum_k x[t, k] * w[n, k] + bias[n]; float FMA in ascending k for every
 // element, whatever T is. x: F32 or BF16; w, bias: F32 or BF16; out: F32 or BF16.
@@ -123,11 +130,12 @@ struct AttentionArgs {
     float scale;
     int window;                 // 0: every key up to the query's position
     const int32_t* positions;   // [T]
-    // keys and values either packed for this step's own tokens ...
+    // keys and values packed for this step's own tokens ...
     const void* k_packed;       // [T, kv_heads, head_dim] or null
     const void* v_packed;
-    const int32_t* token_seq_start;  // [T] packed index of position 0 of the token's sequence
-    // ... or in the cache
+    const int32_t* token_seq_start;  // [T] packed index of the first token the token's sequence brings in this step
+    // ... and/or in the cache. With both, a key at a position before the first one its sequence brings in this
+    // step is read from the cache and every later one from the packed tensors.
     const void* k_pool;
     const void* v_pool;
     const int32_t* page_table;
@@ -146,6 +154,14 @@ void attention_plain(const AttentionArgs& a, cudaStream_t stream);
 bool attention_prefill_supports(int head_dim);
 void attention_prefill(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles,
                        int heads, int kv_heads, int head_dim, float scale, int window, cudaStream_t stream);
+
+// The same for sequences that go on from the cache by any number of tokens: `tiles` is [n_tiles, 5] = (packed index
+// of the sequence's first token of this step, its tokens in this step, first query of the tile among them, the
+// position of its first token of this step, its slot). Keys and values at earlier positions come from the page
+// pools, the step's own from k and v; the cache need not hold the step's own tokens yet.
+void attention_extend(const void* q, const void* k, const void* v, void* out, const int32_t* tiles, int n_tiles,
+                      int heads, int kv_heads, int head_dim, float scale, int window, const void* k_pool,
+                      const void* v_pool, const int32_t* page_table, int table_stride, int ring, cudaStream_t stream);
 
 // ---- attention_prefill_tc.cu ----------------------------------------------------------
 // The same as attention_prefill on the tcgen05 tensor cores (TMA operands, S and PV in tensor

@@ -1,8 +1,12 @@
 """One step's work as the kernels see it: the tokens of all sequences packed one after
 another, with each token's position, slot and sequence.
 
-The requests of a step either all start at their first token (``prefill``: whole prompts of
-unequal lengths) or all go on by one token (``decode``)."""
+Every sequence brings ``n_i >= 1`` tokens that start at its current length (the reference's
+``model_forward(tokens, n, pos0)``, src/model.c:664-690, for many sequences at once). Two
+shapes of a step have kernels of their own and are told apart by ``mode``: ``prefill`` (every
+sequence starts at its first token: whole prompts of unequal lengths) and ``decode`` (every
+sequence goes on by one token). Everything else is ``extend``: prompts in portions, a later
+message onto a live sequence, new sequences joining ones that decode."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -17,7 +21,7 @@ QUERY_TILE = 64  # queries per CTA of the prefill attention kernel
 
 @dataclass
 class StepBatch:
-    mode: str                       # "prefill" or "decode"
+    mode: str                       # "prefill", "decode" or "extend"
     n_seqs: int
     n_tokens: int
     slots: List[int]                # per sequence
@@ -32,6 +36,9 @@ class StepBatch:
     slot_ids: torch.Tensor          # int32 [B]
     seq_ends: torch.Tensor          # int32 [B] lengths after this step
     prefill_tiles: Optional[torch.Tensor] = None  # int32 [tiles, 3]: sequence's first packed index, length, first query
+    extend_tiles: Optional[torch.Tensor] = None   # int32 [tiles, 5]: first packed index, tokens in this step, first query
+                                                  # among them, position of the step's first token, slot
+    seq_starts: Optional[List[int]] = None        # per sequence: its length before this step
     wants_every_row: bool = False   # logits are asked for every token of the step, in order
 
 
@@ -43,12 +50,14 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
     lens = [len(t) for t in token_lists]
     if any(n == 0 for n in lens):
         raise ValueError("every sequence of a step brings at least one token")
+    if any(s < 0 for s in starts) or len(starts) != len(slots) or len(lens) != len(slots):
+        raise ValueError("every sequence of a step needs a slot, a start that is not negative and its tokens")
     if all(s == 0 for s in starts):
         mode = "prefill"
-    elif all(n == 1 for n in lens):
+    elif all(n == 1 for n in lens) and all(s > 0 for s in starts):
         mode = "decode"
     else:
-        raise ValueError("the sequences of a step either all start at their first token or all go on by one token")
+        mode = "extend"
     # the step's numbers, one row per quantity, built with tensor operations (a prompt of thousands of tokens
     # would spend a millisecond in Python loops otherwise)
     n_seqs = len(slots)
@@ -58,8 +67,13 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
     n_tokens = cu[-1]
     # everything the device needs of this step goes up in ONE copy: five rows of n_tokens numbers, then the
     # prefill tiles, the slots, the sequences' ends and the sequences' first packed indices
-    tile_rows = [[cu[i], n, q0] for i, n in enumerate(lens) for q0 in range(0, n, QUERY_TILE)] if mode == "prefill" else []
-    extra = 3 * len(tile_rows) + 2 * n_seqs + (n_seqs + 1)
+    tile_rows: List[List[int]] = []
+    if mode == "prefill":
+        tile_rows = [[cu[i], n, q0] for i, n in enumerate(lens) for q0 in range(0, n, QUERY_TILE)]
+    elif mode == "extend":
+        tile_rows = [[cu[i], n, q0, starts[i], slots[i]] for i, n in enumerate(lens) for q0 in range(0, n, QUERY_TILE)]
+    tile_width = 3 if mode == "prefill" else 5
+    extra = tile_width * len(tile_rows) + 2 * n_seqs + (n_seqs + 1)
     # (pinned memory on a GPU box: the copy below is then asynchronous and the allocator keeps the buffer until it is done)
     flat_host = torch.empty(5 * n_tokens + extra, dtype=torch.int32, pin_memory=device.type == "cuda")
     host = flat_host[:5 * n_tokens].view(5, n_tokens)
@@ -87,9 +101,9 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
     dev = flat_dev[:5 * n_tokens].view(5, n_tokens)
     at = 5 * n_tokens
     tiles = None
-    if mode == "prefill":
-        tiles = flat_dev[at:at + 3 * len(tile_rows)].view(len(tile_rows), 3)
-        at += 3 * len(tile_rows)
+    if tile_rows:
+        tiles = flat_dev[at:at + tile_width * len(tile_rows)].view(len(tile_rows), tile_width)
+        at += tile_width * len(tile_rows)
     per_seq = flat_dev[at:at + 2 * n_seqs].view(2, n_seqs)
     cu_dev = flat_dev[at + 2 * n_seqs:at + 3 * n_seqs + 1]
     return StepBatch(
@@ -97,4 +111,5 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
         max_seq_len=max(s + n for s, n in zip(starts, lens)),
         tokens=dev[0], positions=dev[1], token_slot=dev[2], token_end=dev[3], token_seq_start=dev[4],
         cu_seqlens=cu_dev, slot_ids=per_seq[0], seq_ends=per_seq[1],
-        prefill_tiles=tiles)
+        prefill_tiles=tiles if mode == "prefill" else None, extend_tiles=tiles if mode == "extend" else None,
+        seq_starts=list(starts))

@@ -1,11 +1,14 @@
 """The engine: a model on one GPU with its cache, and the one step function everything
 above it uses (generation, trace replay, benchmarks).
 
-``step`` takes a batch of sequences that either all start (whole prompts of unequal
-lengths, one step) or all go on by one token; it runs only the tokens it is given, as one
-batch, from the cache that earlier steps left, and returns the logits at the wanted places.
-The reference's counterpart is ``model_forward(tokens, n, pos0, mode)`` for its single
-sequence (src/model.h:79-97, src/model.c:664-724).
+``step`` takes a batch of sequences, each with one or more next tokens that start at the
+sequence's current length: whole prompts of unequal lengths, one token each, a prompt in
+portions, a later message onto a live sequence, or any mix of these in one step. It runs only
+the tokens it is given, as one batch, from the cache that earlier steps left, and returns the
+logits at the wanted places. The reference's counterpart is ``model_forward(tokens, n, pos0,
+mode)`` for its single sequence (src/model.h:79-97, src/model.c:664-690), which
+``model_prefill`` calls portion by portion (src/model.c:714-724) and the conversation engine
+calls for every later message on the cache the earlier ones left (src/engine.c:222-241).
 
 Steps of one token per sequence are launch-bound, so their kernels are captured once per
 batch size into a CUDA graph and replayed; the step's numbers (tokens, positions, slots)
@@ -75,22 +78,27 @@ class _DecodeGraph:
         # Keys and values are written twice with the same numbers, which is harmless; a state of
         # fixed size would be advanced twice, so it is put back after the run.
         saved = [s.clone() for s in engine.cache.states]
-        side = torch.cuda.Stream(device=engine.device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            engine.model.forward(self.batch, engine.cache, self.rows, engine._status)
-        torch.cuda.current_stream().wait_stream(side)
-        for state, before in zip(engine.cache.states, saved):
-            state.copy_(before)
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.logits = engine.model.forward(self.batch, engine.cache, self.rows, engine._status)
+        try:
+            side = torch.cuda.Stream(device=engine.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                engine.model.forward(self.batch, engine.cache, self.rows, engine._status)
+            torch.cuda.current_stream().wait_stream(side)
+        finally:
+            for state, before in zip(engine.cache.states, saved):
+                state.copy_(before)
+        # the graph is taken for captured only once the capture has gone through: a failed one leaves no
+        # half-made graph behind that a later step could replay
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = engine.model.forward(self.batch, engine.cache, self.rows, engine._status)
+        self.graph, self.logits = graph, logits
 
 
 class Engine:
     def __init__(self, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", *, max_tokens: int = 4096,
                  max_slots: Optional[int] = None, max_seq_len: Optional[int] = None, device: str = "cuda:0",
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, max_step_tokens: Optional[int] = None):
         self.dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
         if self.dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("dtype must be bfloat16 or float32")
@@ -108,6 +116,11 @@ class Engine:
                                    max_seq_len=self.max_seq_len, dtype=self.dtype, device=self.device)
         self.vocab_size = self.spec.vocab_size
         self.use_graphs = use_graphs
+        # the most tokens one step may bring (all sequences together): it bounds a step's activations, as the
+        # reference's --batch bounds its buffers (src/model.c:669); None: no bound but the cache's
+        if max_step_tokens is not None and max_step_tokens < 1:
+            raise ValueError("max_step_tokens must be at least 1")
+        self.max_step_tokens = max_step_tokens
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._graphs: "OrderedDict[Tuple[int, int], _DecodeGraph]" = OrderedDict()
         self.kernel_launches = 0   # graph replays and eager steps, for the record
@@ -137,7 +150,9 @@ class Engine:
     # ---- the step function ---------------------------------------------------------------
     def step(self, slots: Sequence[int], tokens: Union[Sequence[Sequence[int]], torch.Tensor],
              want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
-        """Runs the next tokens of the sequences in ``slots``.
+        """Runs the next tokens of the sequences in ``slots``: sequence ``i`` brings ``len(tokens[i]) >= 1``
+        tokens, which take the positions from its current length on. Sequences at their first token, sequences
+        that go on by one token and sequences that go on by several may share a step.
 
         ``tokens`` is a list of token lists, one per sequence, or -- for a step of one token
         each -- an int32 device tensor ``[len(slots)]`` (what the sampler returned; it is not
@@ -178,11 +193,10 @@ class Engine:
                     raise StepError(f"wanted place {p} is outside the {k} tokens of sequence {i}")
                 rows.append(first + p)
             first += k
+        if self.max_step_tokens is not None and sum(lens) > self.max_step_tokens:   # src/model.c:669
+            raise StepError(f"the step brings {sum(lens)} tokens, more than max_step_tokens = {self.max_step_tokens}: "
+                            f"feed the prompts in portions")
         decode = all(k == 1 for k in lens) and all(s > 0 for s in starts)
-        if not decode and not all(s == 0 for s in starts):
-            raise StepError("the sequences of a step either all start at their first token or all go on by one token")
-        if not decode and on_device:
-            raise StepError("device tokens are for steps of one token per sequence")
         growth = {slot: k for slot, k in zip(slots, lens)}
         try:
             self.cache.reserve(growth)
@@ -223,7 +237,11 @@ class Engine:
         if on_device:
             g.meta[0].copy_(tokens)
         if g.graph is None:
-            g.capture(self)
+            try:
+                g.capture(self)
+            except BaseException:
+                self._graphs.pop(key, None)
+                raise
         g.graph.replay()
         return g.logits
 

@@ -2,7 +2,8 @@
 sequences that end earlier, and as many batches one after another as there are requests.
 
 The reference's loop serves one prompt (src/main.c:571-600; chat: src/engine.c:149-219);
-what carries over: the prompt goes through in one pass, then one token a step; a stop
+what carries over: the prompts go through in one step (or, where the engine bounds a
+step's tokens, in portions as src/main.c:553-568 cuts them), then one token a step; a stop
 token ends the sequence, is reported and is not fed back; the last token that the limit
 allows is not fed back either (src/main.c:590); prompt plus new tokens must fit the context
 (src/main.c:795-796); a sink receives every token and may ask to stop (src/engine_sink.h).
@@ -50,6 +51,51 @@ class GenerationStats:
         }
 
 
+def prompt_portions(lengths: Sequence[int], limit: Optional[int]) -> List[List[Tuple[int, int, int]]]:
+    """How the prompts of a batch go through when one step may bring at most ``limit`` tokens: a list of steps,
+    each a list of ``(index, begin, end)`` -- prompt ``index`` brings its tokens ``begin:end``. Prompts are taken in
+    order and every step is filled as far as the limit allows; without a limit, or when all prompts fit in it,
+    there is one step with every prompt whole. The reference cuts its single prompt the same way into portions
+    of ``--batch`` tokens (src/main.c:553-568)."""
+    if limit is None or sum(lengths) <= limit:
+        return [[(i, 0, n) for i, n in enumerate(lengths)]]
+    if limit < 1:
+        raise ValueError("a step must be allowed at least one token")
+    steps: List[List[Tuple[int, int, int]]] = [[]]
+    room = limit
+    for i, n in enumerate(lengths):
+        at = 0
+        while at < n:
+            if room == 0:
+                steps.append([])
+                room = limit
+            take = min(n - at, room)
+            steps[-1].append((i, at, at + take))
+            at += take
+            room -= take
+    return steps
+
+
+def _run_prompts(engine, slots: List[int], prompts: List[Sequence[int]]):
+    """Feeds the prompts in as few steps as the engine's ``max_step_tokens`` allows and returns the logits after
+    each prompt's last token, one row per prompt in order."""
+    plan = prompt_portions([len(p) for p in prompts], getattr(engine, "max_step_tokens", None))
+    if len(plan) == 1:
+        return engine.step(slots, [list(p) for p in prompts])
+    rows: List = [None] * len(prompts)
+    for portion in plan:
+        want = [[e - b - 1] if e == len(prompts[i]) else [] for i, b, e in portion]
+        logits = engine.step([slots[i] for i, _, _ in portion], [list(prompts[i][b:e]) for i, b, e in portion], want)
+        at = 0
+        for (i, _, _), w in zip(portion, want):
+            if w:
+                rows[i] = logits[at:at + 1].clone()   # the next step may write over the engine's result
+                at += 1
+    import torch
+
+    return torch.cat(rows, dim=0)
+
+
 class TokenSink:
     """Receives tokens as they are chosen. ``should_stop`` is asked once per step."""
 
@@ -89,7 +135,7 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], options: Generat
         try:
             stats.batches += 1
             t0 = clock()
-            logits = engine.step([slots[r] for r in live], [list(prompts[r]) for r in live])
+            logits = _run_prompts(engine, [slots[r] for r in live], [prompts[r] for r in live])
             states = sampler.new_states(live)
             engine.synchronize()
             t1 = clock()

@@ -336,7 +336,7 @@ class Ops:
             _need(v_packed, "packed values", q.dtype, 3)
             _need(token_seq_start, "token_seq_start", torch.int32, 1)
             kv_heads = k_packed.shape[1]
-        else:
+        if k_pool is not None:
             _need(k_pool, "key pool", q.dtype)
             _need(v_pool, "value pool", q.dtype)
             _need(page_table, "page table", torch.int32, 2)
@@ -383,6 +383,35 @@ class Ops:
                                                      ctypes.c_float(scale), int(window or 0), int(longest), int(variant),
                                                      _ptr(self.error_flag), _stream()))
         return out
+
+    def kv_store(self, k_packed, v_packed, step, cache) -> None:
+        """This step's packed keys and values into the cache (what ``rope_store`` does beside its rotation, for
+        steps whose attention had to read the ring before its rows are replaced)."""
+        _need(k_packed, "packed keys", cache.k_pool.dtype, 3)
+        _need(v_packed, "packed values", cache.k_pool.dtype, 3)
+        T, kv_heads, head_dim = k_packed.shape
+        self._check(self.lib.sm_kv_store(_ptr(k_packed), _ptr(v_packed), _dt(k_packed), T, kv_heads, head_dim,
+                                         _ptr(cache.k_pool), _ptr(cache.v_pool), _ptr(step.positions),
+                                         _ptr(cache.page_table), cache.page_table.shape[1], cache.ring,
+                                         _ptr(step.token_slot), _ptr(step.token_end), _stream()))
+
+    def attention_extend(self, q, k_packed, v_packed, step, scale, window, cache):
+        """Causal attention of sequences that go on from the cache by any number of tokens: keys and values of
+        earlier positions from the cache, the step's own from the packed tensors (the cache need not hold them yet)."""
+        if (self.use_fast_attention and q.dtype == torch.bfloat16 and step.extend_tiles is not None
+                and self.lib.sm_attention_prefill_supports(q.shape[2])):
+            out = self._prefill_operands(q, k_packed, v_packed, step.extend_tiles)
+            _need(cache.k_pool, "key pool", torch.bfloat16)
+            _need(cache.v_pool, "value pool", torch.bfloat16)
+            _need(cache.page_table, "page table", torch.int32, 2)
+            self._check(self.lib.sm_attention_extend(
+                _ptr(q), _ptr(k_packed), _ptr(v_packed), _ptr(out), _ptr(step.extend_tiles), step.extend_tiles.shape[0],
+                q.shape[1], k_packed.shape[1], q.shape[2], ctypes.c_float(scale), int(window or 0), _ptr(cache.k_pool),
+                _ptr(cache.v_pool), _ptr(cache.page_table), cache.page_table.shape[1], cache.ring, _stream()))
+            return out
+        return self.attention_plain(q, step.positions, scale, window, k_packed=k_packed, v_packed=v_packed,
+                                    token_seq_start=step.token_seq_start, k_pool=cache.k_pool, v_pool=cache.v_pool,
+                                    page_table=cache.page_table, ring=cache.ring, token_slot=step.token_slot)
 
     def attention_cached(self, q, step, scale, window, cache, kv_heads):
         """Attention of this step's tokens over the keys and values in the cache."""

@@ -33,8 +33,9 @@ class Attention(Part):
         self.kv_from_cache = bool(spec.get("kv_from_cache", False))
         if self.heads % self.kv_heads:
             raise ValueError(f"kv_heads {self.kv_heads} must divide heads {self.heads}")
-        if self.head_dim % 16 or self.head_dim > 256:
-            raise ValueError(f"head_dim {self.head_dim}: the attention kernels take multiples of 16 up to 256")
+        if self.head_dim % 8 or self.head_dim > 256:
+            # multiples of 16 up to 128 have tensor-core kernels; the other multiples of 8 run on the plain ones
+            raise ValueError(f"head_dim {self.head_dim}: the attention kernels take multiples of 8 up to 256")
         pos_spec: PartSpec = spec["position"]
         self.position = POSITIONS.get(pos_spec.kind)(pos_spec, runtime)
         self.w_qkv = self.b_qkv = self.w_o = None
@@ -67,33 +68,53 @@ class Attention(Part):
 
     # ---- one step ----------------------------------------------------------------------
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
+        """``step.mode`` picks the kernels, not the function computed: ``prefill`` (every sequence at its first
+        token) attends over the step's own packed keys, ``decode`` (one token each) over the cache, ``extend``
+        (anything else) over the cache for earlier positions and the step's own keys for the rest."""
         ops, rt = self.runtime.ops, self.runtime
         T = x.shape[0]
         cos, sin = self.position.tables(rt.max_positions)
-        kv_heads_here = 0 if self.kv_from_cache else self.kv_heads
-        prefill = step.mode == "prefill"
+        own = not self.kv_from_cache
+        mode = step.mode
         if cache.kind != "kv":
             raise RuntimeError("attention needs a key/value cache")
-        q = None
-        if not prefill and not self.kv_from_cache:
+        if mode == "decode" and own:
             # one token per sequence: product, bias, rotation and cache write in one launch
             q = ops.qkv_rope_store_fused(x, self.w_qkv, self.b_qkv, step.positions, cos, sin, self.heads, self.kv_heads,
                                          self.head_dim, self.position.rotary_dim, cache.k_pool, cache.v_pool,
                                          cache.page_table, cache.ring, step.token_slot)
-        if q is not None:
-            att = ops.attention_cached(q, step, self.scale, self.window, cache, self.kv_heads)
-            ops.linear(att.view(T, self.heads * self.head_dim), self.w_o, None, out=residual, accumulate=True)
-            return
+            if q is not None:
+                att = ops.attention_cached(q, step, self.scale, self.window, cache, self.kv_heads)
+                ops.linear(att.view(T, self.heads * self.head_dim), self.w_o, None, out=residual, accumulate=True)
+                return
         qkv = ops.linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
+        # In a windowed group a new row takes the place of the row one ring earlier, which queries of this very step
+        # may still see when sequences go on from the cache: those steps store after they have attended.
+        store_late = own and mode == "extend" and cache.ring > 0
+        write_now = own and not store_late
         q, k_packed, v_packed = ops.rope_store(
-            qkv, step.positions, cos, sin, self.heads, kv_heads_here, self.head_dim, self.position.rotary_dim,
-            rt.dtype, want_packed=prefill and not self.kv_from_cache,
-            k_pool=None if self.kv_from_cache else cache.k_pool, v_pool=None if self.kv_from_cache else cache.v_pool,
+            qkv, step.positions, cos, sin, self.heads, self.kv_heads if own else 0, self.head_dim,
+            self.position.rotary_dim, rt.dtype, want_packed=own and mode != "decode",
+            k_pool=cache.k_pool if write_now else None, v_pool=cache.v_pool if write_now else None,
             page_table=cache.page_table, ring=cache.ring, token_slot=step.token_slot, token_end=step.token_end)
-        if prefill and not self.kv_from_cache:
+        if own and mode == "prefill":
             att = ops.attention_prefill(q, k_packed, v_packed, step, self.scale, self.window)
+        elif own and mode == "extend":
+            att = ops.attention_extend(q, k_packed, v_packed, step, self.scale, self.window, cache)
+            if store_late:
+                ops.kv_store(k_packed, v_packed, step, cache)
         else:
-            if prefill and cache.ring and step.max_seq_len > cache.ring:
-                raise RuntimeError("a prompt longer than the window cannot be read back from a windowed cache")
+            if cache.ring and mode != "decode":
+                self._check_ring_still_holds(step, cache)
             att = ops.attention_cached(q, step, self.scale, self.window, cache, self.kv_heads)
         ops.linear(att.view(T, self.heads * self.head_dim), self.w_o, None, out=residual, accumulate=True)
+
+    def _check_ring_still_holds(self, step, cache) -> None:
+        """A run that reads another run's windowed cache finds this step's rows already written: the oldest key a
+        query of the step sees must not have been replaced by them."""
+        starts = step.seq_starts if step.seq_starts is not None else [0] * step.n_seqs
+        for start, n in zip(starts, step.seq_lens):
+            oldest_needed = max(0, start - (self.window or cache.ring) + 1)
+            if start + n - cache.ring > oldest_needed:
+                raise RuntimeError(f"{n} tokens at position {start} have replaced keys of the windowed cache (ring "
+                                   f"{cache.ring}) that the step's first query still sees: feed fewer tokens a step")

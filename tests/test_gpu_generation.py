@@ -193,9 +193,10 @@ def test_step_refuses_what_it_cannot_run(model_dirs):
         engine.step([s], [[1] * 129])
     engine.step([s], [[1, 2, 3]])
     t = engine.open_sequence()
-    with pytest.raises(StepError, match="either all start"):
-        engine.step([s, t], [[4], [5, 6]])
+    with pytest.raises(StepError, match="appears twice"):
+        engine.step([s, s], [[4], [5, 6]])
     with pytest.raises(StepError, match="wanted place"):
         engine.step([s], [[4]], [[1]])
-    # after the refusals the engine still works (the reference: tests/test_errors.c)
-    assert engine.step([s], [[4]]).shape == (1, 256) and engine.length(s) == 4
+    # after the refusals the engine still works (the reference: tests/test_errors.c); a sequence that goes on and
+    # one that starts share a step
+    assert engine.step([s, t], [[4], [5, 6]]).shape == (2, 256) and engine.length(s) == 4 and engine.length(t) == 2

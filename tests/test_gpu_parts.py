@@ -200,7 +200,8 @@ def test_order_names_a_layer_twice_and_a_layer_reads_anothers_cache(tmp_path):
     requests = {f"r{i}": random_tokens(n, 256, 60 + i) for i, n in enumerate([3, 40, 77])}
     want = {r: _plain_shared_order(folder, t) for r, t in requests.items()}
     for cut, got in (("whole", replay.whole(engine, requests)), ("tail", replay.tail_decoded(engine, requests)),
-                     ("batched", replay.batched(engine, [requests], {r: max(1, len(t) // 2) for r, t in requests.items()}))):
+                     ("batched", replay.batched(engine, [requests], {r: max(1, len(t) // 2) for r, t in requests.items()})),
+                     ("portions", replay.portions(engine, requests, 7, 3))):
         for r in requests:
             assert float((got[r] - want[r]).abs().max()) <= 5e-6, f"{cut} {r}"
 
@@ -299,7 +300,11 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     ids = list(requests)
     cuts = {"whole": replay.whole(engine, requests), "tail": replay.tail_decoded(engine, requests),
             "batched": replay.batched(engine, [{r: requests[r] for r in ids[:3]}, {r: requests[r] for r in ids[2:]}],
-                                      {r: max(1, len(t) // 3) for r, t in requests.items()})}
+                                      {r: max(1, len(t) // 3) for r, t in requests.items()}),
+            # a prompt in portions: the state goes on from where the portion before left it
+            "portions": replay.portions(engine, requests, 9, 4),
+            "joined": replay.joined(engine, {r: requests[r] for r in ids[:2]}, {r: requests[r] for r in ids[2:3]},
+                                    {r: max(1, len(t) // 2) for r, t in requests.items()}, after=2, portion=5)}
     for cut, got in cuts.items():          # the state is carried from step to step and starts at zero in a used slot
         for r in got:
             assert float((got[r] - want[r]).abs().max()) <= 2e-5, f"{cut} {r}"

@@ -56,12 +56,29 @@ def test_one_token_each(n):
     assert step.max_seq_len == max(starts) + 1
 
 
+@pytest.mark.parametrize("starts,lens", [([5], [2]), ([0, 5], [2, 1]), ([64, 0, 3, 200], [65, 7, 1, 130]),
+                                         ([9, 8, 7, 6, 5, 0], [1, 1, 1, 1, 1, 70])])
+def test_sequences_that_go_on_by_any_number_of_tokens(starts, lens):
+    """A prompt in portions, a later message onto a live sequence, new sequences beside ones that decode: the
+    same packing, with tiles that carry each sequence's first position and slot."""
+    slots = [3 * i + 1 for i in range(len(lens))]
+    token_lists = [[(7 * i + j) % 89 for j in range(n)] for i, n in enumerate(lens)]
+    step = pack_step(slots, starts, token_lists, CPU)
+    tokens, positions, token_slot, token_end, seq_start, cu = _by_hand(slots, starts, token_lists)
+    assert step.mode == "extend" and step.prefill_tiles is None and step.seq_starts == starts
+    assert step.tokens.tolist() == tokens and step.positions.tolist() == positions
+    assert step.token_slot.tolist() == token_slot and step.token_end.tolist() == token_end
+    assert step.token_seq_start.tolist() == seq_start and step.cu_seqlens.tolist() == cu
+    assert step.slot_ids.tolist() == slots and step.seq_ends.tolist() == [s + n for s, n in zip(starts, lens)]
+    assert step.max_seq_len == max(s + n for s, n in zip(starts, lens))
+    want_tiles = [[cu[i], n, q0, starts[i], slots[i]] for i, n in enumerate(lens) for q0 in range(0, n, QUERY_TILE)]
+    assert step.extend_tiles.tolist() == want_tiles and step.extend_tiles.dtype == torch.int32
+
+
 def test_what_is_refused():
     with pytest.raises(ValueError, match="at least one sequence"):
         pack_step([], [], [], CPU)
     with pytest.raises(ValueError, match="at least one token"):
         pack_step([0, 1], [0, 0], [[1], []], CPU)
-    with pytest.raises(ValueError, match="all start at their first token or all go on by one"):
-        pack_step([0, 1], [0, 5], [[1, 2], [3]], CPU)       # a prompt beside a sequence that goes on
-    with pytest.raises(ValueError, match="all start at their first token or all go on by one"):
-        pack_step([0], [5], [[1, 2]], CPU)                  # two tokens onto a sequence that has begun
+    with pytest.raises(ValueError, match="not negative"):
+        pack_step([0], [-1], [[1, 2]], CPU)
