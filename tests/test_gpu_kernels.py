@@ -357,6 +357,30 @@ def test_gemm_skinny_norm_prologue_and_gate(ops, T, H, K):
     assert float((got.float() - want).abs().max()) <= 1e-2 * float(want.abs().max()) + 1e-3
 
 
+def _torch_qkv_rope_pools(x, w, b, positions, slots, table, cos, sin, heads, kv_heads, hd, n_pages):
+    """Product, bias, rotation of q and k on pairs (i, i + hd/2) and the cache cells they belong in, computed
+    with PyTorch in float (no kernel of the library): returns q [T, heads, hd] and the two expected pools."""
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    T = x.shape[0]
+    qkv = x.float() @ w.float().T + b.float()
+    q, k, v = qkv.split([heads * hd, kv_heads * hd, kv_heads * hd], dim=1)
+    c, s_ = cos[positions.long()][:, None, :], sin[positions.long()][:, None, :]
+
+    def rot(t):
+        lo, hi = t[..., :hd // 2], t[..., hd // 2:]
+        return torch.cat([lo * c - hi * s_, lo * s_ + hi * c], dim=-1)
+
+    q, k, v = rot(q.view(T, heads, hd)), rot(k.view(T, kv_heads, hd)), v.reshape(T, kv_heads, hd)
+    k_pool = torch.zeros((n_pages, kv_heads, PAGE_SIZE, hd), dtype=torch.float32, device=x.device)
+    v_pool = torch.zeros_like(k_pool)
+    for t in range(T):
+        pos, slot = int(positions[t]), int(slots[t])
+        page = int(table[slot, pos // PAGE_SIZE])
+        k_pool[page, :, pos % PAGE_SIZE] = k[t]
+        v_pool[page, :, pos % PAGE_SIZE] = v[t]
+    return q, k_pool, v_pool
+
+
 @pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (14, 2, 64), (5, 5, 48)])
 def test_fused_qkv_matches_the_separate_kernels(ops, heads, kv_heads, hd):
     from smolmoe_c99_b200.kernels import PAGE_SIZE
@@ -381,6 +405,12 @@ def test_fused_qkv_matches_the_separate_kernels(ops, heads, kv_heads, hd):
     assert float((pools[2].float() - pools[0].float()).abs().max()) <= 2e-2
     assert float((pools[3].float() - pools[1].float()).abs().max()) <= 2e-2
     assert int((pools[2] != 0).sum()) == int((pools[0] != 0).sum())   # the same cells were written
+    # and against a computation that uses no kernel of the library
+    q_t, k_t, v_t = _torch_qkv_rope_pools(x, w, b, positions, slots, table, cos, sin, heads, kv_heads, hd, 20)
+    tol = 8e-3 * float(q_t.abs().max())
+    assert float((q.float() - q_t).abs().max()) <= tol
+    assert float((pools[2].float() - k_t).abs().max()) <= tol and float((pools[3].float() - v_t).abs().max()) <= tol
+    assert torch.equal(pools[2] != 0, k_t != 0) and torch.equal(pools[3] != 0, v_t != 0)
 
 
 @pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (14, 2, 64), (8, 2, 128), (28, 4, 128)])
@@ -418,6 +448,16 @@ def test_fused_qkv_on_the_tcgen05_kernel_matches_the_separate_kernels(ops, heads
     assert float((pools[3].float() - pools[1].float()).abs().max()) <= tol
     assert int((pools[2] != 0).sum()) == int((pools[0] != 0).sum())   # the same cells were written
     assert int((pools[3] != 0).sum()) == int((pools[1] != 0).sum())
+    # and against a computation that uses no kernel of the library. Two tokens may share a cell here (positions
+    # and pages are drawn at random), so cells are compared where exactly one token writes
+    q_t, k_t, v_t = _torch_qkv_rope_pools(x, w, b, positions, slots, table, cos, sin, heads, kv_heads, hd, T * 4)
+    assert float((q.float() - q_t).abs().max()) <= tol
+    cells = [(int(table[int(slots[t]), int(positions[t]) // PAGE_SIZE]), int(positions[t]) % PAGE_SIZE) for t in range(T)]
+    once = [c for c in cells if cells.count(c) == 1]
+    assert len(once) >= T - 4
+    for page, row in once:
+        assert float((pools[2][page, :, row].float() - k_t[page, :, row]).abs().max()) <= tol
+        assert float((pools[3][page, :, row].float() - v_t[page, :, row]).abs().max()) <= tol
 
 
 def test_fused_qkv_refuses_heads_that_straddle_tiles(ops):

@@ -9,11 +9,11 @@ import pytest
 import torch
 
 import plain_model
+from compare import REL
 from tiny import TINY, random_tokens
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-TOL = {"float32": 5e-6, "bfloat16": 1e-2}
 
 
 def _trace(requests, batches, prompt_lens):
@@ -64,7 +64,41 @@ def test_trace_run(model_dirs, tmp_path, name, dtype):
             continue
         got = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(len(wanted), vocab))
         for row, (r, pos) in enumerate(wanted):
-            assert float((got[row] - want[r][pos]).abs().max()) <= TOL[dtype], f"step {i}, request {r}, position {pos}"
+            bound = REL[dtype] * float(want[r][pos].abs().max())
+            assert float((got[row] - want[r][pos]).abs().max()) <= bound, f"step {i}, request {r}, position {pos}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_takes_portions_and_requests_that_join(model_dirs, tmp_path, dtype):
+    """A prompt in portions of 10 tokens; a second request whose prompt arrives while the first decodes."""
+    vocab = TINY["B"]["vocab_size"]
+    a, b = random_tokens(50, vocab, 71), random_tokens(30, vocab, 72)
+    steps, expect = [], []
+    for at in range(0, 40, 10):
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": a[at:at + 10], "want": [0, 9]}], "end": []})
+        expect.append([("a", at), ("a", at + 9)])
+    steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [a[40]], "want": [0]},
+                                                   {"id": "b", "tokens": b[:25], "want": [3, 24]}], "end": []})
+    expect.append([("a", 40), ("b", 3), ("b", 24)])
+    for k in range(5):
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [a[41 + k]], "want": [0]},
+                                                       {"id": "b", "tokens": [b[25 + k]], "want": [0]}],
+                      "end": ["b"] if k == 4 else []})
+        expect.append([("a", 41 + k), ("b", 25 + k)])
+    steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": a[46:], "want": [3]}], "end": ["a"]})
+    expect.append([("a", 49)])
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs["B"], "--dtype", dtype,
+                           "--out", str(out), "--max-tokens", "128"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    want = {"a": plain_model.forward(model_dirs["B"], a, round_like_bf16_engine=(dtype == "bfloat16")),
+            "b": plain_model.forward(model_dirs["B"], b, round_like_bf16_engine=(dtype == "bfloat16"))}
+    for i, wanted in enumerate(expect):
+        got = torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(len(wanted), vocab))
+        for row, (r, pos) in enumerate(wanted):
+            bound = REL[dtype] * float(want[r][pos].abs().max())
+            assert float((got[row] - want[r][pos]).abs().max()) <= bound, f"step {i}, request {r}, position {pos}"
 
 
 def test_trace_run_refuses_more_tokens_than_it_was_sized_for(model_dirs, tmp_path):

@@ -27,8 +27,19 @@ TINY = {
     "D": dict(_BASE, hidden_size=384, intermediate_size=272, num_hidden_layers=2, num_attention_heads=6,
               num_key_value_heads=3, vocab_size=331, max_position_embeddings=4096, rms_norm_eps=1e-5,
               rope_theta=500000.0, tie_word_embeddings=False),
+    # head size 128 (the larger tile of the tcgen05 attention, the fused q/k/v epilogue and the decode kernel's
+    # tensor-map path), given and not width/heads; width, feed-forward and vocabulary no power of two
+    "E": dict(_BASE, hidden_size=264, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=128, vocab_size=515, max_position_embeddings=1024, rms_norm_eps=2e-6,
+              rope_theta=250000.0, tie_word_embeddings=False),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
+
+# The layer sizes of Qwen2.5-0.5B (width 896, 14 heads on 2 kv heads of 64, feed-forward 4864, vocabulary 151,936,
+# tied head) with 2 of its 24 layers: what the kernels see at a real size, small enough for the plain model on the CPU.
+REAL_0_5B_2_LAYERS = dict(_BASE, hidden_size=896, intermediate_size=4864, num_hidden_layers=2, num_attention_heads=14,
+                          num_key_value_heads=2, vocab_size=151936, max_position_embeddings=32768, rms_norm_eps=1e-6,
+                          rope_theta=1000000.0, tie_word_embeddings=True)
 
 
 def make_model_dir(name: str, path: str) -> str:
