@@ -19,10 +19,9 @@ from typing import Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 
+from ..kernels.ops import PAGE_SIZE   # one number for host and kernels; the library's own is checked when it is loaded
 from ..parts.base import KVNeed, StateNeed
 from .allocators import CacheFull, CacheStateError, PageAllocator, SlotAllocator
-
-PAGE_SIZE = 64
 
 
 def pages_for(tokens: int) -> int:

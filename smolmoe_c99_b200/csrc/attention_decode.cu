@@ -423,10 +423,13 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         if (BOX) return (piece >> 3) * (KT * 128) + row * 128 + (((piece & 7) ^ (row & 7)) << 4);
         return (row * LD + piece * 8) * (int)sizeof(__nv_bfloat16);
     };
-    // Whether this warp's tile number i holds the newest position, whose row the kernel before this one writes.
+    // Whether this warp's tile number i holds the place of the newest position, whose row the kernel before this one
+    // writes. In a ring that is the tile of the newest position and, where the window fills its ring and does not
+    // start on a tile's boundary, also the first tile: its masked leading rows are the ring's places of the newest ones.
     auto holds_newest = [&](int i) -> bool {
         const int lo = cta_lo + (warp + kStreamWarps * i) * KT;
-        return pos >= lo && pos < lo + KT;
+        const int place = a.ring > 0 ? pos % a.ring : pos, first = a.ring > 0 ? lo % a.ring : lo;
+        return place >= first && place < first + KT;
     };
     // BOX: the page of this warp's tile number i (looked up ahead of the request, so that the trip to the table
     // is not waited for when the request is made)
@@ -487,15 +490,16 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
             *reinterpret_cast<uint4*>(qs + (size_t)row * LD + col) =
                 in ? *reinterpret_cast<const uint4*>(qrow + (size_t)row * hd + col) : make_uint4(0, 0, 0, 0);
         }
-        // the newest position, if its tile is among those asked for above: as a whole tile now (BOX), else its
-        // row by plain loads and stores into the tile
-        if (pos >= cta_lo && pos < cta_hi) {
+        // the newest position, if its tile is among those asked for above: as a whole tile now (BOX: every tile
+        // that was left out above), else its row by plain loads and stores into the tile
+        if (BOX) {
+            for (int i = 0; i < ahead; ++i)
+                if (holds_newest(i)) request(i, i, false);
+        } else if (pos >= cta_lo && pos < cta_hi) {
             const int t = (pos - cta_lo) / KT, row = (pos - cta_lo) - t * KT;
             const int i = t / kStreamWarps;
             if (t % kStreamWarps == warp && i < ahead) {
-                if (BOX) {
-                    request(i, i, false);
-                } else if (lane < 2 * CPR) {
+                if (lane < 2 * CPR) {
                     const int which = lane / CPR, piece = lane - which * CPR;   // 0: key, 1: value
                     if (piece * 8 < hd) {
                         const size_t o = paged.row_offset(slot, pos, kvh) + piece * 8;

@@ -9,6 +9,7 @@
 #include <exception>
 #include <string>
 
+#include "common.cuh"
 #include "kernels.h"
 
 namespace {
@@ -61,6 +62,9 @@ SM_API void sm_set_dependent_launch(int on) { sm::set_dependent_launch(on != 0);
 
 // The device int that kernels report a bounded wait that ran out into.
 SM_API void sm_set_error_word(int* word) { sm::set_error_word(word); }
+
+// Positions per page of the key/value cache that the kernels are compiled for; the host's cache must use the same.
+SM_API int sm_page_size() { return sm::kPageSize; }
 
 // Kernels enqueued by this library since it was loaded.
 SM_API long long sm_launch_count() { return sm::launch_count(); }

@@ -2,8 +2,8 @@
 (src/main.c:72-126,128-224): the same option names and meanings where the reference has
 them. This library starts at token ids, so ``--prompt`` takes ids ("5 17 3" or "5,17,3")
 and ``--prompt-file`` a file with one prompt of ids per line; ``--batch`` is the number of
-sequences that start together (the reference's ``--batch`` is a prefill chunk of its one
-sequence and has no counterpart: prompts go through whole).
+sequences that start together, and ``--step-tokens`` the most tokens one step brings (what
+the reference calls ``--batch``: the portion of its one sequence's prompt per pass).
 
     python -m smolmoe_c99_b200 MODEL_DIR --prompt "1 2 3" --tokens 16
     python -m smolmoe_c99_b200 --random CONFIG.json --seed 3 --save DIR      # writes a model folder
@@ -49,14 +49,19 @@ def build_parser() -> argparse.ArgumentParser:
     g = p.add_argument_group("resources")
     g.add_argument("--context", type=int, default=None, help="cache positions per sequence (default min(config, 2048))")
     g.add_argument("--batch", type=int, default=8, help="sequences that start together (default 8)")
+    g.add_argument("--step-tokens", type=int, default=None,
+                   help="most tokens one step brings; longer prompts go through in portions (default: no limit)")
     g.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                    help="bfloat16 kernels, or the whole model in true 32-bit")
+    g.add_argument("--kernels", choices=["fast", "plain"], default="fast",
+                   help="plain: every product and attention on the plain kernels, for comparison")
     g = p.add_argument_group("diagnostics")
     g.add_argument("--stats", help="JSON statistics (always printed to stderr)")
     g.add_argument("--trace", help="exact hexadecimal logits of every processed token of every prompt")
     g.add_argument("--hash-logits", action="store_true", help="FNV-1a64 of every raw logit, reported in the stats")
     g.add_argument("--token-ids", help="prompt and generated token ids, one per line; a blank line between requests")
     g.add_argument("--perplexity", action="store_true", help="score the prompts (teacher-forced NLL); no generation")
+    g.add_argument("--profile", action="store_true", help="device time per phase of the forward pass, in the stats")
     g = p.add_argument_group("random weights")
     g.add_argument("--random", metavar="CONFIG.json", help="make random weights for this configuration instead of reading a model")
     g.add_argument("--save", metavar="DIR", help="with --random: write the model folder here and exit")
@@ -100,6 +105,12 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         raise SystemExit("smolmoe: --prompt or --prompt-file with token ids is needed")
     if not args.seed or args.batch <= 0:
         raise SystemExit("smolmoe: seed and batch must be nonzero")   # src/main.c:221
+    if args.tokens < 0 or (args.step_tokens is not None and args.step_tokens <= 0):
+        raise SystemExit("smolmoe: tokens must not be negative and step-tokens must be positive")
+    if args.context is not None and args.context <= 0:
+        raise SystemExit("smolmoe: context must be positive")
+    if not (args.temperature == 0 or 1e-6 <= args.temperature <= 100) or not 0 < args.top_p <= 1 or args.top_k < 0:
+        raise SystemExit("smolmoe: temperature is 0 or in [1e-6, 100], top-p in (0, 1], top-k not negative")   # src/main.c:160-170
 
     import torch
     from .entry import Model
@@ -107,34 +118,54 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     started = time.perf_counter()
     try:
         if args.random:
-            model = Model.from_random(config, args.seed, args.dtype, args.context, args.batch)
+            model = Model.from_random(config, args.seed, args.dtype, args.context, args.batch,
+                                      step_tokens=args.step_tokens, kernels=args.kernels)
         else:
-            model = Model.from_folder(model_dir, args.dtype, args.context, args.batch)
-    except (ValueError, RuntimeError) as e:
+            model = Model.from_folder(model_dir, args.dtype, args.context, args.batch,
+                                      step_tokens=args.step_tokens, kernels=args.kernels)
+    except (ValueError, RuntimeError, OSError) as e:
         raise SystemExit(f"smolmoe: {e}")
     loaded = time.perf_counter()
     engine = model.engine
-    stats = {"version": __version__, "backend": "cuda sm_100a", "dtype": args.dtype, "batch": args.batch,
+    if args.profile:
+        engine.start_profile()
+    stats = {"version": __version__, "backend": f"cuda sm_100a {args.kernels}", "dtype": args.dtype, "batch": args.batch,
              "kv_bytes": engine.cache.bytes_per_token() * engine.cache.max_tokens,
              "weight_bytes": engine.weight_bytes(), "load_seconds": loaded - started}
     logits_hash = FNV_OFFSET
     trace = open(args.trace, "w", encoding="utf-8") if args.trace else None
     try:
         if args.perplexity or trace or args.hash_logits:
-            # every prompt position through the step function, one prompt at a time (src/main.c:553-568)
+            # every prompt position through the step function: the prompts in batches of --batch sequences that
+            # start together, in portions of --step-tokens (src/main.c:553-568); rows are recorded prompt by prompt
+            from .generate import prompt_portions
             nll, nll_tokens = 0.0, 0
-            for prompt in prompts:
-                slot = engine.open_sequence()
-                rows = engine.step([slot], [prompt], [list(range(len(prompt)))]).cpu()
-                engine.close_sequence(slot)
-                for pos in range(len(prompt)):
-                    if trace:
-                        trace.write(str(pos) + "".join(" " + float(v).hex() for v in rows[pos].tolist()) + "\n")
-                    if args.hash_logits:
-                        logits_hash = fnv1a_logits(logits_hash, rows[pos])
-                    if args.perplexity and pos + 1 < len(prompt):
-                        nll += token_nll(rows[pos], prompt[pos + 1])
-                        nll_tokens += 1
+            try:
+                for first in range(0, len(prompts), args.batch):
+                    group = prompts[first:first + args.batch]
+                    slots = [engine.open_sequence() for _ in group]
+                    rows = [[] for _ in group]
+                    for portion in prompt_portions([len(p) for p in group], args.step_tokens):
+                        lg = engine.step([slots[i] for i, _, _ in portion], [group[i][b:e] for i, b, e in portion],
+                                         [list(range(e - b)) for _, b, e in portion]).cpu()
+                        at = 0
+                        for i, b, e in portion:
+                            rows[i].append(lg[at:at + e - b])
+                            at += e - b
+                    for slot in slots:
+                        engine.close_sequence(slot)
+                    for prompt, parts in zip(group, rows):
+                        logits = torch.cat(parts, dim=0)
+                        for pos in range(len(prompt)):
+                            if trace:
+                                trace.write(str(pos) + "".join(" " + float(v).hex() for v in logits[pos].tolist()) + "\n")
+                            if args.hash_logits:
+                                logits_hash = fnv1a_logits(logits_hash, logits[pos])
+                            if args.perplexity and pos + 1 < len(prompt):
+                                nll += token_nll(logits[pos], prompt[pos + 1])
+                                nll_tokens += 1
+            except ValueError as e:
+                raise SystemExit(f"smolmoe: {e}")
             if args.perplexity:
                 mean = nll / nll_tokens if nll_tokens else 0.0
                 stats.update(perplexity_tokens=nll_tokens, nll=mean, perplexity=math.exp(mean))
@@ -159,6 +190,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                 ids = list(prompt) + (completions[i].tokens if completions else [])
                 f.write("\n".join(str(t) for t in ids) + "\n\n")
     stats["logits_hash"] = f"{logits_hash if args.hash_logits else 0:016x}"
+    if args.profile:
+        stats["profile"] = {k: round(v, 6) for k, v in engine.stop_profile().items()}
     line = json.dumps(stats)
     print(line, file=sys.stderr)
     if args.stats:

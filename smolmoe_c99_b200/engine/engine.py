@@ -98,7 +98,7 @@ class _DecodeGraph:
 class Engine:
     def __init__(self, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", *, max_tokens: int = 4096,
                  max_slots: Optional[int] = None, max_seq_len: Optional[int] = None, device: str = "cuda:0",
-                 use_graphs: bool = True, max_step_tokens: Optional[int] = None):
+                 use_graphs: bool = True, max_step_tokens: Optional[int] = None, kernels: str = "fast"):
         self.dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
         if self.dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("dtype must be bfloat16 or float32")
@@ -107,7 +107,7 @@ class Engine:
         self.config = load_config(model_dir)
         self.spec = self.config.model_spec()
         self.max_seq_len = min(self.spec.max_positions, max_seq_len or max_tokens, max_tokens)
-        self.runtime = Runtime(dtype=self.dtype, device=self.device, ops=get_ops(), max_positions=self.max_seq_len)
+        self.runtime = Runtime(dtype=self.dtype, device=self.device, ops=get_ops(kernels), max_positions=self.max_seq_len)
         self.model = DecoderModel(self.spec, self.runtime)
         tensors = load_weights(model_dir, model_param_specs(self.spec), self.dtype, self.device)
         self.model.bind(tensors)
@@ -291,6 +291,23 @@ class Engine:
 
     def synchronize(self) -> None:
         torch.cuda.synchronize(self.device)
+
+    # ---- time per phase --------------------------------------------------------------------
+    def start_profile(self) -> None:
+        """From now on the device time of every step is charged to the reference's phases (src/model.c:312-328).
+        Steps then run kernel by kernel, without graphs (an event cannot be timed inside one); what they compute
+        is unchanged."""
+        from ..kernels.ops import PhaseTimes
+        self._graphs_before_profile = self.use_graphs
+        self.use_graphs = False
+        self.runtime.ops.phase_times = PhaseTimes()
+
+    def stop_profile(self) -> Dict[str, float]:
+        """Seconds per phase since ``start_profile`` (synchronises)."""
+        times = self.runtime.ops.phase_times
+        self.runtime.ops.phase_times = None
+        self.use_graphs = getattr(self, "_graphs_before_profile", self.use_graphs)
+        return times.seconds() if times is not None else {}
 
     def check_status(self) -> None:
         """Raises if a kernel reported a fault since the last check (synchronises)."""

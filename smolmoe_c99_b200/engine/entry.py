@@ -5,8 +5,8 @@ and a sink with callbacks (src/desktop.h:35-72, src/engine_sink.h:9-23). This fo
 shape and keeps the reference's names and meanings of options where it has them (``tokens``,
 ``temperature``, ``top_k``, ``top_p``, ``seed``, ``context``: src/main.c:98-110). ``batch`` is
 the number of sequences that start together; in the reference it is a number of prompt
-tokens per pass of its single sequence (src/main.c:106), which has no counterpart here:
-a prompt goes through in one step.
+tokens per pass of its single sequence (src/main.c:106); its counterpart here is
+``step_tokens``, the most tokens one step may bring.
 
     from smolmoe_c99_b200 import Model
     model = Model.from_folder("path/to/folder")            # config.json + model.safetensors
@@ -33,20 +33,24 @@ class Model:
     # ---- opening -------------------------------------------------------------------------
     @classmethod
     def from_folder(cls, path: str, dtype: str = "bfloat16", context: Optional[int] = None, batch: int = 8,
-                    device: str = "cuda:0") -> "Model":
+                    device: str = "cuda:0", step_tokens: Optional[int] = None, kernels: str = "fast") -> "Model":
         """``context``: positions a sequence may hold (default: the smaller of the model's limit
         and 2048); ``batch``: most sequences that start together. The cache is sized for
-        ``batch`` sequences of ``context`` positions."""
+        ``batch`` sequences of ``context`` positions. ``step_tokens``: the most tokens one step may bring; longer
+        prompts go through in portions (the reference's ``--batch``, src/main.c:106). ``kernels``: ``"fast"`` or
+        ``"plain"`` (every product and attention on the plain kernels, for comparison)."""
         from ..config import load_config
 
         limit = load_config(path).model_spec().max_positions
         context = min(limit, context or DEFAULT_CONTEXT)
         rounded = -(-context // 64) * 64
-        return cls(Engine(path, dtype, max_tokens=rounded * batch, max_slots=batch, max_seq_len=context, device=device))
+        return cls(Engine(path, dtype, max_tokens=rounded * batch, max_slots=batch, max_seq_len=context, device=device,
+                          max_step_tokens=step_tokens, kernels=kernels))
 
     @classmethod
     def from_random(cls, config: Union[dict, object], seed: int, dtype: str = "bfloat16", context: Optional[int] = None,
-                    batch: int = 8, device: str = "cuda:0") -> "Model":
+                    batch: int = 8, device: str = "cuda:0", step_tokens: Optional[int] = None,
+                    kernels: str = "fast") -> "Model":
         """Random weights for a configuration (a ``config.json`` dictionary or a configuration
         object of a registered architecture) and a seed."""
         import tempfile
@@ -57,7 +61,7 @@ class Model:
         cfg = config_from_json(config) if isinstance(config, dict) else config
         with tempfile.TemporaryDirectory(prefix="smolmoe_b200_") as tmp:
             write_random_model(cfg, tmp, seed)
-            return cls.from_folder(tmp, dtype, context, batch, device)
+            return cls.from_folder(tmp, dtype, context, batch, device, step_tokens, kernels)
 
     # ---- generating ----------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], tokens: int = 64, temperature: float = 0.0, top_k: int = 40,

@@ -38,12 +38,14 @@ class GenerationStats:
     decode_forwards: int = 0
     prefill_seconds: float = 0.0
     decode_seconds: float = 0.0
+    ttft_seconds: float = 0.0           # from the start of the call to the first batch's first logits
     batches: int = 0
 
     def as_dict(self) -> Dict[str, float]:
         """The reference's keys and definitions (src/main.c:347-382)."""
         return {
             "prompt_tokens": self.prompt_tokens, "generated_tokens": self.generated_tokens,
+            "processed_tokens": self.prompt_tokens + self.decode_forwards, "ttft_seconds": self.ttft_seconds,
             "prefill_seconds": self.prefill_seconds, "decode_seconds": self.decode_seconds,
             "prefill_tokens_per_second": self.prompt_tokens / self.prefill_seconds if self.prefill_seconds > 0 else 0.0,
             "decode_tokens_per_second": self.decode_forwards / self.decode_seconds if self.decode_seconds > 0 else 0.0,
@@ -140,6 +142,8 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], options: Generat
             engine.synchronize()
             t1 = clock()
             stats.prefill_seconds += t1 - t0
+            if stats.batches == 1:
+                stats.ttft_seconds = t1 - t0
             stats.prompt_tokens += sum(len(prompts[r]) for r in live)
             for produced in range(1, options.max_new_tokens + 1):
                 chosen = sampler.choose(logits, states)

@@ -64,14 +64,18 @@ class DecoderModel:
         """Runs the step's tokens through every layer; returns float logits ``[wanted, vocab]``
         for the packed token indices in ``want_rows`` (int32), or None when none are wanted."""
         ops = self.runtime.ops
+        ops.lap(None)
         residual = ops.embedding(self.embedding, step.tokens, status)
+        ops.lap("embed")
         for run, index in enumerate(self.spec.order):
             self.blocks[index].forward(residual, step, cache.run_view(run))
         if want_rows is None or want_rows.numel() == 0:
             return None
         every_row = getattr(step, "wants_every_row", False)   # the wanted rows are 0..T-1 in order
         x = self.final_norm.forward(residual, None if every_row else want_rows, lazy=True)
-        return ops.linear(x, self.head, None, out_dtype=torch.float32)
+        logits = ops.linear(x, self.head, None, out_dtype=torch.float32)
+        ops.lap("logits")
+        return logits
 
     def weight_bytes(self) -> int:
         """Bytes of every weight a step reads once (a tied head counts once)."""

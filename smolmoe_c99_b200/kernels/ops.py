@@ -10,7 +10,11 @@ import torch
 from .build import load as load_library
 
 F32, BF16 = 0, 1
-PAGE_SIZE = 64  # positions per cache page; must equal sm::kPageSize
+PAGE_SIZE = 64  # positions per cache page; checked against the library's own number when it is loaded
+KERNEL_CHOICES = ("fast", "plain")
+# the reference's phases (src/model.h:38-41, src/model.c:312-328); the ones that have no counterpart here stay 0
+PHASES = ("embed", "norm", "qkv", "rope", "attention", "attn_out", "ffn_up", "activation", "attn_quant", "ffn_down",
+          "routing", "residual", "logits")
 
 
 class KernelError(RuntimeError):
@@ -65,20 +69,52 @@ class NormedRows:
         return self.done
 
 
-class Ops:
-    """The kernel library, loaded (and built if needed) at construction."""
+class PhaseTimes:
+    """Device time per phase of the forward pass, measured with CUDA events between ``lap`` calls (the reference's
+    ``lap()``: src/model.c:312-328). Events only mark the stream; nothing computed changes."""
 
     def __init__(self) -> None:
+        self.marks = []          # (phase or None, event): the time up to an event is charged to its phase
+
+    def lap(self, phase: Optional[str]) -> None:
+        event = torch.cuda.Event(enable_timing=True)
+        event.record()
+        self.marks.append((phase, event))
+
+    def seconds(self) -> dict:
+        """Synchronises and returns seconds per phase (every phase of ``PHASES``, zeros included)."""
+        torch.cuda.synchronize()
+        out = {name: 0.0 for name in PHASES}
+        for (_, before), (phase, event) in zip(self.marks, self.marks[1:]):
+            if phase is not None:
+                out[phase] = out.get(phase, 0.0) + before.elapsed_time(event) / 1000.0
+        return out
+
+
+class Ops:
+    """The kernel library, loaded (and built if needed) at construction. ``kernels="plain"`` routes everything to
+    the plain kernels (CUDA-core products, one-warp-per-query attention) whatever the dtype: the slow side of an
+    A/B comparison, as the reference's ``--scalar`` is of its SIMD kernels (src/main.c:109)."""
+
+    def __init__(self, kernels: str = "fast") -> None:
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: this library runs on an NVIDIA B200 only (no CPU fallback)")
+        if kernels not in KERNEL_CHOICES:
+            raise KernelError(f"kernels must be one of {KERNEL_CHOICES}, got {kernels!r}")
         self.lib = load_library()
+        if int(self.lib.sm_page_size()) != PAGE_SIZE:
+            raise KernelError(f"the kernel library pages the cache by {int(self.lib.sm_page_size())} positions, "
+                              f"the host by {PAGE_SIZE}")
         self.lib.sm_gemm_tc_workspace_bytes.restype = ctypes.c_longlong
         self.lib.sm_launch_count.restype = ctypes.c_longlong
-        self.use_tensor_cores = True  # False routes bfloat16 products to the CUDA-core kernel
+        fast = kernels == "fast"
+        self.kernels = kernels
+        self.phase_times: Optional[PhaseTimes] = None   # set to time the phases of the forward pass
+        self.use_tensor_cores = fast  # False routes bfloat16 products to the CUDA-core kernel
         self.skinny_most_rounds = 2   # plain rows over a longer K go to the tcgen05 kernel (see _skinny_ok)
-        self.use_fast_attention = True  # False routes bfloat16 attention to the plain kernel
+        self.use_fast_attention = fast  # False routes bfloat16 attention to the plain kernel
         self.use_tcgen05_attention = True  # False routes prefill attention to the mma.sync kernel
-        self.use_skinny = True  # False routes products over a handful of tokens to the general kernels
+        self.use_skinny = fast  # False routes products over a handful of tokens to the general kernels
         # more tokens than this go to the tcgen05 kernel (the weight-streaming kernel itself takes up to 32; measured
         # on a B200 at 24 and 32 tokens it is 20-35% behind on every shape from 0.5B to 7B)
         self.skinny_max_tokens = 16
@@ -93,6 +129,12 @@ class Ops:
     def _check(self, status: int) -> None:
         if status:
             raise KernelError(self.lib.sm_last_error().decode("utf-8", "replace"))
+
+    def lap(self, phase: Optional[str]) -> None:
+        """Charges the device time since the last lap to ``phase`` (None: to nothing). A no-op unless
+        ``phase_times`` is set."""
+        if self.phase_times is not None:
+            self.phase_times.lap(phase)
 
     # ---- elementwise -------------------------------------------------------------------
     def embedding(self, table: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -197,7 +239,10 @@ class Ops:
             out = torch.empty((x.shape[0], hidden), dtype=out_dtype, device=x.device)
             return self.gemm_tc(x, w_gate_up, None, out, mode=2, up_offset=hidden)
         gate_up = self.linear(x, w_gate_up, None, out_dtype=torch.float32)
-        return self.swiglu(gate_up, out_dtype)
+        self.lap("ffn_up")
+        out = self.swiglu(gate_up, out_dtype)
+        self.lap("activation")
+        return out
 
     # ---- rows under a norm that has not been computed yet -------------------------------
     @staticmethod
@@ -228,9 +273,18 @@ class Ops:
             # kernel's clusters stream them better (3,584 x 18,944 at 8 tokens: 26 against 39 us; at two rounds the
             # weight-streaming kernel still wins, 1,536 x 8,960: 8 against 11 us)
             return False
-        if w.shape[0] > 32768 and self.use_tensor_cores and self.lib.sm_gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1]):
-            return False   # the output head: thousands of row tiles, where the tcgen05 kernel streams better
+        if (self.use_tensor_cores and self.lib.sm_gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1])
+                and self._row_tiles_fill_the_gpu(w.shape[0])):
+            return False   # enough row tiles to keep every SM streaming on the tcgen05 kernel without any split of K
         return bool(self.lib.sm_gemm_skinny_supports(x.shape[0], w.shape[0], x.shape[1]))
+
+    def _row_tiles_fill_the_gpu(self, rows: int) -> bool:
+        """Whether a product with this many weight rows gives the tcgen05 kernel a full wave of its 128-row tiles at
+        two CTAs an SM without any split of K (measured on 148 SMs: at 296 tiles, 37,888 x 3,584, it takes 45 us against
+        the weight-streaming kernel's 53; at 1,187 tiles, 151,936 x 896, it streams 5.0 TB/s against 3.1)."""
+        if not hasattr(self, "_sm_count"):
+            self._sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        return (rows + 127) // 128 >= 2 * self._sm_count
 
     def gemm_skinny(self, x, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int = 0,
                     up_offset: int = 0) -> torch.Tensor:
@@ -467,11 +521,11 @@ class Ops:
         return out
 
 
-_ops: Optional[Ops] = None
+_ops: dict = {}
 
 
-def get_ops() -> Ops:
-    global _ops
-    if _ops is None:
-        _ops = Ops()
-    return _ops
+def get_ops(kernels: str = "fast") -> Ops:
+    """The shared instance for a choice of kernels."""
+    if kernels not in _ops:
+        _ops[kernels] = Ops(kernels)
+    return _ops[kernels]

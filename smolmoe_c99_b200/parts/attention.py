@@ -84,10 +84,14 @@ class Attention(Part):
                                          self.head_dim, self.position.rotary_dim, cache.k_pool, cache.v_pool,
                                          cache.page_table, cache.ring, step.token_slot)
             if q is not None:
+                ops.lap("qkv")   # with the norm before it, the rotation and the cache write
                 att = ops.attention_cached(q, step, self.scale, self.window, cache, self.kv_heads)
+                ops.lap("attention")
                 ops.linear(att.view(T, self.heads * self.head_dim), self.w_o, None, out=residual, accumulate=True)
+                ops.lap("attn_out")
                 return
         qkv = ops.linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
+        ops.lap("qkv")
         # In a windowed group a new row takes the place of the row one ring earlier, which queries of this very step
         # may still see when sequences go on from the cache: those steps store after they have attended.
         store_late = own and mode == "extend" and cache.ring > 0
@@ -97,6 +101,7 @@ class Attention(Part):
             self.position.rotary_dim, rt.dtype, want_packed=own and mode != "decode",
             k_pool=cache.k_pool if write_now else None, v_pool=cache.v_pool if write_now else None,
             page_table=cache.page_table, ring=cache.ring, token_slot=step.token_slot, token_end=step.token_end)
+        ops.lap("rope")
         if own and mode == "prefill":
             att = ops.attention_prefill(q, k_packed, v_packed, step, self.scale, self.window)
         elif own and mode == "extend":
@@ -107,7 +112,9 @@ class Attention(Part):
             if cache.ring and mode != "decode":
                 self._check_ring_still_holds(step, cache)
             att = ops.attention_cached(q, step, self.scale, self.window, cache, self.kv_heads)
+        ops.lap("attention")
         ops.linear(att.view(T, self.heads * self.head_dim), self.w_o, None, out=residual, accumulate=True)
+        ops.lap("attn_out")
 
     def _check_ring_still_holds(self, step, cache) -> None:
         """A run that reads another run's windowed cache finds this step's rows already written: the oldest key a

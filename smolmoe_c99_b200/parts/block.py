@@ -14,6 +14,7 @@ from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, ParamSpec, Runtime, full
 class PreNormBlock:
     def __init__(self, spec: LayerSpec, runtime: Runtime):
         self.spec = spec
+        self.runtime = runtime
         self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, runtime)
         self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, runtime)
         self.feed_forward_norm = NORMS.get(spec.feed_forward_norm.kind)(spec.feed_forward_norm, runtime)
@@ -46,7 +47,12 @@ class PreNormBlock:
     def forward(self, residual: torch.Tensor, step, cache) -> None:
         # a part that sets ``takes_lazy_norm`` hands its input straight to the kernel library's
         # products and may receive the norm as a handle; any other part gets a tensor
+        ops = self.runtime.ops
         lazy = getattr(self.mixer, "takes_lazy_norm", False)
-        self.mixer.forward(self.mixer_norm.forward(residual, lazy=lazy), residual, step, cache)
+        x = self.mixer_norm.forward(residual, lazy=lazy)
+        ops.lap("norm")
+        self.mixer.forward(x, residual, step, cache)
         lazy = getattr(self.feed_forward, "takes_lazy_norm", False)
-        self.feed_forward.forward(self.feed_forward_norm.forward(residual, lazy=lazy), residual, step)
+        x = self.feed_forward_norm.forward(residual, lazy=lazy)
+        ops.lap("norm")
+        self.feed_forward.forward(x, residual, step)

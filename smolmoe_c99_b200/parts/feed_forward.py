@@ -37,4 +37,6 @@ class GatedMLP(Part):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step) -> None:
         ops = self.runtime.ops
         h = ops.gated_linear(x, self.w_gate_up, self.intermediate, self.runtime.dtype)
+        ops.lap("ffn_up")   # with the norm before it where that is the product's prologue, and the activation
         ops.linear(h, self.w_down, None, out=residual, accumulate=True)
+        ops.lap("ffn_down")

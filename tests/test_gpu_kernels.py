@@ -304,6 +304,65 @@ def test_decode_attention_streamed_shares(ops, heads, kv_heads, hd, window):
     assert float(worst.max()) <= 1e-2, f"sequence {int(worst.argmax())} of {lens[int(worst.argmax())]} positions: {float(worst.max())}"
 
 
+@pytest.mark.parametrize("heads,kv_heads,hd", [(14, 2, 64), (8, 2, 128), (3, 1, 32), (10, 5, 48)])
+@pytest.mark.parametrize("window", [64, 100, 700, 704])
+@pytest.mark.parametrize("many", [False, True])
+def test_decode_attention_at_the_windows_lower_edge(ops, heads, kv_heads, hd, window, many):
+    """The first key a query may see and the one just before it. Every position 0..n-1 is written into the ring in
+    order, so the places outside the window hold real, older rows. A key that outweighs all others sits at the
+    window's first position in the even sequences (its value must come through) and one position earlier in the
+    odd ones (nothing of it may). Windows that fill their ring (64, 704) and windows that leave stale rows in it
+    (100 in 128, 700 in 704); starts that are no multiple of 16; few sequences (one buffer per CTA) and many (shares
+    streamed tile by tile)."""
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    g = torch.Generator().manual_seed(17)
+    B = 320 // kv_heads if many else 4
+    ring = ((window + PAGE_SIZE - 1) // PAGE_SIZE) * PAGE_SIZE
+    lens = [int(x) for x in torch.randint(window + 1, window + 400, (B,), generator=g)]
+    lens[0], lens[1] = window + 1, window + 2          # the window has just begun to slide
+    pages_per_seq = ring // PAGE_SIZE
+    table = torch.randperm(B * pages_per_seq, generator=g).to(torch.int32).view(B, pages_per_seq)
+    k_pool = torch.zeros((B * pages_per_seq, kv_heads, PAGE_SIZE, hd), dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    q = torch.randn((B, heads, hd), generator=g).to(torch.bfloat16)
+    q[:, :, 0] = 8.0
+    want = torch.zeros((B, heads, hd), dtype=torch.float64)
+    scale = 1.0 / math.sqrt(hd)
+    for b, n in enumerate(lens):
+        k = torch.randn((n, kv_heads, hd), generator=g).to(torch.bfloat16)
+        v = torch.randn((n, kv_heads, hd), generator=g).to(torch.bfloat16)
+        start = n - window
+        heavy = start if b % 2 == 0 else start - 1
+        k[heavy] = 0
+        k[heavy, :, 0] = 30.0                      # score 240 * scale against scores of a few units
+        v[heavy] = 5.0
+        for p in range(n):                         # in order: later positions take the places of earlier ones
+            page = int(table[b, (p % ring) // PAGE_SIZE])
+            k_pool[page, :, p % PAGE_SIZE] = k[p]
+            v_pool[page, :, p % PAGE_SIZE] = v[p]
+        for h in range(heads):
+            kh = h // (heads // kv_heads)
+            pr = torch.softmax((k[start:, kh].double() @ q[b, h].double()) * scale, dim=0)
+            want[b, h] = pr @ v[start:, kh].double()
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    slot_ids = torch.arange(B, dtype=torch.int32).cuda()
+    got = ops.attention_decode(q.cuda(), positions, slot_ids, scale, window, k_pool.cuda(), v_pool.cuda(), table.cuda(), ring,
+                               kv_heads, max(lens)).double().cpu()
+    ops.check_error_flag()
+    plain = ops.attention_plain(q.cuda(), positions, scale, window, k_pool=k_pool.cuda(), v_pool=v_pool.cuda(),
+                                page_table=table.cuda(), ring=ring, token_slot=slot_ids, kv_heads=kv_heads).double().cpu()
+    for b in range(B):
+        if b % 2 == 0:
+            assert float((want[b] - 5.0).abs().max()) < 1e-3           # the case is what it is meant to be
+        else:
+            assert float(want[b].abs().max()) < 4.5
+    for name, out in (("cluster kernel", got), ("plain kernel", plain)):
+        worst = (out - want).abs().amax(dim=(1, 2))
+        b = int(worst.argmax())
+        assert float(worst.max()) <= 2e-2, f"{name}: sequence {b} ({lens[b]} positions, heavy key " \
+            f"{'at' if b % 2 == 0 else 'before'} the window's start): off by {float(worst.max()):.3g}"
+
+
 # ---- products over a handful of tokens -----------------------------------------------------
 @pytest.mark.parametrize("T", [1, 3, 8, 9, 16, 32])
 @pytest.mark.parametrize("N,K", [(896, 896), (100, 72), (151, 4864), (1000, 136)])
