@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the Qwen2.5-0.5B-shaped model with random weights on
 one B200, as one JSON line.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--dtype bfloat16|float32] [--impl reference]
 
 A step is one decode step of the whole batch (default: 8 sequences that each hold a
 2,048-token prompt, context 4,096). ``value`` is decoded tokens a second timed on the device
@@ -10,6 +10,10 @@ with CUDA events around K graph replays plus the greedy choice that feeds the ne
 ``e2e`` is the same through ``Model.generate`` with token ids on the host going in and
 coming out. Each decode step reads every weight (~1 GB) and the live cache, more than the
 126 MB of L2, so no flush is needed between steps.
+
+``--impl reference`` times ktfth/smolmoe-c99 itself: the unmodified tree under ``baseline/_ref`` is built with its
+own Makefile and its command line runs a random checkpoint of the same shape (its format: Q8 weights) on the CPU,
+one sequence at a time, which is all it can do.
 """
 import argparse
 import json
@@ -122,6 +126,166 @@ def decode_tokens_per_second(engine, slots, steps, warmup):
     return len(slots) * 1000.0 / ms, ms
 
 
+# ---- the reference arm -------------------------------------------------------------------------------------------
+REF_RECORD = "<40sIIIIQQ"   # a tensor record of the reference's container (tools/checkpoint.py:19 of the reference)
+
+
+def write_reference_checkpoint(folder, cfg, prompt_len, seed=0):
+    """A random checkpoint of the configuration's shape in the reference's own formats, written with numpy (its
+    tools/checkpoint.py does the same row by row in pure Python, which takes hours at this size): the Q8 container
+    (docs/FORMAT.md of the reference: 36-byte blocks of a float scale and 32 int8, tensors sorted by name, the tied
+    head an alias of the embedding), config.ini, a tokenizer whose merges all begin with byte 0, and a prompt of
+    ``prompt_len - 1`` bytes that are never 0: one token a byte after the BOS token it puts first. Weights are
+    N(0, 0.02) rounded to the Q8 grid; the embedding rows of BOS and EOS are zero, so EOS never wins."""
+    import struct
+    import numpy as np
+    d, h, v, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    heads, kv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    if cfg["head_dim"] * heads != d or d % 32 or h % 32:
+        raise ValueError("the reference's Qwen2 layout needs head_dim = hidden / heads and widths that are multiples of 32")
+    kd = kv * (d // heads)
+    tied = bool(cfg["tie_word_embeddings"])
+    specs = {"embed": (v, d, 1), "final_norm": (1, d, 0), "lm_head": (v, d, 1)}
+    for layer in range(L):
+        q = f"l.{layer}."
+        specs.update({q + "attn_norm": (1, d, 0), q + "ffn_norm": (1, d, 0), q + "q": (d, d, 1), q + "k": (kd, d, 1),
+                      q + "v": (kd, d, 1), q + "o": (d, d, 1), q + "router": (1, d, 1), q + "q_bias": (1, d, 0),
+                      q + "k_bias": (1, kd, 0), q + "v_bias": (1, kd, 0), q + "e.0.gate": (h, d, 1), q + "e.0.up": (h, d, 1),
+                      q + "e.0.down": (d, h, 1)})
+    specs = dict(sorted(specs.items()))
+    rng = np.random.default_rng(seed)
+    block = np.dtype([("scale", "<f4"), ("q", "i1", (32,))])
+    record = struct.Struct(REF_RECORD)
+    entries, extents = [], {}
+    with open(os.path.join(folder, "model.smoe"), "wb") as f:
+        f.write(b"SMOEQ8\0" + (b"\2" if tied else b"\1") + struct.pack("<II", len(specs), 0))
+        f.seek(16 + record.size * len(specs))
+        for name, (rows, cols, q8) in specs.items():
+            if tied and name == "lm_head":
+                entries.append(record.pack(name.encode(), rows, cols, q8, 1, *extents["embed"]))
+                continue
+            offset = f.tell()
+            if q8:
+                for first in range(0, rows, 8192):
+                    n = min(rows - first, 8192)
+                    a = np.zeros((n, cols // 32), dtype=block)
+                    if not name.endswith("router"):          # a dense model's router is zero (scripts/hf/qwen2.ts:170)
+                        a["scale"] = 0.02 / 40.0
+                        a["q"] = np.clip(np.rint(rng.standard_normal((n, cols // 32, 32), dtype=np.float32) * 40), -127, 127)
+                    if name in ("embed", "lm_head") and first == 0:
+                        a["q"][256:258] = 0
+                    f.write(a.tobytes())
+            else:
+                vals = np.ones((rows, cols), "<f4") if name.endswith("norm") else (rng.standard_normal((rows, cols)) * 0.02).astype("<f4")
+                f.write(vals.tobytes())
+            extents[name] = (offset, f.tell() - offset)
+            entries.append(record.pack(name.encode(), rows, cols, q8, 0, *extents[name]))
+        f.seek(16)
+        f.write(b"".join(entries))
+    ini = dict(architecture="smolmoe_qwen2", dim=d, hidden_dim=h, layers=L, heads=heads, kv_heads=kv, experts=1, top_k=1,
+               vocab_size=v, max_context=cfg["max_position_embeddings"], shared_experts=0, bos_id=256, eos_id=257,
+               rms_eps=cfg["rms_norm_eps"], rope_theta=int(cfg["rope_theta"]))
+    with open(os.path.join(folder, "config.ini"), "w") as f:
+        f.write("".join(f"{k}={val}\n" for k, val in ini.items()))
+    # vocab - 258 merges (src/tokenizer.c:138-178 of the reference): (0, x), then (a token made so, x), ...: none can
+    # apply to a text without byte 0
+    lines, firsts, nxt = [], [0], 258
+    while len(lines) < v - 258:
+        made = []
+        for a in firsts:
+            for x in range(256):
+                if len(lines) == v - 258:
+                    break
+                lines.append(f"{a} {x}")
+                made.append(nxt)
+                nxt += 1
+        firsts = made
+    with open(os.path.join(folder, "tokenizer.bpe"), "w") as f:
+        f.write("SMBPE1\n" + "\n".join(lines) + "\n")
+    with open(os.path.join(folder, "prompt.bin"), "wb") as f:
+        f.write(bytes(np.random.default_rng(seed + 1).integers(1, 256, size=prompt_len - 1, dtype=np.uint8).tolist()))
+
+
+def reference_arm(args) -> int:
+    """Builds and times the reference. Prints one JSON line; exits 0 whether or not it could be measured."""
+    import shutil
+    import tempfile
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    if args.gpus != 1:
+        return unavailable("ktfth/smolmoe-c99 is a CPU program for one sequence; there is nothing to run on several GPUs")
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.exists(os.path.join(ref, "src", "main.c")):
+        source = "/root/reference"
+        if not os.path.exists(os.path.join(source, "src", "main.c")):
+            return unavailable("no copy of ktfth/smolmoe-c99 under baseline/_ref and none to copy from")
+        shutil.copytree(source, ref, ignore=shutil.ignore_patterns(".git"), dirs_exist_ok=True)
+    if not shutil.which("make") or not (shutil.which("cc") or shutil.which("gcc")):
+        return unavailable("this machine has no make or no C compiler to build ktfth/smolmoe-c99's command line with")
+    raw = base_config()
+    if args.shape != "0.5b":
+        raw.update(OTHER_SHAPES[args.shape])
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    raw["max_position_embeddings"] = args.context
+    if raw["head_dim"] * raw["num_attention_heads"] != raw["hidden_size"]:
+        return unavailable("the reference's smolmoe_qwen2 layout has head_dim = hidden / heads; this shape has not")
+    work = tempfile.mkdtemp(prefix="smolmoe_ref_")
+    try:
+        build = os.path.join(work, "build")
+        binary = os.path.join(build, "smolmoe")
+        made = subprocess.run(["make", "-C", ref, f"BUILD={build}", binary], capture_output=True, text=True)
+        if made.returncode != 0 or not os.path.exists(binary):
+            return unavailable("ktfth/smolmoe-c99's Makefile did not build its command line here: " +
+                               (made.stderr.strip().splitlines() or ["no message"])[-1][:200])
+        write_reference_checkpoint(work, raw, args.prompt_len)
+        env = dict(os.environ, SMOLMOE_KV_CACHE="0")
+        runs = []
+        # its stock path: default threads (physical cores), default --batch 32, greedy; one sequence a run
+        for tokens in (max(2, min(args.warmup, 4) + 1), args.steps + 1) + ((args.steps + 1,) if args.steps <= 64 else ()):
+            stats_file = os.path.join(work, "stats.json")
+            run = subprocess.run([binary, "--model", os.path.join(work, "model.smoe"), "--config", os.path.join(work, "config.ini"),
+                                  "--tokenizer", os.path.join(work, "tokenizer.bpe"), "--prompt-file", os.path.join(work, "prompt.bin"),
+                                  "--tokens", str(tokens), "--context", str(args.context), "--stats", stats_file],
+                                 capture_output=True, env=env)   # (its output is the generated bytes: no text)
+            if run.returncode != 0:
+                return unavailable("ktfth/smolmoe-c99's command line failed on the random checkpoint: " +
+                                   (run.stderr.decode("utf-8", "replace").strip().splitlines() or ["no message"])[-1][:200])
+            with open(stats_file) as f:
+                runs.append(json.load(f))
+        timed = runs[1:]
+        best = max(timed, key=lambda r: r["decode_tokens_per_second"])
+        B = args.batch
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+    value = best["decode_tokens_per_second"]
+    line = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": B * 1000.0 / value if value else None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "q8 weights and activations, float accumulation (the reference's only format)",
+        "data": "synthetic: uniform random byte tokens (seed 1), random weights N(0, 0.02) on the Q8 grid (seed 0)",
+        "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "global_batch": B, "seq_len": args.context,
+                   "prompt_len": args.prompt_len, "parallelism": "none (CPU threads)", "layers": raw["num_hidden_layers"],
+                   "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+                   "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"], "backend": best["backend"],
+                   "threads": best["threads"],
+                   "same_config": "same layer sizes, prompt length and context; Q8 instead of bfloat16; a CPU program that holds "
+                                  "one sequence: a batch of B is B runs one after another, so tokens a second do not grow with B"},
+        "e2e": {"value": best["generated_tokens"] / best["decode_seconds"] if best["decode_seconds"] else None, "unit": "tok/s",
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "note": "its command line from prompt bytes to token ids on the host; no device is involved"},
+        "gpu_launches": 0,
+        "prefill": {"value": best["prefill_tokens_per_second"], "tokens": best["prompt_tokens"], "ms": best["prefill_seconds"] * 1000.0},
+        "points": {"decode_b1": value},
+        "impl": "reference",
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -140,11 +304,11 @@ def main() -> int:
     ap.add_argument("--profile-region", choices=["decode", "prefill"], default=None,
                     help="for ncu --profile-from-start off: run only this region between cudaProfilerStart/Stop "
                          "(decode: 2 eager steps of the batch; prefill: one 2,048-token prompt) and exit")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
+                    help="float32: the true 32-bit path of the whole model (reported under its own metric name)")
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "ktfth/smolmoe-c99 is a C99 CPU program with no Python package (no setup.py/pyproject.toml): pip install fails offline and online alike; it has no GPU path"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not measured")
         return 2
@@ -171,7 +335,10 @@ def main() -> int:
     with tempfile.TemporaryDirectory(prefix="bench_model_") as tmp:
         write_random_model(cfg, tmp, seed=0)
         biggest = B if args.no_points else max(B, 64)
-        model = Model.from_folder(tmp, "bfloat16", context=C, batch=biggest)
+        model = Model.from_folder(tmp, args.dtype, context=C, batch=biggest)
+        model32 = None
+        if args.dtype == "bfloat16" and not args.no_points and not args.profile_region:
+            model32 = Model.from_folder(tmp, "float32", context=C, batch=B)   # the true 32-bit path, for two more points
     engine = model.engine
     V = cfg.vocab_size
 
@@ -224,7 +391,9 @@ def main() -> int:
         engine.close_sequence(s)
     pre_ms = sorted(t_ms)[reps // 2]
     prefill = {"value": P * 1000.0 / pre_ms, "tokens": P, "ms": pre_ms,
-               "frac": prefill_flops(raw, P) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+               "frac": prefill_flops(raw, P) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12) if args.dtype == "bfloat16" else None}
+    if args.dtype == "float32":
+        prefill["note"] = "CUDA-core float FMA, no tensor-core mode: no measured peak to set it against"
 
     # ---- launches of one decode step (counted on an eager step) ----------------------------
     slots = open_and_prefill(B)
@@ -263,19 +432,39 @@ def main() -> int:
             points[f"decode_b{n}"], _ = decode_tokens_per_second(engine, sl, args.steps, args.warmup)
             close(sl)
     engine.check_status()
+    l2_note = f"each step reads {engine.weight_bytes() / 1e9:.2f} GB of weights plus the cache (> 126 MB L2); no flush"
+    if model32 is not None:
+        # the same model in true 32-bit (float weights, cache and FMA chains): prefill of one prompt and decode at B
+        del model, engine
+        torch.cuda.empty_cache()
+        e32 = model32.engine
+        for timed in (False, True):
+            s = e32.open_sequence()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); e32.step([s], one); e1.record()
+            torch.cuda.synchronize()
+            e32.close_sequence(s)
+        points["float32_prefill"] = P * 1000.0 / e0.elapsed_time(e1)
+        sl = [e32.open_sequence() for _ in range(B)]
+        e32.step(sl, prompts(B))
+        points[f"float32_decode_b{B}"], _ = decode_tokens_per_second(e32, sl, min(args.steps, 64), 3)
+        for s in sl:
+            e32.close_sequence(s)
+        e32.check_status()
+    dtype_word = "bf16" if args.dtype == "bfloat16" else "float32"
 
     line = {
-        "metric": METRIC if (args.shape, B, P, C, args.prompt_min) == ("0.5b", 8, 2048, 4096, None) else
-        f"decode tok/s at batch {B} (Qwen2.5-{args.shape.upper()} shape, bf16, prompts of up to {P} tokens, context {C})",
+        "metric": METRIC if (args.shape, B, P, C, args.prompt_min, args.dtype) == ("0.5b", 8, 2048, 4096, None, "bfloat16") else
+        f"decode tok/s at batch {B} (Qwen2.5-{args.shape.upper()} shape, {dtype_word}, prompts of up to {P} tokens, context {C})",
         "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_word,
         "data": "synthetic: uniform random token ids (seed 0), random weights N(0, 0.02) (seed 0)",
         "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "global_batch": B, "seq_len": C, "prompt_len": P,
                    "prompt_min": args.prompt_min if args.prompt_min is not None else P, "parallelism": "none (1 GPU)",
                    "layers": raw["num_hidden_layers"], "layers_of_configuration": layers_full, "hidden": raw["hidden_size"],
                    "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
                    "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"], "tied_embeddings": bool(raw["tie_word_embeddings"]),
-                   "l2": f"each step reads {engine.weight_bytes() / 1e9:.2f} GB of weights plus the cache (> 126 MB L2); no flush"},
+                   "l2": l2_note},
         "clocks": clock_summary, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
         "launches_per_step": launches_per_step, "prefill": prefill, "roofline": roofline, "points": points,
         "impl": "ours",
