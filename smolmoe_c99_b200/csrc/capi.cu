@@ -246,3 +246,47 @@ SM_API int sm_gemm_skinny_qkv(const void* x, const void* norm_w, int norm_w_dt, 
                         (sm::DType)bias_dt, nullptr, sm::BF16, 0, &rope, (cudaStream_t)stream);
     });
 }
+
+// The fused decode step. `layers` points at a device array of n_layers records of 16 8-byte words each:
+// w_qkv, b_qkv, w_o, w_gate_up, w_down, norm1, norm2, k_pool, v_pool, page_table, cos, sin (pointers), then
+// (table_stride, ring), (window, eps1 as float bits), (eps2 as float bits, 0) packed as pairs of 32-bit words.
+SM_API int sm_decode_fused_refusal(int T, int D, int H, int heads, int kv_heads, int head_dim, int V) {
+    const char* why = sm::decode_fused_refusal(T, D, H, heads, kv_heads, head_dim, V);
+    if (why) g_last_error = std::string("decode_fused takes ") + why;
+    return why ? 1 : 0;
+}
+
+SM_API int sm_decode_fused_splits(int T, int kv_heads) { return sm::decode_fused_splits(T, kv_heads); }
+
+SM_API int sm_decode_fused_layer_bytes() { return (int)sizeof(sm::FusedLayer); }
+
+SM_API int sm_decode_fused_blocks(int D, int H, int heads, int kv_heads, int head_dim, int V, int* bk) {
+    return guarded([&] { sm::decode_fused_blocks(D, H, heads, kv_heads, head_dim, V, bk); });
+}
+
+// Writes the 128-byte tensor map of a [rows, K] bfloat16 weight matrix to host memory at `out`.
+SM_API int sm_decode_fused_encode_map(void* out, const void* w, long long rows, int K, int bk) {
+    return guarded([&] { sm::decode_fused_encode_map(out, w, rows, K, bk); });
+}
+
+SM_API int sm_decode_fused(const void* layers, const void* maps, const int* bk, int n_layers, int T, int D, int H, int heads, int kv_heads, int head_dim, int V,
+                           const void* embed, const void* head, const void* norm_f, float eps_f, float scale,
+                           const int32_t* tokens, const int32_t* positions, const int32_t* token_slot, const int32_t* rows,
+                           int n_rows, int att_splits, float* residual, void* q, void* att, void* h, float* att_parts,
+                           int* att_counters, unsigned int* barrier, float* logits, int* error, int32_t* status,
+                           long long* trace, void* stream) {
+    return guarded([&] {
+        sm::FusedArgs a{};
+        a.layers = (const sm::FusedLayer*)layers; a.n_layers = n_layers;
+        a.maps = maps;
+        for (int k = 0; k < 5; ++k) a.bk[k] = bk[k];
+        a.T = T; a.D = D; a.H = H; a.heads = heads; a.kv_heads = kv_heads; a.head_dim = head_dim; a.V = V;
+        a.embed = (const __nv_bfloat16*)embed; a.head = (const __nv_bfloat16*)head; a.norm_f = (const __nv_bfloat16*)norm_f;
+        a.eps_f = eps_f; a.scale_log2 = scale * 1.4426950408889634f;
+        a.tokens = tokens; a.positions = positions; a.token_slot = token_slot; a.rows = rows; a.n_rows = n_rows;
+        a.att_splits = att_splits; a.residual = residual; a.q = (__nv_bfloat16*)q; a.att = (__nv_bfloat16*)att;
+        a.h = (__nv_bfloat16*)h; a.att_parts = att_parts; a.att_counters = att_counters; a.barrier = barrier;
+        a.logits = logits; a.error = error; a.status = status; a.trace = trace;
+        sm::decode_fused(a, (cudaStream_t)stream);
+    });
+}

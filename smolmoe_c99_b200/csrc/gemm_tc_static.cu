@@ -59,6 +59,9 @@ extern "C" __attribute__((visibility("default")))
 int sm_gemm_tc_static(const void* x, const void* w, const void* bias, int bias_dt, void* out, int out_dt, int T, int N,
                       int K, int mode, int up_offset, int* error, void* stream) {
     try {
+        if (T <= 0 || N <= 0)
+            throw std::invalid_argument("sm_gemm_tc_static: T = " + std::to_string(T) + " and N = " + std::to_string(N) +
+                                        " must be positive");
         if (!sm::gemm_tc_supports(T, N, K))
             throw std::invalid_argument("sm_gemm_tc_static: K = " + std::to_string(K) + " must be a positive multiple of 8");
         const size_t need = sm::gemm_tc_workspace_bytes(T, N, K, mode == 2);
@@ -86,8 +89,14 @@ extern "C" __attribute__((visibility("default")))
 int sm_gemm_tc_static_error(void) {
     try {
         int value = 0;
-        cudaError_t e = cudaMemcpy(&value, device_pointers().error, sizeof(int), cudaMemcpyDeviceToHost);
+        int* word = device_pointers().error;
+        cudaError_t e = cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) throw std::runtime_error(std::string("CUDA: ") + cudaGetErrorString(e));
+        if (value != 0) {
+            // read once, then cleared: the next call starts clean (cudaMemset allocates nothing)
+            e = cudaMemset(word, 0, sizeof(int));
+            if (e != cudaSuccess) throw std::runtime_error(std::string("CUDA: ") + cudaGetErrorString(e));
+        }
         return value;
     } catch (const std::exception& ex) {
         sm::set_last_error(ex.what());

@@ -4,6 +4,7 @@
 // with the size in the message rather than compute a wrong result.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -190,6 +191,67 @@ void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, 
                       const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
                       const int32_t* page_table, int table_stride, int ring, int max_len, long long pool_pages,
                       cudaStream_t stream);
+
+// ---- decode_fused.cu ------------------------------------------------------------------
+// One decode step (every sequence goes on by one token) of a stack of standard layers -- RMSNorm, attention with
+// q/k/v bias and full rotation over the paged cache, RMSNorm, gated feed-forward with SiLU -- with final norm and
+// output head, in one persistent kernel for up to 16 tokens; bfloat16 weights, norm weights, biases and cache.
+struct FusedLayer {                  // one per run of a layer, in run order, in device memory
+    const __nv_bfloat16* w_qkv;      // [(heads + 2 kv_heads) * head_dim, D]
+    const __nv_bfloat16* b_qkv;      // [(heads + 2 kv_heads) * head_dim] or null
+    const __nv_bfloat16* w_o;        // [D, heads * head_dim]
+    const __nv_bfloat16* w_gate_up;  // [2 H, D]: gate rows, then up rows
+    const __nv_bfloat16* w_down;     // [D, H]
+    const __nv_bfloat16* norm1;      // [D] before the attention
+    const __nv_bfloat16* norm2;      // [D] before the feed-forward
+    __nv_bfloat16* k_pool;           // this run's page pools
+    __nv_bfloat16* v_pool;
+    const int32_t* page_table;       // [slots, table_stride]
+    const float* cos_table;          // [positions, head_dim / 2]
+    const float* sin_table;
+    int table_stride, ring, window;  // window 0: every key
+    float eps1, eps2;
+    int pad_;
+};
+struct FusedArgs {
+    const FusedLayer* layers;
+    int n_layers;
+    const void* maps;                // device array of 4 * n_layers + 1 tensor maps (decode_fused_encode_map), 128 bytes each:
+                                     // per layer q/k/v, o, gate/up, down; then the head
+    int bk[5];                       // blocks of K a copy of each kind brings (decode_fused_blocks; the maps' boxes)
+    int T, D, H, heads, kv_heads, head_dim, V;
+    const __nv_bfloat16* embed;      // [V, D]
+    const __nv_bfloat16* head;       // [V, D] (the embedding again when tied)
+    const __nv_bfloat16* norm_f;     // [D]
+    float eps_f;
+    float scale_log2;                // attention scale * log2(e)
+    const int32_t* tokens;           // [T]
+    const int32_t* positions;        // [T]
+    const int32_t* token_slot;       // [T]
+    const int32_t* rows;             // [n_rows] tokens whose logits are wanted
+    int n_rows;
+    int att_splits;                  // parts a (sequence, kv head) is cut into (decode_fused_splits)
+    // scratch, all in device memory: float residual [T, D]; q, att [T, heads * head_dim]; h [T, H];
+    // att_parts [T * kv_heads * att_splits * 16 * (head_dim + 2)] floats; att_counters [T * kv_heads] zeros;
+    // barrier: 4 words, zero before the first launch (and after a launch that reported an error)
+    float* residual;
+    __nv_bfloat16* q;
+    __nv_bfloat16* att;
+    __nv_bfloat16* h;
+    float* att_parts;
+    int* att_counters;
+    unsigned int* barrier;
+    float* logits;                   // [n_rows, V]
+    int* error;                      // a bounded wait that ran out leaves a code here (nullable)
+    int32_t* status;                 // |= 1 for a token outside the vocabulary (nullable)
+    long long* trace;                // nullable: CTA 0 leaves the GPU's nanosecond timer here after every phase
+};
+// null if the kernel takes these sizes, else what it takes instead (for the caller's message or fallback)
+const char* decode_fused_refusal(int T, int D, int H, int heads, int kv_heads, int head_dim, int V);
+int decode_fused_splits(int T, int kv_heads);
+void decode_fused_blocks(int D, int H, int heads, int kv_heads, int head_dim, int V, int bk[5]);
+void decode_fused_encode_map(void* out, const void* w, long long rows, int K, int bk);
+void decode_fused(const FusedArgs& a, cudaStream_t stream);
 
 // ---- sampling.cu ----------------------------------------------------------------------
 // out[b] = argmax over the allowed ids of logits[b, :], the lowest id on ties

@@ -19,16 +19,22 @@
 //  * A shape that needs more scratch than the array holds is refused with status 1 and a
 //    message from sm_last_error() that names the bytes needed and the limit; nothing runs.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress,
-//    with that device current) and remembers it. Make that first call outside any stream
-//    capture. Later calls on the same device do no set-up.
-//  * No call allocates or frees: no cudaMalloc, cudaFree, or library routine that does.
+//    with that device current) and remembers it. Make that first call at start-up: outside
+//    any stream capture, and before the stretch of the program in which nothing may be
+//    allocated. Where the CUDA runtime loads modules lazily, that first call is also when
+//    this library's module, and with it the 4 MiB array, comes to lie on the device (an
+//    allocation and a synchronisation by the runtime, once). Later calls on the same device
+//    do no set-up.
+//  * After that, no call allocates or frees: no cudaMalloc, cudaFree, or library routine that
+//    does.
 //  * All calls on a device share the one array, and it keeps whatever the last call left in
 //    it. Nothing in it has to start at zero (every partial sum that is read was written by
 //    the same call), so it is never cleared. Two calls whose kernels may run at the same time
 //    (different streams, or one stream without ordering between them) race on it: keep calls
 //    on one stream, or order them with events.
 //  * `error` may be null; then a word beside the scratch array receives the code of a
-//    bounded wait that ran out, readable with sm_gemm_tc_static_error().
+//    bounded wait that ran out. sm_gemm_tc_static_error() reads it and, if it was set, clears
+//    it: an error is reported once.
 #pragma once
 
 #include <stddef.h>
@@ -44,7 +50,8 @@ extern "C" {
 int sm_gemm_tc_static(const void* x, const void* w, const void* bias, int bias_dt, void* out, int out_dt, int T, int N,
                       int K, int mode, int up_offset, int* error, void* stream);
 
-// The error word used when `error` was null, read back to the host (synchronises the device).
+// The error word used when `error` was null, read back to the host (synchronises the device)
+// and cleared if it was set. -1: the read itself failed (see sm_last_error()).
 int sm_gemm_tc_static_error(void);
 
 #ifdef __cplusplus

@@ -50,6 +50,7 @@ class DecoderModel:
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, runtime)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
+        self._fused = {}     # per cache: what the fused decode step needs, or None where the model is not its case
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.embedding = tensors[self.spec.embedding_name]
@@ -60,10 +61,80 @@ class DecoderModel:
         # a tied head is the same device buffer as the embedding (src/modelfile.c:25-34)
         self.head = self.embedding if self.spec.head_name is None else tensors[self.spec.head_name]
 
+    # ---- a decode step of standard layers in one kernel ---------------------------------------------------
+    def _fused_plan(self, cache):
+        """The layer records of the fused decode step for this cache, built once: every run of ``order`` must be a
+        layer whose parts describe themselves to that kernel, all with the same sizes, in bfloat16."""
+        key = id(cache)
+        if key in self._fused:
+            return self._fused[key]
+        self._fused[key] = None
+        ops, rt = self.runtime.ops, self.runtime
+        if rt.dtype != torch.bfloat16 or not hasattr(self.final_norm, "fused_decode_record"):
+            return None
+        records = []
+        for run, index in enumerate(self.spec.order):
+            block = self.blocks[index]
+            rec = block.fused_decode_record(cache.run_view(run)) if hasattr(block, "fused_decode_record") else None
+            if rec is None:
+                return None
+            records.append(rec)
+        final = self.final_norm.fused_decode_record()
+        if final is None or not records:
+            return None
+        m0, f0 = records[0]["mixer"], records[0]["ffn"]
+        sizes = {"D": m0["hidden"], "H": f0["intermediate"], "heads": m0["heads"], "kv_heads": m0["kv_heads"],
+                 "head_dim": m0["head_dim"], "V": self.spec.vocab_size}
+        tensors = [self.embedding, self.head, final[0]]
+        for rec in records:
+            m, f = rec["mixer"], rec["ffn"]
+            same = (m["hidden"], m["heads"], m["kv_heads"], m["head_dim"], m["scale"], f["hidden"], f["intermediate"]) == \
+                   (sizes["D"], sizes["heads"], sizes["kv_heads"], sizes["head_dim"], m0["scale"], sizes["D"], sizes["H"])
+            if not same or m["k_pool"].dtype != torch.bfloat16:
+                return None
+            tensors += [m["w_qkv"], m["w_o"], f["w_gate_up"], f["w_down"], rec["norm1"][0], rec["norm2"][0]]
+            if m["b_qkv"] is not None:
+                tensors.append(m["b_qkv"])
+        if any(t.dtype != torch.bfloat16 or not t.is_contiguous() for t in tensors):
+            return None
+        if ops.decode_fused_refusal(1, sizes["D"], sizes["H"], sizes["heads"], sizes["kv_heads"], sizes["head_dim"], sizes["V"]):
+            return None
+        from ..kernels.ops import FusedLayerRecord
+        import ctypes
+        table = (FusedLayerRecord * len(records))()
+        for out, rec in zip(table, records):
+            m, f = rec["mixer"], rec["ffn"]
+            out.w_qkv, out.w_o, out.w_gate_up, out.w_down = m["w_qkv"].data_ptr(), m["w_o"].data_ptr(), f["w_gate_up"].data_ptr(), f["w_down"].data_ptr()
+            out.b_qkv = m["b_qkv"].data_ptr() if m["b_qkv"] is not None else None
+            out.norm1, out.norm2 = rec["norm1"][0].data_ptr(), rec["norm2"][0].data_ptr()
+            out.k_pool, out.v_pool, out.page_table = m["k_pool"].data_ptr(), m["v_pool"].data_ptr(), m["page_table"].data_ptr()
+            out.cos_table, out.sin_table = m["cos"].data_ptr(), m["sin"].data_ptr()
+            out.table_stride, out.ring, out.window = m["page_table"].shape[1], m["ring"], m["window"]
+            out.eps1, out.eps2 = rec["norm1"][1], rec["norm2"][1]
+        layers = torch.frombuffer(bytearray(bytes(table)), dtype=torch.uint8).to(rt.device)
+        weights = [w for rec in records for w in (rec["mixer"]["w_qkv"], rec["mixer"]["w_o"], rec["ffn"]["w_gate_up"],
+                                                   rec["ffn"]["w_down"])] + [self.head]
+        maps, bk = ops.decode_fused_maps(weights, sizes, rt.device)
+        plan = {"layers": layers, "maps": maps, "bk": bk, "n_layers": len(records), "sizes": sizes, "norm_f": final[0], "eps_f": final[1],
+                "scale": m0["scale"], "keep": records,
+                "scratch": ops.decode_fused_scratch(sizes["D"], sizes["H"], sizes["heads"], sizes["kv_heads"],
+                                                    sizes["head_dim"], sizes["V"], rt.device)}
+        self._fused[key] = plan
+        return plan
+
     def forward(self, step, cache, want_rows: Optional[torch.Tensor], status: Optional[torch.Tensor] = None):
         """Runs the step's tokens through every layer; returns float logits ``[wanted, vocab]``
         for the packed token indices in ``want_rows`` (int32), or None when none are wanted."""
         ops = self.runtime.ops
+        if (step.mode == "decode" and step.n_tokens <= 16 and getattr(ops, "use_fused_decode", False)
+                and ops.phase_times is None):
+            plan = self._fused_plan(cache)
+            if plan is not None and not ops.decode_fused_refusal(step.n_tokens, *[plan["sizes"][k] for k in
+                                                                 ("D", "H", "heads", "kv_heads", "head_dim", "V")]):
+                rows = want_rows if want_rows is not None and want_rows.numel() else None
+                return ops.decode_fused(plan["layers"], plan["maps"], plan["bk"], plan["n_layers"], plan["sizes"], self.embedding, self.head,
+                                        plan["norm_f"], plan["eps_f"], plan["scale"], step.tokens, step.positions,
+                                        step.token_slot, rows, plan["scratch"], status)
         ops.lap(None)
         residual = ops.embedding(self.embedding, step.tokens, status)
         ops.lap("embed")

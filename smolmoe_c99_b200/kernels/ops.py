@@ -69,6 +69,15 @@ class NormedRows:
         return self.done
 
 
+class FusedLayerRecord(ctypes.Structure):
+    """One layer of the fused decode step, as the kernel library lays it out (``sm::FusedLayer``)."""
+
+    _fields_ = [(name, ctypes.c_void_p) for name in ("w_qkv", "b_qkv", "w_o", "w_gate_up", "w_down", "norm1", "norm2",
+                                                     "k_pool", "v_pool", "page_table", "cos_table", "sin_table")] + \
+               [("table_stride", ctypes.c_int), ("ring", ctypes.c_int), ("window", ctypes.c_int),
+                ("eps1", ctypes.c_float), ("eps2", ctypes.c_float), ("pad_", ctypes.c_int)]
+
+
 class PhaseTimes:
     """Device time per phase of the forward pass, measured with CUDA events between ``lap`` calls (the reference's
     ``lap()``: src/model.c:312-328). Events only mark the stream; nothing computed changes."""
@@ -115,6 +124,10 @@ class Ops:
         self.use_fast_attention = fast  # False routes bfloat16 attention to the plain kernel
         self.use_tcgen05_attention = True  # False routes prefill attention to the mma.sync kernel
         self.use_skinny = fast  # False routes products over a handful of tokens to the general kernels
+        # True runs a decode step of standard layers (up to 16 sequences) as ONE persistent kernel. Off: as measured
+        # on a B200 it is correct but slower than the chain of separate kernels (see csrc/decode_fused.cu).
+        self.use_fused_decode = False
+        self._fused_barriers = []     # barrier words of the fused decode steps, put back to zero after an error
         # more tokens than this go to the tcgen05 kernel (the weight-streaming kernel itself takes up to 32; measured
         # on a B200 at 24 and 32 tokens it is 20-35% behind on every shape from 0.5B to 7B)
         self.skinny_max_tokens = 16
@@ -375,6 +388,8 @@ class Ops:
         code = int(self.error_flag.item())
         if code:
             self.error_flag.zero_()
+            for words in self._fused_barriers:
+                words.zero_()
             raise KernelError(f"a kernel's bounded wait ran out (code {code}); its output is not valid")
 
     # ---- attention ---------------------------------------------------------------------
@@ -492,6 +507,69 @@ class Ops:
             _ptr(slots), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), page_table.shape[1], ring, int(max_len),
             ctypes.c_longlong(k_pool.shape[0]), _stream()))
         return out
+
+    # ---- a whole decode step in one kernel ------------------------------------------------
+    def decode_fused_refusal(self, T, D, H, heads, kv_heads, head_dim, V) -> Optional[str]:
+        """None if the fused decode kernel takes these sizes, else the sizes it takes."""
+        if self.lib.sm_decode_fused_refusal(T, D, H, heads, kv_heads, head_dim, V):
+            return self.lib.sm_last_error().decode("utf-8", "replace")
+        return None
+
+    def decode_fused_scratch(self, D, H, heads, kv_heads, head_dim, V, device) -> dict:
+        """The buffers a model's fused decode steps share (for up to 16 tokens)."""
+        if ctypes.sizeof(FusedLayerRecord) != int(self.lib.sm_decode_fused_layer_bytes()):
+            raise KernelError("the layer record of the fused decode step is laid out differently in the library")
+        T = 16
+        out = {
+            "residual": torch.empty((T, D), dtype=torch.float32, device=device),
+            "q": torch.empty((T, heads * head_dim), dtype=torch.bfloat16, device=device),
+            "att": torch.empty((T, heads * head_dim), dtype=torch.bfloat16, device=device),
+            "h": torch.empty((T, H), dtype=torch.bfloat16, device=device),
+            "att_parts": torch.empty((T * kv_heads * 16 * 16 * (head_dim + 2),), dtype=torch.float32, device=device),
+            "att_counters": torch.zeros((T * kv_heads,), dtype=torch.int32, device=device),
+            "barrier": torch.zeros((4,), dtype=torch.int32, device=device),
+            "logits": torch.empty((T, V), dtype=torch.float32, device=device),
+        }
+        self._fused_barriers.append(out["barrier"])
+        return out
+
+    def decode_fused_maps(self, weights, sizes: dict, device) -> tuple:
+        """The tensor maps of a model's weight matrices for the fused decode step, in the order the kernel uses them
+        (``weights``: per layer q/k/v, o, gate/up, down; then the head), as a device tensor, and the blocks of K a
+        copy of each kind of product brings."""
+        bk = (ctypes.c_int * 5)()
+        self._check(self.lib.sm_decode_fused_blocks(sizes["D"], sizes["H"], sizes["heads"], sizes["kv_heads"],
+                                                     sizes["head_dim"], sizes["V"], bk))
+        host = ctypes.create_string_buffer(128 * len(weights) + 64)
+        base = (ctypes.addressof(host) + 63) // 64 * 64
+        for i, w in enumerate(weights):
+            _need(w, "weight", torch.bfloat16, 2)
+            kind = 4 if i == len(weights) - 1 else i % 4
+            self._check(self.lib.sm_decode_fused_encode_map(ctypes.c_void_p(base + 128 * i), _ptr(w),
+                                                             ctypes.c_longlong(w.shape[0]), w.shape[1], bk[kind]))
+        raw = ctypes.string_at(base, 128 * len(weights))
+        return torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device), [int(x) for x in bk]
+
+    def decode_fused(self, layers: torch.Tensor, maps: torch.Tensor, bk, n_layers: int, sizes: dict, embed, head, norm_f, eps_f: float, scale: float,
+                     tokens, positions, token_slot, rows: Optional[torch.Tensor], scratch: dict,
+                     status: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """One decode step of ``n_layers`` standard layers (records in ``layers``, a uint8 device tensor) with final
+        norm and output head; returns float logits ``[len(rows), V]`` (a view of the scratch) or None."""
+        T = tokens.numel()
+        n_rows = 0 if rows is None else rows.numel()
+        _need(tokens, "tokens", torch.int32, 1)
+        _need(positions, "positions", torch.int32, 1)
+        _need(token_slot, "token_slot", torch.int32, 1)
+        if rows is not None:
+            _need(rows, "rows", torch.int32, 1)
+        splits = int(self.lib.sm_decode_fused_splits(T, sizes["kv_heads"]))
+        self._check(self.lib.sm_decode_fused(
+            _ptr(layers), _ptr(maps), (ctypes.c_int * 5)(*bk), n_layers, T, sizes["D"], sizes["H"], sizes["heads"], sizes["kv_heads"], sizes["head_dim"], sizes["V"],
+            _ptr(embed), _ptr(head), _ptr(norm_f), ctypes.c_float(eps_f), ctypes.c_float(scale), _ptr(tokens), _ptr(positions),
+            _ptr(token_slot), _ptr(rows), n_rows, splits, _ptr(scratch["residual"]), _ptr(scratch["q"]), _ptr(scratch["att"]),
+            _ptr(scratch["h"]), _ptr(scratch["att_parts"]), _ptr(scratch["att_counters"]), _ptr(scratch["barrier"]),
+            _ptr(scratch["logits"]), _ptr(self.error_flag), _ptr(status), _ptr(scratch.get("trace")), _stream()))
+        return scratch["logits"][:n_rows] if n_rows else None
 
     # ---- sampling ----------------------------------------------------------------------
     def argmax(self, logits: torch.Tensor, banned: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):

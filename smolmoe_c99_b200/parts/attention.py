@@ -125,3 +125,15 @@ class Attention(Part):
             if start + n - cache.ring > oldest_needed:
                 raise RuntimeError(f"{n} tokens at position {start} have replaced keys of the windowed cache (ring "
                                    f"{cache.ring}) that the step's first query still sees: feed fewer tokens a step")
+
+    def fused_decode_record(self, cache):
+        """What a kernel that runs whole layers needs of this part and its cache, or None where the part is not the
+        plain case that kernel is written for (keys and values of its own, every dimension rotated)."""
+        if (type(self).forward is not Attention.forward or self.kv_from_cache or cache.kind != "kv"
+                or self.position.rotary_dim != self.head_dim):
+            return None
+        cos, sin = self.position.tables(self.runtime.max_positions)
+        return {"w_qkv": self.w_qkv, "b_qkv": self.b_qkv, "w_o": self.w_o, "hidden": self.hidden, "heads": self.heads,
+                "kv_heads": self.kv_heads, "head_dim": self.head_dim, "scale": self.scale, "window": self.window or 0,
+                "cos": cos, "sin": sin, "k_pool": cache.k_pool, "v_pool": cache.v_pool, "page_table": cache.page_table,
+                "ring": cache.ring}

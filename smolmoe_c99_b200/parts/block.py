@@ -56,3 +56,13 @@ class PreNormBlock:
         x = self.feed_forward_norm.forward(residual, lazy=lazy)
         ops.lap("norm")
         self.feed_forward.forward(x, residual, step)
+
+    def fused_decode_record(self, cache):
+        """This layer as the fused decode step takes it (see ``Ops.decode_fused``), or None if one of its parts has
+        no such description: x += mixer(norm(x)); x += ffn(norm(x)) with the parts' own records."""
+        parts = (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        if type(self).forward is not PreNormBlock.forward or not all(hasattr(part, "fused_decode_record") for part in parts):
+            return None
+        record = {"norm1": self.mixer_norm.fused_decode_record(), "mixer": self.mixer.fused_decode_record(cache),
+                  "norm2": self.feed_forward_norm.fused_decode_record(), "ffn": self.feed_forward.fused_decode_record()}
+        return None if any(v is None for v in record.values()) else record

@@ -40,3 +40,10 @@ class GatedMLP(Part):
         ops.lap("ffn_up")   # with the norm before it where that is the product's prologue, and the activation
         ops.linear(h, self.w_down, None, out=residual, accumulate=True)
         ops.lap("ffn_down")
+
+    def fused_decode_record(self):
+        """What a kernel that runs whole layers needs of this part; None for a subclass with a forward pass of its
+        own, which is not what that kernel computes."""
+        if type(self).forward is not GatedMLP.forward:
+            return None
+        return {"w_gate_up": self.w_gate_up, "w_down": self.w_down, "hidden": self.hidden, "intermediate": self.intermediate}

@@ -34,3 +34,10 @@ class RMSNorm(Part):
         if lazy:
             return self.runtime.ops.rmsnorm_lazy(residual, self.weight, self.eps, self.runtime.dtype, rows)
         return self.runtime.ops.rmsnorm(residual, self.weight, self.eps, self.runtime.dtype, rows)
+
+    def fused_decode_record(self):
+        """What a kernel that runs whole layers needs of this part: ``(weight, eps)``; None for a subclass with a
+        forward pass of its own, which is not what that kernel computes."""
+        if type(self).forward is not RMSNorm.forward:
+            return None
+        return self.weight, self.eps

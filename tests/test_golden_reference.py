@@ -14,11 +14,12 @@ import math
 import os
 import struct
 
+import pytest
 import torch
 
 import plain_model
 
-FIXTURE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_fixture")
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
 def read_container(path):
@@ -54,7 +55,11 @@ def unpermute_rows(t, heads, head_dim):
     return out
 
 
-def test_plain_implementation_agrees_with_the_reference_engine(tmp_path):
+@pytest.mark.parametrize("fixture", ["reference_fixture", "reference_fixture_b"])
+def test_plain_implementation_agrees_with_the_reference_engine(tmp_path, fixture):
+    """reference_fixture: 2 layers, 4 heads in 2 groups of head size 16, rope base 1e4, eps 1e-6, 15 positions;
+    reference_fixture_b: 3 layers, 3 heads on one kv head of head size 32, rope base 1e6, eps 1e-5, 43 positions."""
+    FIXTURE = os.path.join(GOLDEN, fixture)
     ini = dict(line.strip().split("=") for line in open(os.path.join(FIXTURE, "config.ini")) if "=" in line)
     heads, kv_heads, dim = int(ini["heads"]), int(ini["kv_heads"]), int(ini["dim"])
     hd = dim // heads

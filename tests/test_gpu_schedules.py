@@ -150,3 +150,50 @@ def test_a_prepared_step_that_finds_the_cache_full(model_dirs):
     engine.close_sequence(b)
     lg = engine.step([a], [[toks[0][64]]]).cpu()
     assert float((lg[0] - want[0][64]).abs().max()) <= TOL["bfloat16"]
+
+
+# ---- the whole decode step as one persistent kernel (an option: Ops.use_fused_decode) -----------------------------
+FUSED_CONFIGS = {
+    # widths that are multiples of 64 (the kernel's blocks of K), otherwise odd: 6 heads on 2 kv heads of 32, a window
+    # of 70 from layer 1 on (a ring of 128 positions that wraps), untied head
+    "F": dict(TINY["A"], hidden_size=192, intermediate_size=320, num_hidden_layers=3, num_attention_heads=6,
+              num_key_value_heads=2, head_dim=32, vocab_size=331, max_position_embeddings=512, rms_norm_eps=1e-5,
+              rope_theta=30000.0, tie_word_embeddings=False, use_sliding_window=True, sliding_window=70, max_window_layers=1),
+    # head size 128, one kv head
+    "G": dict(TINY["A"], hidden_size=256, intermediate_size=192, num_hidden_layers=2, num_attention_heads=2,
+              num_key_value_heads=1, head_dim=128, vocab_size=515, max_position_embeddings=512, rms_norm_eps=2e-6,
+              rope_theta=250000.0, tie_word_embeddings=True),
+}
+
+
+@pytest.mark.parametrize("name", ["F", "G", "real"])
+def test_the_fused_decode_step(tmp_path, real_size_dir, name):
+    """One persistent kernel for the whole decode step of up to 16 sequences: the same logits as the plain model,
+    through captured graphs, with sequences of unequal lengths that end at different times."""
+    from smolmoe_c99_b200.config import config_from_json
+    from smolmoe_c99_b200.engine.engine import Engine
+    from smolmoe_c99_b200.weights import write_random_model
+    if name == "real":
+        folder, vocab = real_size_dir, REAL_0_5B_2_LAYERS["vocab_size"]
+    else:
+        folder, vocab = write_random_model(config_from_json(FUSED_CONFIGS[name]), str(tmp_path / name), 21), FUSED_CONFIGS[name]["vocab_size"]
+    engine = Engine(folder, "bfloat16", max_tokens=16 * 256, max_slots=16, kernels="fast")
+    ops = engine.runtime.ops
+    before = ops.use_fused_decode
+    ops.use_fused_decode = True
+    try:
+        assert engine.model._fused_plan(engine.cache) is not None, "the model is the fused step's case"
+        for n_seq in ((1, 5, 16) if name != "real" else (3,)):
+            lengths = [20 + (41 * i) % 150 for i in range(n_seq)]
+            requests = {f"r{i}": random_tokens(n, vocab, 800 + i) for i, n in enumerate(lengths)}
+            prompt_lens = {r: len(t) - 4 - (i % 9) for i, (r, t) in enumerate(requests.items())}
+            want = _plain(folder, requests, "bfloat16")
+            launches = int(ops.lib.sm_launch_count())
+            got = replay.batched(engine, [requests], prompt_lens)
+            _check(got, want, "bfloat16", f"fused decode, {n_seq} sequences", REL_WIDE if name == "real" else None)
+        engine.check_status()
+    finally:
+        ops.use_fused_decode = before
+    # a model the fused step does not describe (a width that is no multiple of 64) goes kernel by kernel
+    other = Engine(write_random_model(config_from_json(TINY["C"]), str(tmp_path / "c"), 2), "bfloat16", max_tokens=1024)
+    assert other.model._fused_plan(other.cache) is None

@@ -3,7 +3,8 @@ at the moment of the call (a plug-in inside another program's memory budget, a p
 must not meet cudaMalloc's device-wide synchronisation). Its split-K scratch is a fixed array
 inside the library instead of a workspace from the caller. The test calls it through its
 exported C symbol and compares it with the existing entry point, twice in a row on the same
-array, and checks that a shape beyond the array is refused. It is collected last, so that a
+array, checks that the calls leave the device's free memory as they found it, and that a
+shape beyond the array is refused. It is collected last, so that a
 run that stops at the first failure has already run every other test."""
 import ctypes
 
@@ -49,9 +50,15 @@ def test_static_scratch_entry_point_matches_the_allocating_one():
             want = torch.empty((T, N), dtype=torch.bfloat16 if mode == 2 else torch.float32, device="cuda")
             ops.gemm_tc(x, w, bias, want, mode=mode, up_offset=N if mode == 2 else 0)
             got = torch.full_like(want, float("nan"))
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
             status = _static(lib, x, w, bias, got, mode, N if mode == 2 else 0)
             assert status == 0, lib.sm_last_error().decode()
             torch.cuda.synchronize()
+            if round_ == 1:
+                # what the entry point is for: after a device's first call, a call takes no memory from the device
+                # (the first call of all may load the library's module and with it the array)
+                assert torch.cuda.mem_get_info()[0] == free_before, (T, N, K)
             ref = x.float() @ w[:N].float().T
             if mode == 2:
                 up = x.float() @ w[N:].float().T
@@ -79,6 +86,7 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     assert _static(lib, x, w, None, out, 2, N) == 1
     message = lib.sm_last_error().decode()
     assert str(need) in message and str(SCRATCH_BYTES) in message
+    assert _static(lib, x[:0], w, None, out[:0], 2, N) == 1 and "must be positive" in lib.sm_last_error().decode()
     torch.cuda.synchronize()
     assert float(out.abs().max()) == 0.0                      # nothing ran
     assert _static(lib, x[:8].contiguous(), w, None, out[:8].contiguous(), 2, N) == 0   # the next call still works
