@@ -542,6 +542,9 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     for (int i = 0; i < my_tiles; ++i) {
         if (!__all_sync(0xffffffffu, mbar_wait(&my_bars[s], parity))) {
             if (lane == 0 && a.error) atomicExch(a.error, 6);
+            // the tiles asked for and not used (this one and up to S - 1 after it) may still land in the warp's ring:
+            // one more bounded wait for each before the CTA leaves
+            for (int j = i; j < my_tiles && j < i + S; ++j) mbar_wait(&my_bars[j % S], (uint32_t)(j / S) & 1u);
             break;
         }
         const unsigned char* kt = ring + (size_t)s * kTileBytes;

@@ -27,6 +27,7 @@
 #include <string>
 
 #include "common.cuh"
+#include "drain.cuh"
 #include "kernels.h"
 #include "launch.cuh"
 #include "tcgen05.cuh"
@@ -112,6 +113,7 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     uint64_t* pair_bar = bars + 5;                    // [4] the two warps of a lane quarter have both written their halves' figures
     uint64_t* k_bar = bars + 9;                       // [NSK] a key tile has landed
     uint64_t* v_bar = bars + 9 + NSK;                 // [NSV] a value tile has landed
+    uint64_t* drain_bar = bars + 17;                  // a commit behind the last MMA, on the way out after a failure (NSK + NSV <= 8)
     uint32_t* tmem_slot = (uint32_t*)(bars + 18);
     volatile int* failed = (volatile int*)(tmem_slot + 1);
     float* half_max = (float*)(bars + 20);            // [2 tiles in flight][2 halves][128 rows]: maxima of the halves of the rows' scores
@@ -127,6 +129,7 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
         mbar_init(s_free, kRowThreads);
         mbar_init(p_full, kRowThreads);
         mbar_init(pv_full, 1);
+        mbar_init(drain_bar, 1);
         for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -155,8 +158,13 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
             const uint32_t idesc_s = instr_desc(kBM, kBN);
             const uint32_t idesc_pv = instr_desc(kBM, HD) | (1u << 16);   // B (= V) is MN-major
             // key (value) tile t, counted from kt0, lives in stage t % NSK (NSV); its barrier has parity (t / NSK) & 1
+            // key and value tiles asked for / waited for so far, and whether any MMA was issued: what the way out after
+            // a wait that ran out has to let finish (drain.cuh)
+            int k_issued = 0, k_waited = 0, v_issued = 0, v_waited = 0;
+            bool q_waited = false, any_mma = false;
             auto load_k = [&](int t) {
                 uint8_t* dst = k_s + (size_t)(t % NSK) * kQBytes;
+                ++k_issued;
                 mbar_expect_tx(&k_bar[t % NSK], (uint32_t)kQBytes);
 #pragma unroll
                 for (int b = 0; b < DB; ++b)
@@ -164,6 +172,7 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
             };
             auto load_v = [&](int t) {
                 uint8_t* dst = v_s + (size_t)(t % NSV) * kQBytes;
+                ++v_issued;
                 mbar_expect_tx(&v_bar[t % NSV], (uint32_t)kQBytes);
 #pragma unroll
                 for (int b = 0; b < DB; ++b)
@@ -197,10 +206,12 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
             for (int b = 0; b < DB; ++b) tma_load_2d(q_s + b * kBlockBytes, &map_q, h * HD + b * 64, seq_start + q0, q_bar);
             for (int t = 0; t < NSK && t < n_kt; ++t) load_k(t);
             for (int t = 0; t < NSV && t < n_kt; ++t) load_v(t);
-            bool ok = mbar_wait(q_bar, 0) && mbar_wait(&k_bar[0], 0);
+            bool ok = (q_waited = mbar_wait(q_bar, 0)) && mbar_wait(&k_bar[0], 0);
             if (ok) {
+                k_waited = 1;
                 tc_fence_after();
                 issue_s(0);
+                any_mma = true;
             } else {
                 fail(11);
             }
@@ -215,6 +226,7 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                 tc_fence_after();
                 if (it + 1 < n_kt) {
                     if (!(ok = mbar_wait(&k_bar[(it + 1) % NSK], (uint32_t)((it + 1) / NSK) & 1u))) { fail(13); break; }
+                    k_waited = it + 2;
                     tc_fence_after();
                     issue_s(it + 1);
                 }
@@ -223,8 +235,23 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                 if (!(ok = mbar_wait(p_full, ph))) { fail(14); break; }
                 if (it >= 1 && it - 1 + NSV < n_kt) load_v(it - 1 + NSV);
                 if (!(ok = mbar_wait(&v_bar[it % NSV], (uint32_t)(it / NSV) & 1u))) { fail(15); break; }
+                v_waited = it + 1;
                 tc_fence_after();
                 issue_pv(it);
+            }
+            if (!ok || *failed) {
+                // the way out: every tile asked for lands, every MMA issued finishes, before the CTA gives up its
+                // shared and tensor memory
+                OutstandingFill left[8];
+                if (!q_waited) mbar_wait(q_bar, 0);
+                int n = outstanding_fills(k_issued, k_waited, NSK, left);
+                for (int i = 0; i < n; ++i) mbar_wait(&k_bar[left[i].stage], left[i].parity);
+                n = outstanding_fills(v_issued, v_waited, NSV, left);
+                for (int i = 0; i < n; ++i) mbar_wait(&v_bar[left[i].stage], left[i].parity);
+                if (any_mma) {
+                    umma_commit(drain_bar);
+                    mbar_wait(drain_bar, 0);
+                }
             }
         }
     } else {

@@ -10,6 +10,7 @@
 #include <string>
 
 #include "common.cuh"
+#include "drain.cuh"
 #include "kernels.h"
 
 namespace {
@@ -65,6 +66,16 @@ SM_API void sm_set_error_word(int* word) { sm::set_error_word(word); }
 
 // Positions per page of the key/value cache that the kernels are compiled for; the host's cache must use the same.
 SM_API int sm_page_size() { return sm::kPageSize; }
+
+// The bookkeeping of a CTA's way out after a bounded wait ran out (drain.cuh): which stage barriers, at which parity,
+// still have copies in flight. Host arithmetic, here for tests. Returns their number (at most `stages`).
+SM_API int sm_outstanding_fills(long long issued, long long consumed, int stages, int* stage_out, int* parity_out) {
+    sm::OutstandingFill left[64];
+    if (stages > 64) stages = 64;
+    const int n = sm::outstanding_fills(issued, consumed, stages, left);
+    for (int i = 0; i < n; ++i) { stage_out[i] = left[i].stage; parity_out[i] = (int)left[i].parity; }
+    return n;
+}
 
 // Kernels enqueued by this library since it was loaded.
 SM_API long long sm_launch_count() { return sm::launch_count(); }

@@ -261,7 +261,8 @@ __global__ void __launch_bounds__(kThreads, 3) gemm_skinny_kernel(SkinnyArgs a) 
 #pragma unroll
     for (int j = 0; j < NT; ++j) sq[j] = 0.f;
 
-    for (int round = 0; round < rounds; ++round) {
+    int round = 0;
+    for (; round < rounds; ++round) {
         const int k_lo = k_cta0 + round * a.round_k, k_hi = min(k_cta1, k_lo + a.round_k);
         const int span = k_hi - k_lo, span16 = (span + 15) / 16 * 16;
         if (round > 0) {
@@ -386,7 +387,13 @@ __global__ void __launch_bounds__(kThreads, 3) gemm_skinny_kernel(SkinnyArgs a) 
             }
         }
     }
-    if (failed && threadIdx.x == 0 && a.error) atomicExch(a.error, 5);
+    if (failed && threadIdx.x == 0) {
+        if (a.error) atomicExch(a.error, 5);
+        // the copies of the round that did not arrive in time may still land in this CTA's shared memory: one more
+        // bounded wait for them before anything of it is given up
+        bool landed = false;
+        for (uint32_t spin = 0; spin < kSpinLimit && !landed; ++spin) landed = mbar_try_wait(&weights_bar, (uint32_t)round & 1u);
+    }
     // (on a failure the flow goes on with what there is: the cluster's barrier below must be reached by everyone)
     if (NORM) {
         float (*sq_dst)[TOK] = a.cluster > 1 ? cluster.map_shared_rank(squares, 0) : squares;

@@ -19,7 +19,8 @@
 // split partial sums go to a workspace and a second kernel adds them in split order.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in *error and
-// the CTA drains and leaves without writing.
+// the CTA leaves without writing, after it has waited (bounded again) for the copies it has asked
+// for and the MMAs it has issued (drain.cuh).
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -30,6 +31,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "drain.cuh"
 #include "kernels.h"
 #include "launch.cuh"
 #include "tcgen05.cuh"
@@ -150,6 +152,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint64_t* tempty_bar = tfull_bar + 2;             // [2] accumulator drained
     uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
     volatile int* failed = (volatile int*)(tmem_slot + 1);
+    // for the way out after a failure (drain.cuh): a barrier for a commit behind the last MMA, the stage fills asked for and
+    // waited for, whether any MMA was issued (in the dynamic allocation: a static one would lower its limit)
+    uint64_t& drain_bar = *(uint64_t*)(tmem_slot + 2);
+    long long& fills_issued = *(long long*)(tmem_slot + 4);
+    long long& fills_consumed = *(long long*)(tmem_slot + 6);
+    int& mmas_issued = *(int*)(tmem_slot + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
@@ -160,7 +168,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+        mbar_init(&drain_bar, 1);
         *failed = 0;
+        fills_issued = fills_consumed = 0;
+        mmas_issued = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
@@ -197,6 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         int s = early == p.stages ? 0 : early;
         uint32_t phase = early == p.stages ? 1u : 0u;
+        long long issued = early;
         bool ok = true;
         for (int u = blockIdx.x; u < p.units && ok && !*failed; u += gridDim.x) {
             const Unit w = unit_of(p, u);
@@ -211,9 +223,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 __syncwarp();
                 if (box.active)
                     tma_load_2d(smem + (size_t)s * stage_bytes + box.offset, box.from_x ? &map_x : &map_w, kb * kStageK + box.k, row, &full_bar[s]);
+                ++issued;
                 if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
         }
+        if (lane == 0) fills_issued = issued;
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(kTileM, p.tile_n);
@@ -228,6 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             int s = 0;
             uint32_t phase = 0;
             int i = 0;
+            long long consumed = 0;
             for (int u = blockIdx.x; u < p.units && !*failed; u += gridDim.x, ++i) {
                 const Unit w = unit_of(p, u);
                 const int b = i & 1;
@@ -239,6 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 uint32_t acc = 0;
                 for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
                     if (!mbar_wait(&full_bar[s], phase)) { *failed = 1; atomicExch(p.error, 2); break; }
+                    ++consumed;
                     tc_fence_after();
                     const uint64_t db = da + b_off, du = da + up_off;
 #pragma unroll
@@ -255,6 +271,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 umma_commit(&tfull_bar[b]);        // the accumulator is complete once all MMAs are done
             }
+            fills_consumed = consumed;
+            mmas_issued = consumed > 0;
         }
     } else {
         // epilogue warps 2..5: TMEM lanes of quarter (warp % 4); one output feature per thread
@@ -346,6 +364,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncwarp();
     tc_fence_before();
     __syncthreads();
+    if (*failed) {
+        // the way out after a wait that ran out (drain.cuh): the copies asked for land, the MMAs issued finish, and only
+        // then are tensor memory and this CTA's shared memory given up
+        if (threadIdx.x == 0) {
+            OutstandingFill left[8];
+            const int n = outstanding_fills(fills_issued, fills_consumed, p.stages, left);
+            for (int i = 0; i < n; ++i) mbar_wait(&full_bar[left[i].stage], left[i].parity);
+        }
+        if (warp == 1 && lane == 0 && mmas_issued) {
+            umma_commit(&drain_bar);
+            mbar_wait(&drain_bar, 0);
+        }
+        __syncthreads();
+    }
     tc_fence_after();
     if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
@@ -385,6 +417,10 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     uint64_t* tmem_full_bar = empty_bar + p.stages;
     uint32_t* tmem_slot = (uint32_t*)(tmem_full_bar + 1);
     int* failed = (int*)(tmem_slot + 1);
+    // for the way out after a failure (drain.cuh), in the dynamic allocation (a static one would lower its limit)
+    uint64_t& drain_bar = *(uint64_t*)(tmem_slot + 2);
+    int& fills_issued = *(int*)(tmem_slot + 4);
+    int& fills_consumed = *(int*)(tmem_slot + 5);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, n0 = blockIdx.y * (p.halves ? kTileM / 2 : kTileM), t0 = blockIdx.z * p.tile_n;
@@ -399,7 +435,9 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(tmem_full_bar, 1);
+        mbar_init(&drain_bar, 1);
         *failed = 0;
+        fills_issued = fills_consumed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
@@ -427,6 +465,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 tma_load_2d(smem + (size_t)i * stage_bytes + box.offset, &map_x, (kb_begin + i) * kStageK + box.k, row, &full_bar[i]);
         int s = early == p.stages ? 0 : early;
         uint32_t phase = early == p.stages ? 1u : 0u;
+        int issued = early;
         for (int i = early; i < n_kb; ++i) {
             if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u))) {
                 if (lane == 0) { *failed = 1; atomicExch(p.error, 1); }
@@ -436,8 +475,10 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             __syncwarp();
             if (box.active)
                 tma_load_2d(smem + (size_t)s * stage_bytes + box.offset, box.from_x ? &map_x : &map_w, (kb_begin + i) * kStageK + box.k, row, &full_bar[s]);
+            ++issued;
             if (++s == p.stages) { s = 0; phase ^= 1u; }
         }
+        if (lane == 0) fills_issued = issued;
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(kTileM, p.tile_n);
@@ -450,8 +491,10 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             int s = 0;
             uint32_t phase = 0, acc = 0;
             bool ok = true;
+            int consumed = 0;
             for (int i = 0; i < n_kb && ok; ++i) {
                 if (!mbar_wait(&full_bar[s], phase)) { *failed = 1; atomicExch(p.error, 2); ok = false; break; }
+                ++consumed;
                 tc_fence_after();
                 const uint64_t db = da + b_off, du = da + up_off;
 #pragma unroll
@@ -467,6 +510,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 if (++s == p.stages) { s = 0; phase ^= 1u; da = desc_first; }
             }
             umma_commit(tmem_full_bar);        // the accumulator is complete once all MMAs are done
+            fills_consumed = consumed;
         }
     } else {
         // epilogue warps 2..5: TMEM lanes of quarter (warp % 4)
@@ -697,6 +741,19 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
+    if (*(volatile int*)failed) {
+        // the way out after a wait that ran out (drain.cuh)
+        if (threadIdx.x == 0) {
+            OutstandingFill left[8];
+            const int n = outstanding_fills(fills_issued, fills_consumed, p.stages, left);
+            for (int i = 0; i < n; ++i) mbar_wait(&full_bar[left[i].stage], left[i].parity);
+        }
+        if (warp == 1 && lane == 0 && fills_consumed > 0) {
+            umma_commit(&drain_bar);
+            mbar_wait(&drain_bar, 0);
+        }
+        __syncthreads();
+    }
     tc_fence_after();
     if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
@@ -793,7 +850,7 @@ SmallLaunch small_launch(int tile_n, int splits, bool dual) {
     l.stages = 100 * 1024 / stage_bytes;
     if (l.stages > 8) l.stages = 8;
     if (l.stages < 2) l.stages = 2;
-    l.smem = (size_t)l.stages * stage_bytes + 1024 /*alignment*/ + (2 * l.stages + 1) * 8 + 16;
+    l.smem = (size_t)l.stages * stage_bytes + 1024 /*alignment*/ + (2 * l.stages + 1) * 8 + 32;
     static std::once_flag once;
     std::call_once(once, [] {
         cudaFuncSetAttribute(gemm_tc_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -999,7 +1056,7 @@ void gemm_tc_impl(const void* x, const void* w, const void* bias, DType bias_dt,
     p.stages = budget / stage_bytes;
     if (p.stages > 8) p.stages = 8;
     if (p.stages < 2) throw std::runtime_error("gemm_tc: a pipeline stage does not fit shared memory twice");
-    const size_t smem = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + 2 * kStagingBytes + (2 * p.stages + 4) * 8 + 16;
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + 2 * kStagingBytes + (2 * p.stages + 4) * 8 + 48;
     const CUtensorMap map_w = make_map(w, dual ? up_offset + N : N, K, kBoxRows);
     const CUtensorMap map_x = make_map(x, T, K, p.tile_n < kBoxRows ? p.tile_n : kBoxRows);
     const CUtensorMap map_out = p.tma_out ? make_out_map(out, T, N, out_dt) : map_x;

@@ -139,3 +139,30 @@ def test_truncate_rules():
     s = w.alloc_slot(); w.reserve({s: 100}); w.advance({s: 100})
     with pytest.raises(CacheStateError, match="windowed"):
         w.truncate(s, 40)
+
+
+def test_what_a_cta_that_gives_up_still_has_in_flight():
+    """The bookkeeping behind the kernels' way out after a bounded wait ran out (csrc/drain.cuh), on the host: of the
+    stage fills asked for, those not waited for yet, with the stage and the barrier phase each completes."""
+    import ctypes
+    import shutil
+    if not shutil.which("nvcc") and not __import__("os").path.exists("/usr/local/cuda/bin/nvcc"):
+        import pytest
+        pytest.skip("the kernel library cannot be built here")
+    from smolmoe_c99_b200.kernels.build import load
+    lib = load()
+    stages_out, parity_out = (ctypes.c_int * 64)(), (ctypes.c_int * 64)()
+
+    def left(issued, consumed, stages):
+        n = lib.sm_outstanding_fills(ctypes.c_longlong(issued), ctypes.c_longlong(consumed), stages, stages_out, parity_out)
+        return [(stages_out[i], parity_out[i]) for i in range(n)]
+
+    assert left(0, 0, 4) == [] and left(7, 7, 4) == []
+    assert left(3, 0, 4) == [(0, 0), (1, 0), (2, 0)]                         # the first fills of a ring of four
+    assert left(9, 6, 4) == [(2, 1), (3, 1), (0, 0)]                         # fills 6, 7, 8: second and third time round
+    assert left(13, 9, 4) == [(1, 0), (2, 0), (3, 0), (0, 1)]                # a whole ring outstanding
+    assert len(left(100, 3, 8)) == 8                                         # never more than the ring holds
+    for issued in range(0, 40):
+        for consumed in range(max(0, issued - 5), issued + 1):
+            got = left(issued, consumed, 5)
+            assert got == [(f % 5, (f // 5) & 1) for f in range(consumed, issued)]
