@@ -80,12 +80,20 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(At
             row = packed ? (((unsigned long long)(seq_first + p - pos0) * a.kv_heads + kvh) * hd) | kPackedBit
                          : (unsigned long long)paged.row_offset(slot, p, kvh);
             const T* kr = (const T*)(packed ? a.k_packed : a.k_pool) + (row & ~kPackedBit);
+            // 32 dimensions of the key row are asked for at once (a trip to memory per 8 otherwise); the dot product is
+            // still one fmaf chain over the dimensions in ascending order
             float dot = 0.f;
-            for (int d = 0; d < hd; d += 8) {
-                float kv[8];
-                Load8<T>::load(kr + d, kv);
+            for (int d = 0; d < hd; d += 32) {
+                float kv[4][8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+                for (int c = 0; c < 4; ++c)
+                    if (d + 8 * c < hd) Load8<T>::load(kr + d + 8 * c, kv[c]);
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (d + 8 * c < hd) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + 8 * c + e], kv[c][e], dot);
+                    }
             }
             s = dot * a.scale;
         }
@@ -96,14 +104,30 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(At
 #pragma unroll
         for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= corr;
         int n_valid = min(32, pos - base + 1);
-        for (int j = 0; j < n_valid; ++j) {
-            float pj = __shfl_sync(0xffffffffu, e, j);
-            unsigned long long rj = __shfl_sync(0xffffffffu, row, j);
-            const T* vr = (const T*)((rj & kPackedBit) ? a.v_packed : a.v_pool) + (rj & ~kPackedBit);
+        // the values of 8 keys at a time are asked for before they are used (one row a trip to memory otherwise); they are
+        // still added in ascending key order, one fmaf chain per output dimension
+        for (int j0 = 0; j0 < n_valid; j0 += 8) {
+            float pj[8];
+            float vv[8][kMaxHeadDim / 32];
 #pragma unroll
-            for (int i = 0; i < kMaxHeadDim / 32; ++i) {
-                int d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
+            for (int u = 0; u < 8; ++u) {
+                const int j = j0 + u;      // (lanes past n_valid hold e = 0 and row 0 of their source: harmless to read)
+                pj[u] = __shfl_sync(0xffffffffu, e, j & 31);
+                const unsigned long long rj = __shfl_sync(0xffffffffu, row, j & 31);
+                const bool use = j < n_valid;
+                const T* vr = (const T*)((rj & kPackedBit) ? a.v_packed : a.v_pool) + (rj & ~kPackedBit);
+#pragma unroll
+                for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+                    const int d = lane + 32 * i;
+                    vv[u][i] = (use && d < hd) ? to_float(vr[d]) : 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (j0 + u < n_valid) {
+#pragma unroll
+                    for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = fmaf(pj[u], vv[u][i], acc[i]);
+                }
             }
         }
         m = m_new;

@@ -76,9 +76,61 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const TB* _
     }
 }
 
+// The same product for up to 16 tokens (decode steps of the 32-bit path): the tile above would leave all but a few SMs
+// idle (one CTA per 64 weight rows, K walked by that one CTA). Here a CTA takes 16 weight rows and one thread one
+// output, still as ONE chain of fmaf over k = 0..K-1 in the same operand order, so the bits are those of the tile
+// above; the operands come through shared memory in blocks of 64 of K.
+constexpr int SR = 16, ST = 16, SK = 64;
+
+template <typename TX, typename TW, typename TB, typename TO>
+__global__ void __launch_bounds__(SR * ST)
+gemm_simt_small_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const TB* __restrict__ bias,
+                       TO* __restrict__ out, int T, int N, int K, bool accumulate) {
+    __shared__ float xs[ST][SK + 1];
+    __shared__ float ws[SR][SK + 1];
+    const int n0 = blockIdx.x * SR;
+    const int tid = threadIdx.x, r = tid / ST, t = tid % ST;
+    float acc = 0.f;
+    for (int k0 = 0; k0 < K; k0 += SK) {
+#pragma unroll
+        for (int e = 0; e < (SR * SK) / (SR * ST); ++e) {
+            const int idx = tid + e * SR * ST;
+            const int row = idx / SK, kk = idx % SK, k = k0 + kk;
+            xs[row][kk] = (k < K && row < T) ? to_float(x[(size_t)row * K + k]) : 0.f;
+            ws[row][kk] = (k < K && n0 + row < N) ? to_float(w[(size_t)(n0 + row) * K + k]) : 0.f;
+        }
+        __syncthreads();
+        const int span = min(SK, K - k0);
+        if (span == SK) {
+#pragma unroll
+            for (int kk = 0; kk < SK; ++kk) acc = fmaf(xs[t][kk], ws[r][kk], acc);
+        } else {
+            for (int kk = 0; kk < span; ++kk) acc = fmaf(xs[t][kk], ws[r][kk], acc);
+        }
+        __syncthreads();
+    }
+    const int n = n0 + r;
+    if (t >= T || n >= N) return;
+    float v = acc;
+    if (bias) v += to_float(bias[n]);
+    const size_t o = (size_t)t * N + n;
+    if (accumulate) v += to_float(out[o]);
+    out[o] = from_float<TO>(v);
+}
+
 template <typename TX, typename TW, typename TB>
 static void launch_out(const void* x, const void* w, const void* bias, void* out, DType out_dt, int T, int N,
                        int K, bool accumulate, cudaStream_t stream) {
+    if (T <= ST) {
+        const unsigned blocks = (unsigned)((N + SR - 1) / SR);
+        if (out_dt == F32)
+            gemm_simt_small_kernel<TX, TW, TB, float><<<blocks, SR * ST, 0, stream>>>((const TX*)x, (const TW*)w, (const TB*)bias,
+                                                                                     (float*)out, T, N, K, accumulate);
+        else
+            gemm_simt_small_kernel<TX, TW, TB, __nv_bfloat16><<<blocks, SR * ST, 0, stream>>>(
+                (const TX*)x, (const TW*)w, (const TB*)bias, (__nv_bfloat16*)out, T, N, K, accumulate);
+        return;
+    }
     dim3 grid((N + BN - 1) / BN, (T + BM - 1) / BM);
     if (out_dt == F32)
         gemm_simt_kernel<TX, TW, TB, float><<<grid, 256, 0, stream>>>((const TX*)x, (const TW*)w, (const TB*)bias,
