@@ -116,6 +116,8 @@ class Engine:
                                    max_seq_len=self.max_seq_len, dtype=self.dtype, device=self.device)
         self.vocab_size = self.spec.vocab_size
         self.use_graphs = use_graphs
+        # a generation loop may launch the next one-token step before it has read the tokens just chosen (generate.py)
+        self.runs_ahead = True
         # the most tokens one step may bring (all sequences together): it bounds a step's activations, as the
         # reference's --batch bounds its buffers (src/model.c:669); None: no bound but the cache's
         if max_step_tokens is not None and max_step_tokens < 1:

@@ -78,6 +78,30 @@ def prompt_portions(lengths: Sequence[int], limit: Optional[int]) -> List[List[T
     return steps
 
 
+def _start_read(chosen, buffer: dict):
+    """Asks for the chosen tokens on the host without waiting: a copy into pinned memory and an event behind it.
+    Tensors that are on the host already (a stand-in engine) are handed through."""
+    if not getattr(chosen, "is_cuda", False):
+        return chosen, None
+    import torch
+
+    n = chosen.numel()
+    if buffer.get("host") is None or buffer["host"].numel() < n:
+        buffer["host"] = torch.empty(max(n, 64), dtype=chosen.dtype, pin_memory=True)
+        buffer["event"] = torch.cuda.Event()
+    host = buffer["host"][:n]
+    host.copy_(chosen, non_blocking=True)
+    buffer["event"].record()
+    return host, buffer["event"]
+
+
+def _finish_read(reading) -> List[int]:
+    host, event = reading
+    if event is not None:
+        event.synchronize()
+    return [int(t) for t in host.tolist()]
+
+
 def _run_prompts(engine, slots: List[int], prompts: List[Sequence[int]]):
     """Feeds the prompts in as few steps as the engine's ``max_step_tokens`` allows and returns the logits after
     each prompt's last token, one row per prompt in order."""
@@ -126,6 +150,7 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], options: Generat
     stop = set(options.stop_token_ids)
     results = [Completion(prompt_tokens=len(p)) for p in prompts]
     cancelled = False
+    read_buffer: dict = {}     # pinned memory for the chosen tokens on their way to the host
     for first in range(0, len(prompts), options.batch):
         ids = list(range(first, min(first + options.batch, len(prompts))))
         if cancelled or options.max_new_tokens == 0:
@@ -152,7 +177,19 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], options: Generat
                 prepared = None
                 if produced < options.max_new_tokens and hasattr(engine, "prepare_decode"):
                     prepared = engine.prepare_decode([slots[r] for r in live])
-                tokens = [int(t) for t in chosen.tolist()]   # the one device-to-host read of the step
+                # An engine that takes the chosen tokens on the device can be given the next step before the host has
+                # read them (``runs_ahead``): the GPU then never waits for the host. A sequence that turns out to have
+                # ended with this token has taken one step too many, into a slot that is closed below; no result
+                # depends on it (a row's logits do not depend on what else is in the batch) and its row is dropped.
+                ahead = None
+                if prepared is not None and getattr(engine, "runs_ahead", False):
+                    # the read of the chosen tokens is asked for BEFORE the next step is launched (a read asked for
+                    # after it would wait behind it in the stream), and waited for after
+                    reading = _start_read(chosen, read_buffer)
+                    ahead = engine.launch_prepared(prepared, chosen)
+                    tokens = _finish_read(reading)
+                else:
+                    tokens = [int(t) for t in chosen.tolist()]   # the one device-to-host read of the step
                 keep = []
                 for i, r in enumerate(live):
                     tok = tokens[i]
@@ -174,11 +211,13 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], options: Generat
                     break
                 if not keep:
                     break
-                if len(keep) != len(live):   # shorter requests have ended: the batch shrinks
+                shrunk = len(keep) != len(live)
+                if shrunk:   # shorter requests have ended: the batch shrinks
                     chosen, states = sampler.select(chosen, keep), sampler.select(states, keep)
                     live = [live[i] for i in keep]
-                    prepared = None
-                if prepared is not None:
+                if ahead is not None:
+                    logits = sampler.select(ahead, keep) if shrunk else ahead
+                elif prepared is not None and not shrunk:
                     logits = engine.launch_prepared(prepared, chosen)
                 else:
                     logits = engine.step([slots[r] for r in live], chosen)

@@ -168,3 +168,31 @@ def test_a_two_half_step_changes_no_decision():
     assert halves.steps == plain.steps                 # the same tokens fed to the same slots: no stop token, no last token
     assert halves.launched >= 1 and halves.prepared > halves.launched   # a step whose batch shrank was redone the plain way
     assert not halves.open
+
+
+def test_an_engine_that_runs_ahead_of_the_host():
+    """With ``runs_ahead`` the next step is launched before the host has read the chosen tokens. The completions are
+    the same; a sequence that ended on a stop token has taken that one step into a slot that is closed right after;
+    the last token the limit allows is still never fed; a row's logits of the step that ran ahead are dropped with
+    its sequence."""
+    class Ahead(TwoHalfEngine):
+        runs_ahead = True
+
+    prompts = [[1], [7], [20], [30]]
+    opts = GenerationOptions(max_new_tokens=6, stop_token_ids=(9, 23), batch=4)
+    plain, ahead = FakeEngine(), Ahead()
+    want = generate(plain, FakeSampler(), prompts, opts)
+    stats = GenerationStats()
+    got = generate(ahead, FakeSampler(), prompts, opts, stats=stats)
+    assert [(c.tokens, c.finish_reason) for c in got] == [(c.tokens, c.finish_reason) for c in want]
+    assert [c.tokens for c in got] == [[2, 3, 4, 5, 6, 7], [8, 9], [21, 22, 23], [31, 32, 33, 34, 35, 36]]
+    fed = [s for s in ahead.steps if s[0] == "decode"]
+    # every step but the ones after a batch shrank came through launch_prepared, with the whole batch of that moment
+    assert [tuple(f[0] for f in s[2]) for s in fed][:3] == [(2, 8, 21, 31), (3, 9, 22, 32), (4, 23, 33)]
+    # the stop tokens 9 and 23 were fed once (the step that ran ahead) and their sequences closed; nothing followed them
+    assert sum(1 for s in fed for f in s[2] if f[0] == 9) == 1 and sum(1 for s in fed for f in s[2] if f[0] == 23) == 1
+    assert all(f[0] not in (10, 24) for s in fed for f in s[2])
+    # the sixth token of a request is its last: never fed
+    assert all(f[0] not in (7, 36) for s in fed for f in s[2])
+    assert stats.generated_tokens == 6 + 2 + 3 + 6 and stats.decode_forwards == 4 + 3 + 2 + 2 + 2     # the forwards that counted
+    assert not ahead.open and ahead.free == [0, 1, 2, 3]
