@@ -102,6 +102,86 @@ def _packed_step(lens):
     return pack_step(list(range(len(lens))), [0] * len(lens), [[0] * n for n in lens], torch.device("cuda"))
 
 
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (5, 5, 48), (14, 2, 64), (6, 3, 80), (8, 2, 128), (2, 1, 40)])
+@pytest.mark.parametrize("window", [None, 37, 100])
+def test_attention_of_sequences_that_go_on_from_the_cache(ops, heads, kv_heads, hd, window):
+    """Sequences at different points: one at its start, one that goes on by a single token, others by 7, 64 and 130
+    tokens from positions that are no multiple of anything. Earlier keys and values lie in a paged cache (a ring for a
+    window; every position written in order, so stale rows are real rows), the step's own come packed and are NOT in
+    the cache yet. The tensor-core kernel and the plain kernel (bfloat16 and float) against the float64 formula; then
+    kv_store puts the step's rows where they belong."""
+    from types import SimpleNamespace
+    from smolmoe_c99_b200.engine.batch import pack_step
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    starts, news = [0, 150, 33, 200, 70], [50, 1, 7, 64, 130]
+    B, total = len(starts), [s + n for s, n in zip(starts, news)]
+    ring = ((window + PAGE_SIZE - 1) // PAGE_SIZE) * PAGE_SIZE if window else 0
+    pages_per_seq = (ring or 384) // PAGE_SIZE
+    g = torch.Generator().manual_seed(31)
+    table = torch.randperm(B * pages_per_seq, generator=g).to(torch.int32).view(B, pages_per_seq)
+    k_pool = torch.zeros((B * pages_per_seq, kv_heads, PAGE_SIZE, hd), dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    ks = [torch.randn((n, kv_heads, hd), generator=g).to(torch.bfloat16) for n in total]
+    vs = [torch.randn((n, kv_heads, hd), generator=g).to(torch.bfloat16) for n in total]
+    qs = [torch.randn((n, heads, hd), generator=g).to(torch.bfloat16) for n in total]
+    for b in range(B):
+        for p in range(starts[b]):                    # the cache holds what earlier steps left, and nothing of this step
+            idx = p % ring if ring else p
+            page = int(table[b, idx // PAGE_SIZE])
+            k_pool[page, :, idx % PAGE_SIZE] = ks[b][p]
+            v_pool[page, :, idx % PAGE_SIZE] = vs[b][p]
+    scale = 1.0 / math.sqrt(hd)
+    want = torch.cat([_plain_attention(qs[b], ks[b], vs[b], [total[b]], window, scale)[starts[b]:] for b in range(B)])
+    step = pack_step(list(range(B)), starts, [[0] * n for n in news], torch.device("cuda"))
+    assert step.mode == "extend"
+    q = torch.cat([qs[b][starts[b]:] for b in range(B)]).cuda()
+    k = torch.cat([ks[b][starts[b]:] for b in range(B)]).cuda()
+    v = torch.cat([vs[b][starts[b]:] for b in range(B)]).cuda()
+    cache = SimpleNamespace(k_pool=k_pool.cuda(), v_pool=v_pool.cuda(), page_table=table.cuda(), ring=ring)
+    if hd % 16 == 0:
+        got = ops.attention_extend(q, k, v, step, scale, window, cache).float().cpu()
+        assert float((got - want).abs().max()) <= 2e-2, "tensor-core kernel"
+    plain = ops.attention_plain(q, step.positions, scale, window, k_packed=k, v_packed=v, token_seq_start=step.token_seq_start,
+                                k_pool=cache.k_pool, v_pool=cache.v_pool, page_table=cache.page_table, ring=ring,
+                                token_slot=step.token_slot).float().cpu()
+    assert float((plain - want).abs().max()) <= 1e-2, "plain kernel, bfloat16"
+    cache32 = SimpleNamespace(k_pool=k_pool.float().cuda(), v_pool=v_pool.float().cuda(), page_table=table.cuda(), ring=ring)
+    plain32 = ops.attention_plain(q.float(), step.positions, scale, window, k_packed=k.float(), v_packed=v.float(),
+                                  token_seq_start=step.token_seq_start, k_pool=cache32.k_pool, v_pool=cache32.v_pool,
+                                  page_table=cache32.page_table, ring=ring, token_slot=step.token_slot).cpu()
+    assert float((plain32 - want).abs().max()) <= 2e-5, "plain kernel, float"
+    # the step's rows into the cache: every position of a sequence then lies where a later step looks for it
+    for pools, kk, vv in ((cache, k, v), (cache32, k.float(), v.float())):
+        ops.kv_store(kk, vv, step, pools)
+        at = 0
+        for b in range(B):
+            first_kept = max(0, total[b] - ring) if ring else 0
+            for p in list(range(first_kept, min(total[b], first_kept + 3))) + [total[b] - 1]:
+                idx = p % ring if ring else p
+                page = int(table[b, idx // PAGE_SIZE])
+                assert torch.equal(pools.k_pool[page, :, idx % PAGE_SIZE].float().cpu(), ks[b][p].float()), (b, p)
+                assert torch.equal(pools.v_pool[page, :, idx % PAGE_SIZE].float().cpu(), vs[b][p].float()), (b, p)
+            at += news[b]
+
+
+@pytest.mark.parametrize("T", [1, 5, 16])
+@pytest.mark.parametrize("N,K", [(70, 50), (129, 1000), (16, 4864)])
+def test_gemm_simt_for_few_tokens_gives_the_tile_kernels_bits(ops, T, N, K):
+    """Up to 16 tokens take a kernel of their own in the 32-bit path; its sums are the tile kernel's, bit for bit (the
+    same rows inside a batch of 64 go through the tile kernel)."""
+    x, w, b = _rand((64, K), torch.float32, 1), _rand((N, K), torch.float32, 2, 0.1), _rand((N,), torch.float32, 3)
+    big = ops.gemm_simt(x, w, b, torch.empty((64, N), dtype=torch.float32, device="cuda"))
+    small = ops.gemm_simt(x[:T].contiguous(), w, b, torch.empty((T, N), dtype=torch.float32, device="cuda"))
+    assert torch.equal(small, big[:T])
+    want = x[:T].double() @ w.double().T + b.double()
+    assert float((small.double() - want).abs().max()) <= 1e-5 * math.sqrt(K)
+    acc = _rand((T, N), torch.float32, 4)
+    acc_big = torch.cat([acc, torch.zeros((64 - T, N), device="cuda")]).contiguous()
+    ops.gemm_simt(x[:T].contiguous(), w, None, acc, accumulate=True)
+    ops.gemm_simt(x, w, None, acc_big, accumulate=True)
+    assert torch.equal(acc, acc_big[:T])
+
+
 @pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (5, 5, 48), (14, 2, 64), (6, 3, 80), (8, 2, 128)])
 @pytest.mark.parametrize("window", [None, 37])
 def test_prefill_attention(ops, heads, kv_heads, hd, window):
