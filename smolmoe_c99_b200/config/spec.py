@@ -64,6 +64,14 @@ class ModelSpec:
     layers: Tuple[LayerSpec, ...]
     order: Tuple[int, ...]
     stop_token_ids: Tuple[int, ...] = ()
+    # steps of the model that belong to no layer; the defaults are "none of it" (the Qwen2 decoder has none:
+    # embed_scale = 1 and plain logits, src/model.c:667,654-662 of the reference)
+    embedding_scale: float = 1.0                      # the embeddings are multiplied by this
+    embedding_position: Optional[PartSpec] = None     # a position encoding that is ADDED to the embeddings (kind "learned"), its
+                                                      # tensors named relative to ``embedding_position_prefix``
+    embedding_position_prefix: str = ""
+    head_bias_name: Optional[str] = None              # a bias on the output head
+    logit_softcap: Optional[float] = None             # logits = cap * tanh(logits / cap)
 
     def __post_init__(self) -> None:
         for index in self.order:

@@ -92,8 +92,20 @@ SM_API int sm_rmsnorm(const float* x, const void* w, int w_dt, float eps, void* 
     });
 }
 
-SM_API int sm_swiglu(const float* gate_up, void* out, int out_dt, int T, int H, void* stream) {
-    return guarded([&] { sm::swiglu(gate_up, out, (sm::DType)out_dt, T, H, (cudaStream_t)stream); });
+SM_API int sm_swiglu(const float* gate_up, void* out, int out_dt, int T, int H, int act, void* stream) {
+    return guarded([&] { sm::swiglu(gate_up, out, (sm::DType)out_dt, T, H, act, (cudaStream_t)stream); });
+}
+
+SM_API int sm_scale_inplace(float* x, long long total, float scale, void* stream) {
+    return guarded([&] { sm::scale_inplace(x, (size_t)total, scale, (cudaStream_t)stream); });
+}
+
+SM_API int sm_softcap_inplace(float* x, long long total, float cap, void* stream) {
+    return guarded([&] { sm::softcap_inplace(x, (size_t)total, cap, (cudaStream_t)stream); });
+}
+
+SM_API int sm_add_rows(float* x, const void* table, int table_dt, const int32_t* rows, int T, int D, int n_table_rows, void* stream) {
+    return guarded([&] { sm::add_rows(x, table, (sm::DType)table_dt, rows, T, D, n_table_rows, (cudaStream_t)stream); });
 }
 
 SM_API int sm_rope_store(const float* qkv, int T, int heads, int kv_heads, int head_dim, int rotary_dim,

@@ -21,6 +21,24 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
     return __float2bfloat16_rn(v);
 }
 
+// The activations of a gated feed-forward, act(gate) * up, in one place: a new one is added here (and named in
+// kernels/ops.py); every kernel that folds the activation into a product's epilogue calls these.
+enum Activation : int { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_COUNT = 2 };
+// exact library functions: the stand-alone kernel and the kernels of the 32-bit path
+__device__ __forceinline__ float activate(int act, float g) {
+    if (act == ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + expf(-g));                       // x * sigmoid(x): src/vecmath.c:78-81 of the reference
+}
+// the hardware's exponential and reciprocal (a few ulp of float): epilogues whose result is stored as bfloat16
+__device__ __forceinline__ float activate_fast(int act, float g) {
+    if (act == ACT_GELU_TANH) {
+        const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        const float e = __expf(2.0f * z);               // tanh(z) = 1 - 2 / (e^2z + 1)
+        return 0.5f * g * (2.0f - __fdividef(2.0f, e + 1.0f));
+    }
+    return __fdividef(g, 1.0f + __expf(-g));
+}
+
 // Butterfly reductions: every lane ends with the same value, and the order of the
 // additions depends on nothing but the lane numbers.
 __device__ __forceinline__ float warp_sum(float v) {

@@ -171,23 +171,24 @@ void rmsnorm(const float* x, const void* w, DType w_dt, float eps, void* out, DT
 
 // ---------------------------------------------------------------------------------------
 template <typename TO>
-__global__ void swiglu_kernel(const float* __restrict__ gate_up, TO* __restrict__ out, int H, size_t total) {
+__global__ void swiglu_kernel(const float* __restrict__ gate_up, TO* __restrict__ out, int H, size_t total, int act) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     size_t t = i / H;
     int j = (int)(i - t * H);
     float g = gate_up[t * 2 * H + j];
     float u = gate_up[t * 2 * H + H + j];
-    out[i] = from_float<TO>(u * (g / (1.0f + expf(-g))));
+    out[i] = from_float<TO>(u * activate(act, g));
 }
 
-void swiglu(const float* gate_up, void* out, DType out_dt, int T, int H, cudaStream_t stream) {
+void swiglu(const float* gate_up, void* out, DType out_dt, int T, int H, int act, cudaStream_t stream) {
     size_t total = (size_t)T * H;
     if (!total) return;
+    if (act < 0 || act >= ACT_COUNT) throw std::invalid_argument("swiglu: unknown activation " + std::to_string(act));
     note_launch();
     unsigned blocks = (unsigned)((total + 255) / 256);
-    if (out_dt == F32) swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gate_up, (float*)out, H, total);
-    else swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gate_up, (__nv_bfloat16*)out, H, total);
+    if (out_dt == F32) swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gate_up, (float*)out, H, total, act);
+    else swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gate_up, (__nv_bfloat16*)out, H, total, act);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -296,6 +297,45 @@ __global__ void rope_store_vec_kernel(RopeStoreArgs a, long long total) {
         store4(c + i0, lo);
         store4(c + half + i0, hi);
     }
+}
+
+// Small steps of a model that are no layer's: x *= scale; x = cap * tanh(x / cap); x[t, :] += table[rows[t], :].
+__global__ void scale_kernel(float* x, size_t total, float scale) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] *= scale;
+}
+__global__ void softcap_kernel(float* x, size_t total, float cap) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = cap * tanhf(x[i] / cap);
+}
+template <typename TT>
+__global__ void add_rows_kernel(float* x, const TT* __restrict__ table, const int32_t* __restrict__ rows, int D, int n_table_rows,
+                                size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / D;
+    const int r = rows[t];
+    if (r >= 0 && r < n_table_rows) x[i] += to_float(table[(size_t)r * D + (i - t * D)]);
+}
+
+void scale_inplace(float* x, size_t total, float scale, cudaStream_t stream) {
+    if (!total) return;
+    note_launch();
+    scale_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, total, scale);
+}
+void softcap_inplace(float* x, size_t total, float cap, cudaStream_t stream) {
+    if (!total) return;
+    if (!(cap > 0.f)) throw std::invalid_argument("softcap: the cap must be positive");
+    note_launch();
+    softcap_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, total, cap);
+}
+void add_rows(float* x, const void* table, DType table_dt, const int32_t* rows, int T, int D, int n_table_rows, cudaStream_t stream) {
+    const size_t total = (size_t)T * D;
+    if (!total) return;
+    note_launch();
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (table_dt == F32) add_rows_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)table, rows, D, n_table_rows, total);
+    else add_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)table, rows, D, n_table_rows, total);
 }
 
 // Copies this step's packed keys and values into the cache: one thread per 16 bytes of a (token, kv head) row.

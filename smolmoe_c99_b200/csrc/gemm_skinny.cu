@@ -76,6 +76,7 @@ struct SkinnyArgs {
     int cluster;                // CTAs that share a tile (1, 2 or 4)
     int round_k;                // k elements staged per round (a multiple of 32)
     int* error;
+    int act;                    // SK_SWIGLU: the activation (Activation in common.cuh)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -471,7 +472,7 @@ __global__ void __launch_bounds__(kThreads, 3) gemm_skinny_kernel(SkinnyArgs a) 
         }
         if (NORM) { const float inv = inv_rms(t); v *= inv; u *= inv; }
         const size_t o = (size_t)t * a.N + n;
-        if (a.mode == SK_SWIGLU) v = u * (v / (1.0f + expf(-v)));
+        if (a.mode == SK_SWIGLU) v = u * activate(a.act, v);
         else v += pre;                     // the bias, or what the residual held
         if (a.mode == SK_RESIDUAL || a.out_dt == F32) ((float*)a.out)[o] = v;
         else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(v);
@@ -536,6 +537,9 @@ void gemm_skinny(const void* x, const void* norm_w, DType norm_w_dt, float eps, 
     if (((uintptr_t)x | (uintptr_t)w) & 15) throw std::invalid_argument("gemm_skinny: operands must be 16-byte aligned");
     SkinnyArgs a{};
     a.x = x; a.norm_w = norm_w; a.norm_w_dt = norm_w_dt; a.eps = eps;
+    a.act = mode >> 8;          // mode: the epilogue in its low byte, the gated product's activation above it
+    mode &= 0xff;
+    if (a.act < 0 || a.act >= ACT_COUNT) throw std::invalid_argument("gemm_skinny: unknown activation " + std::to_string(a.act));
     a.w = (const __nv_bfloat16*)w; a.T = T; a.N = N; a.K = K; a.mode = mode;
     a.bias = bias; a.bias_dt = bias_dt; a.out = out; a.out_dt = out_dt; a.up_offset = up_offset;
     a.error = error_word();

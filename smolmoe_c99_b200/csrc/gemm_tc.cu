@@ -71,6 +71,7 @@ struct GemmParams {
     int final_epilogue;       // what the epilogue is once the splits are added up
     int cluster_reduce;       // small kernel: the CTAs along K are one cluster and add their sums up among themselves
     SkinnyRope rope;          // EPI_QKV_ROPE: where q goes and where the cache is (out is unused)
+    int act;                  // the gated product's activation (Activation in common.cuh)
     int halves;               // small kernel, gated product: a tile is 64 gate rows and their 64 up rows in ONE accumulator
                               // (dual = 0); gate and up meet where the splits are added up
 };
@@ -89,7 +90,7 @@ constexpr int kStagingBytes = kChunk * kTileM * 4;          // one staged chunk 
 // one large box.
 // up * gate / (1 + e^-gate) with the hardware's exponential and reciprocal (a few ulp of float; the result is
 // stored as bfloat16). The epilogue's four warps have a scheduler each, so every instruction saved is time.
-__device__ __forceinline__ float gated(float gate, float up) { return up * __fdividef(gate, 1.0f + __expf(-gate)); }
+__device__ __forceinline__ float gated(int act, float gate, float up) { return up * activate_fast(act, gate); }
 
 // A stage lies in shared memory as [weight tile][block of K][128 rows], [second weight tile ...], then
 // [block of K][tile_n token rows], every row 128 bytes.
@@ -308,7 +309,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         float v = g[j];
-                        if (p.epilogue == EPI_SWIGLU) v = gated(v, up[j]);
+                        if (p.epilogue == EPI_SWIGLU) v = gated(p.act, v, up[j]);
                         else v += bias_v;
                         if (p.out_dt == F32) ((float*)stage)[j * kTileM + f] = v;
                         else ((__nv_bfloat16*)stage)[j * kTileM + f] = __float2bfloat16_rn(v);
@@ -346,7 +347,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             if (p.dual) p.workspace[(((size_t)p.splits + w.split) * p.T + t) * p.N + n] = up[j];
                             continue;
                         }
-                        if (p.epilogue == EPI_SWIGLU) v = gated(v, up[j]);
+                        if (p.epilogue == EPI_SWIGLU) v = gated(p.act, v, up[j]);
                         else v += bias_v;
                         if (p.epilogue == EPI_ACCUM) ((float*)p.out)[o] = old[j] + v;
                         else if (p.out_dt == F32) ((float*)p.out)[o] = v;
@@ -562,7 +563,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         if (p.dual) p.workspace[(((size_t)p.splits + split) * p.T + t) * p.N + n] = u[j];
                         continue;
                     }
-                    if (p.epilogue == EPI_SWIGLU) v = gated(v, u[j]);
+                    if (p.epilogue == EPI_SWIGLU) v = gated(p.act, v, u[j]);
                     else v += bias_v;
                     if (p.epilogue == EPI_ACCUM) {
                         ((float*)p.out)[o] = old[j] + v;
@@ -663,7 +664,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
                         u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
                     }
-                    const float v[4] = {gated(g.x, u.x), gated(g.y, u.y), gated(g.z, u.z), gated(g.w, u.w)};
+                    const float v[4] = {gated(p.act, g.x, u.x), gated(p.act, g.y, u.y), gated(p.act, g.z, u.z), gated(p.act, g.w, u.w)};
                     const size_t o = (size_t)t * p.N + n;
                     if (vec && p.out_dt != F32) {
                         __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi2 = __floats2bfloat162_rn(v[2], v[3]);
@@ -711,7 +712,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     const float ups[4] = {u.x, u.y, u.z, u.w};
     #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        if (p.final_epilogue == EPI_SWIGLU) v[e] = gated(v[e], ups[e]);
+                        if (p.final_epilogue == EPI_SWIGLU) v[e] = gated(p.act, v[e], ups[e]);
                         else if (p.bias && n + e < p.N)
                             v[e] += p.bias_dt == F32 ? ((const float*)p.bias)[n + e] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n + e]);
                         v[e] += old[e];
@@ -780,7 +781,7 @@ __global__ void splitk_reduce_kernel(GemmParams p) {
         }
     }
     float v = g;
-    if (p.epilogue == EPI_SWIGLU) v = gated(g, u);
+    if (p.epilogue == EPI_SWIGLU) v = gated(p.act, g, u);
     else if (p.bias) v += p.bias_dt == F32 ? ((const float*)p.bias)[n] : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
     if (p.epilogue == EPI_ACCUM) ((float*)p.out)[i] += v;
     else if (p.out_dt == F32) ((float*)p.out)[i] = v;
@@ -995,12 +996,16 @@ bool qkv_rope_possible(int T, int N, int K, const SkinnyRope& r) {
 
 void gemm_tc_impl(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N,
                   int K, int mode, int up_offset, float* workspace, int* error, const SkinnyRope* rope, cudaStream_t stream) {
+    const int act = mode >> 8;      // mode: the epilogue in its low byte, the gated product's activation above it
+    mode &= 0xff;
+    if (act < 0 || act >= ACT_COUNT) throw std::invalid_argument("gemm_tc: unknown activation " + std::to_string(act));
     if (!gemm_tc_supports(T, N, K))
         throw std::invalid_argument("gemm_tc: K = " + std::to_string(K) + " must be a positive multiple of 8 (TMA rows start on 16 bytes)");
     if (((uintptr_t)x | (uintptr_t)w) & 15) throw std::invalid_argument("gemm_tc: operands must be 16-byte aligned");
     const bool gated_mode = mode == EPI_SWIGLU;
     GemmParams p{};
     p.T = T; p.N = N; p.K = K;
+    p.act = act;
     gemm_tc_plan(T, N, K, gated_mode, &p.tile_n, &p.splits);
     int halves_splits = 0;
     const bool halves = gated_mode && gated_halves_plan(T, N, K, &halves_splits);

@@ -64,7 +64,7 @@ int sm_gemm_tc_static(const void* x, const void* w, const void* bias, int bias_d
                                         " must be positive");
         if (!sm::gemm_tc_supports(T, N, K))
             throw std::invalid_argument("sm_gemm_tc_static: K = " + std::to_string(K) + " must be a positive multiple of 8");
-        const size_t need = sm::gemm_tc_workspace_bytes(T, N, K, mode == 2);
+        const size_t need = sm::gemm_tc_workspace_bytes(T, N, K, (mode & 0xff) == 2);
         if (need > SM_GEMM_TC_STATIC_SCRATCH_BYTES)
             throw std::invalid_argument("sm_gemm_tc_static: this shape (T=" + std::to_string(T) + ", N=" + std::to_string(N) +
                                         ", K=" + std::to_string(K) + ") needs " + std::to_string(need) +

@@ -37,9 +37,15 @@ void embedding(const void* table, DType table_dt, const int32_t* tokens, float* 
 void rmsnorm(const float* x, const void* w, DType w_dt, float eps, void* out, DType out_dt,
              const int32_t* rows, int n_rows, int D, cudaStream_t stream);
 
-// out[t, j] = up[t, j] * (gate[t, j] / (1 + exp(-gate[t, j]))), gate = gate_up[t, j],
-// up = gate_up[t, H + j] (src/vecmath.c:78-81).
-void swiglu(const float* gate_up, void* out, DType out_dt, int T, int H, cudaStream_t stream);
+// out[t, j] = up[t, j] * act(gate[t, j]), gate = gate_up[t, j], up = gate_up[t, H + j]; act 0: SiLU, g / (1 + exp(-g))
+// (src/vecmath.c:78-81), 1: tanh-GELU (Activation in common.cuh).
+void swiglu(const float* gate_up, void* out, DType out_dt, int T, int H, int act, cudaStream_t stream);
+
+// Steps of a model that belong to no layer: x *= scale (an embedding scale); x = cap * tanh(x / cap) (a cap on the
+// logits); x[t, :] += table[rows[t], :] (a table of position vectors added to the embeddings; rows outside it add nothing).
+void scale_inplace(float* x, size_t total, float scale, cudaStream_t stream);
+void softcap_inplace(float* x, size_t total, float cap, cudaStream_t stream);
+void add_rows(float* x, const void* table, DType table_dt, const int32_t* rows, int T, int D, int n_table_rows, cudaStream_t stream);
 
 struct RopeStoreArgs {
     const float* qkv;           // [T, (heads + 2 kv_heads) * head_dim], bias already added
@@ -80,7 +86,7 @@ void gemm_simt(const void* x, DType x_dt, const void* w, DType w_dt, const void*
 // The same product for bfloat16 x and w on the tcgen05 tensor cores (TMA-fed, accumulator
 // in tensor memory). mode 0: out = x w^T + bias (out F32 or BF16); 1: float out += x w^T;
 // 2: out = act(x w_gate^T) * (x w_up^T) where w holds the gate rows [0, N) and the up rows
-// [up_offset, up_offset + N). Shapes whose K is split over several CTAs need a workspace
+// [up_offset, up_offset + N); the activation (Activation in common.cuh) travels in mode's second byte: 2 | act << 8. Shapes whose K is split over several CTAs need a workspace
 // of gemm_tc_workspace_bytes(). *error becomes non-zero if a bounded wait ran out.
 bool gemm_tc_supports(int T, int N, int K);
 size_t gemm_tc_workspace_bytes(int T, int N, int K, bool dual);

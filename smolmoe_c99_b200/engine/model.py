@@ -8,7 +8,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..config.spec import ModelSpec
-from ..parts import BLOCKS, NORMS, ParamSpec, Runtime, full_name
+from ..parts import BLOCKS, NORMS, POSITIONS, ParamSpec, Runtime, full_name
 
 
 def model_param_specs(spec: ModelSpec) -> List[ParamSpec]:
@@ -19,6 +19,10 @@ def model_param_specs(spec: ModelSpec) -> List[ParamSpec]:
     out += NORMS.get(spec.final_norm.kind).param_specs(spec.final_norm, spec.final_norm_prefix)
     if spec.head_name is not None:
         out.append(ParamSpec("head", spec.head_name, (spec.vocab_size, spec.hidden_size)))
+    if spec.head_bias_name is not None:
+        out.append(ParamSpec("head_bias", spec.head_bias_name, (spec.vocab_size,)))
+    if spec.embedding_position is not None:
+        out += POSITIONS.get(spec.embedding_position.kind).param_specs(spec.embedding_position, spec.embedding_position_prefix)
     names = [s.name for s in out]
     if len(set(names)) != len(names):
         dup = sorted({n for n in names if names.count(n) > 1})
@@ -50,6 +54,13 @@ class DecoderModel:
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, runtime)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
+        self.head_bias: Optional[torch.Tensor] = None
+        self.embedding_position = None
+        if spec.embedding_position is not None:
+            self.embedding_position = POSITIONS.get(spec.embedding_position.kind)(spec.embedding_position, runtime)
+            if not hasattr(self.embedding_position, "add_to"):
+                raise ValueError(f"position encoding {spec.embedding_position.kind!r} cannot be added to the embeddings "
+                                 f"(it has no add_to)")
         self._fused = {}     # per cache: what the fused decode step needs, or None where the model is not its case
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -60,6 +71,15 @@ class DecoderModel:
         self.final_norm.bind({s.key: tensors[s.name] for s in norm_specs})
         # a tied head is the same device buffer as the embedding (src/modelfile.c:25-34)
         self.head = self.embedding if self.spec.head_name is None else tensors[self.spec.head_name]
+        self.head_bias = tensors[self.spec.head_bias_name] if self.spec.head_bias_name is not None else None
+        if self.embedding_position is not None:
+            pos_specs = type(self.embedding_position).param_specs(self.spec.embedding_position, self.spec.embedding_position_prefix)
+            self.embedding_position.bind({s.key: tensors[s.name] for s in pos_specs})
+
+    def _plain_ends(self) -> bool:
+        """Whether the model's first and last steps are the plain ones: embedding, final norm, head."""
+        s = self.spec
+        return s.embedding_scale == 1.0 and s.embedding_position is None and s.head_bias_name is None and s.logit_softcap is None
 
     # ---- a decode step of standard layers in one kernel ---------------------------------------------------
     def _fused_plan(self, cache):
@@ -70,7 +90,7 @@ class DecoderModel:
             return self._fused[key]
         self._fused[key] = None
         ops, rt = self.runtime.ops, self.runtime
-        if rt.dtype != torch.bfloat16 or not hasattr(self.final_norm, "fused_decode_record"):
+        if rt.dtype != torch.bfloat16 or not hasattr(self.final_norm, "fused_decode_record") or not self._plain_ends():
             return None
         records = []
         for run, index in enumerate(self.spec.order):
@@ -137,6 +157,10 @@ class DecoderModel:
                                         step.token_slot, rows, plan["scratch"], status)
         ops.lap(None)
         residual = ops.embedding(self.embedding, step.tokens, status)
+        if self.spec.embedding_scale != 1.0:
+            ops.scale_(residual, self.spec.embedding_scale)
+        if self.embedding_position is not None:
+            self.embedding_position.add_to(residual, step)
         ops.lap("embed")
         for run, index in enumerate(self.spec.order):
             self.blocks[index].forward(residual, step, cache.run_view(run))
@@ -144,14 +168,18 @@ class DecoderModel:
             return None
         every_row = getattr(step, "wants_every_row", False)   # the wanted rows are 0..T-1 in order
         x = self.final_norm.forward(residual, None if every_row else want_rows, lazy=True)
-        logits = ops.linear(x, self.head, None, out_dtype=torch.float32)
+        logits = ops.linear(x, self.head, self.head_bias, out_dtype=torch.float32)
+        if self.spec.logit_softcap is not None:
+            ops.softcap_(logits, self.spec.logit_softcap)
         ops.lap("logits")
         return logits
 
     def weight_bytes(self) -> int:
         """Bytes of every weight a step reads once (a tied head counts once)."""
         seen, total = set(), 0
-        tensors = [self.embedding if self.head is self.embedding else self.head]
+        tensors = [self.embedding if self.head is self.embedding else self.head, self.head_bias]
+        if self.embedding_position is not None:
+            tensors += [v for v in vars(self.embedding_position).values() if isinstance(v, torch.Tensor)]
         for block in self.blocks:
             for part in (block.mixer_norm, block.mixer, block.feed_forward_norm, block.feed_forward):
                 tensors += [v for v in vars(part).values() if isinstance(v, torch.Tensor)]

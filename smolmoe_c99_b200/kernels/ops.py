@@ -12,6 +12,8 @@ from .build import load as load_library
 F32, BF16 = 0, 1
 PAGE_SIZE = 64  # positions per cache page; checked against the library's own number when it is loaded
 KERNEL_CHOICES = ("fast", "plain")
+# activations of a gated feed-forward, by the numbers the kernels know them by (Activation in csrc/common.cuh)
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1}
 # the reference's phases (src/model.h:38-41, src/model.c:312-328); the ones that have no counterpart here stay 0
 PHASES = ("embed", "norm", "qkv", "rope", "attention", "attn_out", "ffn_up", "activation", "attn_quant", "ffn_down",
           "routing", "residual", "logits")
@@ -174,12 +176,43 @@ class Ops:
                      rows: Optional[torch.Tensor] = None) -> NormedRows:
         return NormedRows(self, x, weight, eps, out_dtype, rows)
 
-    def swiglu(self, gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    def swiglu(self, gate_up: torch.Tensor, out_dtype: torch.dtype, activation: str = "silu") -> torch.Tensor:
         _need(gate_up, "gate_up", torch.float32, 2)
         hidden = gate_up.shape[1] // 2
         out = torch.empty((gate_up.shape[0], hidden), dtype=out_dtype, device=gate_up.device)
-        self._check(self.lib.sm_swiglu(_ptr(gate_up), _ptr(out), _dt(out), gate_up.shape[0], hidden, _stream()))
+        self._check(self.lib.sm_swiglu(_ptr(gate_up), _ptr(out), _dt(out), gate_up.shape[0], hidden,
+                                       self.activation_code(activation), _stream()))
         return out
+
+    @staticmethod
+    def activation_code(name: str) -> int:
+        if name not in ACTIVATIONS:
+            raise KernelError(f"unknown activation {name!r}: the kernels know {', '.join(sorted(ACTIVATIONS))}")
+        return ACTIVATIONS[name]
+
+    # ---- steps of a model that belong to no layer ------------------------------------------
+    def scale_(self, x: torch.Tensor, scale: float) -> torch.Tensor:
+        """x *= scale, in place (float)."""
+        _need(x, "x", torch.float32)
+        self._check(self.lib.sm_scale_inplace(_ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(scale), _stream()))
+        return x
+
+    def softcap_(self, x: torch.Tensor, cap: float) -> torch.Tensor:
+        """x = cap * tanh(x / cap), in place (float)."""
+        _need(x, "x", torch.float32)
+        self._check(self.lib.sm_softcap_inplace(_ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), _stream()))
+        return x
+
+    def add_rows_(self, x: torch.Tensor, table: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        """x[t, :] += table[rows[t], :], in place (x float)."""
+        _need(x, "x", torch.float32, 2)
+        _need(table, "table", ndim=2)
+        _need(rows, "rows", torch.int32, 1)
+        if table.shape[1] != x.shape[1] or rows.numel() != x.shape[0]:
+            raise KernelError(f"add_rows shapes do not agree: x {tuple(x.shape)}, table {tuple(table.shape)}, rows {rows.numel()}")
+        self._check(self.lib.sm_add_rows(_ptr(x), _ptr(table), _dt(table), _ptr(rows), x.shape[0], x.shape[1], table.shape[0],
+                                         _stream()))
+        return x
 
     def rope_store(self, qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim, rotary_dim, out_dtype,
                    want_packed, k_pool=None, v_pool=None, page_table=None, ring=0, token_slot=None, token_end=None):
@@ -242,18 +275,20 @@ class Ops:
             return self.gemm_tc(x, w, bias, out, mode=1 if accumulate else 0)
         return self.gemm_simt(x, w, bias, out, accumulate)
 
-    def gated_linear(self, x, w_gate_up: torch.Tensor, hidden: int, out_dtype: torch.dtype) -> torch.Tensor:
+    def gated_linear(self, x, w_gate_up: torch.Tensor, hidden: int, out_dtype: torch.dtype,
+                     activation: str = "silu") -> torch.Tensor:
         """act(x @ w_gate.T) * (x @ w_up.T) with w_gate_up = [w_gate; w_up]."""
+        act = self.activation_code(activation)
         if self._skinny_ok(x, w_gate_up, gated=True):
             out = torch.empty((x.shape[0], hidden), dtype=out_dtype, device=w_gate_up.device)
-            return self.gemm_skinny(x, w_gate_up, None, out, mode=2, up_offset=hidden)
+            return self.gemm_skinny(x, w_gate_up, None, out, mode=2, up_offset=hidden, activation=act)
         x = self.materialize(x)
         if self._tensor_core_ok(x, w_gate_up):
             out = torch.empty((x.shape[0], hidden), dtype=out_dtype, device=x.device)
-            return self.gemm_tc(x, w_gate_up, None, out, mode=2, up_offset=hidden)
+            return self.gemm_tc(x, w_gate_up, None, out, mode=2, up_offset=hidden, activation=act)
         gate_up = self.linear(x, w_gate_up, None, out_dtype=torch.float32)
         self.lap("ffn_up")
-        out = self.swiglu(gate_up, out_dtype)
+        out = self.swiglu(gate_up, out_dtype, activation)
         self.lap("activation")
         return out
 
@@ -300,7 +335,7 @@ class Ops:
         return (rows + 127) // 128 >= 2 * self._sm_count
 
     def gemm_skinny(self, x, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int = 0,
-                    up_offset: int = 0) -> torch.Tensor:
+                    up_offset: int = 0, activation: int = 0) -> torch.Tensor:
         """mode 0: out = x w^T + bias; 1: float out += x w^T; 2: gated (see gemm_tc)."""
         norm_w, eps, src = (x.weight, x.eps, x.residual) if isinstance(x, NormedRows) else (None, 0.0, x)
         _need(src, "x", torch.float32 if norm_w is not None else torch.bfloat16, 2)
@@ -314,7 +349,7 @@ class Ops:
             raise KernelError("accumulation needs a float32 output")
         self._check(self.lib.sm_gemm_skinny(
             _ptr(src), _ptr(norm_w), _dt(norm_w) if norm_w is not None else F32, ctypes.c_float(eps), _ptr(w), T, N, K,
-            mode, _ptr(bias), _dt(bias) if bias is not None else F32, _ptr(out), _dt(out), up_offset, _stream()))
+            mode | (activation << 8), _ptr(bias), _dt(bias) if bias is not None else F32, _ptr(out), _dt(out), up_offset, _stream()))
         return out
 
     def qkv_rope_store_fused(self, x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim,
@@ -359,7 +394,7 @@ class Ops:
                 and bool(self.lib.sm_gemm_tc_supports(x.shape[0], w.shape[0], x.shape[1])))
 
     def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int = 0,
-                up_offset: int = 0) -> torch.Tensor:
+                up_offset: int = 0, activation: int = 0) -> torch.Tensor:
         """The tcgen05 product. mode 0: out = x w^T + bias; 1: float out += x w^T;
         2: out = act(x w[:N]^T) * (x w[up_offset:up_offset+N]^T)."""
         _need(x, "x", torch.bfloat16, 2)
@@ -379,7 +414,7 @@ class Ops:
         need = int(self.lib.sm_gemm_tc_workspace_bytes(T, N, K, int(mode == 2)))
         workspace = torch.empty((need // 4,), dtype=torch.float32, device=x.device) if need else None
         self._check(self.lib.sm_gemm_tc(_ptr(x), _ptr(w), _ptr(bias), _dt(bias) if bias is not None else F32, _ptr(out),
-                                        _dt(out), T, N, K, mode, up_offset, _ptr(workspace), _ptr(self.error_flag),
+                                        _dt(out), T, N, K, mode | (activation << 8), up_offset, _ptr(workspace), _ptr(self.error_flag),
                                         _stream()))
         return out
 

@@ -18,8 +18,11 @@ class GatedMLP(Part):
         super().__init__(spec, runtime)
         self.hidden = int(spec["hidden_size"])
         self.intermediate = int(spec["intermediate_size"])
-        if spec.get("activation", "silu") != "silu":
-            raise ValueError(f"gated_mlp: activation {spec.get('activation')!r} is not built (silu is)")
+        from ..kernels.ops import ACTIVATIONS
+        self.activation = spec.get("activation", "silu")
+        if self.activation not in ACTIVATIONS:     # the kernels fold the activation into the product's epilogue
+            raise ValueError(f"gated_mlp: activation {self.activation!r} is not one the kernels know "
+                             f"({', '.join(sorted(ACTIVATIONS))})")
         self.w_gate_up = self.w_down = None
 
     @classmethod
@@ -36,7 +39,7 @@ class GatedMLP(Part):
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step) -> None:
         ops = self.runtime.ops
-        h = ops.gated_linear(x, self.w_gate_up, self.intermediate, self.runtime.dtype)
+        h = ops.gated_linear(x, self.w_gate_up, self.intermediate, self.runtime.dtype, self.activation)
         ops.lap("ffn_up")   # with the norm before it where that is the product's prologue, and the activation
         ops.linear(h, self.w_down, None, out=residual, accumulate=True)
         ops.lap("ffn_down")
@@ -45,5 +48,7 @@ class GatedMLP(Part):
         """What a kernel that runs whole layers needs of this part; None for a subclass with a forward pass of its
         own, which is not what that kernel computes."""
         if type(self).forward is not GatedMLP.forward:
+            return None
+        if self.activation != "silu":
             return None
         return {"w_gate_up": self.w_gate_up, "w_down": self.w_down, "hidden": self.hidden, "intermediate": self.intermediate}

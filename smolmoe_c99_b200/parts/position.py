@@ -13,7 +13,7 @@ from typing import Tuple
 import torch
 
 from ..config.spec import PartSpec
-from .base import POSITIONS, Part, Runtime
+from .base import POSITIONS, ParamSpec, Part, Runtime, full_name
 
 
 @POSITIONS.register("rope")
@@ -52,3 +52,26 @@ class NoPosition(Part):
             z = torch.zeros((n_positions, 0), dtype=torch.float32, device=self.runtime.device)
             self._tables = (z, z.clone())
         return self._tables
+
+
+@POSITIONS.register("learned")
+class LearnedPositions(Part):
+    """A table of position vectors that is added to the embeddings (an absolute position encoding): the kind of
+    encoding that belongs to the model's first step, not to a mixer. ``add_to`` adds row ``position`` of the table to
+    every token's row of the residual."""
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        super().__init__(spec, runtime)
+        self.size, self.positions = int(spec["size"]), int(spec["positions"])
+        self.rotary_dim = 0
+        self.table = None
+
+    @classmethod
+    def param_specs(cls, spec: PartSpec, prefix: str):
+        return [ParamSpec("table", full_name(prefix, spec.names["table"]), (int(spec["positions"]), int(spec["size"])))]
+
+    def bind(self, tensors) -> None:
+        self.table = tensors["table"]
+
+    def add_to(self, residual: torch.Tensor, step) -> None:
+        self.runtime.ops.add_rows_(residual, self.table, step.positions)

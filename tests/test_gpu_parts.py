@@ -56,6 +56,33 @@ def test_position_part(theta, rotary_dim):
     assert torch.equal(cos.cpu(), want_cos) and torch.equal(sin.cpu(), want_sin)     # double angles, rounded once
 
 
+def _gelu_tanh(g):
+    return 0.5 * g * (1 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T", [5, 40, 300])
+def test_feed_forward_part_with_another_activation(dtype, T):
+    """tanh-GELU instead of SiLU: an entry of the activations the kernels know, through every kernel that folds the
+    activation into the product (a handful of tokens, up to 64, more) and the stand-alone one of the 32-bit path."""
+    from smolmoe_c99_b200.config import PartSpec
+    from smolmoe_c99_b200.parts import FEED_FORWARDS
+    D, H = 96, 160
+    spec = PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": H, "activation": "gelu_pytorch_tanh"},
+                    {"gate": "mlp.g", "up": "mlp.u", "down": "mlp.d"})
+    part = FEED_FORWARDS.get("gated_mlp")(spec, _runtime(dtype))
+    g, u, d = (_rand(s, i, 0.1, dtype) for i, s in enumerate([(H, D), (H, D), (D, H)]))
+    part.bind({"gate": g.to(DEV), "up": u.to(DEV), "down": d.to(DEV)})
+    x, res = _rand((T, D), 5, 2.0, dtype), _rand((T, D), 6)
+    want = res + (_gelu_tanh(x.float() @ g.float().T) * (x.float() @ u.float().T)) @ d.float().T
+    got = res.to(DEV)
+    part.forward(x.to(DEV), got, None)
+    # bfloat16: the hidden activations are stored rounded (2^-9 of their size); against the largest output
+    bound = 2e-5 if dtype == torch.float32 else 1e-2 * float(want.abs().max())
+    assert float((got.cpu() - want).abs().max()) <= bound
+    assert part.fused_decode_record() is None          # the whole-step kernel is written for SiLU
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_feed_forward_part(dtype):
     from smolmoe_c99_b200.config import PartSpec
@@ -437,3 +464,69 @@ def test_a_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
     for cut, got in cuts.items():
         for r in got:
             assert float((got[r] - want[r]).abs().max()) <= 2e-5, f"{cut} {r}"
+
+
+# ---- steps of a model that belong to no layer ----------------------------------------------------------------------
+class ToyEndsConfig:
+    """Model A with what a Qwen2 decoder does not have at its two ends: embeddings scaled by 8, a learned table of
+    position vectors added to them, a bias on the output head, logits capped at 5, and tanh-GELU in layer 1's MLP."""
+    SCALE, CAP = 8.0, 5.0
+
+    def __init__(self, base):
+        self.base = base
+
+    @classmethod
+    def from_json(cls, raw):
+        from smolmoe_c99_b200.config import Qwen2Config
+        return cls(Qwen2Config.from_json(raw))
+
+    def to_json(self):
+        return dict(self.base.to_json(), architectures=["ToyEndsForCausalLM"])
+
+    def model_spec(self):
+        from smolmoe_c99_b200.config import PartSpec
+        spec = self.base.model_spec()
+        l0, l1 = spec.layers
+        gelu = replace(l1.feed_forward, params=dict(l1.feed_forward.params, activation="gelu_tanh"))
+        table = PartSpec("learned", {"size": self.base.hidden_size, "positions": self.base.max_position_embeddings},
+                         {"table": "weight"})
+        return replace(spec, architecture="ToyEndsForCausalLM", layers=(l0, replace(l1, feed_forward=gelu)),
+                       embedding_scale=self.SCALE, embedding_position=table, embedding_position_prefix="model.embed_positions",
+                       head_bias_name="lm_head.bias", logit_softcap=self.CAP)
+
+
+def _plain_toy_ends(model_dir, tokens):
+    cfg = plain_model.read_config(model_dir)
+    w = plain_model.read_safetensors(os.path.join(model_dir, "model.safetensors"))
+    n = len(tokens)
+    cos, sin = plain_model.rope_tables(n, plain_model.head_dim_of(cfg), cfg["rope_theta"])
+    x = plain_model.embed(w["model.embed_tokens.weight"], tokens) * ToyEndsConfig.SCALE + w["model.embed_positions.weight"][:n]
+    x = plain_model.ffn_block(plain_model.attention_block(x, w, "model.layers.0", cfg, 0, cos, sin), w, "model.layers.0", cfg, None)
+    x = plain_model.attention_block(x, w, "model.layers.1", cfg, 1, cos, sin)
+    y = plain_model.rmsnorm(x, w["model.layers.1.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+    p = "model.layers.1.mlp"
+    x = x + (_gelu_tanh(y @ w[f"{p}.gate_proj.weight"].T) * (y @ w[f"{p}.up_proj.weight"].T)) @ w[f"{p}.down_proj.weight"].T
+    logits = plain_model.rmsnorm(x, w["model.norm.weight"], cfg["rms_norm_eps"]) @ w["model.embed_tokens.weight"].T + w["lm_head.bias"]
+    return ToyEndsConfig.CAP * torch.tanh(logits / ToyEndsConfig.CAP)
+
+
+def test_a_model_with_other_ends(tmp_path):
+    """An embedding scale, added position vectors, a head bias and a cap on the logits are fields of the model's
+    description, and another activation an entry of a table: an architecture defined here uses all of them."""
+    from smolmoe_c99_b200.config import config_from_json, register_architecture
+    from smolmoe_c99_b200.engine.engine import Engine
+    from smolmoe_c99_b200.weights import write_random_model
+    register_architecture("ToyEndsForCausalLM", ToyEndsConfig)
+    cfg = config_from_json(dict(TINY["A"], architectures=["ToyEndsForCausalLM"]))
+    folder = write_random_model(cfg, str(tmp_path / "ends"), 13)
+    requests = {f"r{i}": random_tokens(n, 256, 80 + i) for i, n in enumerate([3, 40, 77])}
+    want = {r: _plain_toy_ends(folder, t) for r, t in requests.items()}
+    assert max(float(v.abs().max()) for v in want.values()) > 0.5            # the head bias and the scale make real logits
+    for dtype, tol in (("float32", 2e-5), ("bfloat16", 5e-2)):
+        engine = Engine(folder, dtype, max_tokens=1024, max_slots=3)
+        assert engine.model._fused_plan(engine.cache) is None                 # not the whole-step kernel's case
+        for cut, got in (("whole", replay.whole(engine, requests)), ("tail", replay.tail_decoded(engine, requests)),
+                         ("batched", replay.batched(engine, [requests], {r: max(1, len(t) // 2) for r, t in requests.items()})),
+                         ("portions", replay.portions(engine, requests, 9, 4))):
+            for r in requests:
+                assert float((got[r] - want[r]).abs().max()) <= tol, f"{dtype} {cut} {r}"
