@@ -80,20 +80,12 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(At
             row = packed ? (((unsigned long long)(seq_first + p - pos0) * a.kv_heads + kvh) * hd) | kPackedBit
                          : (unsigned long long)paged.row_offset(slot, p, kvh);
             const T* kr = (const T*)(packed ? a.k_packed : a.k_pool) + (row & ~kPackedBit);
-            // 32 dimensions of the key row are asked for at once (a trip to memory per 8 otherwise); the dot product is
-            // still one fmaf chain over the dimensions in ascending order
             float dot = 0.f;
-            for (int d = 0; d < hd; d += 32) {
-                float kv[4][8];
+            for (int d = 0; d < hd; d += 8) {
+                float kv[8];
+                Load8<T>::load(kr + d, kv);
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    if (d + 8 * c < hd) Load8<T>::load(kr + d + 8 * c, kv[c]);
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    if (d + 8 * c < hd) {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + 8 * c + e], kv[c][e], dot);
-                    }
+                for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
             }
             s = dot * a.scale;
         }
