@@ -306,13 +306,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     tmem_ld32(acc_addr + (uint32_t)c0, g);
                     if (p.dual) tmem_ld32(acc_addr + (uint32_t)(p.tile_n + c0), up);
                     const int f = quarter * 32 + lane;
+                    // (the choice of the activation stays outside the loop over the chunk's 32 values: this epilogue's
+                    // instruction count is what a gated unit's time is made of)
+                    if (p.epilogue == EPI_SWIGLU) {
+                        if (p.act == ACT_SILU) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float v = g[j];
-                        if (p.epilogue == EPI_SWIGLU) v = gated(p.act, v, up[j]);
-                        else v += bias_v;
-                        if (p.out_dt == F32) ((float*)stage)[j * kTileM + f] = v;
-                        else ((__nv_bfloat16*)stage)[j * kTileM + f] = __float2bfloat16_rn(v);
+                            for (int j = 0; j < 32; ++j) g[j] = up[j] * __fdividef(g[j], 1.0f + __expf(-g[j]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) g[j] = gated(p.act, g[j], up[j]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) g[j] += bias_v;
+                    }
+                    if (p.out_dt == F32) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) ((float*)stage)[j * kTileM + f] = g[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) ((__nv_bfloat16*)stage)[j * kTileM + f] = __float2bfloat16_rn(g[j]);
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     epilogue_barrier();
