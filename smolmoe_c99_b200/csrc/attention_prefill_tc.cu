@@ -436,18 +436,8 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
 // A [T, width] row-major bfloat16 matrix, boxes of 128 rows x 64 elements, 128-byte swizzle; rows and columns
 // outside the matrix read as zero.
 CUtensorMap make_map(const void* base, int T, int width) {
-    CUtensorMap map;
-    cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)T};
-    cuuint64_t strides[1] = {(cuuint64_t)width * 2};
-    cuuint32_t box[2] = {64, 128};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = tensor_map_encoder()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        throw std::runtime_error("attention_prefill_tc: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r) +
-                                 " for a " + std::to_string(T) + " x " + std::to_string(width) + " matrix");
-    return map;
+    return tiled_map_2d("attention_prefill_tc", CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, (uint64_t)width, (uint64_t)T, (uint64_t)width * 2,
+                        64, 128, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
 
 template <int HD, bool TWO>

@@ -169,6 +169,12 @@ SM_API long long sm_gemm_tc_workspace_bytes(int T, int N, int K, int dual) {
     return (long long)sm::gemm_tc_workspace_bytes(T, N, K, dual != 0);
 }
 
+SM_API void sm_gemm_pair_enable(int on) { sm::gemm_pair_enable(on != 0); }
+
+SM_API int sm_gemm_pair_takes(const void* x, const void* w, const void* out, int out_dt, int T, int N, int K, int mode) {
+    return sm::gemm_pair_takes(x, w, out, (sm::DType)out_dt, T, N, K, mode) ? 1 : 0;
+}
+
 SM_API int sm_gemm_tc_plan(int T, int N, int K, int dual, int* tile_n, int* splits) {
     return guarded([&] { sm::gemm_tc_plan(T, N, K, dual != 0, tile_n, splits); });
 }

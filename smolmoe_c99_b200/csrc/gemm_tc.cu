@@ -804,36 +804,16 @@ __global__ void splitk_reduce_kernel(GemmParams p) {
 // A [rows, K] row-major bfloat16 matrix, boxes of box_rows x 64 elements, 128-byte swizzle.
 // Rows and columns outside the matrix read as zero.
 CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
-    CUtensorMap map;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = tensor_map_encoder()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                             elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        throw std::runtime_error("gemm_tc: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r) +
-                                 " for a " + std::to_string(rows) + " x " + std::to_string(K) + " matrix");
-    return map;
+    return tiled_map_2d("gemm_tc", CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, (uint64_t)K, (uint64_t)rows, (uint64_t)K * 2, kBlockK,
+                        (uint32_t)box_rows, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
 
 // The [T, N] row-major output, boxes of kChunk tokens x 128 features, no swizzle. Stores and
 // adds outside the matrix are dropped.
 CUtensorMap make_out_map(void* base, int T, int N, DType dt) {
-    CUtensorMap map;
     const size_t elem_bytes = dt == F32 ? 4 : 2;
-    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)T};
-    cuuint64_t strides[1] = {(cuuint64_t)N * elem_bytes};
-    cuuint32_t box[2] = {(cuuint32_t)kTileM, (cuuint32_t)kChunk};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = tensor_map_encoder()(&map, dt == F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
-                             dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        throw std::runtime_error("gemm_tc: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r) +
-                                 " for the " + std::to_string(T) + " x " + std::to_string(N) + " output");
-    return map;
+    return tiled_map_2d("gemm_tc", dt == F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, (uint64_t)N,
+                        (uint64_t)T, (uint64_t)N * elem_bytes, kTileM, kChunk, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE);
 }
 
 int device_sm_count() {
@@ -1019,6 +999,11 @@ void gemm_tc_impl(const void* x, const void* w, const void* bias, DType bias_dt,
     if (!gemm_tc_supports(T, N, K))
         throw std::invalid_argument("gemm_tc: K = " + std::to_string(K) + " must be a positive multiple of 8 (TMA rows start on 16 bytes)");
     if (((uintptr_t)x | (uintptr_t)w) & 15) throw std::invalid_argument("gemm_tc: operands must be 16-byte aligned");
+    // many tokens: the two-CTA kernel
+    if (!rope && gemm_pair_takes(x, w, out, out_dt, T, N, K, mode)) {
+        gemm_pair(x, w, bias, bias_dt, out, out_dt, T, N, K, mode | act << 8, up_offset, error, stream);
+        return;
+    }
     const bool gated_mode = mode == EPI_SWIGLU;
     GemmParams p{};
     p.T = T; p.N = N; p.K = K;

@@ -102,6 +102,16 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits);
 void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N,
              int K, int mode, int up_offset, float* workspace, int* error, cudaStream_t stream);
 
+// ---- gemm_pair.cu ---------------------------------------------------------------------
+// The same product (modes 0, 1, 2 of gemm_tc) for many tokens: two CTAs on one tile of 256 tokens with the two-CTA
+// tcgen05.mma. gemm_tc() goes this way by itself where gemm_pair_takes() says so (512 tokens and more, operands and
+// output on 16 bytes, output rows a multiple of 16 bytes); gemm_pair_enable(false) keeps every product on the
+// one-CTA kernel, for comparisons.
+bool gemm_pair_takes(const void* x, const void* w, const void* out, DType out_dt, int T, int N, int K, int mode);
+void gemm_pair_enable(bool on);
+void gemm_pair(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N, int K,
+               int mode, int up_offset, int* error, cudaStream_t stream);
+
 // ---- gemm_skinny.cu -------------------------------------------------------------------
 // The product for a handful of tokens (T <= 32) and bfloat16 weights, with the layer's
 // surroundings folded in. x is bfloat16 [T, K], or -- when norm_w is given -- the float

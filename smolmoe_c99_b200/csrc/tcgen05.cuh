@@ -10,6 +10,8 @@
 
 #include <mutex>
 #include <stdexcept>
+#include <string>
+#include <unordered_map>
 
 namespace sm {
 namespace tc5 {
@@ -201,6 +203,52 @@ inline EncodeTiledFn tensor_map_encoder() {
     });
     if (!fn) throw std::runtime_error("the driver does not provide cuTensorMapEncodeTiled");
     return fn;
+}
+
+// A two-dimensional tiled tensor map of a row-major matrix (dims and box as {inner, outer}; what lies outside reads as
+// zero and is dropped on the way out). A map is a function of these arguments alone, and a model's launches ask for
+// the same few hundred over and over (the weights, and activation buffers that the allocator hands out again), so
+// maps are kept: the driver's encoder is then off the path of a launch.
+struct TiledMapKey {
+    const void* base;
+    uint64_t inner, outer, pitch;
+    uint32_t box_inner, box_outer;
+    int type, swizzle, promotion;
+    bool operator==(const TiledMapKey& o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && pitch == o.pitch && box_inner == o.box_inner &&
+               box_outer == o.box_outer && type == o.type && swizzle == o.swizzle && promotion == o.promotion;
+    }
+};
+struct TiledMapKeyHash {
+    size_t operator()(const TiledMapKey& k) const {
+        uint64_t h = (uint64_t)(uintptr_t)k.base * 0x9E3779B97F4A7C15ull;
+        h ^= (k.inner * 0xC2B2AE3D27D4EB4Full) ^ (k.outer << 21) ^ (k.pitch << 7) ^ ((uint64_t)k.box_inner << 40) ^
+             ((uint64_t)k.box_outer << 50) ^ ((uint64_t)(k.type * 64 + k.swizzle * 8 + k.promotion) << 56);
+        return (size_t)(h ^ (h >> 29));
+    }
+};
+inline CUtensorMap tiled_map_2d(const char* who, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t outer,
+                                uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle,
+                                CUtensorMapL2promotion promotion) {
+    static std::mutex lock;
+    static std::unordered_map<TiledMapKey, CUtensorMap, TiledMapKeyHash> kept;
+    const TiledMapKey key{base, inner, outer, pitch_bytes, box_inner, box_outer, (int)type, (int)swizzle, (int)promotion};
+    std::lock_guard<std::mutex> hold(lock);
+    auto found = kept.find(key);
+    if (found != kept.end()) return found->second;
+    CUtensorMap map;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = tensor_map_encoder()(&map, type, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      swizzle, promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        throw std::runtime_error(std::string(who) + ": cuTensorMapEncodeTiled failed with code " + std::to_string((int)r) + " for a " +
+                                 std::to_string(outer) + " x " + std::to_string(inner) + " matrix");
+    if (kept.size() >= 8192) kept.clear();
+    kept.emplace(key, map);
+    return map;
 }
 
 }  // namespace tc5

@@ -48,7 +48,9 @@ def _need(t: torch.Tensor, what: str, dtype=None, ndim=None) -> torch.Tensor:
 
 
 def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # (the raw handle: building torch's Stream object for every launch cost 3.4 us of the ~12 a launch takes on the host,
+    # and the prefill of a small model is bound by the host's launches)
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 class NormedRows:
@@ -411,12 +413,18 @@ class Ops:
             raise KernelError(f"bias has {bias.numel()} elements, expected {N}")
         if T == 0:
             return out
-        need = int(self.lib.sm_gemm_tc_workspace_bytes(T, N, K, int(mode == 2)))
+        paired = self.lib.sm_gemm_pair_takes(_ptr(x), _ptr(w), _ptr(out), _dt(out), T, N, K, mode)
+        need = 0 if paired else int(self.lib.sm_gemm_tc_workspace_bytes(T, N, K, int(mode == 2)))
         workspace = torch.empty((need // 4,), dtype=torch.float32, device=x.device) if need else None
         self._check(self.lib.sm_gemm_tc(_ptr(x), _ptr(w), _ptr(bias), _dt(bias) if bias is not None else F32, _ptr(out),
                                         _dt(out), T, N, K, mode | (activation << 8), up_offset, _ptr(workspace), _ptr(self.error_flag),
                                         _stream()))
         return out
+
+    def gemm_pair_enable(self, on: bool) -> None:
+        """Whether products of 512 tokens and more go to the two-CTA kernel (the default) or stay on the one-CTA
+        kernel: for comparisons of the two."""
+        self.lib.sm_gemm_pair_enable(int(bool(on)))
 
     def check_error_flag(self) -> None:
         """Raises if a kernel gave up on a bounded wait since the last check (synchronises)."""

@@ -53,6 +53,45 @@ def test_gemm_tc_gated(ops, T, H, K):
     assert float((out.float() - want).abs().max()) <= 8e-3 * float(want.abs().max()) + 1e-3
 
 
+@pytest.mark.parametrize("T,N,K", [(512, 896, 896), (2048, 896, 4864), (700, 200, 72), (1100, 1152, 896), (513, 136, 264),
+                                   (4096, 2048, 128), (8192, 512, 64)])
+@pytest.mark.parametrize("mode", ["store_f32", "store_bf16", "accumulate", "gated"])
+def test_gemm_pair(ops, T, N, K, mode):
+    """Products of 512 tokens and more go to the kernel in which two CTAs share a tile of 256 tokens: against a float
+    product, and against the one-CTA kernel on the same data."""
+    x = _rand((T, K), torch.bfloat16, 11)
+    w = _rand((2 * N if mode == "gated" else N, K), torch.bfloat16, 12, 0.05)
+    bias = _rand((N,), torch.bfloat16, 13)
+    start = _rand((T, N), torch.float32, 14)
+
+    def run():
+        if mode == "gated":
+            out = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
+            return ops.gemm_tc(x, w, None, out, mode=2, up_offset=N)
+        if mode == "accumulate":
+            return ops.gemm_tc(x, w, None, start.clone(), mode=1)
+        out = torch.empty((T, N), dtype=torch.float32 if mode == "store_f32" else torch.bfloat16, device="cuda")
+        return ops.gemm_tc(x, w, bias, out, mode=0)
+
+    if mode == "gated":
+        g, u = x.float() @ w[:N].float().T, x.float() @ w[N:].float().T
+        want = u * (g / (1 + torch.exp(-g)))
+    else:
+        want = x.float() @ w.float().T + (start if mode == "accumulate" else bias.float())
+    got = run()
+    ops.check_error_flag()
+    ops.gemm_pair_enable(False)
+    try:
+        single = run()
+        ops.check_error_flag()
+    finally:
+        ops.gemm_pair_enable(True)
+    rounding = 0.0 if got.dtype == torch.float32 else 8e-3 * float(want.abs().max())
+    tol = 1e-3 * math.sqrt(K) * 0.05 + rounding + (1e-3 if mode == "gated" else 0.0)
+    assert float((got.float() - want).abs().max()) <= tol
+    assert float((got.float() - single.float()).abs().max()) <= tol
+
+
 def test_gemm_tc_refuses_unaligned_k(ops):
     from smolmoe_c99_b200.kernels import KernelError
     x, w = _rand((4, 100), torch.bfloat16, 1), _rand((16, 100), torch.bfloat16, 2)
