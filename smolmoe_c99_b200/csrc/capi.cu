@@ -250,6 +250,18 @@ SM_API int sm_gemm_tc_qkv(const void* x, const void* w, int T, int K, const void
     });
 }
 
+SM_API int sm_gemm_pair_qkv(const void* x, const void* w, int T, int K, const void* bias, int bias_dt, int heads, int kv_heads,
+                            int head_dim, const int32_t* positions, const float* cos_table, const float* sin_table, void* q_out,
+                            void* k_packed, void* v_packed, void* k_pool, void* v_pool, const int32_t* page_table,
+                            int table_stride, int ring, const int32_t* token_slot, const int32_t* token_end, int* error,
+                            int* taken, void* stream) {
+    return guarded([&] {
+        sm::PairRope rope{heads, kv_heads, head_dim, positions, cos_table, sin_table, q_out, k_packed, v_packed, k_pool, v_pool,
+                          page_table, table_stride, ring, token_slot, token_end};
+        *taken = sm::gemm_pair_qkv(x, w, bias, (sm::DType)bias_dt, T, K, rope, error, (cudaStream_t)stream) ? 1 : 0;
+    });
+}
+
 SM_API int sm_gemm_skinny_supports(int T, int N, int K) { return sm::gemm_skinny_supports(T, N, K) ? 1 : 0; }
 
 SM_API int sm_gemm_skinny_rounds(int T, int N, int K, int gated) { return sm::gemm_skinny_rounds(T, N, K, gated != 0); }

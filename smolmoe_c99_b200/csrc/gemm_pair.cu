@@ -54,7 +54,7 @@ constexpr int kThreads = 192;
 constexpr int kStagingBytes = kRows * 128;   // one chunk on its way out: 128 token rows of 128 bytes, swizzled
 constexpr int kPairMinTokens = 512;  // below this the one-CTA kernel's smaller token tiles fill the machine better
 
-enum PairEpilogue : int { P_STORE = 0, P_ACCUM = 1, P_GATED = 2 };
+enum PairEpilogue : int { P_STORE = 0, P_ACCUM = 1, P_GATED = 2, P_QKV = 3 };
 
 struct PairParams {
     int T, N, K;
@@ -69,7 +69,9 @@ struct PairParams {
     int out_dt;
     int* error;
     int tiles_f, units;       // feature tiles; units = feature tiles x token tiles
+    PairRope rope;            // P_QKV: the heads, the rotation's tables and where q, keys and values go
 };
+
 
 using namespace tc5;
 
@@ -118,7 +120,7 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_in_cluster(uint32_t bar_in_cluster) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_in_cluster) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_in_cluster) : "memory");
 }
 // Bounded wait on a barrier of this CTA on which the partner arrives too.
 __device__ __forceinline__ bool mbar_wait_pair(uint64_t* bar, uint32_t parity) {
@@ -198,9 +200,182 @@ __device__ __forceinline__ PairUnit pair_unit(const PairParams& p, int u, int ra
     return r;
 }
 
+// One group of 32 columns of this thread's token on its way out: the values (for a gated product act(gate) * up, else
+// the sum plus the bias) as 16-byte pieces of the staged row.
+template <bool WIDE, bool GATED>
+__device__ __forceinline__ void group_out(const PairParams& p, uint32_t (&gr)[32], uint32_t (&ur)[32], int n_first, uint8_t* stage,
+                                          int row, int first_piece) {
+    float g[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(gr[j]);
+    if (GATED) {
+        // (the choice of the activation stays outside the loop over the 32 values: this epilogue's instruction count
+        // is what a gated unit's time is made of)
+        if (p.act == ACT_SILU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(ur[j]) * __fdividef(g[j], 1.0f + __expf(-g[j]));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(ur[j]) * activate_fast(p.act, g[j]);
+        }
+    } else if (p.bias) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) g[j] += bias_at(p, n_first + j);
+    }
+    if (WIDE) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            stage_piece(stage, row, first_piece + j, make_uint4(__float_as_uint(g[4 * j]), __float_as_uint(g[4 * j + 1]),
+                                                                __float_as_uint(g[4 * j + 2]), __float_as_uint(g[4 * j + 3])));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            stage_piece(stage, row, first_piece + j, make_uint4(pack_bf16(g[8 * j], g[8 * j + 1]), pack_bf16(g[8 * j + 2], g[8 * j + 3]),
+                                                                pack_bf16(g[8 * j + 4], g[8 * j + 5]), pack_bf16(g[8 * j + 6], g[8 * j + 7])));
+    }
+}
+
+// The epilogue of one unit for this thread's token: 64 columns a turn, as two groups of 32 whose loads from tensor
+// memory run one group ahead of the arithmetic. A turn of float output fills both staging buffers (a row of 32 floats
+// is the 128 bytes a staged row holds), a turn of bfloat16 output one buffer, the other still being read by the store
+// of the turn before.
+template <bool WIDE, bool GATED>
+__device__ __forceinline__ void unit_out(const PairParams& p, const PairUnit& w, uint32_t acc, int row, uint8_t* staging,
+                                         uint32_t& turn_count, bool issuer, const CUtensorMap& map_out) {
+    const int out_cols = GATED ? p.half : p.tile_f;
+    uint32_t ga[32], ua[32], gb[32], ub[32];
+    tmem_ld32_issue(acc, ga);
+    if (GATED) tmem_ld32_issue(acc + (uint32_t)p.half, ua);
+    for (int c0 = 0; c0 < out_cols; c0 += 64, ++turn_count) {
+        if (w.n0 + c0 >= p.N) break;                 // the same for all epilogue threads
+        uint8_t* first = WIDE ? staging : staging + (turn_count & 1u) * kStagingBytes;
+        uint8_t* second = WIDE ? staging + kStagingBytes : first;
+        // the stores that used these buffers have read them
+        if (issuer) {
+            if (WIDE) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        }
+        epilogue_barrier();
+        tmem_ld_wait(ga);
+        if (GATED) tmem_ld_wait(ua);
+        tmem_ld32_issue(acc + (uint32_t)(c0 + 32), gb);
+        if (GATED) tmem_ld32_issue(acc + (uint32_t)(p.half + c0 + 32), ub);
+        group_out<WIDE, GATED>(p, ga, ua, w.n0 + c0, first, row, 0);
+        tmem_ld_wait(gb);
+        if (GATED) tmem_ld_wait(ub);
+        if (c0 + 64 < out_cols && w.n0 + c0 + 64 < p.N) {
+            tmem_ld32_issue(acc + (uint32_t)(c0 + 64), ga);
+            if (GATED) tmem_ld32_issue(acc + (uint32_t)(p.half + c0 + 64), ua);
+        }
+        group_out<WIDE, GATED>(p, gb, ub, w.n0 + c0 + 32, second, row, WIDE ? 0 : 4);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        epilogue_barrier();
+        if (issuer) {
+            if (p.epilogue == P_ACCUM) {
+                tma_add_2d(&map_out, first, w.n0 + c0, w.t0);
+                tma_add_2d(&map_out, second, w.n0 + c0 + 32, w.t0);
+            } else {
+                tma_store_2d(&map_out, first, w.n0 + c0, w.t0);
+                if (WIDE) tma_store_2d(&map_out, second, w.n0 + c0 + 32, w.t0);
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+    }
+}
+
+// The epilogue of a q/k/v product: the tile's columns are whole heads (64 or 128 wide). Each thread adds the bias to its
+// token's row of a head, rotates it by the token's position if it is a query or key head (pairs (i, i + head_dim / 2),
+// the angle's cosine and sine from the tables, all in float), rounds to bfloat16 once and hands the head to TMA: queries
+// to q_out, keys and values to the packed tensors of the step; keys and values also go straight from the registers into
+// the paged cache (unless the ring has no place for the position any more).
+__device__ __forceinline__ void qkv_heads_out(const PairParams& p, const PairUnit& w, uint32_t acc, int row, uint8_t* staging,
+                                              uint32_t& chunk_count, bool issuer, const CUtensorMap& map_q,
+                                              const CUtensorMap& map_k, const CUtensorMap& map_v) {
+    const PairRope& r = p.rope;
+    const int hd = r.head_dim, half = hd >> 1, chunks = hd / 64;
+    const int t = w.t0 + row;
+    const bool live = t < p.T;
+    const int pos = live ? r.positions[t] : 0;
+    for (int col0 = 0; col0 < p.tile_f; col0 += hd) {
+        const int head = (w.n0 + col0) / hd;
+        if (head >= r.heads + 2 * r.kv_heads) break;           // the same for all epilogue threads
+        const bool is_q = head < r.heads, is_v = head >= r.heads + r.kv_heads;
+        const int kvh = is_q ? 0 : head - r.heads - (is_v ? r.kv_heads : 0);
+        // a head of 128 takes both staging buffers, a head of 64 the one that the head before did not take
+        uint8_t* first = chunks == 2 ? staging : staging + (chunk_count & 1u) * kStagingBytes;
+        if (issuer) {
+            if (chunks == 2) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        }
+        epilogue_barrier();
+        __nv_bfloat16* pool_row = nullptr;
+        if (!is_q && live && r.k_pool != nullptr && !(r.ring > 0 && pos < r.token_end[t] - r.ring)) {
+            const PagedKV paged{r.page_table, r.table_stride, r.ring, r.kv_heads, hd};
+            pool_row = (__nv_bfloat16*)(is_v ? r.v_pool : r.k_pool) + paged.row_offset(r.token_slot[t], pos, kvh);
+        }
+        for (int s = 0; s < half; s += 32) {
+            uint32_t lo_r[32], hi_r[32];
+            tmem_ld32_issue(acc + (uint32_t)(col0 + s), lo_r);
+            tmem_ld32_issue(acc + (uint32_t)(col0 + half + s), hi_r);
+            tmem_ld_wait(lo_r);
+            tmem_ld_wait(hi_r);
+            float lo[32], hi[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { lo[j] = __uint_as_float(lo_r[j]); hi[j] = __uint_as_float(hi_r[j]); }
+            if (p.bias) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    lo[j] += bias_at(p, w.n0 + col0 + s + j);
+                    hi[j] += bias_at(p, w.n0 + col0 + half + s + j);
+                }
+            }
+            if (!is_v) {
+                const float4* c4 = (const float4*)(r.cos_table + (size_t)pos * half + s);
+                const float4* s4 = (const float4*)(r.sin_table + (size_t)pos * half + s);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 c = __ldg(c4 + j), sn = __ldg(s4 + j);
+                    const float cs[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float a = lo[4 * j + e], b = hi[4 * j + e];
+                        lo[4 * j + e] = a * cs[e] - b * ss[e];
+                        hi[4 * j + e] = a * ss[e] + b * cs[e];
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 l = make_uint4(pack_bf16(lo[8 * j], lo[8 * j + 1]), pack_bf16(lo[8 * j + 2], lo[8 * j + 3]),
+                                           pack_bf16(lo[8 * j + 4], lo[8 * j + 5]), pack_bf16(lo[8 * j + 6], lo[8 * j + 7]));
+                const uint4 h = make_uint4(pack_bf16(hi[8 * j], hi[8 * j + 1]), pack_bf16(hi[8 * j + 2], hi[8 * j + 3]),
+                                           pack_bf16(hi[8 * j + 4], hi[8 * j + 5]), pack_bf16(hi[8 * j + 6], hi[8 * j + 7]));
+                const int lo_col = s + 8 * j, hi_col = half + s + 8 * j;      // columns within the head
+                stage_piece(first + (lo_col >> 6) * kStagingBytes, row, (lo_col & 63) >> 3, l);
+                stage_piece(first + (hi_col >> 6) * kStagingBytes, row, (hi_col & 63) >> 3, h);
+                if (pool_row) {
+                    *(uint4*)(pool_row + lo_col) = l;
+                    *(uint4*)(pool_row + hi_col) = h;
+                }
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        epilogue_barrier();
+        if (issuer) {
+            const CUtensorMap* map = is_q ? &map_q : (is_v ? &map_v : &map_k);
+            const bool wanted = is_q || r.k_packed != nullptr;
+            if (wanted)
+                for (int c = 0; c < chunks; ++c) tma_store_2d(map, first + c * kStagingBytes, (is_q ? head : kvh) * hd + 64 * c, w.t0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        ++chunk_count;
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                 const __grid_constant__ CUtensorMap map_out, PairParams p) {
+                 const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, PairParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // (the same offset in both CTAs: the instruction addresses the partner's tiles by this CTA's descriptors)
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -226,6 +401,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     uint32_t tmem_cols = 32;
     while ((int)tmem_cols < 2 * p.tile_f) tmem_cols <<= 1;
 
+    if (threadIdx.x == 32) {
+        prefetch_tensor_map(&map_w);
+        prefetch_tensor_map(&map_x);
+        prefetch_tensor_map(&map_out);
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 8); }
@@ -251,12 +431,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         const int early = min(p.stages, kb_total);
         {
             const PairUnit w = pair_unit(p, pair, rank);        // the grid never has more pairs than units
-            for (int i = 0; i < early; ++i) {
-                if (leader && lane == 0) mbar_expect_tx(&full_bar[i], 2u * (uint32_t)stage_bytes);
-                __syncwarp();
-                if (box.active && !box.from_x)
+            if (leader && lane == 0)
+                for (int i = 0; i < early; ++i) mbar_expect_tx(&full_bar[i], 2u * (uint32_t)stage_bytes);
+            __syncwarp();
+            if (box.active && !box.from_x)
+                for (int i = 0; i < early; ++i)
                     tma_load_2d_pair(smem + (size_t)i * stage_bytes + box.offset, &map_w, i * kStageK + box.k, w.w0 + box.row, full0 + 8u * i);
-            }
             pdl_wait();
             for (int i = 0; i < early; ++i)
                 if (box.active && box.from_x)
@@ -336,9 +516,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         const bool issuer = warp == 2 && lane == 0;
         const int row = quarter * 32 + lane;
         const uint32_t tempty0 = in_cta(smem_u32(tempty_bar), 0);
-        const bool wide = p.out_dt == F32;                 // a chunk is 128 bytes of a row: 32 floats or 64 bfloat16
-        const int chunk_cols = wide ? 32 : 64;
-        const int out_cols = p.epilogue == P_GATED ? p.half : p.tile_f;
         int i = 0;
         uint32_t chunk_count = 0;
         pdl_wait();   // the output (read for "+=") and everything written below come after the kernel before
@@ -351,65 +528,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             if (!ok) break;
             tc_fence_after();
             const uint32_t acc = tmem_base + (uint32_t)(b * p.tile_f) + ((uint32_t)(quarter * 32) << 16);
-            if (w.t0 < p.T) {
-                for (int c0 = 0; c0 < out_cols; c0 += chunk_cols, ++chunk_count) {
-                    if (w.n0 + c0 >= p.N) break;             // the same for all epilogue threads
-                    uint8_t* stage = staging + (chunk_count & 1u) * kStagingBytes;
-                    // the store that used this buffer two chunks ago has read it
-                    if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                    epilogue_barrier();
-                    if (wide) {
-                        float g[32];
-                        tmem_ld32(acc + (uint32_t)c0, g);
-                        if (p.bias) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) g[j] += bias_at(p, w.n0 + c0 + j);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            stage_piece(stage, row, j, make_uint4(__float_as_uint(g[4 * j]), __float_as_uint(g[4 * j + 1]),
-                                                                  __float_as_uint(g[4 * j + 2]), __float_as_uint(g[4 * j + 3])));
-                    } else {
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            float g[32];
-                            tmem_ld32(acc + (uint32_t)(c0 + 32 * h), g);
-                            if (p.epilogue == P_GATED) {
-                                float up[32];
-                                tmem_ld32(acc + (uint32_t)(p.half + c0 + 32 * h), up);
-                                // (the choice of the activation stays outside the loop over the 32 values)
-                                if (p.act == ACT_SILU) {
-#pragma unroll
-                                    for (int j = 0; j < 32; ++j) g[j] = up[j] * __fdividef(g[j], 1.0f + __expf(-g[j]));
-                                } else {
-#pragma unroll
-                                    for (int j = 0; j < 32; ++j) g[j] = up[j] * activate_fast(p.act, g[j]);
-                                }
-                            } else if (p.bias) {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) g[j] += bias_at(p, w.n0 + c0 + 32 * h + j);
-                            }
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                stage_piece(stage, row, 4 * h + j, make_uint4(pack_bf16(g[8 * j], g[8 * j + 1]), pack_bf16(g[8 * j + 2], g[8 * j + 3]),
-                                                                              pack_bf16(g[8 * j + 4], g[8 * j + 5]), pack_bf16(g[8 * j + 6], g[8 * j + 7])));
-                        }
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    epilogue_barrier();
-                    if (issuer) {
-                        if (p.epilogue == P_ACCUM) tma_add_2d(&map_out, stage, w.n0 + c0, w.t0);
-                        else tma_store_2d(&map_out, stage, w.n0 + c0, w.t0);
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    }
-                }
+            if (p.epilogue == P_QKV) {
+                if (w.t0 < p.T) qkv_heads_out(p, w, acc, row, staging, chunk_count, issuer, map_out, map_k, map_v);
+            } else if (w.t0 < p.T) {
+                if (p.epilogue == P_GATED) unit_out<false, true>(p, w, acc, row, staging, chunk_count, issuer, map_out);
+                else if (p.out_dt == F32) unit_out<true, false>(p, w, acc, row, staging, chunk_count, issuer, map_out);
+                else unit_out<false, false>(p, w, acc, row, staging, chunk_count, issuer, map_out);
             }
             // this accumulator may be overwritten by the MMAs of the unit after next
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_in_cluster(tempty0 + 8u * b);
         }
-        if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory stays valid until read
+        if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory stays valid until read
     }
     __syncwarp();
     tc_fence_before();
@@ -514,8 +645,51 @@ void gemm_pair(const void* x, const void* w, const void* bias, DType bias_dt, vo
     });
     const int pairs = p.units < pairs_on_gpu ? p.units : pairs_on_gpu;
     launch_kernel("gemm_pair", gemm_pair_kernel, dim3(2 * pairs), dim3(kThreads), smem, stream, 2, dependent_launch_enabled(), map_w,
-                  map_x, map_out, p);
+                  map_x, map_out, map_out, map_out, p);
     note_launch(1);
+}
+
+bool gemm_pair_qkv(const void* x, const void* w, const void* bias, DType bias_dt, int T, int K, const PairRope& rope, int* error,
+                   cudaStream_t stream) {
+    const int N = (rope.heads + 2 * rope.kv_heads) * rope.head_dim;
+    if (!g_pair_enabled || T < kPairMinTokens || K <= 0 || K % 8 || rope.heads <= 0 || rope.kv_heads < 0) return false;
+    if (rope.head_dim != 64 && rope.head_dim != 128) return false;      // whole heads per 128 columns, 128 bytes a piece of a row
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)rope.q_out | (uintptr_t)rope.k_packed | (uintptr_t)rope.v_packed |
+         (uintptr_t)rope.k_pool | (uintptr_t)rope.v_pool | (uintptr_t)rope.cos_table | (uintptr_t)rope.sin_table) & 15)
+        return false;
+    if ((rope.k_packed == nullptr) != (rope.v_packed == nullptr) || (rope.k_pool == nullptr) != (rope.v_pool == nullptr)) return false;
+    PairParams p{};
+    p.T = T; p.N = N; p.K = K;
+    p.epilogue = P_QKV;
+    p.tile_f = 128;
+    p.half = 64;
+    p.tiles_f = (N + 127) / 128;
+    p.bias = bias; p.bias_dt = bias_dt;
+    p.out_dt = BF16;
+    p.error = error;
+    p.rope = rope;
+    p.units = p.tiles_f * ((T + 2 * kRows - 1) / (2 * kRows));
+    const int stage_bytes = kRows * kStageK * 2 + p.half * kStageK * 2;
+    const int budget = 227 * 1024 - 1024 - 2 * kStagingBytes - 256;
+    p.stages = budget / stage_bytes;
+    if (p.stages > 8) p.stages = 8;
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + 2 * kStagingBytes + (2 * p.stages + 5) * 8 + 64;
+    const CUtensorMap map_w = pair_operand_map(w, N, K);
+    const CUtensorMap map_x = pair_operand_map(x, T, K);
+    const CUtensorMap map_q = pair_out_map(rope.q_out, T, rope.heads * rope.head_dim, BF16);
+    const bool packed = rope.k_packed != nullptr && rope.kv_heads > 0;
+    const CUtensorMap map_k = packed ? pair_out_map(rope.k_packed, T, rope.kv_heads * rope.head_dim, BF16) : map_q;
+    const CUtensorMap map_v = packed ? pair_out_map(rope.v_packed, T, rope.kv_heads * rope.head_dim, BF16) : map_q;
+    static std::once_flag attr_once;
+    std::call_once(attr_once, [] {
+        cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    });
+    const int pairs_on_gpu = pair_sm_count() / 2;
+    const int pairs = p.units < pairs_on_gpu ? p.units : pairs_on_gpu;
+    launch_kernel("gemm_pair", gemm_pair_kernel, dim3(2 * pairs), dim3(kThreads), smem, stream, 2, dependent_launch_enabled(), map_w,
+                  map_x, map_q, map_k, map_v, p);
+    note_launch(1);
+    return true;
 }
 
 }  // namespace sm

@@ -111,6 +111,27 @@ bool gemm_pair_takes(const void* x, const void* w, const void* out, DType out_dt
 void gemm_pair_enable(bool on);
 void gemm_pair(const void* x, const void* w, const void* bias, DType bias_dt, void* out, DType out_dt, int T, int N, int K,
                int mode, int up_offset, int* error, cudaStream_t stream);
+// q/k/v rows of many tokens with bias, rotation and the cache write in the product's epilogue: rotated queries to q_out,
+// rotated keys and the values to the step's packed tensors (where given) and into the paged pools (where given, and
+// where the ring still has a place for the position). Head sizes 64 and 128, every dimension rotated. Returns false,
+// having done nothing, where the product is not taken.
+struct PairRope {
+    int heads, kv_heads, head_dim;
+    const int32_t* positions;   // [T]
+    const float* cos_table;     // [positions, head_dim / 2]
+    const float* sin_table;
+    void* q_out;                // bfloat16 [T, heads, head_dim]
+    void* k_packed;             // bfloat16 [T, kv_heads, head_dim] or null
+    void* v_packed;
+    void* k_pool;               // or null: nothing is written to the cache
+    void* v_pool;
+    const int32_t* page_table;
+    int table_stride, ring;
+    const int32_t* token_slot;  // [T]
+    const int32_t* token_end;   // [T]
+};
+bool gemm_pair_qkv(const void* x, const void* w, const void* bias, DType bias_dt, int T, int K, const PairRope& rope, int* error,
+                   cudaStream_t stream);
 
 // ---- gemm_skinny.cu -------------------------------------------------------------------
 // The product for a handful of tokens (T <= 32) and bfloat16 weights, with the layer's

@@ -247,6 +247,48 @@ class Ops:
             _ptr(token_slot), _ptr(token_end), _stream()))
         return q, kp, vp
 
+    def qkv_rope_store_many(self, x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim, rotary_dim,
+                            want_packed, k_pool=None, v_pool=None, page_table=None, ring=0, token_slot=None, token_end=None):
+        """The q/k/v product of many tokens with bias, rotation and the cache write in its epilogue (what ``linear`` and
+        ``rope_store`` do in two launches through a float copy of q, k and v). Returns (q, k_packed, v_packed) like
+        ``rope_store``, or None, having done nothing, where the kernel does not take the product (fewer than 512
+        tokens, other head sizes than 64 and 128, a partial rotation, float operands): the caller then goes the
+        other way."""
+        if (not self.use_tensor_cores or w_qkv.dtype != torch.bfloat16 or self._dtype_of(x) != torch.bfloat16
+                or x.shape[0] < 512 or head_dim not in (64, 128) or rotary_dim != head_dim):
+            return None
+        x = self.materialize(x)
+        _need(x, "x", torch.bfloat16, 2)
+        _need(w_qkv, "w_qkv", torch.bfloat16, 2)
+        T, K = x.shape
+        if w_qkv.shape != ((heads + 2 * kv_heads) * head_dim, K):
+            raise KernelError(f"q/k/v weights are {tuple(w_qkv.shape)}, expected {((heads + 2 * kv_heads) * head_dim, K)}")
+        _need(positions, "positions", torch.int32, 1)
+        _need(cos_table, "cos table", torch.float32, 2)
+        _need(sin_table, "sin table", torch.float32, 2)
+        if cos_table.shape[1] != head_dim // 2:
+            raise KernelError("cos/sin tables do not match head_dim")
+        q = torch.empty((T, heads, head_dim), dtype=torch.bfloat16, device=x.device)
+        kp = vp = None
+        if want_packed and kv_heads:
+            kp = torch.empty((T, kv_heads, head_dim), dtype=torch.bfloat16, device=x.device)
+            vp = torch.empty_like(kp)
+        table_stride = 0
+        if k_pool is not None:
+            _need(k_pool, "key pool", torch.bfloat16)
+            _need(v_pool, "value pool", torch.bfloat16)
+            _need(page_table, "page table", torch.int32, 2)
+            _need(token_slot, "token_slot", torch.int32, 1)
+            _need(token_end, "token_end", torch.int32, 1)
+            table_stride = page_table.shape[1]
+        taken = ctypes.c_int(0)
+        self._check(self.lib.sm_gemm_pair_qkv(
+            _ptr(x), _ptr(w_qkv), T, K, _ptr(b_qkv), _dt(b_qkv) if b_qkv is not None else F32, heads, kv_heads, head_dim,
+            _ptr(positions), _ptr(cos_table), _ptr(sin_table), _ptr(q), _ptr(kp), _ptr(vp), _ptr(k_pool), _ptr(v_pool),
+            _ptr(page_table), table_stride, ring, _ptr(token_slot), _ptr(token_end), _ptr(self.error_flag),
+            ctypes.byref(taken), _stream()))
+        return (q, kp, vp) if taken.value else None
+
     # ---- matrix products ---------------------------------------------------------------
     def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
                   accumulate: bool = False) -> torch.Tensor:

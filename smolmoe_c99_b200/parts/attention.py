@@ -90,18 +90,26 @@ class Attention(Part):
                 ops.linear(att.view(T, self.heads * self.head_dim), self.w_o, None, out=residual, accumulate=True)
                 ops.lap("attn_out")
                 return
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
-        ops.lap("qkv")
         # In a windowed group a new row takes the place of the row one ring earlier, which queries of this very step
         # may still see when sequences go on from the cache: those steps store after they have attended.
         store_late = own and mode == "extend" and cache.ring > 0
         write_now = own and not store_late
-        q, k_packed, v_packed = ops.rope_store(
-            qkv, step.positions, cos, sin, self.heads, self.kv_heads if own else 0, self.head_dim,
-            self.position.rotary_dim, rt.dtype, want_packed=own and mode != "decode",
-            k_pool=cache.k_pool if write_now else None, v_pool=cache.v_pool if write_now else None,
-            page_table=cache.page_table, ring=cache.ring, token_slot=step.token_slot, token_end=step.token_end)
-        ops.lap("rope")
+        where = dict(k_pool=cache.k_pool if write_now else None, v_pool=cache.v_pool if write_now else None,
+                     page_table=cache.page_table, ring=cache.ring, token_slot=step.token_slot, token_end=step.token_end)
+        # many tokens: product, bias, rotation and the cache write in one launch
+        fused = ops.qkv_rope_store_many(x, self.w_qkv, self.b_qkv, step.positions, cos, sin, self.heads,
+                                        self.kv_heads if own else 0, self.head_dim, self.position.rotary_dim,
+                                        want_packed=own and mode != "decode", **where)
+        if fused is not None:
+            q, k_packed, v_packed = fused
+            ops.lap("qkv")
+        else:
+            qkv = ops.linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
+            ops.lap("qkv")
+            q, k_packed, v_packed = ops.rope_store(
+                qkv, step.positions, cos, sin, self.heads, self.kv_heads if own else 0, self.head_dim,
+                self.position.rotary_dim, rt.dtype, want_packed=own and mode != "decode", **where)
+            ops.lap("rope")
         if own and mode == "prefill":
             att = ops.attention_prefill(q, k_packed, v_packed, step, self.scale, self.window)
         elif own and mode == "extend":

@@ -638,6 +638,65 @@ def test_fused_qkv_on_the_tcgen05_kernel_matches_the_separate_kernels(ops, heads
         assert float((pools[3][page, :, row].float() - v_t[page, :, row]).abs().max()) <= tol
 
 
+@pytest.mark.parametrize("heads,kv_heads,hd", [(14, 2, 64), (3, 1, 128), (8, 2, 128), (5, 3, 64), (4, 0, 64)])
+@pytest.mark.parametrize("T,K,ring", [(512, 896, 0), (777, 136, 0), (2048, 896, 0), (900, 264, 256)])
+def test_fused_qkv_of_many_tokens(ops, heads, kv_heads, hd, T, K, ring):
+    """512 tokens and more: bias, rotation, the packed keys and values and the cache write in the epilogue of the
+    two-CTA product, against PyTorch in float. Two sequences that go on from unequal positions, scattered pages; with
+    a ring, the positions that it has no place for any more must not be written."""
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    N = (heads + 2 * kv_heads) * hd
+    x, w, b = _rand((T, K), torch.bfloat16, 1), _rand((N, K), torch.bfloat16, 2, 0.05), _rand((N,), torch.bfloat16, 3)
+    first = T // 3
+    starts, lens = [37, 0], [first, T - first]
+    positions = torch.cat([torch.arange(s0, s0 + n) for s0, n in zip(starts, lens)]).to(torch.int32).cuda()
+    token_slot = torch.cat([torch.full((n,), slot) for slot, n in zip([1, 0], lens)]).to(torch.int32).cuda()
+    token_end = torch.cat([torch.full((n,), s0 + n) for s0, n in zip(starts, lens)]).to(torch.int32).cuda()
+    pages_per_slot = (ring or (max(s0 + n for s0, n in zip(starts, lens)) + PAGE_SIZE)) // PAGE_SIZE + (0 if ring else 1)
+    g = torch.Generator().manual_seed(9)
+    table = torch.randperm(2 * pages_per_slot, generator=g).to(torch.int32).view(2, pages_per_slot).cuda()
+    n_pos = int(positions.max()) + 1
+    half = hd // 2
+    ang = torch.arange(n_pos, dtype=torch.float64)[:, None] * torch.pow(
+        torch.tensor(1e6, dtype=torch.float64), -torch.arange(half, dtype=torch.float64) * 2 / hd)
+    cos, sin = torch.cos(ang).float().cuda(), torch.sin(ang).float().cuda()
+    kvh = max(kv_heads, 1)
+    k_pool = torch.zeros((2 * pages_per_slot, kvh, PAGE_SIZE, hd), dtype=torch.bfloat16, device="cuda")
+    v_pool = torch.zeros_like(k_pool)
+    got = ops.qkv_rope_store_many(x, w, b, positions, cos, sin, heads, kv_heads, hd, hd, want_packed=True, k_pool=k_pool,
+                                  v_pool=v_pool, page_table=table, ring=ring, token_slot=token_slot, token_end=token_end)
+    ops.check_error_flag()
+    assert got is not None, "the two-CTA kernel did not take this product"
+    q, kp, vp = got
+    qkv = x.float() @ w.float().T + b.float()
+    q_t, k_t, v_t = qkv.split([heads * hd, kv_heads * hd, kv_heads * hd], dim=1)
+    c, s_ = cos[positions.long()][:, None, :], sin[positions.long()][:, None, :]
+
+    def rot(t):
+        lo, hi = t[..., :half], t[..., half:]
+        return torch.cat([lo * c - hi * s_, lo * s_ + hi * c], dim=-1)
+
+    q_t = rot(q_t.reshape(T, heads, hd))
+    tol = 1e-3 * math.sqrt(K) * 0.05 + 8e-3 * float(q_t.abs().max())
+    assert float((q.float() - q_t).abs().max()) <= tol
+    if not kv_heads:
+        assert kp is None and vp is None and float(k_pool.abs().max()) == 0.0
+        return
+    k_t, v_t = rot(k_t.reshape(T, kv_heads, hd)), v_t.reshape(T, kv_heads, hd)
+    assert float((kp.float() - k_t).abs().max()) <= tol and float((vp.float() - v_t).abs().max()) <= tol
+    want_k, want_v = torch.zeros_like(k_pool, dtype=torch.float32), torch.zeros_like(v_pool, dtype=torch.float32)
+    for t in range(T):
+        pos, slot, end = int(positions[t]), int(token_slot[t]), int(token_end[t])
+        if ring and pos < end - ring:
+            continue
+        idx = pos % ring if ring else pos
+        page = int(table[slot, idx // PAGE_SIZE])
+        want_k[page, :, idx % PAGE_SIZE] = k_t[t]
+        want_v[page, :, idx % PAGE_SIZE] = v_t[t]
+    assert float((k_pool.float() - want_k).abs().max()) <= tol and float((v_pool.float() - want_v).abs().max()) <= tol
+    assert torch.equal(k_pool != 0, want_k != 0) and torch.equal(v_pool != 0, want_v != 0)
+
+
 def test_fused_qkv_refuses_heads_that_straddle_tiles(ops):
     """Head sizes that do not divide 128 are left to the separate kernels."""
     from smolmoe_c99_b200.kernels import PAGE_SIZE
