@@ -40,11 +40,14 @@ class StepBatch:
                                                   # among them, position of the step's first token, slot
     seq_starts: Optional[List[int]] = None        # per sequence: its length before this step
     wants_every_row: bool = False   # logits are asked for every token of the step, in order
+    packed: Optional[torch.Tensor] = None         # the one device buffer that the tensors above are views of
 
 
 def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence[Sequence[int]],
-              device: torch.device) -> StepBatch:
-    """``starts[i]`` is the length of sequence ``i`` before this step."""
+              device: torch.device, into: Optional[torch.Tensor] = None) -> StepBatch:
+    """``starts[i]`` is the length of sequence ``i`` before this step. ``into``: a device buffer that a step of the
+    same shape (the same numbers of tokens) was packed into before; the step's numbers are copied there, so that
+    kernels captured in a graph find them where they found the earlier step's."""
     if not slots:
         raise ValueError("a step needs at least one sequence")
     lens = [len(t) for t in token_lists]
@@ -97,7 +100,13 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
         host[4] = firsts[seq_of]
     tail = [x for row in tile_rows for x in row] + list(slots) + [s + n for s, n in zip(starts, lens)] + cu
     flat_host[5 * n_tokens:] = torch.tensor(tail, dtype=torch.int32)
-    flat_dev = flat_host.to(device, non_blocking=True)
+    if into is None:
+        flat_dev = flat_host.to(device, non_blocking=True)
+    else:
+        if into.numel() != flat_host.numel() or into.dtype != torch.int32:
+            raise ValueError("the buffer was packed for a step of another shape")
+        into.copy_(flat_host, non_blocking=True)
+        flat_dev = into
     dev = flat_dev[:5 * n_tokens].view(5, n_tokens)
     at = 5 * n_tokens
     tiles = None
@@ -112,4 +121,4 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], token_lists: Sequence
         tokens=dev[0], positions=dev[1], token_slot=dev[2], token_end=dev[3], token_seq_start=dev[4],
         cu_seqlens=cu_dev, slot_ids=per_seq[0], seq_ends=per_seq[1],
         prefill_tiles=tiles if mode == "prefill" else None, extend_tiles=tiles if mode == "extend" else None,
-        seq_starts=list(starts))
+        seq_starts=list(starts), packed=flat_dev)

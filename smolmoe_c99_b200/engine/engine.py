@@ -33,6 +33,7 @@ from .model import DecoderModel, cache_needs, model_param_specs
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 SPAN_BUCKET = 256    # decode graphs are captured for key spans rounded up to this, doubling from there on
 MAX_GRAPHS = 32
+MAX_STEP_GRAPHS = 4  # captured steps of prompts (each keeps the activations of its tokens)
 
 
 class StepError(ValueError):
@@ -95,6 +96,35 @@ class _DecodeGraph:
         self.graph, self.logits = graph, logits
 
 
+class _StepGraph:
+    """One captured step of prompts or prompt portions: the numbers of tokens of its sequences and the wanted rows
+    are fixed, everything else (tokens, positions, slots, pages) is data that each replay brings.
+
+    A small model's prompt step is ~200 launches of a few microseconds of device time each, and the host needs
+    longer to issue them than the device to run them. A shape that comes again (every full portion of a long
+    prompt fed in portions; a benchmark's prompt) is therefore captured the second time it is seen."""
+
+    def __init__(self, engine: "Engine", rows: List[int]):
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.packed: Optional[torch.Tensor] = None
+        self.batch: Optional[StepBatch] = None
+        self.want_rows = torch.tensor(rows, dtype=torch.int32).to(engine.device) if rows else None
+
+    def run(self, engine: "Engine", slots, starts, tokens) -> Optional[torch.Tensor]:
+        batch = pack_step(slots, starts, tokens, engine.device, into=self.packed)
+        if self.graph is None:
+            # (No run outside the capture first: the shape's first step ran kernel by kernel, which loaded the kernels
+            # and set their attributes. Nothing runs during the capture, so the replay below is this step's one run.)
+            self.packed, self.batch = batch.packed, batch
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = engine.model.forward(batch, engine.cache, self.want_rows, engine._status)
+            self.graph, self.logits = graph, logits
+        self.graph.replay()
+        return self.logits
+
+
 class Engine:
     def __init__(self, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", *, max_tokens: int = 4096,
                  max_slots: Optional[int] = None, max_seq_len: Optional[int] = None, device: str = "cuda:0",
@@ -125,6 +155,11 @@ class Engine:
         self.max_step_tokens = max_step_tokens
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._graphs: "OrderedDict[Tuple[int, int], _DecodeGraph]" = OrderedDict()
+        # steps of prompts: how often a shape was seen, and the captured ones (a few: each keeps its activations)
+        self._step_seen: "OrderedDict[tuple, int]" = OrderedDict()
+        self._step_graphs: "OrderedDict[tuple, _StepGraph]" = OrderedDict()
+        self.step_graph_max_tokens = 16384
+        self._has_ring = any(group.ring > 0 for group in self.cache.groups)
         self.kernel_launches = 0   # graph replays and eager steps, for the record
 
     # ---- construction from random weights ------------------------------------------------
@@ -212,12 +247,39 @@ class Engine:
         else:
             if on_device:
                 tokens = [[int(t)] for t in tokens.tolist()]
-            batch = pack_step(slots, starts, tokens, self.device)
-            want_rows = torch.tensor(rows, dtype=torch.int32).to(self.device) if rows else None
-            logits = self.model.forward(batch, self.cache, want_rows, self._status)
+            logits = self._prompt_step(slots, starts, tokens, lens, rows)
         self.kernel_launches += 1
         self.cache.advance(growth)
         return logits
+
+    def _prompt_step(self, slots, starts, tokens, lens, rows) -> Optional[torch.Tensor]:
+        """A step that is not one token each: eagerly, or -- a shape seen before -- as a captured graph."""
+        first = all(s == 0 for s in starts)
+        # (a windowed group's late store and the check of its ring are decided on the host from the starts: those
+        # steps stay eager unless every sequence is at its first token)
+        if self.use_graphs and sum(lens) <= self.step_graph_max_tokens and (first or not self._has_ring):
+            key = (first, tuple(lens), tuple(rows))
+            g = self._step_graphs.get(key)
+            if g is None:
+                seen = self._step_seen.pop(key, 0) + 1
+                self._step_seen[key] = seen
+                while len(self._step_seen) > 64:
+                    self._step_seen.popitem(last=False)
+                if seen >= 2:
+                    while len(self._step_graphs) >= MAX_STEP_GRAPHS:
+                        self._step_graphs.popitem(last=False)
+                    g = self._step_graphs[key] = _StepGraph(self, rows)
+            else:
+                self._step_graphs.move_to_end(key)
+            if g is not None:
+                try:
+                    return g.run(self, slots, starts, tokens)
+                except BaseException:
+                    self._step_graphs.pop(key, None)
+                    raise
+        batch = pack_step(slots, starts, tokens, self.device)
+        want_rows = torch.tensor(rows, dtype=torch.int32).to(self.device) if rows else None
+        return self.model.forward(batch, self.cache, want_rows, self._status)
 
     def _decode_graph(self, slots, starts, tokens, on_device) -> torch.Tensor:
         n = len(slots)

@@ -111,6 +111,45 @@ def test_a_decode_graph_replayed_with_some_rows_wanted(model_dirs, dtype):
     assert float((some[1].cpu() - want[2][-2]).abs().max()) <= TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_prompt_steps_of_a_shape_seen_before_are_replayed(model_dirs, name, dtype):
+    """The second step of a shape (the same numbers of tokens and wanted rows) is captured, later ones are replayed
+    with other tokens, slots and starting positions: the logits are those of an engine without graphs, bit for
+    bit, for whole prompts and for prompts that go on in portions (C has a windowed group: its portions stay eager),
+    and the shapes kept are few."""
+    from smolmoe_c99_b200.engine.engine import Engine, MAX_STEP_GRAPHS
+    vocab = TINY[name]["vocab_size"]
+    engine = Engine(model_dirs[name], dtype, max_tokens=4096, max_slots=8)
+    plain = Engine(model_dirs[name], dtype, max_tokens=4096, max_slots=8, use_graphs=False)
+    longest = TINY[name]["max_position_embeddings"] // 2          # every prompt goes on by as many tokens again
+    shapes = [(min(70, longest), 5), (33,), (min(70, longest), 5), (min(129, longest), min(64, longest - 1), 3), (17,)]
+    for round_ in range(4):
+        for si, lens in enumerate(shapes):
+            toks = [random_tokens(2 * n, vocab, 1000 * round_ + 10 * si + i) for i, n in enumerate(lens)]
+            want = [[n - 1] if i % 2 == 0 else [0, n // 2] for i, n in enumerate(lens)]
+            got = []
+            for e in (engine, plain):
+                # slots in another order every round, so that the replay brings other slots and pages
+                spare = [e.open_sequence() for _ in range(round_ % 3)]
+                slots = [e.open_sequence() for _ in lens]
+                first = e.step(slots, [t[:n] for t, n in zip(toks, lens)], want).clone()
+                second = e.step(slots, [t[n:] for t, n in zip(toks, lens)], want).clone()    # goes on from the cache
+                got.append((first, second))
+                for slot in slots + spare:
+                    e.close_sequence(slot)
+            assert torch.equal(got[0][0], got[1][0]), f"round {round_}, whole prompts {lens}"
+            assert torch.equal(got[0][1], got[1][1]), f"round {round_}, portions {lens}"
+    assert 0 < len(engine._step_graphs) <= MAX_STEP_GRAPHS
+    assert not plain._step_graphs
+    # and against the plain implementation once, through a replayed graph
+    toks = random_tokens(33, vocab, 77)
+    slot = engine.open_sequence()
+    lg = engine.step([slot], [toks], [[32]]).cpu()
+    ref = plain_model.forward(model_dirs[name], toks, round_like_bf16_engine=(dtype == "bfloat16"))
+    assert float((lg[0] - ref[32]).abs().max()) <= TOL[dtype]
+
+
 def test_graphs_are_dropped_and_captured_again(model_dirs, monkeypatch):
     """More batch sizes than graphs are kept: the oldest is dropped, and a step of its size captures it again."""
     from smolmoe_c99_b200.engine import engine as engine_module
