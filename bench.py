@@ -359,6 +359,7 @@ def main() -> int:
     if args.profile_region:
         one = prompts(1)
         if args.profile_region == "prefill":
+            engine.use_graphs = False    # kernel by kernel: the same kernels that the captured step replays
             s = engine.open_sequence(); engine.step([s], one); engine.close_sequence(s)
             torch.cuda.synchronize()
             s = engine.open_sequence()

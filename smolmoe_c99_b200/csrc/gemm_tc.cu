@@ -964,7 +964,8 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
     // Up to 64 tokens the CTAs along K can be one cluster that adds its sums up in shared memory: at most 8 of them. More
     // splits would go through a workspace and a second kernel (896 x 4864 at 64 tokens took 10 splits and the reduce
     // kernel; with 8 in a cluster the decode step of the 0.5B sizes at batch 64 went from 1.36 to 1.31 ms).
-    if (T <= 64 && sp > 8 && small_launch(tn, 8, dual).cluster) sp = 8;
+    // Up to 16 tokens the many splits and the reduce kernel are the faster way (the step at batch 16: 0.93 against 1.00 ms).
+    if (T > 16 && T <= 64 && sp > 8 && small_launch(tn, 8, dual).cluster) sp = 8;
     // no empty split: every unit along K gets at least one block
     const int per = (kb + sp - 1) / sp;
     sp = (kb + per - 1) / per;
