@@ -290,7 +290,8 @@ __device__ __forceinline__ void unit_out(const PairParams& p, const PairUnit& w,
 // the paged cache (unless the ring has no place for the position any more).
 __device__ __forceinline__ void qkv_heads_out(const PairParams& p, const PairUnit& w, uint32_t acc, int row, uint8_t* staging,
                                               uint32_t& chunk_count, bool issuer, const CUtensorMap& map_q,
-                                              const CUtensorMap& map_k, const CUtensorMap& map_v) {
+                                              const CUtensorMap& map_k, const CUtensorMap& map_v, bool tables_held,
+                                              const float4 (&held_cos)[8], const float4 (&held_sin)[8]) {
     const PairRope& r = p.rope;
     const int hd = r.head_dim, half = hd >> 1, chunks = hd / 64;
     const int t = w.t0 + row;
@@ -334,7 +335,7 @@ __device__ __forceinline__ void qkv_heads_out(const PairParams& p, const PairUni
                 const float4* s4 = (const float4*)(r.sin_table + (size_t)pos * half + s);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const float4 c = __ldg(c4 + j), sn = __ldg(s4 + j);
+                    const float4 c = tables_held ? held_cos[j] : __ldg(c4 + j), sn = tables_held ? held_sin[j] : __ldg(s4 + j);
                     const float cs[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -522,6 +523,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         for (int u = pair; u < p.units; u += pairs, ++i) {
             const PairUnit w = pair_unit(p, u, rank);
             const int b = i & 1;
+            // q/k/v with heads of 64: this token's row of the cosine and sine tables (32 floats each) is asked for while
+            // the unit's MMAs still run, and serves every head of the unit (each thread reads a row of its own: 32 lines
+            // a warp and instruction, which on the way out cost as much as the rest of the epilogue)
+            float4 held_cos[8], held_sin[8];
+            const bool tables_held = p.epilogue == P_QKV && p.rope.head_dim == 64;
+            if (tables_held) {
+                const int t = w.t0 + row;
+                const int pos = t < p.T ? p.rope.positions[t] : 0;
+                const float4* c4 = (const float4*)(p.rope.cos_table + (size_t)pos * 32);
+                const float4* s4 = (const float4*)(p.rope.sin_table + (size_t)pos * 32);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { held_cos[j] = __ldg(c4 + j); held_sin[j] = __ldg(s4 + j); }
+            }
             bool ok = mbar_wait_pair(&tfull_bar[b], ((uint32_t)i >> 1) & 1u);
             if (!ok && lane == 0) { *failed = 1; atomicExch(p.error, 3); }
             ok = __all_sync(0xffffffffu, ok && *failed == 0);
@@ -529,7 +543,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             tc_fence_after();
             const uint32_t acc = tmem_base + (uint32_t)(b * p.tile_f) + ((uint32_t)(quarter * 32) << 16);
             if (p.epilogue == P_QKV) {
-                if (w.t0 < p.T) qkv_heads_out(p, w, acc, row, staging, chunk_count, issuer, map_out, map_k, map_v);
+                if (w.t0 < p.T) qkv_heads_out(p, w, acc, row, staging, chunk_count, issuer, map_out, map_k, map_v, tables_held, held_cos, held_sin);
             } else if (w.t0 < p.T) {
                 if (p.epilogue == P_GATED) unit_out<false, true>(p, w, acc, row, staging, chunk_count, issuer, map_out);
                 else if (p.out_dt == F32) unit_out<true, false>(p, w, acc, row, staging, chunk_count, issuer, map_out);
