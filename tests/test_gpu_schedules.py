@@ -55,6 +55,56 @@ def test_wide_batches_of_unequal_lengths(model_dirs, name, dtype):
     engine.check_status()
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_long_prompts_on_the_two_cta_products(model_dirs, name):
+    """Steps of 512 tokens and more take the two-CTA products and the q/k/v epilogue that rotates and stores (head
+    sizes 64 and 128): a whole prompt, the same prompt in two portions (the second reads the cache), and two prompts
+    in one step, against the plain implementation; and against the same engine with those products switched off."""
+    from smolmoe_c99_b200.engine.engine import Engine
+    vocab, longest = TINY[name]["vocab_size"], TINY[name]["max_position_embeddings"]
+    n = min(900, longest - 20)
+    requests = {"long": random_tokens(n, vocab, 71), "other": random_tokens(n - 250, vocab, 72)}
+    want = _plain(model_dirs[name], requests, "bfloat16")
+    engine = Engine(model_dirs[name], "bfloat16", max_tokens=4096, max_slots=4, use_graphs=False)
+    rows = list(range(0, n, 37)) + [n - 1]
+
+    def run(lists, cuts):
+        slots = [engine.open_sequence() for _ in lists]
+        out = [[] for _ in lists]
+        at = 0
+        for cut in cuts + [None]:
+            part = [t[at:cut] for t in lists]
+            live = [i for i, t in enumerate(part) if t]
+            want_rows = [[r - at for r in rows if at <= r < at + len(part[i])] for i in live]
+            lg = engine.step([slots[i] for i in live], [part[i] for i in live], want_rows)
+            k = 0
+            for i, w in zip(live, want_rows):
+                out[i].append(lg[k:k + len(w)].clone())
+                k += len(w)
+            at = cut
+        for s in slots:
+            engine.close_sequence(s)
+        return [torch.cat(o).cpu() for o in out]
+
+    def picked(rid):
+        return want[rid][[r for r in rows if r < len(requests[rid])]]
+
+    ops = engine.runtime.ops
+    whole = run([requests["long"]], [])[0]
+    portions = run([requests["long"]], [n - 520])[0]          # 520 tokens onto a cache of the rest
+    both = run([requests["long"], requests["other"]], [])
+    ops.gemm_pair_enable(False)
+    try:
+        single = run([requests["long"]], [])[0]
+    finally:
+        ops.gemm_pair_enable(True)
+    engine.check_status()
+    for what, got, rid in (("whole", whole, "long"), ("two portions", portions, "long"), ("two prompts", both[0], "long"),
+                           ("two prompts", both[1], "other"), ("one-CTA products", single, "long")):
+        _check({rid: got}, {rid: picked(rid)}, "bfloat16", what)
+    assert float((whole - single).abs().max()) <= 1e-2 * float(single.abs().max())
+
+
 @pytest.fixture(scope="module")
 def real_size_dir(tmp_path_factory):
     from smolmoe_c99_b200.config import config_from_json
