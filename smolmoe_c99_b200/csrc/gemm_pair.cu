@@ -1,4 +1,4 @@
-// out[t, n] = sum_k x[t, k] * w[n, k] for more than 128 tokens (prefill, prompt portions, large decode batches): two CTAs on two SMs work as a pair on one tile of
+// out[t, n] = sum_k x[t, k] * w[n, k] for more than 160 tokens (prefill, prompt portions, large decode batches): two CTAs on two SMs work as a pair on one tile of
 // 256 tokens x 128 or 256 output features with the two-CTA form of tcgen05.mma (cta_group::2).
 //
 // Why a pair. A tcgen05.mma reads both operands from shared memory. With one CTA and a 128 x 128 tile every 16 elements
@@ -52,8 +52,8 @@ constexpr int kUmmaK = 16;
 constexpr int kBoxRows = 64;         // rows of one TMA box
 constexpr int kThreads = 192;
 constexpr int kStagingBytes = kRows * 128;   // one chunk on its way out: 128 token rows of 128 bytes, swizzled
-constexpr int kPairMinTokens = 129;  // (a pair's tile is 256 tokens. Measured on the 0.5B sizes, whole prompt steps: 100 tokens 1.80 ms
-                                      // against 1.68 with the one-CTA kernel, 200 tokens 1.85 against 2.03, 700 tokens 2.17 against 3.13)
+constexpr int kPairMinTokens = 161;  // (a pair's tile is 256 tokens. Measured on the 0.5B sizes, whole prompt steps: 160 tokens 1.84 ms
+                                      // against 1.77 with the one-CTA kernel, 176 tokens 1.86 against 1.93, 700 tokens 2.17 against 3.13)
 
 enum PairEpilogue : int { P_STORE = 0, P_ACCUM = 1, P_GATED = 2, P_QKV = 3 };
 

@@ -104,7 +104,7 @@ void gemm_tc(const void* x, const void* w, const void* bias, DType bias_dt, void
 
 // ---- gemm_pair.cu ---------------------------------------------------------------------
 // The same product (modes 0, 1, 2 of gemm_tc) for many tokens: two CTAs on one tile of 256 tokens with the two-CTA
-// tcgen05.mma. gemm_tc() goes this way by itself where gemm_pair_takes() says so (more than 128 tokens, operands and
+// tcgen05.mma. gemm_tc() goes this way by itself where gemm_pair_takes() says so (more than 160 tokens, operands and
 // output on 16 bytes, output rows a multiple of 16 bytes); gemm_pair_enable(false) keeps every product on the
 // one-CTA kernel, for comparisons.
 bool gemm_pair_takes(const void* x, const void* w, const void* out, DType out_dt, int T, int N, int K, int mode);

@@ -251,11 +251,11 @@ class Ops:
                             want_packed, k_pool=None, v_pool=None, page_table=None, ring=0, token_slot=None, token_end=None):
         """The q/k/v product of many tokens with bias, rotation and the cache write in its epilogue (what ``linear`` and
         ``rope_store`` do in two launches through a float copy of q, k and v). Returns (q, k_packed, v_packed) like
-        ``rope_store``, or None, having done nothing, where the kernel does not take the product (128 tokens or
+        ``rope_store``, or None, having done nothing, where the kernel does not take the product (160 tokens or
         fewer, other head sizes than 64 and 128, a partial rotation, float operands): the caller then goes the
         other way."""
         if (not self.use_tensor_cores or w_qkv.dtype != torch.bfloat16 or self._dtype_of(x) != torch.bfloat16
-                or x.shape[0] <= 128 or head_dim not in (64, 128) or rotary_dim != head_dim):
+                or x.shape[0] <= 160 or head_dim not in (64, 128) or rotary_dim != head_dim):
             return None
         x = self.materialize(x)
         _need(x, "x", torch.bfloat16, 2)
@@ -464,7 +464,7 @@ class Ops:
         return out
 
     def gemm_pair_enable(self, on: bool) -> None:
-        """Whether products of more than 128 tokens go to the two-CTA kernel (the default) or stay on the one-CTA
+        """Whether products of more than 160 tokens go to the two-CTA kernel (the default) or stay on the one-CTA
         kernel: for comparisons of the two."""
         self.lib.sm_gemm_pair_enable(int(bool(on)))
 

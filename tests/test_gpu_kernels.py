@@ -27,8 +27,8 @@ def _rand(shape, dtype, seed, scale=1.0):
 @pytest.mark.parametrize("pairs", [True, False])
 def test_gemm_tc(ops, T, N, K, mode, pairs):
     """``pairs``: above 64 tokens the two-CTA kernel (the default) or the one-CTA kernel."""
-    if not pairs and T <= 128:
-        pytest.skip("up to 128 tokens there is one kernel")
+    if not pairs and T <= 160:
+        pytest.skip("up to 160 tokens there is one kernel")
     ops.gemm_pair_enable(pairs)
     try:
         _gemm_tc_case(ops, T, N, K, mode)
@@ -57,8 +57,8 @@ def _gemm_tc_case(ops, T, N, K, mode):
                                    (40, 202, 2048), (64, 18944, 3584), (70, 160, 1024)])
 @pytest.mark.parametrize("pairs", [True, False])
 def test_gemm_tc_gated(ops, T, H, K, pairs):
-    if not pairs and T <= 128:
-        pytest.skip("up to 128 tokens there is one kernel")
+    if not pairs and T <= 160:
+        pytest.skip("up to 160 tokens there is one kernel")
     ops.gemm_pair_enable(pairs)
     try:
         _gemm_tc_gated_case(ops, T, H, K)
@@ -77,10 +77,10 @@ def _gemm_tc_gated_case(ops, T, H, K):
 
 
 @pytest.mark.parametrize("T,N,K", [(512, 896, 896), (2048, 896, 4864), (700, 200, 72), (1100, 1152, 896), (513, 136, 264),
-                                   (4096, 2048, 128), (8192, 512, 64), (130, 896, 4864), (129, 136, 72), (300, 1152, 896)])
+                                   (4096, 2048, 128), (8192, 512, 64), (161, 896, 4864), (170, 136, 72), (300, 1152, 896)])
 @pytest.mark.parametrize("mode", ["store_f32", "store_bf16", "accumulate", "gated"])
 def test_gemm_pair(ops, T, N, K, mode):
-    """Products of more than 128 tokens go to the kernel in which two CTAs share a tile of 256 tokens: against a float
+    """Products of more than 160 tokens go to the kernel in which two CTAs share a tile of 256 tokens: against a float
     product, and against the one-CTA kernel on the same data."""
     x = _rand((T, K), torch.bfloat16, 11)
     w = _rand((2 * N if mode == "gated" else N, K), torch.bfloat16, 12, 0.05)
@@ -662,9 +662,9 @@ def test_fused_qkv_on_the_tcgen05_kernel_matches_the_separate_kernels(ops, heads
 
 
 @pytest.mark.parametrize("heads,kv_heads,hd", [(14, 2, 64), (3, 1, 128), (8, 2, 128), (5, 3, 64), (4, 0, 64)])
-@pytest.mark.parametrize("T,K,ring", [(512, 896, 0), (777, 136, 0), (2048, 896, 0), (900, 264, 256), (129, 896, 0), (200, 136, 128)])
+@pytest.mark.parametrize("T,K,ring", [(512, 896, 0), (777, 136, 0), (2048, 896, 0), (900, 264, 256), (161, 896, 0), (200, 136, 128)])
 def test_fused_qkv_of_many_tokens(ops, heads, kv_heads, hd, T, K, ring):
-    """More than 128 tokens: bias, rotation, the packed keys and values and the cache write in the epilogue of the
+    """More than 160 tokens: bias, rotation, the packed keys and values and the cache write in the epilogue of the
     two-CTA product, against PyTorch in float. Two sequences that go on from unequal positions, scattered pages; with
     a ring, the positions that it has no place for any more must not be written."""
     from smolmoe_c99_b200.kernels import PAGE_SIZE

@@ -57,7 +57,7 @@ def test_wide_batches_of_unequal_lengths(model_dirs, name, dtype):
 
 @pytest.mark.parametrize("name", ["D", "E"])
 def test_long_prompts_on_the_two_cta_products(model_dirs, name):
-    """Steps of more than 128 tokens take the two-CTA products and the q/k/v epilogue that rotates and stores (head
+    """Steps of more than 160 tokens take the two-CTA products and the q/k/v epilogue that rotates and stores (head
     sizes 64 and 128): a whole prompt, the same prompt in two portions (the second reads the cache), and two prompts
     in one step, against the plain implementation; and against the same engine with those products switched off."""
     from smolmoe_c99_b200.engine.engine import Engine
