@@ -396,7 +396,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
 
-// The kernel for at most 64 tokens (decode batches beyond the weight-streaming kernel, and the
+// The kernel for at most 160 tokens (decode batches beyond the weight-streaming kernel, short prompts, and the
 // output head): one CTA per work unit, few registers, two CTAs to an SM. With so few tokens a
 // unit is nothing but a stream of weight tiles, and two small CTAs keep more of them in flight
 // than one persistent CTA does (measured on the 151,936 x 896 head at 8 tokens: 54 against 75 us).
@@ -882,6 +882,13 @@ SmallLaunch small_launch(int tile_n, int splits, bool dual) {
 
 }  // namespace
 
+namespace {
+// Up to this many tokens a product goes to the small kernel (one CTA per unit, K split inside a cluster), above it to the
+// two-CTA kernel of gemm_pair.cu. Measured on the 0.5B sizes, whole prompt steps with the small kernel against the
+// persistent one: 65 tokens 1.34 against 1.44 ms, 128 tokens 1.45 against 1.77, 160 tokens 1.66 against 1.77.
+constexpr int small_tokens() { return 160; }
+}  // namespace
+
 bool gemm_tc_supports(int T, int N, int K) { return T > 0 && N > 0 && K > 0 && K % 8 == 0; }
 
 namespace {
@@ -921,7 +928,9 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
     const int tiles_m = (N + kTileM - 1) / kTileM;
     const int t16 = ((T + 15) / 16) * 16;
     const int kb = (K + kStageK - 1) / kStageK;   // stages of K
-    if (T <= 64) {
+    if (T <= small_tokens()) {
+        // (a token tile of more than 64 rows is loaded as boxes of 64 rows: a multiple of 64)
+        const int t16 = T <= 64 ? ((T + 15) / 16) * 16 : ((T + 63) / 64) * 64;
         // A handful of tokens: the product is bound by reading the weights once. One token tile (so that no
         // weight row is read twice) and, where the row tiles are too few to fill the machine, K split among the
         // CTAs of a cluster: as many as still run in ONE wave (measured at 64 tokens: 38 row tiles of a gated
@@ -961,11 +970,11 @@ void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
         if (sp > 16) sp = 16;
         if (sp < 1) sp = 1;
     }
-    // Up to 64 tokens the CTAs along K can be one cluster that adds its sums up in shared memory: at most 8 of them. More
+    // In the small kernel the CTAs along K can be one cluster that adds its sums up in shared memory: at most 8 of them. More
     // splits would go through a workspace and a second kernel (896 x 4864 at 64 tokens took 10 splits and the reduce
     // kernel; with 8 in a cluster the decode step of the 0.5B sizes at batch 64 went from 1.36 to 1.31 ms).
     // Up to 16 tokens the many splits and the reduce kernel are the faster way (the step at batch 16: 0.93 against 1.00 ms).
-    if (T > 16 && T <= 64 && sp > 8 && small_launch(tn, 8, dual).cluster) sp = 8;
+    if (T > 16 && T <= small_tokens() && sp > 8 && small_launch(tn, 8, dual).cluster) sp = 8;
     // no empty split: every unit along K gets at least one block
     const int per = (kb + sp - 1) / sp;
     sp = (kb + per - 1) / per;
@@ -977,16 +986,16 @@ size_t gemm_tc_workspace_bytes(int T, int N, int K, bool dual) {
     int tn, sp;
     gemm_tc_plan(T, N, K, dual, &tn, &sp);
     if (dual && gated_halves_plan(T, N, K, &sp)) return 0;
-    if (sp > 1 && T <= 64 && small_launch(tn, sp, dual).cluster) return 0;   // the splits are added up inside a cluster
+    if (sp > 1 && T <= small_tokens() && small_launch(tn, sp, dual).cluster) return 0;   // the splits are added up inside a cluster
     return sp > 1 ? (size_t)sp * (dual ? 2 : 1) * T * N * sizeof(float) : 0;
 }
 
 namespace {
 
-// Whether the fused q/k/v epilogue can take this product: the small kernel (at most 64 tokens) with its sums added up
+// Whether the fused q/k/v epilogue can take this product: the small kernel (at most 160 tokens) with its sums added up
 // inside the CTA or the cluster, and heads that do not straddle the tiles of 128 rows.
 bool qkv_rope_possible(int T, int N, int K, const SkinnyRope& r) {
-    if (T > 64 || !gemm_tc_supports(T, N, K) || r.head_dim < 16 || kTileM % r.head_dim || r.rotary_dim != r.head_dim) return false;
+    if (T > small_tokens() || !gemm_tc_supports(T, N, K) || r.head_dim < 16 || kTileM % r.head_dim || r.rotary_dim != r.head_dim) return false;
     int tn, sp;
     gemm_tc_plan(T, N, K, false, &tn, &sp);
     return sp == 1 || small_launch(tn, sp, false).cluster;
@@ -1028,7 +1037,7 @@ void gemm_tc_impl(const void* x, const void* w, const void* bias, DType bias_dt,
     const int final_mode = rope ? (int)EPI_QKV_ROPE : mode;
     if (rope) p.rope = *rope;
     p.epilogue = p.splits > 1 ? EPI_PARTIAL : final_mode;
-    if (p.splits > 1 && !workspace && !(T <= 64 && small_launch(p.tile_n, p.splits, dual).cluster))
+    if (p.splits > 1 && !workspace && !(T <= small_tokens() && small_launch(p.tile_n, p.splits, dual).cluster))
         throw std::invalid_argument("gemm_tc: this shape splits K and needs a workspace");
     if (rope && !qkv_rope_possible(T, N, K, *rope))
         throw std::invalid_argument("gemm_tc: the fused q/k/v epilogue does not take this shape");
@@ -1038,7 +1047,7 @@ void gemm_tc_impl(const void* x, const void* w, const void* bias, DType bias_dt,
     // (a chunk is 32 tokens, so the token tile must hold at least one)
     p.tma_out = p.splits == 1 && p.tile_n >= kChunk && ((size_t)N * out_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0 ? 1 : 0;
     const int stage_bytes = kTileM * kStageK * 2 * (dual ? 2 : 1) + p.tile_n * kStageK * 2;
-    if (T <= 64) {
+    if (T <= small_tokens()) {
         // few tokens: one CTA per unit, two CTAs to an SM
         const SmallLaunch l = small_launch(p.tile_n, p.splits, dual);
         p.tma_out = 0;

@@ -90,7 +90,7 @@ void gemm_simt(const void* x, DType x_dt, const void* w, DType w_dt, const void*
 // of gemm_tc_workspace_bytes(). *error becomes non-zero if a bounded wait ran out.
 bool gemm_tc_supports(int T, int N, int K);
 size_t gemm_tc_workspace_bytes(int T, int N, int K, bool dual);
-// q/k/v rows of up to 64 tokens with bias, rotation and the cache write in the product's epilogue (q to rope.q_out,
+// q/k/v rows of up to 160 tokens with bias, rotation and the cache write in the product's epilogue (q to rope.q_out,
 // rotated keys and values into the paged pools): x [T, K] bfloat16, w [(heads + 2 kv_heads) * head_dim, K]. Returns
 // false, having done nothing, where the shape is not taken (heads that straddle tiles of 128 rows, K split more
 // than a cluster's ways): the caller then runs the product and rope_store().

@@ -14,8 +14,8 @@
 // SM_GEMM_TC_STATIC_SCRATCH_BYTES (4 MiB) of device memory per GPU, held until the process
 // exits. The caller passes only inputs and outputs (device pointers) and a stream.
 //
-//    4 MiB covers what decoding needs at the model sizes this library is measured on (the
-//    largest there: 2.1 MB for q/k/v at 64 tokens); the planner's worst cases reach about 10 MB.
+//    4 MiB covers what decoding needs at the model sizes this library is measured on (most products need
+//    none: up to 8 splits of K are added up inside a cluster); the planner's worst cases reach about 10 MB.
 //  * A shape that needs more scratch than the array holds is refused with status 1 and a
 //    message from sm_last_error() that names the bytes needed and the limit; nothing runs.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress,

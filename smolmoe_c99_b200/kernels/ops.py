@@ -417,10 +417,10 @@ class Ops:
 
     def _qkv_rope_store_tc(self, x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim, k_pool, v_pool,
                            page_table, ring, token_slot) -> Optional[torch.Tensor]:
-        """The same for up to 64 tokens on the tcgen05 kernel, whose split-K clusters do bias, rotation and cache
+        """The same for up to 160 tokens on the tcgen05 kernel, whose split-K clusters do bias, rotation and cache
         write where they add their sums up. None when the shape is not taken."""
         T, K = x.shape
-        if (T > 64 or 128 % head_dim or not self.use_tensor_cores or w_qkv.dtype != torch.bfloat16
+        if (T > 160 or 128 % head_dim or not self.use_tensor_cores or w_qkv.dtype != torch.bfloat16
                 or self._dtype_of(x) != torch.bfloat16 or not self.lib.sm_gemm_tc_supports(T, w_qkv.shape[0], K)):
             return None
         rows = self.materialize(x)

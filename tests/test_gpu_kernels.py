@@ -615,9 +615,9 @@ def test_fused_qkv_matches_the_separate_kernels(ops, heads, kv_heads, hd):
 
 
 @pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (3, 1, 32), (14, 2, 64), (8, 2, 128), (28, 4, 128)])
-@pytest.mark.parametrize("T,K", [(17, 96), (40, 896), (64, 3584)])
+@pytest.mark.parametrize("T,K", [(17, 96), (40, 896), (64, 3584), (100, 896), (160, 264)])
 def test_fused_qkv_on_the_tcgen05_kernel_matches_the_separate_kernels(ops, heads, kv_heads, hd, T, K):
-    """17 to 64 tokens: bias, rotation and the cache write happen where the split-K cluster of the tcgen05 kernel adds
+    """17 to 160 tokens: bias, rotation and the cache write happen where the split-K cluster of the tcgen05 kernel adds
     its sums up (one split included). Unequal positions, scattered pages, row counts that are no multiple of 128."""
     from smolmoe_c99_b200.kernels import PAGE_SIZE
     N = (heads + 2 * kv_heads) * hd

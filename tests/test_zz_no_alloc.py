@@ -37,9 +37,10 @@ def test_static_scratch_entry_point_matches_the_allocating_one():
     lib = ops.lib
     lib.sm_gemm_tc_static.restype = ctypes.c_int
     lib.sm_gemm_tc_static_error.restype = ctypes.c_int
-    # shapes whose reduction is split over several CTAs that exchange their sums through global memory, so that
-    # the scratch is really used (up to 64 tokens the splits are the CTAs of a cluster and need none)
-    cases = [(100, 896, 4864, 0), (80, 640, 1024, 0), (70, 160, 1024, 2)]
+    # shapes whose reduction is split over more CTAs than a cluster holds, which exchange their sums through global
+    # memory, so that the scratch is really used (a few tokens over a long K and few row tiles; up to 8 splits are the
+    # CTAs of a cluster and need none)
+    cases = [(16, 896, 4864, 0), (10, 640, 4096, 0), (12, 160, 4096, 2)]
     for round_ in range(2):                       # two calls in a row per shape: the array is shared and never cleared
         for T, N, K, mode in cases:
             need = int(lib.sm_gemm_tc_workspace_bytes(T, N, K, int(mode == 2)))
@@ -77,7 +78,7 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     lib = get_ops().lib
     lib.sm_gemm_tc_static.restype = ctypes.c_int
     N, K = 512, 4864                                          # a gated product: two accumulators, K split several ways
-    sizes = {T: int(lib.sm_gemm_tc_workspace_bytes(T, N, K, 1)) for T in (72, 96, 128)}
+    sizes = {T: int(lib.sm_gemm_tc_workspace_bytes(T, N, K, 1)) for T in (200, 256, 300)}
     too_big = [T for T, need in sizes.items() if need > SCRATCH_BYTES]
     assert too_big, f"no shape of this family exceeds the array: {sizes}"
     T, need = too_big[0], sizes[too_big[0]]
