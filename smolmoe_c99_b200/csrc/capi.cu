@@ -242,10 +242,11 @@ SM_API int sm_attention_decode(const void* q, void* out, int B, int heads, int k
 SM_API int sm_gemm_tc_qkv(const void* x, const void* w, int T, int K, const void* bias, int bias_dt, int heads, int kv_heads,
                           int head_dim, int rotary_dim, const int32_t* positions, const float* cos_table,
                           const float* sin_table, void* q_out, void* k_pool, void* v_pool, const int32_t* page_table,
-                          int table_stride, int ring, const int32_t* token_slot, int* error, int* taken, void* stream) {
+                          int table_stride, int ring, const int32_t* token_slot, void* k_packed, void* v_packed,
+                          const int32_t* token_end, int* error, int* taken, void* stream) {
     return guarded([&] {
         sm::SkinnyRope rope{heads, kv_heads, head_dim, rotary_dim, positions, cos_table, sin_table, q_out,
-                            k_pool, v_pool, page_table, table_stride, ring, token_slot};
+                            k_pool, v_pool, page_table, table_stride, ring, token_slot, k_packed, v_packed, token_end};
         *taken = sm::gemm_tc_qkv_rope(x, w, bias, (sm::DType)bias_dt, T, K, rope, error, (cudaStream_t)stream) ? 1 : 0;
     });
 }

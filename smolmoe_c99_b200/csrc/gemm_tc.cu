@@ -644,20 +644,26 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                             vh[e] = r1;
                         }
                     }
-                    __nv_bfloat16* dst;
-                    if (head < r.heads) {
-                        dst = (__nv_bfloat16*)r.q_out + ((size_t)t * r.heads + head) * hd + d;
-                    } else {
-                        const int kvh = is_v ? head - r.heads - r.kv_heads : head - r.heads;
-                        dst = (__nv_bfloat16*)(is_v ? r.v_pool : r.k_pool) + paged.row_offset(r.token_slot[t], pos, kvh) + d;
-                    }
                     __nv_bfloat162 a0 = __floats2bfloat162_rn(vl[0], vl[1]), a1 = __floats2bfloat162_rn(vl[2], vl[3]);
                     __nv_bfloat162 b0 = __floats2bfloat162_rn(vh[0], vh[1]), b1 = __floats2bfloat162_rn(vh[2], vh[3]);
                     uint2 pl, ph;
                     pl.x = *reinterpret_cast<uint32_t*>(&a0); pl.y = *reinterpret_cast<uint32_t*>(&a1);
                     ph.x = *reinterpret_cast<uint32_t*>(&b0); ph.y = *reinterpret_cast<uint32_t*>(&b1);
-                    *reinterpret_cast<uint2*>(dst) = pl;
-                    *reinterpret_cast<uint2*>(dst + half) = ph;
+                    auto store = [&](__nv_bfloat16* dst) {
+                        *reinterpret_cast<uint2*>(dst) = pl;
+                        *reinterpret_cast<uint2*>(dst + half) = ph;
+                    };
+                    if (head < r.heads) {
+                        store((__nv_bfloat16*)r.q_out + ((size_t)t * r.heads + head) * hd + d);
+                    } else {
+                        // keys and values: into the paged cache (with a ring, not the positions it has no place for any
+                        // more) and, where the step attends over its own packed keys, into those
+                        const int kvh = is_v ? head - r.heads - r.kv_heads : head - r.heads;
+                        if (r.k_pool != nullptr && !(r.ring > 0 && r.token_end != nullptr && pos < r.token_end[t] - r.ring))
+                            store((__nv_bfloat16*)(is_v ? r.v_pool : r.k_pool) + paged.row_offset(r.token_slot[t], pos, kvh) + d);
+                        if (r.k_packed != nullptr)
+                            store((__nv_bfloat16*)(is_v ? r.v_packed : r.k_packed) + ((size_t)t * r.kv_heads + kvh) * hd + d);
+                    }
                 }
             } else if (p.halves) {
                 // the tile's rows 0-63 are gate rows n0.., rows 64-127 the up rows of the same features

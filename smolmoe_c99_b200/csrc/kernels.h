@@ -150,6 +150,10 @@ struct SkinnyRope {
     const int32_t* page_table;
     int table_stride, ring;
     const int32_t* token_slot;  // [T]
+    // only the tcgen05 kernel's epilogue (gemm_tc_qkv_rope) reads these; null where a step has no use for them:
+    void* k_packed = nullptr;   // bfloat16 [T, kv_heads, head_dim]: rotated keys of the step, beside (or instead of) the cache
+    void* v_packed = nullptr;
+    const int32_t* token_end = nullptr;   // [T] the token's sequence length after the step: with a ring, older positions are not stored
 };
 bool gemm_skinny_supports(int T, int N, int K);
 // Rounds in which a CTA of the kernel takes its share of K for these sizes (1: all of its weights are in

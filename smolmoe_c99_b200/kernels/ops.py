@@ -254,6 +254,11 @@ class Ops:
         ``rope_store``, or None, having done nothing, where the kernel does not take the product (160 tokens or
         fewer, other head sizes than 64 and 128, a partial rotation, float operands): the caller then goes the
         other way."""
+        if x.shape[0] <= 160 and rotary_dim == head_dim:
+            # few tokens: the small tcgen05 kernel's epilogue does the same (head sizes that divide 128)
+            got = self._qkv_rope_store_tc(x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim, k_pool,
+                                          v_pool, page_table, ring, token_slot, want_packed=True, token_end=token_end)
+            return got if got is None or want_packed else (got[0], None, None)
         if (not self.use_tensor_cores or w_qkv.dtype != torch.bfloat16 or self._dtype_of(x) != torch.bfloat16
                 or x.shape[0] <= 160 or head_dim not in (64, 128) or rotary_dim != head_dim):
             return None
@@ -416,22 +421,31 @@ class Ops:
         return q
 
     def _qkv_rope_store_tc(self, x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim, k_pool, v_pool,
-                           page_table, ring, token_slot) -> Optional[torch.Tensor]:
+                           page_table, ring, token_slot, want_packed=False, token_end=None):
         """The same for up to 160 tokens on the tcgen05 kernel, whose split-K clusters do bias, rotation and cache
-        write where they add their sums up. None when the shape is not taken."""
+        write where they add their sums up. Returns q, or with ``want_packed`` (q, k_packed, v_packed) for a step that
+        attends over its own packed keys; ``token_end`` keeps positions that a ring has no place for out of the cache.
+        None when the shape is not taken."""
         T, K = x.shape
         if (T > 160 or 128 % head_dim or not self.use_tensor_cores or w_qkv.dtype != torch.bfloat16
-                or self._dtype_of(x) != torch.bfloat16 or not self.lib.sm_gemm_tc_supports(T, w_qkv.shape[0], K)):
+                or self._dtype_of(x) != torch.bfloat16 or not self.lib.sm_gemm_tc_supports(T, w_qkv.shape[0], K)
+                or (k_pool is not None and k_pool.dtype != torch.bfloat16)):
             return None
         rows = self.materialize(x)
         q = torch.empty((T, heads, head_dim), dtype=torch.bfloat16, device=rows.device)
+        kp = vp = None
+        if want_packed and kv_heads:
+            kp = torch.empty((T, kv_heads, head_dim), dtype=torch.bfloat16, device=rows.device)
+            vp = torch.empty_like(kp)
         taken = ctypes.c_int(0)
         self._check(self.lib.sm_gemm_tc_qkv(
             _ptr(rows), _ptr(w_qkv), T, K, _ptr(b_qkv), _dt(b_qkv) if b_qkv is not None else F32, heads, kv_heads,
             head_dim, head_dim, _ptr(positions), _ptr(cos_table), _ptr(sin_table), _ptr(q), _ptr(k_pool), _ptr(v_pool),
-            _ptr(page_table), page_table.shape[1], ring, _ptr(token_slot), _ptr(self.error_flag), ctypes.byref(taken),
-            _stream()))
-        return q if taken.value else None
+            _ptr(page_table), page_table.shape[1], ring, _ptr(token_slot), _ptr(kp), _ptr(vp), _ptr(token_end),
+            _ptr(self.error_flag), ctypes.byref(taken), _stream()))
+        if not taken.value:
+            return None
+        return (q, kp, vp) if want_packed else q
 
     def _tensor_core_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
         return (self.use_tensor_cores and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
