@@ -888,10 +888,12 @@ SmallLaunch small_launch(int tile_n, int splits, bool dual) {
 
 }  // namespace
 
+
 namespace {
 // Up to this many tokens a product goes to the small kernel (one CTA per unit, K split inside a cluster), above it to the
 // two-CTA kernel of gemm_pair.cu. Measured on the 0.5B sizes, whole prompt steps with the small kernel against the
-// persistent one: 65 tokens 1.34 against 1.44 ms, 128 tokens 1.45 against 1.77, 160 tokens 1.66 against 1.77.
+// persistent one: 65 tokens 1.34 against 1.44 ms, 128 tokens 1.33 against 1.77, 160 tokens 1.53 against 1.77; beyond that
+// the small kernel falls behind the two-CTA one (176 tokens 2.08 against 1.86).
 constexpr int small_tokens() { return 160; }
 }  // namespace
 
@@ -899,14 +901,14 @@ bool gemm_tc_supports(int T, int N, int K) { return T > 0 && N > 0 && K > 0 && K
 
 namespace {
 
-// A gated product over up to 64 tokens as tiles of 64 gate rows + their 64 up rows in one accumulator: half the
+// A gated product of the small kernel as tiles of 64 gate rows + their 64 up rows in one accumulator: half the
 // shared memory of two accumulators, so two CTAs to an SM and twice the tiles. Gate and up meet where the
 // cluster adds its sums up, so the plan needs that path (one split included). Returns the CTAs along K.
 bool gated_halves_plan(int T, int N, int K, int* splits) {
-    if (T > 64) return false;
+    if (T > small_tokens()) return false;
     const int sms = device_sm_count();
     const int tiles = (N + kTileM / 2 - 1) / (kTileM / 2);
-    const int t16 = ((T + 15) / 16) * 16;
+    const int t16 = T <= 64 ? ((T + 15) / 16) * 16 : ((T + 63) / 64) * 64;    // (above 64 rows: boxes of 64 rows)
     const int kb = (K + kStageK - 1) / kStageK;
     const SmallLaunch l = small_launch(t16, 2, false);
     int per_sm = (int)((size_t)227 * 1024 / l.smem);
@@ -927,7 +929,7 @@ bool gated_halves_plan(int T, int N, int K, int* splits) {
 
 void gemm_tc_plan(int T, int N, int K, bool dual, int* tile_n, int* splits) {
     if (dual && gated_halves_plan(T, N, K, splits)) {
-        *tile_n = ((T + 15) / 16) * 16;
+        *tile_n = T <= 64 ? ((T + 15) / 16) * 16 : ((T + 63) / 64) * 64;
         return;
     }
     const int sms = device_sm_count();
