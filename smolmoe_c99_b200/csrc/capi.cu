@@ -280,10 +280,11 @@ SM_API int sm_gemm_skinny_qkv(const void* x, const void* norm_w, int norm_w_dt, 
                               const void* bias, int bias_dt, int heads, int kv_heads, int head_dim, int rotary_dim,
                               const int32_t* positions, const float* cos_table, const float* sin_table, void* q_out,
                               void* k_pool, void* v_pool, const int32_t* page_table, int table_stride, int ring,
-                              const int32_t* token_slot, void* stream) {
+                              const int32_t* token_slot, void* k_packed, void* v_packed, const int32_t* token_end,
+                              void* stream) {
     return guarded([&] {
         sm::SkinnyRope rope{heads, kv_heads, head_dim, rotary_dim, positions, cos_table, sin_table, q_out,
-                            k_pool, v_pool, page_table, table_stride, ring, token_slot};
+                            k_pool, v_pool, page_table, table_stride, ring, token_slot, k_packed, v_packed, token_end};
         sm::gemm_skinny(x, norm_w, (sm::DType)norm_w_dt, eps, w, T, (heads + 2 * kv_heads) * head_dim, K, 3, bias,
                         (sm::DType)bias_dt, nullptr, sm::BF16, 0, &rope, (cudaStream_t)stream);
     });

@@ -73,6 +73,9 @@ struct SkinnyArgs {
     const int32_t* page_table;
     int table_stride, ring;
     const int32_t* token_slot;
+    void* k_packed;             // or null: the step's rotated keys and its values, packed [T, kv_heads, head_dim]
+    void* v_packed;
+    const int32_t* token_end;   // or null: with a ring, positions before token_end - ring are not stored
     int cluster;                // CTAs that share a tile (1, 2 or 4)
     int round_k;                // k elements staged per round (a multiple of 32)
     int* error;
@@ -204,6 +207,8 @@ __global__ void __launch_bounds__(kThreads, 3) gemm_skinny_kernel(SkinnyArgs a) 
     float pre_a = 0.f, pre_b = 0.f, pre_cos = 1.f, pre_sin = 0.f;
     __nv_bfloat16* dst_lo = nullptr;
     __nv_bfloat16* dst_hi = nullptr;
+    __nv_bfloat16* packed_lo = nullptr;      // keys and values also go to the step's packed tensors, where it has them
+    __nv_bfloat16* packed_hi = nullptr;
     if (a.mode == SK_QKV_ROPE) {
         const int r = threadIdx.x / TOK, t = threadIdx.x - r * TOK;
         if (r < 8 && t < a.T) {
@@ -225,11 +230,20 @@ __global__ void __launch_bounds__(kThreads, 3) gemm_skinny_kernel(SkinnyArgs a) 
             } else {
                 const bool is_v = head >= a.heads + a.kv_heads;
                 const int kvh = is_v ? head - a.heads - a.kv_heads : head - a.heads;
-                PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
-                dst_lo = (__nv_bfloat16*)(is_v ? a.v_pool : a.k_pool) + paged.row_offset(a.token_slot[t], pos, kvh);
+                if (a.k_pool != nullptr && !(a.ring > 0 && a.token_end != nullptr && pos < a.token_end[t] - a.ring)) {
+                    PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
+                    dst_lo = (__nv_bfloat16*)(is_v ? a.v_pool : a.k_pool) + paged.row_offset(a.token_slot[t], pos, kvh);
+                }
+                if (a.k_packed != nullptr) {
+                    packed_lo = (__nv_bfloat16*)(is_v ? a.v_packed : a.k_packed) + ((size_t)t * a.kv_heads + kvh) * hd;
+                    packed_hi = packed_lo + d_hi;
+                    packed_lo += d_lo;
+                }
             }
-            dst_hi = dst_lo + d_hi;
-            dst_lo += d_lo;
+            if (dst_lo != nullptr) {
+                dst_hi = dst_lo + d_hi;
+                dst_lo += d_lo;
+            }
         }
     } else {
         // the others: thread -> (row r, token t) of the tile, twice if there are more than 256 of them
@@ -454,8 +468,14 @@ __global__ void __launch_bounds__(kThreads, 3) gemm_skinny_kernel(SkinnyArgs a) 
         lo += pre_a;
         hi += pre_b;
         const float r0 = lo * pre_cos - hi * pre_sin, r1 = lo * pre_sin + hi * pre_cos;   // cos 1, sin 0 for v
-        *dst_lo = __float2bfloat16_rn(r0);
-        *dst_hi = __float2bfloat16_rn(r1);
+        if (dst_lo != nullptr) {
+            *dst_lo = __float2bfloat16_rn(r0);
+            *dst_hi = __float2bfloat16_rn(r1);
+        }
+        if (packed_lo != nullptr) {
+            *packed_lo = __float2bfloat16_rn(r0);
+            *packed_hi = __float2bfloat16_rn(r1);
+        }
         return;
     }
 #pragma unroll
@@ -554,6 +574,7 @@ void gemm_skinny(const void* x, const void* norm_w, DType norm_w_dt, float eps, 
         a.positions = rope->positions; a.cos_table = rope->cos_table; a.sin_table = rope->sin_table;
         a.q_out = rope->q_out; a.k_pool = rope->k_pool; a.v_pool = rope->v_pool; a.page_table = rope->page_table;
         a.table_stride = rope->table_stride; a.ring = rope->ring; a.token_slot = rope->token_slot;
+        a.k_packed = rope->k_packed; a.v_packed = rope->v_packed; a.token_end = rope->token_end;
         tiles = N / 16;
     }
     {

@@ -150,7 +150,7 @@ struct SkinnyRope {
     const int32_t* page_table;
     int table_stride, ring;
     const int32_t* token_slot;  // [T]
-    // only the tcgen05 kernel's epilogue (gemm_tc_qkv_rope) reads these; null where a step has no use for them:
+    // null where a step has no use for them:
     void* k_packed = nullptr;   // bfloat16 [T, kv_heads, head_dim]: rotated keys of the step, beside (or instead of) the cache
     void* v_packed = nullptr;
     const int32_t* token_end = nullptr;   // [T] the token's sequence length after the step: with a ring, older positions are not stored

@@ -256,8 +256,9 @@ class Ops:
         other way."""
         if x.shape[0] <= 160 and rotary_dim == head_dim:
             # few tokens: the small tcgen05 kernel's epilogue does the same (head sizes that divide 128)
-            got = self._qkv_rope_store_tc(x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim, k_pool,
-                                          v_pool, page_table, ring, token_slot, want_packed=True, token_end=token_end)
+            got = self.qkv_rope_store_fused(x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim,
+                                            rotary_dim, k_pool, v_pool, page_table, ring, token_slot, want_packed=True,
+                                            token_end=token_end)
             return got if got is None or want_packed else (got[0], None, None)
         if (not self.use_tensor_cores or w_qkv.dtype != torch.bfloat16 or self._dtype_of(x) != torch.bfloat16
                 or x.shape[0] <= 160 or head_dim not in (64, 128) or rotary_dim != head_dim):
@@ -402,23 +403,32 @@ class Ops:
         return out
 
     def qkv_rope_store_fused(self, x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim,
-                             rotary_dim, k_pool, v_pool, page_table, ring, token_slot) -> Optional[torch.Tensor]:
-        """For a handful of tokens: q/k/v product, bias, rotation and cache write in one launch.
-        Returns q [T, heads, head_dim], or None when the shapes are not the fused kernel's."""
-        if head_dim % 16 or rotary_dim != head_dim or k_pool is None or k_pool.dtype != torch.bfloat16:
+                             rotary_dim, k_pool, v_pool, page_table, ring, token_slot, want_packed=False, token_end=None):
+        """For up to 160 tokens: q/k/v product, bias, rotation and cache write in one launch (the weight-streaming
+        kernel with the norm as its prologue for a handful of tokens, else the small tcgen05 kernel).
+        Returns q [T, heads, head_dim], or with ``want_packed`` (q, k_packed, v_packed) for a step that attends over
+        its own packed keys; ``token_end`` keeps positions that a ring has no place for out of the cache; ``k_pool``
+        None writes nothing to the cache. None when the shapes are not the fused kernels'."""
+        if head_dim % 16 or rotary_dim != head_dim or (k_pool is not None and k_pool.dtype != torch.bfloat16):
+            return None
+        if k_pool is None and not want_packed:
             return None
         if not self._skinny_ok(x, w_qkv):
             return self._qkv_rope_store_tc(x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim,
-                                           k_pool, v_pool, page_table, ring, token_slot)
+                                           k_pool, v_pool, page_table, ring, token_slot, want_packed, token_end)
         norm_w, eps, src = (x.weight, x.eps, x.residual) if isinstance(x, NormedRows) else (None, 0.0, x)
         T, K = src.shape
         q = torch.empty((T, heads, head_dim), dtype=torch.bfloat16, device=src.device)
+        kp = vp = None
+        if want_packed and kv_heads:
+            kp = torch.empty((T, kv_heads, head_dim), dtype=torch.bfloat16, device=src.device)
+            vp = torch.empty_like(kp)
         self._check(self.lib.sm_gemm_skinny_qkv(
             _ptr(src), _ptr(norm_w), _dt(norm_w) if norm_w is not None else F32, ctypes.c_float(eps), _ptr(w_qkv), T, K,
             _ptr(b_qkv), _dt(b_qkv) if b_qkv is not None else F32, heads, kv_heads, head_dim, rotary_dim,
             _ptr(positions), _ptr(cos_table), _ptr(sin_table), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
-            page_table.shape[1], ring, _ptr(token_slot), _stream()))
-        return q
+            page_table.shape[1], ring, _ptr(token_slot), _ptr(kp), _ptr(vp), _ptr(token_end), _stream()))
+        return (q, kp, vp) if want_packed else q
 
     def _qkv_rope_store_tc(self, x, w_qkv, b_qkv, positions, cos_table, sin_table, heads, kv_heads, head_dim, k_pool, v_pool,
                            page_table, ring, token_slot, want_packed=False, token_end=None):

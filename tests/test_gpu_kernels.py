@@ -663,8 +663,9 @@ def test_fused_qkv_on_the_tcgen05_kernel_matches_the_separate_kernels(ops, heads
 
 @pytest.mark.parametrize("heads,kv_heads,hd", [(14, 2, 64), (3, 1, 128), (8, 2, 128), (5, 3, 64), (4, 0, 64)])
 @pytest.mark.parametrize("T,K,ring", [(512, 896, 0), (777, 136, 0), (2048, 896, 0), (900, 264, 256), (161, 896, 0), (200, 136, 128),
-                                      # up to 160 tokens the small kernel's epilogue does it
-                                      (20, 896, 0), (100, 136, 0), (160, 264, 128)])
+                                      # up to 160 tokens the small kernel's epilogue does it, for a handful of tokens
+                                      # the weight-streaming kernel's
+                                      (20, 896, 0), (100, 136, 0), (160, 264, 128), (5, 96, 0), (12, 264, 128)])
 def test_fused_qkv_of_many_tokens(ops, heads, kv_heads, hd, T, K, ring):
     """More than 160 tokens: bias, rotation, the packed keys and values and the cache write in the epilogue of the
     two-CTA product, against PyTorch in float. Two sequences that go on from unequal positions, scattered pages; with
