@@ -58,6 +58,8 @@ struct DecodeArgs {
     int own_bytes;                // shared memory a CTA uses for itself: the buffers, later the warps' results
     int stages;                   // streaming kernel: tiles a warp keeps in flight
     int* error;                   // streaming kernel: where a wait that ran out is recorded
+    int late;                     // rows of one sequence at several new positions: the kernel before wrote more than the
+                                  // newest row of a sequence, so nothing of the cache is read before the wait for it
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -221,6 +223,8 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
 
     // The whole share is asked for at once: thread -> (row, 16-byte piece) in turn, whole tiles (rows past the end
     // are zeros). The row of position `pos`, which the kernel before this one writes, is left out.
+    const bool late = a.late != 0;
+    if (late) pdl_wait();
     {
         __nv_bfloat16* kb = kv_all;
         __nv_bfloat16* vb = kv_all + buf_elems;
@@ -228,7 +232,7 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
         for (int idx = threadIdx.x; idx < rows * CPR; idx += kThreads) {
             const int row = idx / CPR, col = (idx - row * CPR) * 8;
             const int key = cta_lo + row;
-            if (key == pos) continue;
+            if (key == pos && !late) continue;
             const bool in = key < cta_hi && col < hd;
             const size_t o = in ? paged.row_offset(slot, key, kvh) + col : 0;
             cp_async16(kb + (size_t)row * LD + col, a.k_pool + o, in);
@@ -249,7 +253,7 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(DecodeArgs a
             *reinterpret_cast<uint4*>(qs + (size_t)row * LD + col) =
                 in ? *reinterpret_cast<const uint4*>(qrow + (size_t)row * hd + col) : make_uint4(0, 0, 0, 0);
         }
-        if (pos >= cta_lo && pos < cta_hi) {
+        if (!late && pos >= cta_lo && pos < cta_hi) {
             const int row = pos - cta_lo;
             if (threadIdx.x < 2 * CPR) {
                 const int which = threadIdx.x / CPR, col = (threadIdx.x - which * CPR) * 8;   // 0: key, 1: value
@@ -476,8 +480,10 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         }
     };
     const int ahead = min(S, my_tiles);
+    const bool late = a.late != 0;
+    if (late) pdl_wait();
     for (int i = 0; i < ahead; ++i)
-        if (!(BOX && holds_newest(i))) request(i, i, true);
+        if (late || !(BOX && holds_newest(i))) request(i, i, !late);
 
     pdl_wait();   // q and the newest key and value come from the kernel before
 
@@ -492,7 +498,9 @@ decode_attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         }
         // the newest position, if its tile is among those asked for above: as a whole tile now (BOX: every tile
         // that was left out above), else its row by plain loads and stores into the tile
-        if (BOX) {
+        if (late) {
+            // (every tile was asked for whole, after the wait)
+        } else if (BOX) {
             for (int i = 0; i < ahead; ++i)
                 if (holds_newest(i)) request(i, i, false);
         } else if (pos >= cta_lo && pos < cta_hi) {
@@ -953,7 +961,7 @@ void attention_decode_plan(int B, int heads, int kv_heads, int head_dim, int win
 
 void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
                       const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
-                      const int32_t* page_table, int table_stride, int ring, int max_len, long long pool_pages,
+                      const int32_t* page_table, int table_stride, int ring, int max_len, long long pool_pages, bool late,
                       cudaStream_t stream) {
     if (B <= 0) return;
     if (!attention_decode_supports(heads, kv_heads, head_dim))
@@ -965,7 +973,7 @@ void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, 
     const int visible = window > 0 && window < max_len ? window : max_len;
     DecodeArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
                  page_table, table_stride, ring, slots, positions, B, heads, kv_heads, head_dim, window, 1,
-                 scale * 1.4426950408889634f, 0, 0, 0, nullptr};
+                 scale * 1.4426950408889634f, 0, 0, 0, nullptr, late ? 1 : 0};
     note_launch();
     switch ((head_dim + 31) / 32) {
         case 1: launch<1>(a, visible, pool_pages, stream); break;

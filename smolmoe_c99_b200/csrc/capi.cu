@@ -231,10 +231,10 @@ SM_API int sm_attention_decode_plan(int B, int heads, int kv_heads, int head_dim
 SM_API int sm_attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale,
                                int window, const int32_t* positions, const int32_t* slots, const void* k_pool,
                                const void* v_pool, const int32_t* page_table, int table_stride, int ring, int max_len,
-                               long long pool_pages, void* stream) {
+                               long long pool_pages, int late, void* stream) {
     return guarded([&] {
         sm::attention_decode(q, out, B, heads, kv_heads, head_dim, scale, window, positions, slots, k_pool, v_pool,
-                             page_table, table_stride, ring, max_len, pool_pages, (cudaStream_t)stream);
+                             page_table, table_stride, ring, max_len, pool_pages, late != 0, (cudaStream_t)stream);
     });
 }
 

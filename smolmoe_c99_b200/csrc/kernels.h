@@ -228,9 +228,11 @@ bool attention_decode_supports(int heads, int kv_heads, int head_dim);
 // buffer, buffers, bytes of shared memory per CTA; for shares that are streamed tile by tile: CTAs, 0, tiles a
 // warp keeps in flight, bytes of shared memory.
 void attention_decode_plan(int B, int heads, int kv_heads, int head_dim, int window, int max_len, int* plan);
+// `late`: the rows are not one new token per sequence but several new positions of a sequence (a short later message):
+// the kernel before wrote more of the cache than each row's newest position, so nothing is read before the wait for it.
 void attention_decode(const void* q, void* out, int B, int heads, int kv_heads, int head_dim, float scale, int window,
                       const int32_t* positions, const int32_t* slots, const void* k_pool, const void* v_pool,
-                      const int32_t* page_table, int table_stride, int ring, int max_len, long long pool_pages,
+                      const int32_t* page_table, int table_stride, int ring, int max_len, long long pool_pages, bool late,
                       cudaStream_t stream);
 
 // ---- decode_fused.cu ------------------------------------------------------------------

@@ -111,8 +111,11 @@ class _StepGraph:
         self.batch: Optional[StepBatch] = None
         self.want_rows = torch.tensor(rows, dtype=torch.int32).to(engine.device) if rows else None
 
-    def run(self, engine: "Engine", slots, starts, tokens) -> Optional[torch.Tensor]:
+    def run(self, engine: "Engine", slots, starts, tokens, span: int) -> Optional[torch.Tensor]:
         batch = pack_step(slots, starts, tokens, engine.device, into=self.packed)
+        # (kernels that size themselves by the longest sequence do so for the span the graph is kept for, not for
+        # this step's own longest sequence)
+        batch.max_seq_len = max(batch.max_seq_len, span)
         if self.graph is None:
             # (No run outside the capture first: the shape's first step ran kernel by kernel, which loaded the kernels
             # and set their attributes. Nothing runs during the capture, so the replay below is this step's one run.)
@@ -258,7 +261,16 @@ class Engine:
         # (a windowed group's late store and the check of its ring are decided on the host from the starts: those
         # steps stay eager unless every sequence is at its first token)
         if self.use_graphs and sum(lens) <= self.step_graph_max_tokens and (first or not self._has_ring):
-            key = (first, tuple(lens), tuple(rows))
+            # Sequences that go on from the cache: the longest of them after the step, rounded up the way the decode
+            # graphs' spans are, is part of the shape (the attention over the cache is launched for it).
+            span = 0
+            if not first:
+                longest = max(s + n for s, n in zip(starts, lens))
+                span = SPAN_BUCKET
+                while span < longest:
+                    span *= 2
+                span = min(span, -(-self.max_seq_len // 128) * 128)
+            key = (first, tuple(lens), tuple(rows), span)
             g = self._step_graphs.get(key)
             if g is None:
                 seen = self._step_seen.pop(key, 0) + 1
@@ -273,7 +285,7 @@ class Engine:
                 self._step_graphs.move_to_end(key)
             if g is not None:
                 try:
-                    return g.run(self, slots, starts, tokens)
+                    return g.run(self, slots, starts, tokens, span)
                 except BaseException:
                     self._step_graphs.pop(key, None)
                     raise

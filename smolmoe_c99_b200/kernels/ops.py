@@ -135,6 +135,8 @@ class Ops:
         # more tokens than this go to the tcgen05 kernel (the weight-streaming kernel itself takes up to 32; measured
         # on a B200 at 24 and 32 tokens it is 20-35% behind on every shape from 0.5B to 7B)
         self.skinny_max_tokens = 16
+        # steps of up to this many tokens that go on from the cache attend with the decode kernel, a row a token
+        self.extend_rows_as_decode = 64 if fast else 0
         self.skinny_single_round_above_8 = True
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.lib.sm_set_error_word.restype = None
@@ -573,9 +575,17 @@ class Ops:
                                          _ptr(cache.page_table), cache.page_table.shape[1], cache.ring,
                                          _ptr(step.token_slot), _ptr(step.token_end), _stream()))
 
-    def attention_extend(self, q, k_packed, v_packed, step, scale, window, cache):
+    def attention_extend(self, q, k_packed, v_packed, step, scale, window, cache, cache_written=False):
         """Causal attention of sequences that go on from the cache by any number of tokens: keys and values of
         earlier positions from the cache, the step's own from the packed tensors (the cache need not hold them yet)."""
+        if (self.use_fast_attention and q.dtype == torch.bfloat16 and q.shape[0] <= self.extend_rows_as_decode
+                and cache.ring == 0 and cache_written and cache.k_pool.dtype == torch.bfloat16
+                and self.lib.sm_attention_decode_supports(q.shape[1], k_packed.shape[1], q.shape[2])):
+            # a few tokens onto a live sequence: every token as a row of the decode kernel, which shares a row's keys
+            # out among the CTAs of a cluster (the tiled kernel below has one CTA per 64 queries and head, each with the
+            # whole chain of keys to itself: 8 tokens onto 2,000 took 2.0 ms a step with it)
+            return self.attention_decode(q, step.positions, step.token_slot, scale, window, cache.k_pool, cache.v_pool,
+                                         cache.page_table, cache.ring, k_packed.shape[1], step.max_seq_len, late=True)
         if (self.use_fast_attention and q.dtype == torch.bfloat16 and step.extend_tiles is not None
                 and self.lib.sm_attention_prefill_supports(q.shape[2])):
             out = self._prefill_operands(q, k_packed, v_packed, step.extend_tiles)
@@ -601,8 +611,11 @@ class Ops:
                                     page_table=cache.page_table, ring=cache.ring, token_slot=step.token_slot,
                                     kv_heads=kv_heads)
 
-    def attention_decode(self, q, positions, slots, scale, window, k_pool, v_pool, page_table, ring, kv_heads, max_len):
-        """One new token per sequence (row b of q belongs to slots[b] at positions[b])."""
+    def attention_decode(self, q, positions, slots, scale, window, k_pool, v_pool, page_table, ring, kv_heads, max_len,
+                         late=False):
+        """One new token per sequence (row b of q belongs to slots[b] at positions[b]). ``late``: the rows are several
+        new positions of a sequence, all of them in the cache already (a short later message onto a live sequence);
+        each row attends over the cache up to its own position."""
         _need(q, "q", torch.bfloat16, 3)
         B, heads, head_dim = q.shape
         _need(positions, "positions", torch.int32, 1)
@@ -614,7 +627,7 @@ class Ops:
         self._check(self.lib.sm_attention_decode(
             _ptr(q), _ptr(out), B, heads, kv_heads, head_dim, ctypes.c_float(scale), int(window or 0), _ptr(positions),
             _ptr(slots), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), page_table.shape[1], ring, int(max_len),
-            ctypes.c_longlong(k_pool.shape[0]), _stream()))
+            ctypes.c_longlong(k_pool.shape[0]), int(bool(late)), _stream()))
         return out
 
     # ---- a whole decode step in one kernel ------------------------------------------------

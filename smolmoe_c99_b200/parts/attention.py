@@ -113,7 +113,7 @@ class Attention(Part):
         if own and mode == "prefill":
             att = ops.attention_prefill(q, k_packed, v_packed, step, self.scale, self.window)
         elif own and mode == "extend":
-            att = ops.attention_extend(q, k_packed, v_packed, step, self.scale, self.window, cache)
+            att = ops.attention_extend(q, k_packed, v_packed, step, self.scale, self.window, cache, cache_written=write_now)
             if store_late:
                 ops.kv_store(k_packed, v_packed, step, cache)
         else:

@@ -141,6 +141,31 @@ def test_gemm_simt(ops, xd, wd, od, T, N, K):
 
 
 # ---- attention ---------------------------------------------------------------------------
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (14, 2, 64), (8, 2, 128), (3, 1, 48)])
+@pytest.mark.parametrize("first", [3, 30, 2040])
+def test_decode_attention_with_several_rows_of_a_sequence(ops, heads, kv_heads, hd, first):
+    """A short later message: every new token of a sequence is a row of the decode kernel (``late``), each attending
+    over the cache up to its own position, beside rows of another sequence; against the plain kernel."""
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    n_new, other = 9, 5
+    longest = first + n_new
+    pages_per_slot = -(-max(longest, 700) // PAGE_SIZE)
+    g = torch.Generator().manual_seed(first)
+    k_pool = _rand((2 * pages_per_slot, kv_heads, PAGE_SIZE, hd), torch.bfloat16, 31, 0.5)
+    v_pool = _rand((2 * pages_per_slot, kv_heads, PAGE_SIZE, hd), torch.bfloat16, 32, 0.5)
+    table = torch.randperm(2 * pages_per_slot, generator=g).to(torch.int32).view(2, pages_per_slot).cuda()
+    positions = torch.tensor(list(range(first, first + n_new)) + list(range(600, 600 + other)), dtype=torch.int32).cuda()
+    slots = torch.tensor([1] * n_new + [0] * other, dtype=torch.int32).cuda()
+    q = _rand((n_new + other, heads, hd), torch.bfloat16, 33)
+    scale = 1.0 / math.sqrt(hd)
+    got = ops.attention_decode(q, positions, slots, scale, None, k_pool, v_pool, table, 0, kv_heads, max(longest, 605), late=True)
+    ops.check_error_flag()
+    want = ops.attention_plain(q, positions, scale, None, k_pool=k_pool, v_pool=v_pool, page_table=table, ring=0,
+                               token_slot=slots, kv_heads=kv_heads)
+    assert float((got.float() - want.float()).abs().max()) <= 1e-2
+
+
+
 def _plain_attention(q, k, v, lens, window, scale):
     """q [T, H, hd], k/v [T, KH, hd] packed sequences; float64 reference on the CPU."""
     q, k, v = q.double().cpu(), k.double().cpu(), v.double().cpu()
