@@ -54,9 +54,13 @@ __host__ __device__ constexpr int value_stages(int head_dim, bool two) { return 
 struct PrefillTcArgs {
     __nv_bfloat16* out;       // [T, heads, HD]
     const int32_t* tiles;     // [n_tiles, 3]: packed index of the sequence's first token, its length, first query (tiles of 64)
+                              // over the cache [n_tiles, 5]: ... of the step's tokens, then the position of the step's first
+                              // token and the sequence's slot
     int heads, kv_heads, window;
     float scale_log2;         // scale * log2(e)
     int* error;
+    const int32_t* page_table;    // over the cache: [slots][table_stride]
+    int table_stride;
 };
 
 // Descriptor of an "MN-major" operand tile with 128-byte swizzle: rows of the reduction dimension are 128
@@ -81,7 +85,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // passes). It wins when every SM has many more key tiles to do than the longest chain of one CTA (long prompts):
 // one CTA's waits are then the other's work. With few tiles an SM (2,048 tokens) the launch waits for the
 // longest chain, which a second CTA on its SM only slows.
-template <int HD, bool TWO>
+// CACHED: the sequences go on from the cache, which holds the step's own keys and values too (the q/k/v epilogue wrote
+// them): keys and values come from the paged pools, a tile of 128 positions as the two pages that hold them (the tensor
+// maps are over the pools, boxes of one page of one kv head), and a query sees the positions up to its own.
+template <int HD, bool TWO, bool CACHED>
 __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
@@ -94,7 +101,10 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     // the longest chains of key tiles begin at once and the short ones fill the SMs that become free
     const int tile = (int)gridDim.y - 1 - (int)blockIdx.y, h = blockIdx.x;
     pdl_launch_dependents();
-    const int seq_start = a.tiles[3 * tile], seq_len = a.tiles[3 * tile + 1], q0 = a.tiles[3 * tile + 2];
+    constexpr int TW = CACHED ? 5 : 3;
+    // seq_len: the sequence's tokens in this step; pos0: the position of the first of them (0 without a cache)
+    const int seq_start = a.tiles[TW * tile], seq_len = a.tiles[TW * tile + 1], q0 = a.tiles[TW * tile + 2];
+    const int pos0 = CACHED ? a.tiles[TW * tile + 3] : 0, slot = CACHED ? a.tiles[TW * tile + 4] : 0;
     if (q0 % kBM) return;                             // the second half of a tile of 128 queries
     const int kvh = h / (a.heads / a.kv_heads);
 
@@ -142,11 +152,12 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
     pdl_wait();   // q, k and v come from the kernel before; the tiles' list was written before the step's first kernel
 
-    // key tiles this query tile sees
-    const int q_last = min(q0 + kBM, seq_len) - 1;
-    const int first_key = a.window > 0 ? max(0, q0 - a.window + 1) : 0;
+    // key tiles this query tile sees (positions of the sequence, from 0)
+    const int q_last = pos0 + min(q0 + kBM, seq_len) - 1;
+    const int first_key = a.window > 0 ? max(0, pos0 + q0 - a.window + 1) : 0;
     const int kt0 = first_key / kBN;
     const int n_kt = q_last / kBN - kt0 + 1;
+    const int last_page = (pos0 + seq_len - 1) / kPageSize;       // the last page the sequence holds
     auto fail = [&](int code) {
         *failed = 1;
         if (a.error) atomicExch(a.error, code);
@@ -162,21 +173,39 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
             // a wait that ran out has to let finish (drain.cuh)
             int k_issued = 0, k_waited = 0, v_issued = 0, v_waited = 0;
             bool q_waited = false, any_mma = false;
+            // Over the cache a tile is the two pages of its 128 positions, each one box (64 rows of one kv head); a page the
+            // sequence does not hold yet is replaced by its last one (its rows are masked, but must be numbers).
+            auto pool_row = [&](int t, int half) {
+                const int page = min(2 * (kt0 + t) + half, last_page);
+                return (a.page_table[(size_t)slot * a.table_stride + page] * a.kv_heads + kvh) * kPageSize;
+            };
             auto load_k = [&](int t) {
                 uint8_t* dst = k_s + (size_t)(t % NSK) * kQBytes;
                 ++k_issued;
                 mbar_expect_tx(&k_bar[t % NSK], (uint32_t)kQBytes);
 #pragma unroll
-                for (int b = 0; b < DB; ++b)
-                    tma_load_2d(dst + b * kBlockBytes, &map_k, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &k_bar[t % NSK]);
+                for (int b = 0; b < DB; ++b) {
+                    if (CACHED) {
+                        tma_load_2d(dst + b * kBlockBytes, &map_k, b * 64, pool_row(t, 0), &k_bar[t % NSK]);
+                        tma_load_2d(dst + b * kBlockBytes + kBlockBytes / 2, &map_k, b * 64, pool_row(t, 1), &k_bar[t % NSK]);
+                    } else {
+                        tma_load_2d(dst + b * kBlockBytes, &map_k, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &k_bar[t % NSK]);
+                    }
+                }
             };
             auto load_v = [&](int t) {
                 uint8_t* dst = v_s + (size_t)(t % NSV) * kQBytes;
                 ++v_issued;
                 mbar_expect_tx(&v_bar[t % NSV], (uint32_t)kQBytes);
 #pragma unroll
-                for (int b = 0; b < DB; ++b)
-                    tma_load_2d(dst + b * kBlockBytes, &map_v, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &v_bar[t % NSV]);
+                for (int b = 0; b < DB; ++b) {
+                    if (CACHED) {
+                        tma_load_2d(dst + b * kBlockBytes, &map_v, b * 64, pool_row(t, 0), &v_bar[t % NSV]);
+                        tma_load_2d(dst + b * kBlockBytes + kBlockBytes / 2, &map_v, b * 64, pool_row(t, 1), &v_bar[t % NSV]);
+                    } else {
+                        tma_load_2d(dst + b * kBlockBytes, &map_v, kvh * HD + b * 64, seq_start + (kt0 + t) * kBN, &v_bar[t % NSV]);
+                    }
+                }
             };
             // The descriptors of a tile's k-steps differ in the start address only (bits 0-13, in units of 16 bytes):
             // built once, then advanced by an addition; this thread has nobody to hide its arithmetic behind.
@@ -258,7 +287,8 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
         // ---- 256 threads, two per query row: its lane of tensor memory, and 64 of the tile's 128 keys ----------
         const int quarter = warp & 3, half = warp >> 2;
         const int row = quarter * 32 + (threadIdx.x & 31);
-        const int qpos = q0 + row;
+        const int qpos = pos0 + q0 + row;           // the query's position in its sequence
+        const int seq_end = pos0 + seq_len;         // positions the sequence holds after this step
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         constexpr int OW = HD / 2;          // columns of the output this thread keeps
         float o[OW];
@@ -283,9 +313,9 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
             const int n0 = (kt0 + it) * kBN + half * 64;     // this thread's first key of the tile
             // every key of the tile visible to every query of the tile: no mask needed
             const int t0 = (kt0 + it) * kBN;
-            const bool full = t0 + kBN - 1 <= q0 && t0 + kBN - 1 < seq_len && (a.window <= 0 || t0 > q0 + kBM - 1 - a.window);
+            const bool full = t0 + kBN - 1 <= pos0 + q0 && t0 + kBN - 1 < seq_end && (a.window <= 0 || t0 > pos0 + q0 + kBM - 1 - a.window);
             // otherwise this row sees the keys n0 + j with vis_lo <= j <= vis_hi
-            const int vis_hi = min(qpos, seq_len - 1) - n0;
+            const int vis_hi = min(qpos, seq_end - 1) - n0;
             const int vis_lo = a.window > 0 ? qpos - a.window + 1 - n0 : -(1 << 30);
             if (!mbar_wait(s_full, (uint32_t)it & 1u)) { fail(18); ok = false; break; }
             tc_fence_after();
@@ -416,9 +446,9 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
         mbar_arrive(&pair_bar[quarter]);
         if (!mbar_wait(&pair_bar[quarter], (uint32_t)n_kt & 1u)) { fail(20); ok = false; }
         l += half_sum[(half ^ 1) * 128 + row];
-        if (ok && !*failed && qpos < seq_len) {
+        if (ok && !*failed && q0 + row < seq_len) {
             const float inv = 1.0f / l;
-            __nv_bfloat16* orow = a.out + ((size_t)(seq_start + qpos) * a.heads + h) * HD + half * OW;
+            __nv_bfloat16* orow = a.out + ((size_t)(seq_start + q0 + row) * a.heads + h) * HD + half * OW;
 #pragma unroll
             for (int i = 0; i < OW; i += 8)
                 *reinterpret_cast<uint4*>(orow + i) =
@@ -440,14 +470,14 @@ CUtensorMap make_map(const void* base, int T, int width) {
                         64, 128, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
 
-template <int HD, bool TWO>
+template <int HD, bool TWO, bool CACHED = false>
 void launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillTcArgs& a, int n_tiles,
             cudaStream_t stream) {
     constexpr int DB = HD / 64;
     // alignment; Q, the stages of K and V, P; barriers; maxima and sums
     const size_t smem = 1024 + (size_t)((1 + key_stages(HD, TWO) + value_stages(HD, TWO)) * DB + 2) * kBlockBytes + 160 +
                         3 * 256 * sizeof(float);
-    auto kernel = prefill_attention_tc_kernel<HD, TWO>;
+    auto kernel = prefill_attention_tc_kernel<HD, TWO, CACHED>;
     static bool prepared = false;
     if (!prepared) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -476,7 +506,7 @@ void attention_prefill_tc(const void* q, const void* k, const void* v, void* out
     const CUtensorMap mq = make_map(q, T, heads * head_dim);
     const CUtensorMap mk = make_map(k, T, kv_heads * head_dim);
     const CUtensorMap mv = make_map(v, T, kv_heads * head_dim);
-    PrefillTcArgs a{(__nv_bfloat16*)out, tiles, heads, kv_heads, window, scale * 1.4426950408889634f, error};
+    PrefillTcArgs a{(__nv_bfloat16*)out, tiles, heads, kv_heads, window, scale * 1.4426950408889634f, error, nullptr, 0};
     note_launch();
     if (head_dim == 128) {
         launch<128, false>(mq, mk, mv, a, n_tiles, stream);
@@ -494,6 +524,45 @@ void attention_prefill_tc(const void* q, const void* k, const void* v, void* out
     }
     if (two) launch<64, true>(mq, mk, mv, a, n_tiles, stream);
     else launch<64, false>(mq, mk, mv, a, n_tiles, stream);
+}
+
+
+bool attention_extend_tc_supports(int heads, int kv_heads, int head_dim, long long pool_pages) {
+    return attention_prefill_tc_supports(heads, kv_heads, head_dim) && pool_pages > 0 &&
+           pool_pages * kv_heads * kPageSize < (1ll << 31);
+}
+
+void attention_extend_tc(const void* q, void* out, const int32_t* tiles, int n_tiles, int T, int heads, int kv_heads, int head_dim,
+                         float scale, int window, const void* k_pool, const void* v_pool, const int32_t* page_table,
+                         int table_stride, long long pool_pages, int longest, int variant, int* error, cudaStream_t stream) {
+    if (n_tiles <= 0) return;
+    if (!attention_extend_tc_supports(heads, kv_heads, head_dim, pool_pages))
+        throw std::invalid_argument("attention_extend_tc: head_dim " + std::to_string(head_dim) + " is not 64 or 128, or the pool has too many rows for a tensor map");
+    if (n_tiles > 65535) throw std::invalid_argument("attention_extend_tc: more than 65535 tiles of 64 queries");
+    if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15)
+        throw std::invalid_argument("attention_extend_tc: operands must be 16-byte aligned");
+    const CUtensorMap mq = make_map(q, T, heads * head_dim);
+    // the pools [pages, kv heads, 64 positions, head_dim] as rows of head_dim: a box is one page of one kv head, 64 columns wide
+    const uint64_t rows = (uint64_t)pool_pages * kv_heads * kPageSize;
+    const CUtensorMap mk = tiled_map_2d("attention_extend_tc", CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, k_pool, (uint64_t)head_dim, rows,
+                                        (uint64_t)head_dim * 2, 64, kPageSize, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    const CUtensorMap mv = tiled_map_2d("attention_extend_tc", CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, v_pool, (uint64_t)head_dim, rows,
+                                        (uint64_t)head_dim * 2, 64, kPageSize, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    PrefillTcArgs a{(__nv_bfloat16*)out, tiles, heads, kv_heads, window, scale * 1.4426950408889634f, error, page_table, table_stride};
+    note_launch();
+    if (head_dim == 128) {
+        launch<128, false, true>(mq, mk, mv, a, n_tiles, stream);
+        return;
+    }
+    bool two = variant == 1;
+    if (variant < 0) {
+        // (as in attention_prefill_tc: two CTAs an SM where every SM has at least as many key tiles to do as the longest chain)
+        const long long chain = ((longest > 0 ? longest : T) + kBN - 1) / kBN;
+        const long long total = (long long)heads * ((T + kBM - 1) / kBM) * chain;
+        two = total >= chain * kSmCount * 2;
+    }
+    if (two) launch<64, true, true>(mq, mk, mv, a, n_tiles, stream);
+    else launch<64, false, true>(mq, mk, mv, a, n_tiles, stream);
 }
 
 }  // namespace sm

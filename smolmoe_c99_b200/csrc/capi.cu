@@ -220,6 +220,20 @@ SM_API int sm_attention_prefill_tc(const void* q, const void* k, const void* v, 
     });
 }
 
+SM_API int sm_attention_extend_tc_supports(int heads, int kv_heads, int head_dim, long long pool_pages) {
+    return sm::attention_extend_tc_supports(heads, kv_heads, head_dim, pool_pages) ? 1 : 0;
+}
+
+SM_API int sm_attention_extend_tc(const void* q, void* out, const int32_t* tiles, int n_tiles, int T, int heads, int kv_heads,
+                                  int head_dim, float scale, int window, const void* k_pool, const void* v_pool,
+                                  const int32_t* page_table, int table_stride, long long pool_pages, int longest, int variant,
+                                  int* error, void* stream) {
+    return guarded([&] {
+        sm::attention_extend_tc(q, out, tiles, n_tiles, T, heads, kv_heads, head_dim, scale, window, k_pool, v_pool, page_table,
+                                table_stride, pool_pages, longest, variant, error, (cudaStream_t)stream);
+    });
+}
+
 SM_API int sm_attention_decode_supports(int heads, int kv_heads, int head_dim) {
     return sm::attention_decode_supports(heads, kv_heads, head_dim) ? 1 : 0;
 }

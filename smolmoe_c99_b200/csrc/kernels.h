@@ -217,6 +217,14 @@ void attention_prefill_tc(const void* q, const void* k, const void* v, void* out
                           int heads, int kv_heads, int head_dim, float scale, int window, int longest, int variant,
                           int* error, cudaStream_t stream);
 
+// The same kernel for sequences that go on from the cache by many tokens (prompt portions): keys and values come from
+// the paged pools, which must hold the step's own tokens already; `tiles` [n_tiles, 5] as attention_extend takes them,
+// `longest` the longest sequence after the step. No windowed group (its ring is written after the attention).
+bool attention_extend_tc_supports(int heads, int kv_heads, int head_dim, long long pool_pages);
+void attention_extend_tc(const void* q, void* out, const int32_t* tiles, int n_tiles, int T, int heads, int kv_heads, int head_dim,
+                         float scale, int window, const void* k_pool, const void* v_pool, const int32_t* page_table,
+                         int table_stride, long long pool_pages, int longest, int variant, int* error, cudaStream_t stream);
+
 // ---- attention_decode.cu --------------------------------------------------------------
 // One new token per sequence over the paged cache for bfloat16: a cluster of CTAs per
 // (sequence, kv head) splits the visible positions and merges through distributed shared

@@ -139,6 +139,10 @@ class Ops:
         # on the 0.5B sizes against the tiled kernel: 100 tokens onto 2,000 1.60 against 2.65 ms a step, 256 onto 6,000
         # 3.69 against 5.97, 512 onto 2,000 3.50 against 3.54, 768 onto 2,000 4.50 against 3.82).
         self.extend_rows_as_decode = 512 if fast else 0
+        # ... and up to this many where the tcgen05 attention can read its keys from the cache (head sizes 64 and 128, no
+        # window): 160 tokens onto 2,000 take 2.15 ms either way, 300 tokens 2.93 as rows against 2.56 as tiles, 512 onto
+        # 8,000 6.85 against 4.43
+        self.extend_rows_as_decode_tc = 176 if fast else 0
         self.skinny_single_round_above_8 = True
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.lib.sm_set_error_word.restype = None
@@ -580,14 +584,31 @@ class Ops:
     def attention_extend(self, q, k_packed, v_packed, step, scale, window, cache, cache_written=False):
         """Causal attention of sequences that go on from the cache by any number of tokens: keys and values of
         earlier positions from the cache, the step's own from the packed tensors (the cache need not hold them yet)."""
-        if (self.use_fast_attention and q.dtype == torch.bfloat16 and q.shape[0] <= self.extend_rows_as_decode
-                and cache.ring == 0 and cache_written and cache.k_pool.dtype == torch.bfloat16
+        from_cache = (self.use_fast_attention and q.dtype == torch.bfloat16 and cache.ring == 0 and cache_written
+                      and cache.k_pool.dtype == torch.bfloat16)
+        tiles_from_cache = (from_cache and self.use_tcgen05_attention and step.extend_tiles is not None and not window
+                            and self.lib.sm_attention_extend_tc_supports(q.shape[1], k_packed.shape[1], q.shape[2],
+                                                                         ctypes.c_longlong(cache.k_pool.shape[0])))
+        rows_limit = self.extend_rows_as_decode_tc if tiles_from_cache else self.extend_rows_as_decode
+        if (from_cache and q.shape[0] <= rows_limit
                 and self.lib.sm_attention_decode_supports(q.shape[1], k_packed.shape[1], q.shape[2])):
             # a few tokens onto a live sequence: every token as a row of the decode kernel, which shares a row's keys
-            # out among the CTAs of a cluster (the tiled kernel below has one CTA per 64 queries and head, each with the
-            # whole chain of keys to itself: 8 tokens onto 2,000 took 2.0 ms a step with it)
+            # out among the CTAs of a cluster (the tiled kernels below have one CTA per 64 or 128 queries and head, each
+            # with the whole chain of keys to itself: 8 tokens onto 2,000 took 2.0 ms a step that way)
             return self.attention_decode(q, step.positions, step.token_slot, scale, window, cache.k_pool, cache.v_pool,
                                          cache.page_table, cache.ring, k_packed.shape[1], step.max_seq_len, late=True)
+        if tiles_from_cache:
+            # many tokens onto the cache (prompt portions): the tcgen05 kernel, with every key from the paged pools
+            _need(q, "q", torch.bfloat16, 3)
+            _need(step.extend_tiles, "tiles", torch.int32, 2)
+            _need(cache.page_table, "page table", torch.int32, 2)
+            out = torch.empty_like(q)
+            self._check(self.lib.sm_attention_extend_tc(
+                _ptr(q), _ptr(out), _ptr(step.extend_tiles), step.extend_tiles.shape[0], q.shape[0], q.shape[1],
+                k_packed.shape[1], q.shape[2], ctypes.c_float(scale), int(window or 0), _ptr(cache.k_pool), _ptr(cache.v_pool),
+                _ptr(cache.page_table), cache.page_table.shape[1], ctypes.c_longlong(cache.k_pool.shape[0]),
+                int(step.max_seq_len), -1, _ptr(self.error_flag), _stream()))
+            return out
         if (self.use_fast_attention and q.dtype == torch.bfloat16 and step.extend_tiles is not None
                 and self.lib.sm_attention_prefill_supports(q.shape[2])):
             out = self._prefill_operands(q, k_packed, v_packed, step.extend_tiles)

@@ -251,6 +251,52 @@ def test_attention_of_sequences_that_go_on_from_the_cache(ops, heads, kv_heads, 
             at += news[b]
 
 
+@pytest.mark.parametrize("heads,kv_heads,hd", [(14, 2, 64), (4, 4, 64), (8, 2, 128)])
+@pytest.mark.parametrize("starts,news", [([700, 0, 33, 1000], [600, 130, 64, 530]), ([2000], [1000]), ([1, 127, 128], [300, 129, 257])])
+def test_attention_of_many_tokens_onto_the_cache(ops, heads, kv_heads, hd, starts, news):
+    """Prompt portions: sequences go on by hundreds of tokens from positions that are no multiple of a tile, and the
+    cache holds the step's own keys and values already. The tcgen05 kernel reads every key from the paged pools (pages
+    in a random order; rows past a sequence's end hold other numbers and must not count) and is compared with the
+    plain kernel in float. One key far back stands out for one query of each sequence."""
+    from types import SimpleNamespace
+    from smolmoe_c99_b200.engine.batch import pack_step
+    from smolmoe_c99_b200.kernels import PAGE_SIZE
+    B, total = len(starts), [s + n for s, n in zip(starts, news)]
+    pages_per_seq = -(-max(total) // PAGE_SIZE) + 1
+    g = torch.Generator().manual_seed(sum(news))
+    table = torch.randperm(B * pages_per_seq, generator=g).to(torch.int32).view(B, pages_per_seq)
+    k_pool = torch.randn((B * pages_per_seq, kv_heads, PAGE_SIZE, hd), generator=g).to(torch.bfloat16)
+    v_pool = torch.randn((B * pages_per_seq, kv_heads, PAGE_SIZE, hd), generator=g).to(torch.bfloat16)
+    qs = [torch.randn((n, heads, hd), generator=g).to(torch.bfloat16) for n in news]
+    for b in range(B):
+        # the last query of the sequence looks hard at one key near the sequence's start
+        far = min(5, total[b] - 1)
+        page = int(table[b, far // PAGE_SIZE])
+        qs[b][-1] = k_pool[page, :, far % PAGE_SIZE].repeat_interleave(heads // kv_heads, dim=0) * 3.0
+    step = pack_step(list(range(B)), starts, [[0] * n for n in news], torch.device("cuda"))
+    assert step.mode == "extend"
+    q = torch.cat(qs).cuda()
+    assert q.shape[0] > ops.extend_rows_as_decode_tc
+    packed = torch.empty((q.shape[0], kv_heads, hd), dtype=torch.bfloat16, device="cuda")     # not read
+    cache = SimpleNamespace(k_pool=k_pool.cuda(), v_pool=v_pool.cuda(), page_table=table.cuda(), ring=0)
+    scale = 1.0 / math.sqrt(hd)
+    launches = int(ops.lib.sm_launch_count())
+    got = ops.attention_extend(q, packed, packed, step, scale, None, cache, cache_written=True).float()
+    ops.check_error_flag()
+    assert int(ops.lib.sm_launch_count()) == launches + 1
+    want = ops.attention_plain(q.float(), step.positions, scale, None, k_pool=cache.k_pool.float(), v_pool=cache.v_pool.float(),
+                               page_table=cache.page_table, ring=0, token_slot=step.token_slot, kv_heads=kv_heads)
+    assert float((got - want).abs().max()) <= 2e-2
+    at = 0
+    for b in range(B):
+        at += news[b]
+        far = min(5, total[b] - 1)
+        page = int(table[b, far // PAGE_SIZE])
+        for h in (0, heads - 1):
+            v_far = cache.v_pool[page, h // (heads // kv_heads), far % PAGE_SIZE].float()
+            assert float((got[at - 1, h] - v_far).abs().max()) <= 5e-2, (b, h)
+
+
 @pytest.mark.parametrize("T", [1, 5, 16])
 @pytest.mark.parametrize("N,K", [(70, 50), (129, 1000), (16, 4864)])
 def test_gemm_simt_for_few_tokens_gives_the_tile_kernels_bits(ops, T, N, K):

@@ -59,7 +59,8 @@ def test_wide_batches_of_unequal_lengths(model_dirs, name, dtype):
 def test_long_prompts_on_the_two_cta_products(model_dirs, name):
     """Steps of more than 160 tokens take the two-CTA products and the q/k/v epilogue that rotates and stores (head
     sizes 64 and 128): a whole prompt, the same prompt in two portions (the second reads the cache), and two prompts
-    in one step, against the plain implementation; and against the same engine with those products switched off."""
+    in one step, two prompts in three portions (the tcgen05 attention reads keys and values from the cache's pages),
+    against the plain implementation; and against the same engine with those products switched off."""
     from smolmoe_c99_b200.engine.engine import Engine
     vocab, longest = TINY[name]["vocab_size"], TINY[name]["max_position_embeddings"]
     n = min(900, longest - 20)
@@ -92,6 +93,7 @@ def test_long_prompts_on_the_two_cta_products(model_dirs, name):
     ops = engine.runtime.ops
     whole = run([requests["long"]], [])[0]
     portions = run([requests["long"]], [n - 520])[0]          # 520 tokens onto a cache of the rest
+    thirds = run([requests["long"], requests["other"]], [n - 610, n - 290])     # unequal sequences go on together, twice
     both = run([requests["long"], requests["other"]], [])
     ops.gemm_pair_enable(False)
     try:
@@ -100,6 +102,7 @@ def test_long_prompts_on_the_two_cta_products(model_dirs, name):
         ops.gemm_pair_enable(True)
     engine.check_status()
     for what, got, rid in (("whole", whole, "long"), ("two portions", portions, "long"), ("two prompts", both[0], "long"),
+                           ("three portions", thirds[0], "long"), ("three portions", thirds[1], "other"),
                            ("two prompts", both[1], "other"), ("one-CTA products", single, "long")):
         _check({rid: got}, {rid: picked(rid)}, "bfloat16", what)
     assert float((whole - single).abs().max()) <= 1e-2 * float(single.abs().max())
