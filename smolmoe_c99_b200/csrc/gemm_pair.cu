@@ -52,6 +52,7 @@ constexpr int kUmmaK = 16;
 constexpr int kBoxRows = 64;         // rows of one TMA box
 constexpr int kThreads = 192;
 constexpr int kStagingBytes = kRows * 128;   // one chunk on its way out: 128 token rows of 128 bytes, swizzled
+constexpr int kBiasBytes = 256 * 4;          // the biases of a unit's columns
 constexpr int kPairMinTokens = 161;  // (a pair's tile is 256 tokens. Measured on the 0.5B sizes, whole prompt steps: 160 tokens 1.84 ms
                                       // against 1.77 with the one-CTA kernel, 176 tokens 1.86 against 1.93, 700 tokens 2.17 against 3.13)
 
@@ -204,7 +205,7 @@ __device__ __forceinline__ PairUnit pair_unit(const PairParams& p, int u, int ra
 // One group of 32 columns of this thread's token on its way out: the values (for a gated product act(gate) * up, else
 // the sum plus the bias) as 16-byte pieces of the staged row.
 template <bool WIDE, bool GATED>
-__device__ __forceinline__ void group_out(const PairParams& p, uint32_t (&gr)[32], uint32_t (&ur)[32], int n_first, uint8_t* stage,
+__device__ __forceinline__ void group_out(const PairParams& p, uint32_t (&gr)[32], uint32_t (&ur)[32], const float* bias32, uint8_t* stage,
                                           int row, int first_piece) {
     float g[32];
 #pragma unroll
@@ -219,9 +220,13 @@ __device__ __forceinline__ void group_out(const PairParams& p, uint32_t (&gr)[32
 #pragma unroll
             for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(ur[j]) * activate_fast(p.act, g[j]);
         }
-    } else if (p.bias) {
+    } else if (bias32) {
+        // (the unit's biases lie in shared memory: every thread reads the same word, once a group)
 #pragma unroll
-        for (int j = 0; j < 32; ++j) g[j] += bias_at(p, n_first + j);
+        for (int j = 0; j < 8; ++j) {
+            const float4 b = ((const float4*)bias32)[j];
+            g[4 * j] += b.x; g[4 * j + 1] += b.y; g[4 * j + 2] += b.z; g[4 * j + 3] += b.w;
+        }
     }
     if (WIDE) {
 #pragma unroll
@@ -242,7 +247,7 @@ __device__ __forceinline__ void group_out(const PairParams& p, uint32_t (&gr)[32
 // of the turn before.
 template <bool WIDE, bool GATED>
 __device__ __forceinline__ void unit_out(const PairParams& p, const PairUnit& w, uint32_t acc, int row, uint8_t* staging,
-                                         uint32_t& turn_count, bool issuer, const CUtensorMap& map_out) {
+                                         uint32_t& turn_count, bool issuer, const CUtensorMap& map_out, const float* bias_s) {
     const int out_cols = GATED ? p.half : p.tile_f;
     uint32_t ga[32], ua[32], gb[32], ub[32];
     tmem_ld32_issue(acc, ga);
@@ -261,14 +266,14 @@ __device__ __forceinline__ void unit_out(const PairParams& p, const PairUnit& w,
         if (GATED) tmem_ld_wait(ua);
         tmem_ld32_issue(acc + (uint32_t)(c0 + 32), gb);
         if (GATED) tmem_ld32_issue(acc + (uint32_t)(p.half + c0 + 32), ub);
-        group_out<WIDE, GATED>(p, ga, ua, w.n0 + c0, first, row, 0);
+        group_out<WIDE, GATED>(p, ga, ua, bias_s ? bias_s + c0 : nullptr, first, row, 0);
         tmem_ld_wait(gb);
         if (GATED) tmem_ld_wait(ub);
         if (c0 + 64 < out_cols && w.n0 + c0 + 64 < p.N) {
             tmem_ld32_issue(acc + (uint32_t)(c0 + 64), ga);
             if (GATED) tmem_ld32_issue(acc + (uint32_t)(p.half + c0 + 64), ua);
         }
-        group_out<WIDE, GATED>(p, gb, ub, w.n0 + c0 + 32, second, row, WIDE ? 0 : 4);
+        group_out<WIDE, GATED>(p, gb, ub, bias_s ? bias_s + c0 + 32 : nullptr, second, row, WIDE ? 0 : 4);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         epilogue_barrier();
         if (issuer) {
@@ -292,7 +297,7 @@ __device__ __forceinline__ void unit_out(const PairParams& p, const PairUnit& w,
 __device__ __forceinline__ void qkv_heads_out(const PairParams& p, const PairUnit& w, uint32_t acc, int row, uint8_t* staging,
                                               uint32_t& chunk_count, bool issuer, const CUtensorMap& map_q,
                                               const CUtensorMap& map_k, const CUtensorMap& map_v, bool tables_held,
-                                              const float4 (&held_cos)[8], const float4 (&held_sin)[8]) {
+                                              const float4 (&held_cos)[8], const float4 (&held_sin)[8], const float* bias_s) {
     const PairRope& r = p.rope;
     const int hd = r.head_dim, half = hd >> 1, chunks = hd / 64;
     const int t = w.t0 + row;
@@ -324,11 +329,14 @@ __device__ __forceinline__ void qkv_heads_out(const PairParams& p, const PairUni
             float lo[32], hi[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) { lo[j] = __uint_as_float(lo_r[j]); hi[j] = __uint_as_float(hi_r[j]); }
-            if (p.bias) {
+            if (bias_s) {
+                const float4* bl = (const float4*)(bias_s + col0 + s);
+                const float4* bh = (const float4*)(bias_s + col0 + half + s);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    lo[j] += bias_at(p, w.n0 + col0 + s + j);
-                    hi[j] += bias_at(p, w.n0 + col0 + half + s + j);
+                for (int j = 0; j < 8; ++j) {
+                    const float4 l = bl[j], h = bh[j];
+                    lo[4 * j] += l.x; lo[4 * j + 1] += l.y; lo[4 * j + 2] += l.z; lo[4 * j + 3] += l.w;
+                    hi[4 * j] += h.x; hi[4 * j + 1] += h.y; hi[4 * j + 2] += h.z; hi[4 * j + 3] += h.w;
                 }
             }
             if (!is_v) {
@@ -355,9 +363,21 @@ __device__ __forceinline__ void qkv_heads_out(const PairParams& p, const PairUni
                 const int lo_col = s + 8 * j, hi_col = half + s + 8 * j;      // columns within the head
                 stage_piece(first + (lo_col >> 6) * kStagingBytes, row, (lo_col & 63) >> 3, l);
                 stage_piece(first + (hi_col >> 6) * kStagingBytes, row, (hi_col & 63) >> 3, h);
-                if (pool_row) {
-                    *(uint4*)(pool_row + lo_col) = l;
-                    *(uint4*)(pool_row + hi_col) = h;
+            }
+        }
+        if (!is_q && r.k_pool != nullptr) {
+            // Keys and values into the cache, from the staged rows of this warp's own 32 tokens: eight lanes write the
+            // 128 bytes of a row's chunk side by side (a thread writing its own row would touch 32 lines an instruction)
+            __syncwarp();
+            const int lane = row & 31, piece = lane & 7;
+            for (int c = 0; c < chunks; ++c) {
+                const uint8_t* chunk = first + c * kStagingBytes;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int src = 4 * i + (lane >> 3);                   // the lane whose token this is
+                    __nv_bfloat16* dst = (__nv_bfloat16*)__shfl_sync(0xffffffffu, (unsigned long long)pool_row, src);
+                    const int rr = (row & ~31) + src;
+                    if (dst) *(uint4*)(dst + 64 * c + 8 * piece) = *(const uint4*)(chunk + rr * 128 + ((piece ^ (rr & 7)) << 4));
                 }
             }
         }
@@ -394,6 +414,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     long long& fills_issued = *(long long*)(tmem_slot + 2);
     long long& fills_consumed = *(long long*)(tmem_slot + 4);
     int& mmas_issued = *(int*)(tmem_slot + 6);
+    float* bias_s = (float*)((uint8_t*)full_bar + 256);                       // [tile_f] the biases of the unit on its way out
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = (int)cluster_rank();
@@ -407,6 +428,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         prefetch_tensor_map(&map_w);
         prefetch_tensor_map(&map_x);
         prefetch_tensor_map(&map_out);
+        if (p.epilogue == P_QKV && p.rope.k_packed != nullptr) {
+            prefetch_tensor_map(&map_k);
+            prefetch_tensor_map(&map_v);
+        }
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -537,6 +562,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
                 for (int j = 0; j < 8; ++j) { held_cos[j] = __ldg(c4 + j); held_sin[j] = __ldg(s4 + j); }
             }
+            if (p.bias) {
+                // the unit's biases into shared memory while its MMAs run (the unit before has been read out)
+                epilogue_barrier();
+                for (int c = row; c < p.tile_f; c += kRows) bias_s[c] = bias_at(p, w.n0 + c);
+                epilogue_barrier();
+            }
             bool ok = mbar_wait_pair(&tfull_bar[b], ((uint32_t)i >> 1) & 1u);
             if (!ok && lane == 0) { *failed = 1; atomicExch(p.error, 3); }
             ok = __all_sync(0xffffffffu, ok && *failed == 0);
@@ -544,11 +575,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             tc_fence_after();
             const uint32_t acc = tmem_base + (uint32_t)(b * p.tile_f) + ((uint32_t)(quarter * 32) << 16);
             if (p.epilogue == P_QKV) {
-                if (w.t0 < p.T) qkv_heads_out(p, w, acc, row, staging, chunk_count, issuer, map_out, map_k, map_v, tables_held, held_cos, held_sin);
+                if (w.t0 < p.T) qkv_heads_out(p, w, acc, row, staging, chunk_count, issuer, map_out, map_k, map_v, tables_held, held_cos, held_sin,
+                                                 p.bias ? bias_s : nullptr);
             } else if (w.t0 < p.T) {
-                if (p.epilogue == P_GATED) unit_out<false, true>(p, w, acc, row, staging, chunk_count, issuer, map_out);
-                else if (p.out_dt == F32) unit_out<true, false>(p, w, acc, row, staging, chunk_count, issuer, map_out);
-                else unit_out<false, false>(p, w, acc, row, staging, chunk_count, issuer, map_out);
+                if (p.epilogue == P_GATED) unit_out<false, true>(p, w, acc, row, staging, chunk_count, issuer, map_out, nullptr);
+                else if (p.out_dt == F32) unit_out<true, false>(p, w, acc, row, staging, chunk_count, issuer, map_out, p.bias ? bias_s : nullptr);
+                else unit_out<false, false>(p, w, acc, row, staging, chunk_count, issuer, map_out, p.bias ? bias_s : nullptr);
             }
             // this accumulator may be overwritten by the MMAs of the unit after next
             tc_fence_before();
@@ -647,10 +679,10 @@ void gemm_pair(const void* x, const void* w, const void* bias, DType bias_dt, vo
     p.error = error;
     p.units = p.tiles_f * tiles_t;
     const int stage_bytes = kRows * kStageK * 2 + p.half * kStageK * 2;
-    const int budget = 227 * 1024 - 1024 - 2 * kStagingBytes - 256;
+    const int budget = 227 * 1024 - 1024 - 2 * kStagingBytes - 256 - kBiasBytes;
     p.stages = budget / stage_bytes;
     if (p.stages > 8) p.stages = 8;
-    const size_t smem = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + 2 * kStagingBytes + (2 * p.stages + 5) * 8 + 64;
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + 2 * kStagingBytes + 256 /*barriers*/ + kBiasBytes;
     const CUtensorMap map_w = pair_operand_map(w, p.epilogue == P_GATED ? up_offset + N : N, K);
     const CUtensorMap map_x = pair_operand_map(x, T, K);
     const CUtensorMap map_out = pair_out_map(out, T, N, out_dt);
@@ -685,10 +717,10 @@ bool gemm_pair_qkv(const void* x, const void* w, const void* bias, DType bias_dt
     p.rope = rope;
     p.units = p.tiles_f * ((T + 2 * kRows - 1) / (2 * kRows));
     const int stage_bytes = kRows * kStageK * 2 + p.half * kStageK * 2;
-    const int budget = 227 * 1024 - 1024 - 2 * kStagingBytes - 256;
+    const int budget = 227 * 1024 - 1024 - 2 * kStagingBytes - 256 - kBiasBytes;
     p.stages = budget / stage_bytes;
     if (p.stages > 8) p.stages = 8;
-    const size_t smem = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + 2 * kStagingBytes + (2 * p.stages + 5) * 8 + 64;
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024 /*alignment*/ + 2 * kStagingBytes + 256 /*barriers*/ + kBiasBytes;
     const CUtensorMap map_w = pair_operand_map(w, N, K);
     const CUtensorMap map_x = pair_operand_map(x, T, K);
     const CUtensorMap map_q = pair_out_map(rope.q_out, T, rope.heads * rope.head_dim, BF16);
