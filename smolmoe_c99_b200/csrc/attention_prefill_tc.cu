@@ -4,20 +4,22 @@
 // scans [start, pos] per query and head: src/model.c:459-491, src/kernels.c:1156-1176), for
 // head sizes 64 and 128.
 //
-// One CTA per (tile of 128 queries of one sequence, head): 256 threads, two to a query row (64 of a
-// key tile's 128 scores and half of the output's columns each), and a ninth warp whose first thread
-// issues the copies and the MMAs. Q, and tiles of 128
-// keys and values, come into shared memory by TMA (128-byte swizzle). For every key tile:
+// One CTA per (tile of 128 queries of one sequence, head): 256 threads, two to a query row, and a ninth warp whose
+// first thread issues the copies and the MMAs. Q, and tiles of 128 keys and values, come into shared memory by TMA
+// (128-byte swizzle). A row's two threads are two streams of their own over the keys: thread `half` takes keys
+// 64 * half .. 64 * half + 63 of every tile, with a reference maximum, a sum and an output accumulator of its own, and
+// the two are put together once, after the last tile. For every key tile:
 //   S = Q K^T   tcgen05.mma 128 x 128 x head_dim, both operands K-major, S (float) in tensor memory;
-//   a row's two threads read their halves of it (their lane of tensor memory) with tcgen05.ld,
-//   mask, agree on the running maximum through shared memory, and write P = exp2(S - max) as
-//   bfloat16 into shared memory in the swizzled K-major layout an MMA operand needs;
-//   PV = P V    tcgen05.mma 128 x head_dim x 128 with V as it lies in memory ([key][dim], the
-//   "MN-major" operand form), into a second accumulator; the threads add their columns of PV to
-//   the output they keep in registers, rescaled when the maximum moved.
-// The row threads and the issuing thread meet only at mbarriers: S of the next tile is issued as
-// soon as the rows of this one are in registers, and PV of a tile is added to the output during
-// the next tile's arithmetic, so the tensor core works under the softmax.
+//   each thread reads its 64 scores (its lane of tensor memory) with tcgen05.ld, masks them and writes
+//   P = exp2(S * scale - reference) as bfloat16 into shared memory in the swizzled K-major layout an MMA operand needs;
+//   O_half += P_half V_half   tcgen05.mma 128 x head_dim x 64 with V as it lies in memory ([key][dim], the "MN-major"
+//   operand form), accumulating over the tiles in tensor memory, one accumulator per stream.
+// The reference is lazy: it moves only when a tile's maximum exceeds it by more than 2^8 (P then stays below 256, and the
+// float sums have room); only then do the threads of that warp read their accumulators, rescale them and write them
+// back (tcgen05.st) before P is handed over. So a tile's chain is: scores, maximum, exponentials, P; nothing is read
+// back from the PV product and the row's threads exchange nothing until the end.
+// The row threads and the issuing thread meet only at mbarriers: S of the next tile is issued as soon as the rows of
+// this one are in registers, and PV runs under the next tile's arithmetic.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in *error and the
 // CTA leaves without writing.
@@ -96,7 +98,8 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     constexpr int DB = HD / 64;                       // blocks of 64 columns of the head dimension
     constexpr int kQBytes = DB * kBlockBytes;         // Q tile, and one K or V tile
     constexpr int NSK = key_stages(HD, TWO), NSV = value_stages(HD, TWO);
-    constexpr uint32_t kTmemCols = 256;               // S: 128 columns, PV: HD columns
+    constexpr uint32_t kTmemCols = HD == 64 ? 256 : 512;   // S: 128 columns, then one output accumulator of HD columns per stream
+    constexpr int PB = (HD == 64 && !TWO) ? 2 : 1;    // buffers of P: with two, P of a tile is written while PV of the tile before reads its own
     // CTAs start in the order of their index, the heads of one tile together: late tiles (most keys) first, so that
     // the longest chains of key tiles begin at once and the short ones fill the SMs that become free
     const int tile = (int)gridDim.y - 1 - (int)blockIdx.y, h = blockIdx.x;
@@ -113,21 +116,24 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     uint8_t* q_s = smem;                              // [DB][128 queries][128 B]
     uint8_t* k_s = q_s + kQBytes;                     // NSK x [DB][128 keys][128 B]
     uint8_t* v_s = k_s + NSK * kQBytes;               // NSV x [DB][128 keys][128 B]
-    uint8_t* p_s = v_s + NSV * kQBytes;               // [2][128 queries][128 B]: keys 0-63 and 64-127 of the tile
-    uint64_t* bars = (uint64_t*)(p_s + 2 * kBlockBytes);
+    uint8_t* p_s = v_s + NSV * kQBytes;               // [PB][2][128 queries][128 B]: keys 0-63 and 64-127 of the tile
+    uint64_t* bars = (uint64_t*)(p_s + PB * 2 * kBlockBytes);
     uint64_t* q_bar = bars;                           // Q has landed
     uint64_t* s_full = bars + 1;                      // the MMAs of S are done
     uint64_t* s_free = bars + 2;                      // all rows of S are in registers
     uint64_t* p_full = bars + 3;                      // all rows of P are in shared memory (and PV of the tile before is read)
-    uint64_t* pv_full = bars + 4;                     // the MMAs of PV are done
-    uint64_t* pair_bar = bars + 5;                    // [4] the two warps of a lane quarter have both written their halves' figures
+    // the MMAs of PV of tile t are done: two barriers, for even and odd tiles, so that a wait for the tile before the
+    // last one issued can be told from a wait for the last
+    auto pv_bar = [&](int t) { return (t & 1) ? bars + 19 : bars + 4; };
+    auto pv_parity = [](int t) { return (uint32_t)(t >> 1) & 1u; };
+    uint64_t* pair_bar = bars + 5;                    // [4] the two warps of a lane quarter have both written their streams' figures
     uint64_t* k_bar = bars + 9;                       // [NSK] a key tile has landed
     uint64_t* v_bar = bars + 9 + NSK;                 // [NSV] a value tile has landed
     uint64_t* drain_bar = bars + 17;                  // a commit behind the last MMA, on the way out after a failure (NSK + NSV <= 8)
     uint32_t* tmem_slot = (uint32_t*)(bars + 18);
     volatile int* failed = (volatile int*)(tmem_slot + 1);
-    float* half_max = (float*)(bars + 20);            // [2 tiles in flight][2 halves][128 rows]: maxima of the halves of the rows' scores
-    float* half_sum = half_max + 512;                 // [2 halves][128 rows]: the sums, at the end
+    float* half_max = (float*)(bars + 20);            // [2 streams][128 rows]: the streams' references, at the end
+    float* half_sum = half_max + 512;                 // [2 streams][128 rows]: their sums
 
     const int warp = threadIdx.x >> 5;
 
@@ -138,7 +144,8 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
         mbar_init(s_full, 1);
         mbar_init(s_free, kRowThreads);
         mbar_init(p_full, kRowThreads);
-        mbar_init(pv_full, 1);
+        mbar_init(pv_bar(0), 1);
+        mbar_init(pv_bar(1), 1);
         mbar_init(drain_bar, 1);
         for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
         *failed = 0;
@@ -220,15 +227,16 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                 }
                 umma_commit(s_full);
             };
-            auto issue_pv = [&](int t) {    // PV = P V for tile t, whose P lies in shared memory
+            auto issue_pv = [&](int t) {    // O_half += P_half V_half for tile t, whose P lies in shared memory
                 const uint64_t desc_v = desc_v0 + (uint64_t)(((uint32_t)(t % NSV) * kQBytes) >> 4);
+                const uint64_t desc_pt = desc_p + (uint64_t)(((uint32_t)(t % PB) * 2 * kBlockBytes) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < kBN / 16; ++ks) {
                     const uint64_t p_off = (uint64_t)(((uint32_t)(ks / 4) * kBlockBytes + (uint32_t)(ks % 4) * 32) >> 4);
                     const uint64_t v_off = (uint64_t)(((uint32_t)ks * 16 * 128) >> 4);   // 16 keys of 128 bytes
-                    umma_bf16(tmem_pv, desc_p + p_off, desc_v + v_off, idesc_pv, ks > 0 ? 1u : 0u);
+                    umma_bf16(tmem_pv + (uint32_t)((ks / 4) * HD), desc_pt + p_off, desc_v + v_off, idesc_pv, (t > 0 || (ks % 4) > 0) ? 1u : 0u);
                 }
-                umma_commit(pv_full);
+                umma_commit(pv_bar(t));
             };
             mbar_expect_tx(q_bar, (uint32_t)kQBytes);
 #pragma unroll
@@ -259,10 +267,13 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                     tc_fence_after();
                     issue_s(it + 1);
                 }
-                // P of tile it is in shared memory, and the threads have read PV of the tile before: that one's
-                // value stage may take tile it - 1 + NSV
+                // P of tile it is in shared memory. Once PV of the tile before is done, that one's value stage may take
+                // tile it - 1 + NSV.
                 if (!(ok = mbar_wait(p_full, ph))) { fail(14); break; }
-                if (it >= 1 && it - 1 + NSV < n_kt) load_v(it - 1 + NSV);
+                if (it >= 1 && it - 1 + NSV < n_kt) {
+                    if (!(ok = mbar_wait(pv_bar(it - 1), pv_parity(it - 1)))) { fail(22); break; }
+                    load_v(it - 1 + NSV);
+                }
                 if (!(ok = mbar_wait(&v_bar[it % NSV], (uint32_t)(it / NSV) & 1u))) { fail(15); break; }
                 v_waited = it + 1;
                 tc_fence_after();
@@ -290,23 +301,32 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
         const int qpos = pos0 + q0 + row;           // the query's position in its sequence
         const int seq_end = pos0 + seq_len;         // positions the sequence holds after this step
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        constexpr int OW = HD / 2;          // columns of the output this thread keeps
-        float o[OW];
-#pragma unroll
-        for (int i = 0; i < OW; ++i) o[i] = 0.f;
-        float m = -CUDART_INF_F, l = 0.f;   // the row's running maximum, and the sum over this thread's keys
+        constexpr int OW = HD / 2;          // columns of the output this thread writes at the end
+        constexpr float kLazy = 8.0f;       // the reference moves when a tile's maximum exceeds it by more than this (log2)
+        const uint32_t tmem_o = tmem_pv + lane_base + (uint32_t)(half * HD);    // this stream's output accumulator
+        float m = -CUDART_INF_F, l = 0.f;   // the stream's reference maximum, and the sum of its P against it
         bool ok = true;
-        // adds this thread's columns of PV of tile t (complete when pv_full has its phase t) to the output
-        auto add_pv = [&](int t) {
-            if (!mbar_wait(pv_full, (uint32_t)t & 1u)) { fail(17); ok = false; return; }
-            tc_fence_after();
+        // After a tile's maximum is known: where any thread of the warp has to move its reference, every thread of the
+        // warp does (tensor memory is read and written by whole warps), rescaling its sum and, from the second tile on,
+        // its accumulator, which PV of the tile before has to have left alone by then.
+        auto settle_reference = [&](int it, float mloc) {
+            if (!__any_sync(0xffffffffu, mloc > m + kLazy)) return;
+            const float mx = fmaxf(m, mloc);
+            const float corr = mx == -CUDART_INF_F ? 1.0f : ex2_approx(m - mx);    // 0 for a stream that has seen no key yet
+            if (it > 0) {
+                if (!mbar_wait(pv_bar(it - 1), pv_parity(it - 1))) { fail(17); ok = false; return; }
+                tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < OW / 32; ++c) {
-                float pv[32];
-                tmem_ld32(tmem_pv + lane_base + (uint32_t)(half * OW + c * 32), pv);
+                for (int c = 0; c < HD / 32; ++c) {
+                    float acc[32];
+                    tmem_ld32(tmem_o + (uint32_t)(c * 32), acc);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) o[c * 32 + j] += pv[j];
+                    for (int j = 0; j < 32; ++j) acc[j] *= corr;
+                    tmem_st32(tmem_o + (uint32_t)(c * 32), acc);
+                }
             }
+            l *= corr;
+            m = mx;
         };
 
         for (int it = 0; it < n_kt && ok; ++it) {
@@ -317,6 +337,7 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
             // otherwise this row sees the keys n0 + j with vis_lo <= j <= vis_hi
             const int vis_hi = min(qpos, seq_end - 1) - n0;
             const int vis_lo = a.window > 0 ? qpos - a.window + 1 - n0 : -(1 << 30);
+            uint8_t* prow = p_s + (size_t)((it % PB) * 2 + half) * kBlockBytes + (size_t)row * 128;
             if (!mbar_wait(s_full, (uint32_t)it & 1u)) { fail(18); ok = false; break; }
             tc_fence_after();
             if constexpr (!TWO) {
@@ -337,19 +358,13 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                 for (int e = 0; e < 8; ++e) raw8[e] = sv[e];
     #pragma unroll
                 for (int j = 8; j < 64; ++j) raw8[j & 7] = fmaxf(raw8[j & 7], sv[j]);
-                float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
-                                  fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
-                // the other half's maximum, through shared memory; the two warps of a lane quarter meet at their own barrier
-                half_max[(it & 1) * 256 + half * 128 + row] = raw;
-                mbar_arrive(&pair_bar[quarter]);
-                if (!mbar_wait(&pair_bar[quarter], (uint32_t)it & 1u)) { fail(19); ok = false; break; }
-                raw = fmaxf(raw, half_max[(it & 1) * 256 + (half ^ 1) * 128 + row]);
-                const float mx = fmaxf(m, raw * a.scale_log2);
-                // a row that has seen no key yet keeps m = -inf; 0 as its reference avoids inf - inf
-                const float ref = mx == -CUDART_INF_F ? 0.f : mx;
-                const float corr = ex2_approx(m - ref);
-                m = mx;
-                // P = 2^(S * scale - max) as bfloat16, and its sum
+                const float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
+                                        fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
+                settle_reference(it, raw * a.scale_log2);
+                if (!ok) break;
+                // a stream that has seen no key yet keeps m = -inf; 0 as its reference avoids inf - inf
+                const float ref = m == -CUDART_INF_F ? 0.f : m;
+                // P = 2^(S * scale - reference) as bfloat16, and its sum
                 uint32_t pk[32];
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};
     #pragma unroll
@@ -359,16 +374,10 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                     sum4[(j / 2) & 3] += p0 + p1;
                     pk[j / 2] = pack_bf16(p0, p1);
                 }
-                l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-                // the tile before: its PV into the output (it ran under this tile's arithmetic), which also frees P
-                if (it > 0) add_pv(it - 1);
-                if (!ok) break;
-                if (corr != 1.0f) {
-    #pragma unroll
-                    for (int i = 0; i < OW; ++i) o[i] *= corr;
-                }
+                l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                // this buffer of P was read by PV of tile it - PB
+                if (it >= PB && !mbar_wait(pv_bar(it - PB), pv_parity(it - PB))) { fail(23); ok = false; break; }
                 // this thread's 64 keys are block `half` of P: pieces of 8 keys (16 bytes), swizzled with the row
-                uint8_t* prow = p_s + (size_t)half * kBlockBytes + (size_t)row * 128;
     #pragma unroll
                 for (int piece = 0; piece < 8; ++piece)
                     *reinterpret_cast<uint4*>(prow + ((piece ^ (row & 7)) << 4)) =
@@ -394,23 +403,13 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     #pragma unroll
                     for (int j = 0; j < 32; ++j) raw8[j & 7] = fmaxf(raw8[j & 7], sv[j]);
                 }
-                float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
-                                  fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
-                half_max[(it & 1) * 256 + half * 128 + row] = raw;
-                mbar_arrive(&pair_bar[quarter]);
-                if (!mbar_wait(&pair_bar[quarter], (uint32_t)it & 1u)) { fail(19); ok = false; break; }
-                raw = fmaxf(raw, half_max[(it & 1) * 256 + (half ^ 1) * 128 + row]);
-                const float mx = fmaxf(m, raw * a.scale_log2);
-                const float ref = mx == -CUDART_INF_F ? 0.f : mx;
-                const float corr = ex2_approx(m - ref);
-                m = mx;
-                if (it > 0) add_pv(it - 1);   // (it ran under this tile's first pass; this also frees P)
+                const float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
+                                        fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
+                settle_reference(it, raw * a.scale_log2);
                 if (!ok) break;
-                if (corr != 1.0f) {
-    #pragma unroll
-                    for (int i = 0; i < OW; ++i) o[i] *= corr;
-                }
-                uint8_t* prow = p_s + (size_t)half * kBlockBytes + (size_t)row * 128;
+                const float ref = m == -CUDART_INF_F ? 0.f : m;
+                // the one buffer of P was read by PV of the tile before
+                if (it >= PB && !mbar_wait(pv_bar(it - PB), pv_parity(it - PB))) { fail(23); ok = false; break; }
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};
     #pragma unroll
                 for (int part = 0; part < 2; ++part) {
@@ -433,27 +432,48 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                         *reinterpret_cast<uint4*>(prow + ((piece ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                     }
                 }
-                l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+                l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             }
-            // P is written: make it visible to the tensor core's reads, then tell the issuing thread
+            // P is written (and a moved reference's accumulator is back in tensor memory): make it visible to the tensor
+            // core's reads, then tell the issuing thread
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             mbar_arrive(p_full);
         }
-        if (ok && n_kt > 0) add_pv(n_kt - 1);
-        // the row's sum is the two halves' (both against the same maximum)
+        // The two streams of a row put together: their references and sums through shared memory, their accumulators read
+        // from tensor memory by both threads, each for its half of the output's columns.
+        half_max[half * 128 + row] = m;
         half_sum[half * 128 + row] = l;
         mbar_arrive(&pair_bar[quarter]);
-        if (!mbar_wait(&pair_bar[quarter], (uint32_t)n_kt & 1u)) { fail(20); ok = false; }
-        l += half_sum[(half ^ 1) * 128 + row];
-        if (ok && !*failed && q0 + row < seq_len) {
-            const float inv = 1.0f / l;
+        if (!mbar_wait(&pair_bar[quarter], 0)) { fail(20); ok = false; }
+        if (ok && n_kt > 0 && !mbar_wait(pv_bar(n_kt - 1), pv_parity(n_kt - 1))) { fail(17); ok = false; }
+        tc_fence_after();
+        if (__all_sync(0xffffffffu, ok && !*failed)) {
+            const float m_other = half_max[(half ^ 1) * 128 + row], l_other = half_sum[(half ^ 1) * 128 + row];
+            const float top = fmaxf(m, m_other);
+            const float w_mine = m == -CUDART_INF_F ? 0.f : ex2_approx(m - top);
+            const float w_other = m_other == -CUDART_INF_F ? 0.f : ex2_approx(m_other - top);
+            const float sum = l * w_mine + l_other * w_other;
+            const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+            const float w0 = (half == 0 ? w_mine : w_other) * inv, w1 = (half == 0 ? w_other : w_mine) * inv;   // streams 0 and 1
+            const bool live = q0 + row < seq_len;
             __nv_bfloat16* orow = a.out + ((size_t)(seq_start + q0 + row) * a.heads + h) * HD + half * OW;
 #pragma unroll
-            for (int i = 0; i < OW; i += 8)
-                *reinterpret_cast<uint4*>(orow + i) =
-                    make_uint4(pack_bf16(o[i] * inv, o[i + 1] * inv), pack_bf16(o[i + 2] * inv, o[i + 3] * inv),
-                               pack_bf16(o[i + 4] * inv, o[i + 5] * inv), pack_bf16(o[i + 6] * inv, o[i + 7] * inv));
+            for (int c = 0; c < OW / 32; ++c) {
+                float o0[32], o1[32];
+                tmem_ld32(tmem_pv + lane_base + (uint32_t)(half * OW + c * 32), o0);
+                tmem_ld32(tmem_pv + lane_base + (uint32_t)(HD + half * OW + c * 32), o1);
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        float r[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) r[e] = o0[i + e] * w0 + o1[i + e] * w1;
+                        *reinterpret_cast<uint4*>(orow + c * 32 + i) =
+                            make_uint4(pack_bf16(r[0], r[1]), pack_bf16(r[2], r[3]), pack_bf16(r[4], r[5]), pack_bf16(r[6], r[7]));
+                    }
+                }
+            }
         }
     }
     __syncwarp();
@@ -475,7 +495,8 @@ void launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
             cudaStream_t stream) {
     constexpr int DB = HD / 64;
     // alignment; Q, the stages of K and V, P; barriers; maxima and sums
-    const size_t smem = 1024 + (size_t)((1 + key_stages(HD, TWO) + value_stages(HD, TWO)) * DB + 2) * kBlockBytes + 160 +
+    const int p_buffers = (HD == 64 && !TWO) ? 2 : 1;
+    const size_t smem = 1024 + (size_t)((1 + key_stages(HD, TWO) + value_stages(HD, TWO)) * DB + 2 * p_buffers) * kBlockBytes + 160 +
                         3 * 256 * sizeof(float);
     auto kernel = prefill_attention_tc_kernel<HD, TWO, CACHED>;
     static bool prepared = false;
