@@ -357,7 +357,9 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     #pragma unroll
                 for (int e = 0; e < 8; ++e) raw8[e] = sv[e];
     #pragma unroll
-                for (int j = 8; j < 64; ++j) raw8[j & 7] = fmaxf(raw8[j & 7], sv[j]);
+                for (int j = 8; j < 64; j += 16)
+    #pragma unroll
+                    for (int e = 0; e < 8; ++e) raw8[e] = fmax3(raw8[e], sv[j + e], sv[j + 8 + e]);
                 const float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
                                         fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
                 settle_reference(it, raw * a.scale_log2);
@@ -365,16 +367,23 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                 // a stream that has seen no key yet keeps m = -inf; 0 as its reference avoids inf - inf
                 const float ref = m == -CUDART_INF_F ? 0.f : m;
                 // P = 2^(S * scale - reference) as bfloat16, and its sum
+                // (the scaling and the sums two at a time, with the packed float instructions)
                 uint32_t pk[32];
-                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint64_t scale2 = pack_f32x2(a.scale_log2, a.scale_log2), ref2 = pack_f32x2(-ref, -ref);
+                uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};      // (the bits of two float zeros)
     #pragma unroll
                 for (int j = 0; j < 64; j += 2) {
-                    const float p0 = ex2_approx(fmaf(sv[j], a.scale_log2, -ref));
-                    const float p1 = ex2_approx(fmaf(sv[j + 1], a.scale_log2, -ref));
-                    sum4[(j / 2) & 3] += p0 + p1;
+                    float x0, x1;
+                    unpack_f32x2(fma_f32x2(pack_f32x2(sv[j], sv[j + 1]), scale2, ref2), x0, x1);
+                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                    sum2[(j / 2) & 3] = add_f32x2(sum2[(j / 2) & 3], pack_f32x2(p0, p1));
                     pk[j / 2] = pack_bf16(p0, p1);
                 }
-                l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                {
+                    float lo, hi;
+                    unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), lo, hi);
+                    l += lo + hi;
+                }
                 // this buffer of P was read by PV of tile it - PB
                 if (it >= PB && !mbar_wait(pv_bar(it - PB), pv_parity(it - PB))) { fail(23); ok = false; break; }
                 // this thread's 64 keys are block `half` of P: pieces of 8 keys (16 bytes), swizzled with the row
@@ -401,7 +410,9 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                 for (int part = 0; part < 2; ++part) {
                     read_scores(part);
     #pragma unroll
-                    for (int j = 0; j < 32; ++j) raw8[j & 7] = fmaxf(raw8[j & 7], sv[j]);
+                    for (int j = 0; j < 32; j += 16)
+    #pragma unroll
+                        for (int e = 0; e < 8; ++e) raw8[e] = fmax3(raw8[e], sv[j + e], sv[j + 8 + e]);
                 }
                 const float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
                                         fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
@@ -410,7 +421,8 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                 const float ref = m == -CUDART_INF_F ? 0.f : m;
                 // the one buffer of P was read by PV of the tile before
                 if (it >= PB && !mbar_wait(pv_bar(it - PB), pv_parity(it - PB))) { fail(23); ok = false; break; }
-                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint64_t scale2 = pack_f32x2(a.scale_log2, a.scale_log2), ref2 = pack_f32x2(-ref, -ref);
+                uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};      // (the bits of two float zeros)
     #pragma unroll
                 for (int part = 0; part < 2; ++part) {
                     read_scores(part);
@@ -423,16 +435,21 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
                         uint32_t pk[4];
     #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const float p0 = ex2_approx(fmaf(sv[c * 8 + 2 * e], a.scale_log2, -ref));
-                            const float p1 = ex2_approx(fmaf(sv[c * 8 + 2 * e + 1], a.scale_log2, -ref));
-                            sum4[e] += p0 + p1;
+                            float x0, x1;
+                            unpack_f32x2(fma_f32x2(pack_f32x2(sv[c * 8 + 2 * e], sv[c * 8 + 2 * e + 1]), scale2, ref2), x0, x1);
+                            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                            sum2[e] = add_f32x2(sum2[e], pack_f32x2(p0, p1));
                             pk[e] = pack_bf16(p0, p1);
                         }
                         const int piece = part * 4 + c;
                         *reinterpret_cast<uint4*>(prow + ((piece ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                     }
                 }
-                l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                {
+                    float lo, hi;
+                    unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), lo, hi);
+                    l += lo + hi;
+                }
             }
             // P is written (and a moved reference's accumulator is back in tensor memory): make it visible to the tensor
             // core's reads, then tell the issuing thread
