@@ -554,8 +554,8 @@ void attention_prefill_tc(const void* q, const void* k, const void* v, void* out
     if (variant < 0) {
         // Two CTAs an SM when every SM has at least as many key tiles to do as the longest chain of one CTA has
         // (estimated as if every sequence were as long as the longest). Measured on a B200, 14 heads of 64, one
-        // CTA against two: one prompt of 2,048 tokens 34.6 / 39.0 us, of 4,096 95 / 77, of 8,192 305 / 238, of
-        // 16,384 1,115 / 855 (563 TFLOP/s); eight prompts of 2,048 216 / 165; four of 1,024 43 / 41.
+        // CTA against two: one prompt of 2,048 tokens 28.1 / 35.0 us, of 4,096 86 / 66, of 8,192 286 / 206, of
+        // 16,384 1,047 / 745 (645 TFLOP/s); eight prompts of 2,048 198 / 146; four of 1,024 37 / 34.
         const long long chain = ((longest > 0 && longest < T ? longest : T) + kBN - 1) / kBN;
         const long long total = (long long)heads * ((T + kBM - 1) / kBM) * (chain + 1) / 2;
         two = total >= chain * kSmCount;
