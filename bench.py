@@ -357,7 +357,7 @@ def main() -> int:
             engine.close_sequence(s)
 
     if args.profile_region:
-        one = prompts(1)
+        one = [torch.randint(0, V, (P,), generator=gen).tolist()]      # always of P tokens, whatever --prompt-min says of the batch
         if args.profile_region == "prefill":
             engine.use_graphs = False    # kernel by kernel: the same kernels that the captured step replays
             s = engine.open_sequence(); engine.step([s], one); engine.close_sequence(s)
@@ -378,7 +378,7 @@ def main() -> int:
         return 0
 
     # ---- prefill of one 2,048-token prompt ------------------------------------------------
-    one = prompts(1)
+    one = [torch.randint(0, V, (P,), generator=gen).tolist()]      # always of P tokens, whatever --prompt-min says of the batch
     for _ in range(2):
         s = engine.open_sequence(); engine.step([s], one); engine.close_sequence(s)
     torch.cuda.synchronize()

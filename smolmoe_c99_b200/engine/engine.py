@@ -40,6 +40,30 @@ class StepError(ValueError):
     """The step's arguments cannot be run (bad token, unknown slot, no room)."""
 
 
+def _capture(device, run):
+    """``run()`` captured into a CUDA graph on a stream of its own: returns (graph, what run returned).
+
+    ``torch.cuda.graph`` is not used: on entry it collects Python garbage and gives the allocator's cached blocks back
+    to the driver, which took ~0.4 s with a few GB cached -- a stall in the middle of generation whenever a batch
+    reaches a span for which no graph has been captured yet."""
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph.capture_begin()
+        try:
+            out = run()
+        except BaseException:
+            try:
+                graph.capture_end()      # the stream must leave capture mode whatever happened
+            except Exception:
+                pass
+            raise
+        graph.capture_end()
+    torch.cuda.current_stream().wait_stream(side)
+    return graph, out
+
+
 class _DecodeGraph:
     """One captured decode step for a batch size and key span."""
 
@@ -90,10 +114,8 @@ class _DecodeGraph:
                 state.copy_(before)
         # the graph is taken for captured only once the capture has gone through: a failed one leaves no
         # half-made graph behind that a later step could replay
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = engine.model.forward(self.batch, engine.cache, self.rows, engine._status)
-        self.graph, self.logits = graph, logits
+        self.graph, self.logits = _capture(
+            engine.device, lambda: engine.model.forward(self.batch, engine.cache, self.rows, engine._status))
 
 
 class _StepGraph:
@@ -120,10 +142,8 @@ class _StepGraph:
             # (No run outside the capture first: the shape's first step ran kernel by kernel, which loaded the kernels
             # and set their attributes. Nothing runs during the capture, so the replay below is this step's one run.)
             self.packed, self.batch = batch.packed, batch
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = engine.model.forward(batch, engine.cache, self.want_rows, engine._status)
-            self.graph, self.logits = graph, logits
+            self.graph, self.logits = _capture(
+                engine.device, lambda: engine.model.forward(batch, engine.cache, self.want_rows, engine._status))
         self.graph.replay()
         return self.logits
 
