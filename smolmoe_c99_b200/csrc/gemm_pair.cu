@@ -55,6 +55,10 @@ constexpr int kStagingBytes = kRows * 128;   // one chunk on its way out: 128 to
 constexpr int kBiasBytes = 256 * 4;          // the biases of a unit's columns
 constexpr int kPairMinTokens = 161;  // (a pair's tile is 256 tokens. Measured on the 0.5B sizes, whole prompt steps: 160 tokens 1.84 ms
                                       // against 1.77 with the one-CTA kernel, 176 tokens 1.86 against 1.93, 700 tokens 2.17 against 3.13)
+// A gated product is ahead here from 65 tokens, where the one-CTA kernel's token tile leaves 64 (0.5B sizes, 65 / 160 tokens:
+// 12.0 / 15.9 -> 10.1 / 10.0 us a launch; 7B sizes: 68 / 90 -> 50 / 53); a q/k/v product with its rotation and the += products
+// stay with the one-CTA kernel up to 160 tokens (down at 160 tokens: 11.5 us there against 21.4 here, one pair a feature tile).
+constexpr int kPairMinTokensGated = 65;
 
 enum PairEpilogue : int { P_STORE = 0, P_ACCUM = 1, P_GATED = 2, P_QKV = 3 };
 
@@ -644,7 +648,7 @@ void gemm_pair_enable(bool on) { g_pair_enabled = on; }
 
 bool gemm_pair_takes(const void* x, const void* w, const void* out, DType out_dt, int T, int N, int K, int mode) {
     const int epilogue = mode & 0xff;
-    if (!g_pair_enabled || T < kPairMinTokens || N <= 0 || K <= 0 || K % 8) return false;
+    if (!g_pair_enabled || T < (epilogue == P_GATED ? kPairMinTokensGated : kPairMinTokens) || N <= 0 || K <= 0 || K % 8) return false;
     if (epilogue != P_STORE && epilogue != P_ACCUM && epilogue != P_GATED) return false;
     if (epilogue == P_ACCUM && out_dt != F32) return false;
     if (epilogue == P_GATED && out_dt != BF16) return false;
