@@ -55,10 +55,12 @@ constexpr int kStagingBytes = kRows * 128;   // one chunk on its way out: 128 to
 constexpr int kBiasBytes = 256 * 4;          // the biases of a unit's columns
 constexpr int kPairMinTokens = 161;  // (a pair's tile is 256 tokens. Measured on the 0.5B sizes, whole prompt steps: 160 tokens 1.84 ms
                                       // against 1.77 with the one-CTA kernel, 176 tokens 1.86 against 1.93, 700 tokens 2.17 against 3.13)
-// A gated product is ahead here from 65 tokens, where the one-CTA kernel's token tile leaves 64 (0.5B sizes, 65 / 160 tokens:
-// 12.0 / 15.9 -> 10.1 / 10.0 us a launch; 7B sizes: 68 / 90 -> 50 / 53); a q/k/v product with its rotation and the += products
+// A gated product is ahead here earlier: launch by launch from 65 tokens, where the one-CTA kernel's token tile leaves 64
+// (0.5B sizes, 65 / 160 tokens: 12.0 / 15.9 -> 10.1 / 10.0 us; 7B sizes: 68 / 90 -> 50 / 53), but inside a whole step only
+// from about 112 (its CTAs fill the SMs, so its neighbours in the chain overlap it less: prompt steps of 65 / 100 / 128 / 160
+// tokens 1.19 / 1.28 / 1.32 / 1.52 -> 1.21 / 1.29 / 1.30 / 1.43 ms). A q/k/v product with its rotation and the += products
 // stay with the one-CTA kernel up to 160 tokens (down at 160 tokens: 11.5 us there against 21.4 here, one pair a feature tile).
-constexpr int kPairMinTokensGated = 65;
+constexpr int kPairMinTokensGated = 112;
 
 enum PairEpilogue : int { P_STORE = 0, P_ACCUM = 1, P_GATED = 2, P_QKV = 3 };
 

@@ -54,13 +54,13 @@ def _gemm_tc_case(ops, T, N, K, mode):
 
 
 @pytest.mark.parametrize("T,H,K", [(1, 4864, 896), (8, 4864, 896), (64, 160, 96), (300, 520, 264), (2048, 1024, 128),
-                                   (40, 202, 2048), (64, 18944, 3584), (70, 160, 1024), (65, 4864, 896), (129, 202, 264),
+                                   (40, 202, 2048), (64, 18944, 3584), (70, 160, 1024), (112, 4864, 896), (129, 202, 264),
                                    (160, 520, 96)])
 @pytest.mark.parametrize("pairs", [True, False])
 def test_gemm_tc_gated(ops, T, H, K, pairs):
-    """(a gated product goes to the two-CTA kernel from 65 tokens)"""
-    if not pairs and T <= 64:
-        pytest.skip("up to 64 tokens there is one kernel")
+    """(a gated product goes to the two-CTA kernel from 112 tokens)"""
+    if not pairs and T < 112:
+        pytest.skip("up to 111 tokens there is one kernel")
     ops.gemm_pair_enable(pairs)
     try:
         _gemm_tc_gated_case(ops, T, H, K)
@@ -80,7 +80,7 @@ def _gemm_tc_gated_case(ops, T, H, K):
 
 @pytest.mark.parametrize("T,N,K", [(512, 896, 896), (2048, 896, 4864), (700, 200, 72), (1100, 1152, 896), (513, 136, 264),
                                    (4096, 2048, 128), (8192, 512, 64), (161, 896, 4864), (170, 136, 72), (300, 1152, 896),
-                                   (100, 1152, 896), (65, 136, 72)])
+                                   (120, 1152, 896), (112, 136, 72)])
 @pytest.mark.parametrize("mode", ["store_f32", "store_bf16", "accumulate", "gated"])
 def test_gemm_pair(ops, T, N, K, mode):
     """Products of more than 160 tokens go to the kernel in which two CTAs share a tile of 256 tokens: against a float
