@@ -18,6 +18,13 @@
 // epilogue of the CTA's own 128 tokens. Tensor memory holds two accumulators, so the next unit's MMAs run while the
 // epilogue drains the last. The kernel is persistent: pair i takes units i, i + pairs, ...
 //
+// Few tiles and a long K (the down product of a prompt of a few hundred tokens has 7 to 35 tiles for 74 pairs, and a pair
+// streams K at what its two SMs take from L2): the launch then puts two pairs into one cluster of four CTAs, each pair
+// with half of the tile's K. Every CTA leaves its share of the sums in its own shared memory (over the stages, idle by
+// then), the cluster meets at a barrier, and each pair finishes half of the tile's columns: a thread reads its token's row
+// of them from both pairs through distributed shared memory, adds them in the order of the pairs and hands the sum to
+// TMA's float add. The order is fixed, so the result does not depend on which pair was first.
+//
 // The barriers. All "stage is full" barriers are the leader's: both CTAs' TMA copies count their bytes on them (the
 // cta_group::2 form of the copy may signal the partner's barrier), and the leader expects the bytes of both. "Stage
 // is empty" and "accumulator complete" are signalled by tcgen05.commit to the barrier of the same name in both CTAs at
@@ -61,6 +68,9 @@ constexpr int kPairMinTokens = 161;  // (a pair's tile is 256 tokens. Measured o
 // tokens 1.19 / 1.28 / 1.32 / 1.52 -> 1.21 / 1.29 / 1.30 / 1.43 ms). A q/k/v product with its rotation and the += products
 // stay with the one-CTA kernel up to 160 tokens (down at 160 tokens: 11.5 us there against 21.4 here, one pair a feature tile).
 constexpr int kPairMinTokensGated = 112;
+// Pairs that may share a unit's K. The kernel takes 2 or 4; with 4 (clusters of 8 CTAs) whole prompt steps of the 0.5B sizes were
+// no faster than with 2 (176 / 512 / 1,024 tokens: 1.57 / 1.76 / 2.05 ms against 1.54 / 1.74 / 2.06; 1.68 / 1.86 / 2.16 without).
+constexpr int kPairMaxSplits = 2;
 
 enum PairEpilogue : int { P_STORE = 0, P_ACCUM = 1, P_GATED = 2, P_QKV = 3 };
 
@@ -77,6 +87,8 @@ struct PairParams {
     int out_dt;
     int* error;
     int tiles_f, units;       // feature tiles; units = feature tiles x token tiles
+    int splits;               // pairs that share a unit's K (1, 2 or 4): a cluster of 2 * splits CTAs, each pair with
+    int kb_per;               // kb_per stages of K, their sums added up through distributed shared memory
     PairRope rope;            // P_QKV: the heads, the rotation's tables and where q, keys and values go
 };
 
@@ -112,8 +124,7 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a,
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 // Arrives, once the MMAs issued so far are done, on the barrier at this address in BOTH CTAs of the pair.
-__device__ __forceinline__ void umma_commit_both(uint64_t* bar) {
-    const uint16_t both = 3;
+__device__ __forceinline__ void umma_commit_both(uint64_t* bar, uint16_t both) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(smem_u32(bar)), "h"(both) : "memory");
 }
@@ -400,6 +411,72 @@ __device__ __forceinline__ void qkv_heads_out(const PairParams& p, const PairUni
     }
 }
 
+// Split K: this CTA's share of a tile's sums (128 tokens x 128 features, float) out of tensor memory into its shared
+// memory, over the stages, which are idle once the pair's MMAs are done: four chunks of 32 columns in the staged layout.
+__device__ __forceinline__ void split_stash(uint32_t acc, int row, uint8_t* smem) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld32(acc + (uint32_t)(c * 32), v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            stage_piece(smem + c * kStagingBytes, row, j, make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                                                                    __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3])));
+    }
+}
+
+// Split K, after the cluster's barrier: pair `slice` finishes columns [slice * 128 / splits, +128 / splits) of the tile.
+// Each thread adds up its token's row of those columns over the pairs, always in the order of the pairs (the sums do
+// not depend on who was first), reading the other pairs' shares from their CTAs of the same rank through distributed
+// shared memory, and the sum is added to the output by TMA.
+__device__ __forceinline__ void split_finish(const PairParams& p, const PairUnit& w, bool issuer, int row, int rank, int slice,
+                                             uint8_t* smem, uint8_t* staging, const CUtensorMap& map_out, bool failed) {
+    const int chunks = 4 / p.splits;                // chunks of 32 columns a pair finishes
+    for (int cc = 0; cc < chunks; ++cc) {
+        const int c = slice * chunks + cc;
+        float4 sum[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!failed) {
+            // (all the loads first, then the additions: a load from another SM's shared memory takes about a microsecond)
+            const uint32_t mine = smem_u32(smem + c * kStagingBytes + row * 128);
+            float4 v[4][8];
+#pragma unroll
+            for (int s2 = 0; s2 < 4; ++s2) {
+                if (s2 < p.splits) {
+                    const uint32_t theirs = in_cta(mine, (uint32_t)(2 * s2 + rank));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                     : "=f"(v[s2][j].x), "=f"(v[s2][j].y), "=f"(v[s2][j].z), "=f"(v[s2][j].w)
+                                     : "r"(theirs + (uint32_t)((j ^ (row & 7)) << 4)));
+                }
+            }
+#pragma unroll
+            for (int s2 = 0; s2 < 4; ++s2) {
+                if (s2 < p.splits) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        sum[j].x += v[s2][j].x; sum[j].y += v[s2][j].y; sum[j].z += v[s2][j].z; sum[j].w += v[s2][j].w;
+                    }
+                }
+            }
+        }
+        uint8_t* out_chunk = staging + (cc & 1) * kStagingBytes;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            stage_piece(out_chunk, row, j, make_uint4(__float_as_uint(sum[j].x), __float_as_uint(sum[j].y), __float_as_uint(sum[j].z),
+                                                      __float_as_uint(sum[j].w)));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        epilogue_barrier();
+        if (issuer && !failed && w.t0 < p.T) {
+            tma_add_2d(&map_out, out_chunk, w.n0 + c * 32, w.t0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+    }
+    if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory stays valid until read
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_k,
@@ -423,9 +500,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     float* bias_s = (float*)((uint8_t*)full_bar + 256);                       // [tile_f] the biases of the unit on its way out
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rank = (int)cluster_rank();
+    const uint32_t crank = cluster_rank();
+    const int rank = (int)(crank & 1u);              // within the pair
+    const int slice = (int)(crank >> 1);             // which share of K this pair has, where a cluster holds several pairs
+    const uint32_t lead = crank & ~1u;               // the pair's leader, as a rank of the cluster
+    const uint16_t both = (uint16_t)(3u << lead);    // the pair, as a mask of the cluster's CTAs
     const bool leader = rank == 0;
-    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int pair = (int)blockIdx.x / (2 * p.splits), pairs = (int)gridDim.x / (2 * p.splits);
     pdl_launch_dependents();
     uint32_t tmem_cols = 32;
     while ((int)tmem_cols < 2 * p.tile_f) tmem_cols <<= 1;
@@ -454,11 +535,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     pair_barrier();            // the partner's barriers exist before anything is signalled on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int kb_total = (p.K + kStageK - 1) / kStageK;
+    const int kb_first = slice * p.kb_per;            // this pair's stages of K
+    const int kb_total = min(p.kb_per, (p.K + kStageK - 1) / kStageK - kb_first);
 
     if (warp == 0) {
         const PairBox box = pair_box(lane, p);
-        const uint32_t full0 = in_cta(smem_u32(full_bar), 0);   // the leader's "full" barriers
+        const uint32_t full0 = in_cta(smem_u32(full_bar), lead);   // the leader's "full" barriers
         // The weights do not depend on the kernel before this one: the weight tiles of the first unit's first stages
         // are asked for before the wait for it, the token tiles after.
         const int early = min(p.stages, kb_total);
@@ -469,11 +551,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             __syncwarp();
             if (box.active && !box.from_x)
                 for (int i = 0; i < early; ++i)
-                    tma_load_2d_pair(smem + (size_t)i * stage_bytes + box.offset, &map_w, i * kStageK + box.k, w.w0 + box.row, full0 + 8u * i);
+                    tma_load_2d_pair(smem + (size_t)i * stage_bytes + box.offset, &map_w, (kb_first + i) * kStageK + box.k, w.w0 + box.row, full0 + 8u * i);
             pdl_wait();
             for (int i = 0; i < early; ++i)
                 if (box.active && box.from_x)
-                    tma_load_2d_pair(smem + (size_t)i * stage_bytes + box.offset, &map_x, i * kStageK + box.k, w.t0 + box.row, full0 + 8u * i);
+                    tma_load_2d_pair(smem + (size_t)i * stage_bytes + box.offset, &map_x, (kb_first + i) * kStageK + box.k, w.t0 + box.row, full0 + 8u * i);
         }
         int s = early == p.stages ? 0 : early;
         uint32_t phase = early == p.stages ? 1u : 0u;
@@ -491,7 +573,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 if (leader && lane == 0) mbar_expect_tx(&full_bar[s], 2u * (uint32_t)stage_bytes);
                 __syncwarp();
                 if (box.active)
-                    tma_load_2d_pair(smem + (size_t)s * stage_bytes + box.offset, box.from_x ? &map_x : &map_w, kb * kStageK + box.k, row,
+                    tma_load_2d_pair(smem + (size_t)s * stage_bytes + box.offset, box.from_x ? &map_x : &map_w, (kb_first + kb) * kStageK + box.k, row,
                                      full0 + 8u * s);
                 ++issued;
                 if (++s == p.stages) { s = 0; phase ^= 1u; }
@@ -533,12 +615,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                         umma_bf16_pair(d, da + (k / (kBlockK / kUmmaK)) * a_atom + sub, db + (k / (kBlockK / kUmmaK)) * b_atom + sub, idesc, acc);
                         acc = 1;
                     }
-                    umma_commit_both(&empty_bar[s]);   // the stage is free in both CTAs once these MMAs have read it
+                    umma_commit_both(&empty_bar[s], both);   // the stage is free in both CTAs once these MMAs have read it
                     da += stage_step;
                     if (++s == p.stages) { s = 0; phase ^= 1u; da = desc_first; }
                 }
                 if (*failed) break;
-                umma_commit_both(&tfull_bar[b]);       // the accumulator is complete in both CTAs
+                umma_commit_both(&tfull_bar[b], both); // the accumulator is complete in both CTAs
             }
             fills_consumed = consumed;
             mmas_issued = consumed > 0;
@@ -548,7 +630,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         const int quarter = warp & 3;
         const bool issuer = warp == 2 && lane == 0;
         const int row = quarter * 32 + lane;
-        const uint32_t tempty0 = in_cta(smem_u32(tempty_bar), 0);
+        const uint32_t tempty0 = in_cta(smem_u32(tempty_bar), lead);
         int i = 0;
         uint32_t chunk_count = 0;
         pdl_wait();   // the output (read for "+=") and everything written below come after the kernel before
@@ -583,6 +665,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             if (p.epilogue == P_QKV) {
                 if (w.t0 < p.T) qkv_heads_out(p, w, acc, row, staging, chunk_count, issuer, map_out, map_k, map_v, tables_held, held_cos, held_sin,
                                                  p.bias ? bias_s : nullptr);
+            } else if (p.splits > 1) {
+                split_stash(acc, row, smem);
             } else if (w.t0 < p.T) {
                 if (p.epilogue == P_GATED) unit_out<false, true>(p, w, acc, row, staging, chunk_count, issuer, map_out, nullptr);
                 else if (p.out_dt == F32) unit_out<true, false>(p, w, acc, row, staging, chunk_count, issuer, map_out, p.bias ? bias_s : nullptr);
@@ -594,6 +678,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             if (lane == 0) mbar_arrive_in_cluster(tempty0 + 8u * b);
         }
         if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory stays valid until read
+    }
+    if (p.splits > 1) {
+        // Every pair of the cluster has its share of the sums in its CTAs' shared memory (or has given up: the barrier is
+        // met either way). Each pair then finishes its share of the tile's columns.
+        __syncwarp();
+        pair_barrier();
+        if (warp >= 2) {
+            const PairUnit w = pair_unit(p, pair, rank);            // one unit a cluster
+            split_finish(p, w, warp == 2 && lane == 0, (warp & 3) * 32 + lane, rank, slice, smem, staging, map_out, *failed != 0);
+        }
     }
     __syncwarp();
     tc_fence_before();
@@ -640,6 +734,35 @@ int pair_sm_count() {
         if (count <= 0) count = 148;
     }
     return count;
+}
+
+// How many clusters of `size` CTAs with this much shared memory the GPU runs at once.
+int pair_clusters_at_once(int size, size_t smem) {
+    struct Known { int size; size_t smem; int clusters; };
+    static std::mutex lock;
+    static Known known[8];
+    static int n_known = 0;
+    std::lock_guard<std::mutex> hold(lock);
+    for (int i = 0; i < n_known; ++i)
+        if (known[i].size == size && known[i].smem == smem) return known[i].clusters;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(size, 1, 1);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    if (n_known < 8) known[n_known++] = {size, smem, n};
+    return n;
 }
 
 bool g_pair_enabled = true;
@@ -696,9 +819,23 @@ void gemm_pair(const void* x, const void* w, const void* bias, DType bias_dt, vo
     std::call_once(attr_once, [] {
         cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     });
-    const int pairs = p.units < pairs_on_gpu ? p.units : pairs_on_gpu;
-    launch_kernel("gemm_pair", gemm_pair_kernel, dim3(2 * pairs), dim3(kThreads), smem, stream, 2, dependent_launch_enabled(), map_w,
-                  map_x, map_out, map_out, map_out, p);
+    // A "+=" product with few tiles and a long K (the down product of a prompt of a few hundred tokens: 7 to 35 tiles for
+    // 74 pairs, each streaming all of K at what one SM takes from L2): the pairs of a cluster share a tile's K and add
+    // their sums up through distributed shared memory, in a fixed order.
+    const int kb_total = (K + kStageK - 1) / kStageK;
+    p.splits = 1;
+    p.kb_per = kb_total;
+    if (p.epilogue == P_ACCUM && p.tile_f == 128) {
+        for (int s = kPairMaxSplits; s >= 2; s >>= 1)
+            if (p.units * s <= pairs_on_gpu && kb_total >= 4 * s && p.units <= pair_clusters_at_once(2 * s, smem)) {
+                p.splits = s;
+                p.kb_per = (kb_total + s - 1) / s;
+                break;
+            }
+    }
+    const int pairs = p.splits > 1 ? p.units : (p.units < pairs_on_gpu ? p.units : pairs_on_gpu);
+    launch_kernel("gemm_pair", gemm_pair_kernel, dim3(2 * p.splits * pairs), dim3(kThreads), smem, stream, 2 * p.splits,
+                  dependent_launch_enabled(), map_w, map_x, map_out, map_out, map_out, p);
     note_launch(1);
 }
 
@@ -722,6 +859,8 @@ bool gemm_pair_qkv(const void* x, const void* w, const void* bias, DType bias_dt
     p.error = error;
     p.rope = rope;
     p.units = p.tiles_f * ((T + 2 * kRows - 1) / (2 * kRows));
+    p.splits = 1;
+    p.kb_per = (K + kStageK - 1) / kStageK;
     const int stage_bytes = kRows * kStageK * 2 + p.half * kStageK * 2;
     const int budget = 227 * 1024 - 1024 - 2 * kStagingBytes - 256 - kBiasBytes;
     p.stages = budget / stage_bytes;

@@ -80,11 +80,13 @@ def _gemm_tc_gated_case(ops, T, H, K):
 
 @pytest.mark.parametrize("T,N,K", [(512, 896, 896), (2048, 896, 4864), (700, 200, 72), (1100, 1152, 896), (513, 136, 264),
                                    (4096, 2048, 128), (8192, 512, 64), (161, 896, 4864), (170, 136, 72), (300, 1152, 896),
-                                   (120, 1152, 896), (112, 136, 72)])
+                                   (120, 1152, 896), (112, 136, 72), (512, 896, 4864), (1000, 896, 4864), (256, 904, 2048),
+                                   (300, 136, 1024), (700, 520, 4104)])
 @pytest.mark.parametrize("mode", ["store_f32", "store_bf16", "accumulate", "gated"])
 def test_gemm_pair(ops, T, N, K, mode):
     """Products of more than 160 tokens go to the kernel in which two CTAs share a tile of 256 tokens: against a float
-    product, and against the one-CTA kernel on the same data."""
+    product, and against the one-CTA kernel on the same data. ("accumulate" with few tiles and a long K: two or four pairs
+    of a cluster share a tile's K.)"""
     x = _rand((T, K), torch.bfloat16, 11)
     w = _rand((2 * N if mode == "gated" else N, K), torch.bfloat16, 12, 0.05)
     bias = _rand((N,), torch.bfloat16, 13)
