@@ -1,12 +1,14 @@
-// Attention of one query against its visible keys, one warp per (token, head), for any
+// Attention of one query against its visible keys, one CTA of eight warps per (token, head), for any
 // head size that is a multiple of 8 up to 256 and any number of heads and groups.
 //
 // It is the attention of the true 32-bit path (whole prompts, prompts in portions, single
-// tokens and any mix of them in one step) and the fallback of the bfloat16 path. Keys are visited in ascending order in groups of 32 counted from
-// the first visible key, with a running maximum and sum (the reference's two-pass softmax,
-// src/kernels.c:1138-1176, gives the same value up to rounding). What a query's result
-// depends on: the query, its visible keys and values, the scale and the window -- not the
-// batch, not the step it came in, not where the keys lie in the cache.
+// tokens and any mix of them in one step) and the fallback of the bfloat16 path. Keys are visited in groups of 32 counted
+// from the first visible key: warp w takes the groups w, w + 8, ... in ascending order with a running maximum and sum
+// of its own, and the eight warps' results are put together in the order of the warps (the reference's two-pass softmax,
+// src/kernels.c:1138-1176, gives the same value up to rounding). The number of warps is the same in every launch, so
+// what a query's result depends on is the query, its visible keys and values, the scale and the window -- not the
+// batch, not the step it came in, not where the keys lie in the cache. (One warp a query left a decode step of 8
+// sequences over 2,048 positions with 112 warps on the whole GPU: 33 of the step's 46 ms.)
 #include <math_constants.h>
 
 #include <stdexcept>
@@ -17,7 +19,7 @@
 
 namespace sm {
 
-constexpr int kWarpsPerBlock = 4;
+constexpr int kWarpsPerBlock = 8;      // the warps that share one query's keys
 constexpr int kMaxHeadDim = 256;
 
 template <typename T> struct Load8;
@@ -44,10 +46,11 @@ template <> struct Load8<__nv_bfloat16> {
 // (positions before the first one the sequence brings in this step in the cache, the step's own packed).
 template <typename T, int SRC>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(AttentionArgs a) {
-    __shared__ __align__(16) float q_shared[kWarpsPerBlock][kMaxHeadDim];
+    __shared__ __align__(16) float q_shared[kMaxHeadDim];
+    __shared__ float warp_m[kWarpsPerBlock], warp_l[kWarpsPerBlock];
+    __shared__ float warp_acc[kWarpsPerBlock][kMaxHeadDim];
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    long long item = (long long)blockIdx.x * kWarpsPerBlock + warp;
-    if (item >= (long long)a.T * a.heads) return;  // whole warp leaves together
+    long long item = blockIdx.x;
     int t = (int)(item / a.heads), h = (int)(item % a.heads);
     int hd = a.head_dim;
     int kvh = h / (a.heads / a.kv_heads);  // src/model.c:461
@@ -55,9 +58,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(At
     int start = (a.window > 0 && pos >= a.window) ? pos - a.window + 1 : 0;  // src/model.c:462
 
     const T* q = (const T*)a.q + ((size_t)t * a.heads + h) * hd;
-    float* qs = q_shared[warp];
-    for (int d = lane; d < hd; d += 32) qs[d] = to_float(q[d]);
-    __syncwarp();
+    float* qs = q_shared;
+    for (int d = threadIdx.x; d < hd; d += kWarpsPerBlock * 32) qs[d] = to_float(q[d]);
+    __syncthreads();
 
     constexpr unsigned long long kPackedBit = 1ull << 63;   // marks a row offset into the packed tensors
     PagedKV paged{a.page_table, a.table_stride, a.ring, a.kv_heads, hd};
@@ -70,7 +73,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(At
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
 
-    for (int base = start; base <= pos; base += 32) {
+    for (int base = start + 32 * warp; base <= pos; base += 32 * kWarpsPerBlock) {
         int p = base + lane;
         bool valid = p <= pos;
         unsigned long long row = 0;
@@ -124,12 +127,31 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attention_plain_kernel(At
         }
         m = m_new;
     }
-    float inv = 1.0f / l;
-    T* o = (T*)a.out + ((size_t)t * a.heads + h) * hd;
+    // the warps' results, put together in the order of the warps (a warp without a group: m = -inf, weight 0)
+    if (lane == 0) { warp_m[warp] = m; warp_l[warp] = l; }
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) {
         int d = lane + 32 * i;
-        if (d < hd) o[d] = from_float<T>(acc[i] * inv);
+        if (d < hd) warp_acc[warp][d] = acc[i];
+    }
+    __syncthreads();
+    float top = warp_m[0];          // (warp 0 always has the first group, which holds a visible key)
+#pragma unroll
+    for (int w = 1; w < kWarpsPerBlock; ++w) top = fmaxf(top, warp_m[w]);
+    float weight[kWarpsPerBlock];
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarpsPerBlock; ++w) {
+        weight[w] = expf(warp_m[w] - top);      // exp(-inf) = 0
+        sum = fmaf(warp_l[w], weight[w], sum);
+    }
+    float inv = 1.0f / sum;
+    T* o = (T*)a.out + ((size_t)t * a.heads + h) * hd;
+    for (int d = threadIdx.x; d < hd; d += kWarpsPerBlock * 32) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarpsPerBlock; ++w) v = fmaf(warp_acc[w][d], weight[w], v);
+        o[d] = from_float<T>(v * inv);
     }
 }
 
@@ -147,7 +169,8 @@ void attention_plain(const AttentionArgs& a, cudaStream_t stream) {
         throw std::invalid_argument("attention_plain: packed keys need packed values and each token's sequence start");
     note_launch();
     long long items = (long long)a.T * a.heads;
-    unsigned blocks = (unsigned)((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    if (items > 0x7fffffffll) throw std::invalid_argument("attention_plain: more than 2^31 - 1 (token, head) pairs in one step");
+    unsigned blocks = (unsigned)items;
     int threads = kWarpsPerBlock * 32;
     if (a.dt == F32) {
         if (src == 0) attention_plain_kernel<float, 0><<<blocks, threads, 0, stream>>>(a);
