@@ -219,7 +219,7 @@ def reference_arm(args) -> int:
         return unavailable("ktfth/smolmoe-c99 is a CPU program for one sequence; there is nothing to run on several GPUs")
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.exists(os.path.join(ref, "src", "main.c")):
-        source = "/root/reference"
+        source = os.environ.get("SMOLMOE_C99_SOURCE", "/root/reference")
         if not os.path.exists(os.path.join(source, "src", "main.c")):
             return unavailable("no copy of ktfth/smolmoe-c99 under baseline/_ref and none to copy from")
         shutil.copytree(source, ref, ignore=shutil.ignore_patterns(".git"), dirs_exist_ok=True)
