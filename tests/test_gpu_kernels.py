@@ -278,6 +278,12 @@ def test_attention_of_many_tokens_onto_the_cache(ops, heads, kv_heads, hd, start
         far = min(5, total[b] - 1)
         page = int(table[b, far // PAGE_SIZE])
         qs[b][-1] = k_pool[page, :, far % PAGE_SIZE].repeat_interleave(heads // kv_heads, dim=0) * 3.0
+        # ... and the query before it at a key near the sequence's end: the scores of all earlier tiles are small beside
+        # it, so the running reference moves late and what has been accumulated by then is rescaled
+        if news[b] >= 2:
+            near = total[b] - 3
+            page = int(table[b, near // PAGE_SIZE])
+            qs[b][-2] = k_pool[page, :, near % PAGE_SIZE].repeat_interleave(heads // kv_heads, dim=0) * 3.0
     step = pack_step(list(range(B)), starts, [[0] * n for n in news], torch.device("cuda"))
     assert step.mode == "extend"
     q = torch.cat(qs).cuda()
@@ -300,6 +306,12 @@ def test_attention_of_many_tokens_onto_the_cache(ops, heads, kv_heads, hd, start
         for h in (0, heads - 1):
             v_far = cache.v_pool[page, h // (heads // kv_heads), far % PAGE_SIZE].float()
             assert float((got[at - 1, h] - v_far).abs().max()) <= 5e-2, (b, h)
+        if news[b] >= 2:
+            near = total[b] - 3
+            page = int(table[b, near // PAGE_SIZE])
+            for h in (0, heads - 1):
+                v_near = cache.v_pool[page, h // (heads // kv_heads), near % PAGE_SIZE].float()
+                assert float((got[at - 2, h] - v_near).abs().max()) <= 5e-2, (b, h, "late key")
 
 
 @pytest.mark.parametrize("T", [1, 5, 16])
@@ -368,9 +380,16 @@ def test_prefill_attention_finds_a_far_key(ops, kernel):
     k[far] = 0
     k[far, 0, 0] = 40.0
     q[n - 1, :, 0] = 40.0   # score 1600/8 = 200 for the far key, O(1) for the others
+    # and one key in the query tile's last but one key tile dominates for another query: the running maximum moves
+    # late, after tiles of small scores have been accumulated
+    late = n - 140
+    k[late] = 0
+    k[late, 0, 1] = 40.0
+    q[n - 2, :, 1] = 40.0
     step = _packed_step([n])
     got = run(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), None).float()
     assert float((got[n - 1, 0] - v[far, 0].float()).abs().max()) <= 2e-2
+    assert float((got[n - 2, 0] - v[late, 0].float()).abs().max()) <= 2e-2
     # with a window that ends just after it, it is out of sight
     got_w = run(q, k, v, step.prefill_tiles, 1.0 / math.sqrt(hd), n - 1 - far).float()
     assert float((got_w[n - 1, 0] - v[far, 0].float()).abs().max()) > 0.1
