@@ -594,10 +594,13 @@ void attention_extend_tc(const void* q, void* out, const int32_t* tiles, int n_t
     }
     bool two = variant == 1;
     if (variant < 0) {
-        // (as in attention_prefill_tc: two CTAs an SM where every SM has at least as many key tiles to do as the longest chain)
+        // (as in attention_prefill_tc: two CTAs an SM where every SM has at least as many key tiles to do as the longest chain;
+        // the query tiles' chains are estimated as those of one sequence that ends at `longest`: chain, chain - 1, ...)
         const long long chain = ((longest > 0 ? longest : T) + kBN - 1) / kBN;
-        const long long total = (long long)heads * ((T + kBM - 1) / kBM) * chain;
-        two = total >= chain * kSmCount * 2;
+        const long long q_tiles = (T + kBM - 1) / kBM;
+        const long long shortest = chain - q_tiles + 1 > 1 ? chain - q_tiles + 1 : 1;
+        const long long total = (long long)heads * q_tiles * (chain + shortest) / 2;
+        two = total >= chain * kSmCount;
     }
     if (two) launch<64, true, true>(mq, mk, mv, a, n_tiles, stream);
     else launch<64, false, true>(mq, mk, mv, a, n_tiles, stream);

@@ -143,6 +143,7 @@ class Ops:
         # window): 160 tokens onto 2,000 take 2.15 ms either way, 300 tokens 2.93 as rows against 2.56 as tiles, 512 onto
         # 8,000 6.85 against 4.43
         self.extend_rows_as_decode_tc = 176 if fast else 0
+        self.extend_tc_variant = -1     # that kernel with one CTA an SM (0), two (1, head size 64), or as the launcher chooses
         self.skinny_single_round_above_8 = True
         self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.lib.sm_set_error_word.restype = None
@@ -607,7 +608,7 @@ class Ops:
                 _ptr(q), _ptr(out), _ptr(step.extend_tiles), step.extend_tiles.shape[0], q.shape[0], q.shape[1],
                 k_packed.shape[1], q.shape[2], ctypes.c_float(scale), int(window or 0), _ptr(cache.k_pool), _ptr(cache.v_pool),
                 _ptr(cache.page_table), cache.page_table.shape[1], ctypes.c_longlong(cache.k_pool.shape[0]),
-                int(step.max_seq_len), -1, _ptr(self.error_flag), _stream()))
+                int(step.max_seq_len), int(self.extend_tc_variant), _ptr(self.error_flag), _stream()))
             return out
         if (self.use_fast_attention and q.dtype == torch.bfloat16 and step.extend_tiles is not None
                 and self.lib.sm_attention_prefill_supports(q.shape[2])):

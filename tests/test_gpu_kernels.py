@@ -258,7 +258,8 @@ def test_attention_of_sequences_that_go_on_from_the_cache(ops, heads, kv_heads, 
 
 @pytest.mark.parametrize("heads,kv_heads,hd", [(14, 2, 64), (4, 4, 64), (8, 2, 128)])
 @pytest.mark.parametrize("starts,news", [([700, 0, 33, 1000], [600, 130, 64, 530]), ([2000], [1000]), ([1, 127, 128], [300, 129, 257])])
-def test_attention_of_many_tokens_onto_the_cache(ops, heads, kv_heads, hd, starts, news):
+@pytest.mark.parametrize("variant", [0, 1])
+def test_attention_of_many_tokens_onto_the_cache(ops, heads, kv_heads, hd, starts, news, variant):
     """Prompt portions: sequences go on by hundreds of tokens from positions that are no multiple of a tile, and the
     cache holds the step's own keys and values already. The tcgen05 kernel reads every key from the paged pools (pages
     in a random order; rows past a sequence's end hold other numbers and must not count) and is compared with the
@@ -292,7 +293,11 @@ def test_attention_of_many_tokens_onto_the_cache(ops, heads, kv_heads, hd, start
     cache = SimpleNamespace(k_pool=k_pool.cuda(), v_pool=v_pool.cuda(), page_table=table.cuda(), ring=0)
     scale = 1.0 / math.sqrt(hd)
     launches = int(ops.lib.sm_launch_count())
-    got = ops.attention_extend(q, packed, packed, step, scale, None, cache, cache_written=True).float()
+    ops.extend_tc_variant = variant          # one CTA an SM, or two (head size 64; 128 has the one form)
+    try:
+        got = ops.attention_extend(q, packed, packed, step, scale, None, cache, cache_written=True).float()
+    finally:
+        ops.extend_tc_variant = -1
     ops.check_error_flag()
     assert int(ops.lib.sm_launch_count()) == launches + 1
     want = ops.attention_plain(q.float(), step.positions, scale, None, k_pool=cache.k_pool.float(), v_pool=cache.v_pool.float(),
