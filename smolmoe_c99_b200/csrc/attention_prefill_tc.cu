@@ -357,9 +357,11 @@ __global__ void __launch_bounds__(kThreads, TWO ? 2 : 1) prefill_attention_tc_ke
     #pragma unroll
                 for (int e = 0; e < 8; ++e) raw8[e] = sv[e];
     #pragma unroll
-                for (int j = 8; j < 64; j += 16)
+                for (int j = 8; j + 8 < 64; j += 16)
     #pragma unroll
                     for (int e = 0; e < 8; ++e) raw8[e] = fmax3(raw8[e], sv[j + e], sv[j + 8 + e]);
+    #pragma unroll
+                for (int e = 0; e < 8; ++e) raw8[e] = fmaxf(raw8[e], sv[56 + e]);
                 const float raw = fmaxf(fmaxf(fmaxf(raw8[0], raw8[1]), fmaxf(raw8[2], raw8[3])),
                                         fmaxf(fmaxf(raw8[4], raw8[5]), fmaxf(raw8[6], raw8[7])));
                 settle_reference(it, raw * a.scale_log2);
